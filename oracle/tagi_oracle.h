@@ -1,0 +1,70 @@
+/* CPU restatement of the reference's TAGI Linear / Conv2d arithmetic.
+ *
+ * TEST INFRASTRUCTURE ONLY: the parity tests, the smoke check and the CPU leg
+ * of the benchmark call this; the product library never does.
+ *
+ * Pinning: the reference ships no golden vectors or op-level tests for Linear
+ * or Conv2d, so this restatement is pinned by the reference's own CPU classes
+ * executed in the build container (oracle/_ref/libtagi_ref.so, built by
+ * oracle/Makefile from the reference's sources) and by the fixtures under
+ * tests/golden/ that were generated from those classes.
+ *
+ * Layouts (row-major, flat): activations / deltas [B][features]; Linear weights
+ * [N][K]; conv activations [B][C][H][W], conv weights [fo][fi][k][k], conv
+ * outputs [B][fo][ho*wo].
+ */
+#ifndef TAGI_ORACLE_H
+#define TAGI_ORACLE_H
+#include <stddef.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct {
+    int B, fi, hi, wi, fo, ho, wo, k, stride, pad, pad_type, has_bias;
+} tagi_oracle_conv_geom;
+
+/* Output extent, src/conv2d_layer.cpp:581-628: pad_type 1 -> (w - k + 2p)/s + 1,
+ * pad_type 2 -> (w - k + p)/s + 1, else (w - k)/s + 1. Returns -1 (the reference
+ * raises) when the numerator is not divisible by the stride. */
+int tagi_oracle_conv_out_size(int k, int stride, int wi, int hi, int pad, int pad_type, int *wo, int *ho);
+
+#define TAGI_ORACLE_DECL(ACC, S)                                                                                  \
+    void tagi_oracle_linear_fwd##S(int B, int K, int N, int has_bias, const float *mu_w, const float *var_w,      \
+                                   const float *mu_b, const float *var_b, const float *mu_a, const float *var_a,  \
+                                   ACC *mu_z, ACC *var_z);                                                        \
+    void tagi_oracle_linear_bwd_state##S(int B, int K, int N, const float *mu_w, const float *jcb,                \
+                                         const float *dmu_z, const float *dvar_z, ACC *dmu_a, ACC *dvar_a);       \
+    void tagi_oracle_linear_bwd_param##S(int B, int K, int N, int has_bias, const float *var_w,                   \
+                                         const float *var_b, const float *mu_a, const float *dmu_z,               \
+                                         const float *dvar_z, ACC *dmu_w, ACC *dvar_w, ACC *dmu_b, ACC *dvar_b);  \
+    void tagi_oracle_conv2d_fwd##S(const tagi_oracle_conv_geom *g, const float *mu_w, const float *var_w,         \
+                                   const float *mu_b, const float *var_b, const float *mu_a, const float *var_a,  \
+                                   ACC *mu_z, ACC *var_z);                                                        \
+    void tagi_oracle_conv2d_bwd_state##S(const tagi_oracle_conv_geom *g, const float *mu_w, const float *jcb,     \
+                                         const float *dmu_z, const float *dvar_z, ACC *dmu_a, ACC *dvar_a);       \
+    void tagi_oracle_conv2d_bwd_param##S(const tagi_oracle_conv_geom *g, const float *var_w, const float *var_b,  \
+                                         const float *mu_a, const float *dmu_z, const float *dvar_z, ACC *dmu_w,  \
+                                         ACC *dvar_w, ACC *dmu_b, ACC *dvar_b);
+TAGI_ORACLE_DECL(float, _f32)
+TAGI_ORACLE_DECL(double, _f64)
+
+/* Neighbours of the path, fp32 elementwise, needed to run whole training steps. */
+/* ReLU moments, src/activation.cpp:7-29. */
+void tagi_oracle_relu(size_t n, const float *mu_z, const float *var_z, float *mu_a, float *var_a, float *jcb);
+/* Output innovation, src/base_output_updater.cpp:8-29: all n entries. */
+void tagi_oracle_output_delta(size_t n, const float *mu_a, const float *var_a, const float *jcb, const float *obs,
+                              const float *var_obs, float *dmu, float *dvar);
+/* Index-selected innovation (hierarchical softmax), src/base_output_updater.cpp:67-93: dmu/dvar (B*n_out entries)
+ * are zeroed first (src/base_output_updater.cpp:281,300), then n_sel = B*n_enc entries are written; selected_idx
+ * is one-based within a sample. */
+void tagi_oracle_output_delta_selected(int B, int n_out, int n_enc, const float *mu_a, const float *var_a,
+                                       const float *jcb, const float *obs, const float *var_obs,
+                                       const int *selected_idx, float *dmu, float *dvar);
+/* Capped parameter update, src/base_layer.cpp:116-187; returns how many variances were reset to 1e-5. */
+int tagi_oracle_param_update(int batch_size, size_t n, float *mu, float *var, const float *dmu, const float *dvar);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
