@@ -1,0 +1,325 @@
+#!/usr/bin/env python
+"""Benchmark of the TAGI Linear hot path (forward + state-delta backward + parameter-delta backward).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+Workload: the single-layer micro-benchmark configuration, FP32, batch 1024, 4096 -> 4096, seeded synthetic
+tensors with the stated distributions. One step = tagi_linear_fwd + tagi_linear_bwd_state +
+tagi_linear_bwd_param (with bias deltas) through the C ABI. Algorithmic work per step = 14*B*K*N FLOP
+(6 forward + 4 state backward + 4 parameter backward).
+
+With N > 1 (launched by torchrun, one rank per GPU) every rank runs the step on its own batch shard of 1024
+samples against a full parameter replica (weak scaling) and the parameter deltas are averaged across ranks with
+an NCCL allreduce inside the timed region, which is the one exchange step of the data-parallel path.
+
+`--impl reference` times the reference's CPU implementation (the compiled reference classes in oracle/_ref when
+present, else the CPU restatement in oracle/) on the host cores, on a bounded batch sample of the same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "tests")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+B, K, N = 1024, 4096, 4096
+FLOP_FWD, FLOP_STATE, FLOP_PARAM = 6.0 * B * K * N, 4.0 * B * K * N, 4.0 * B * K * N
+FLOP_STEP = FLOP_FWD + FLOP_STATE + FLOP_PARAM
+METRIC = "TAGI Linear fwd+bwd TFLOP/s"
+UNIT = "TFLOP/s"
+WORKLOAD = "linear_fp32_B1024_4096x4096 (fwd + state-delta bwd + param-delta bwd, bias on)"
+# FP32 FFMA peak of a B200: 148 SMs x 128 lanes x 2 FLOP x 1.965 GHz (maximum SM clock)
+FP32_NOMINAL_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12
+
+
+def make_inputs(seed, batch=B):
+    """Seeded tensors with the distributions of the micro-benchmark configuration. N(0, 1e-2) for the bias mean
+    and the mean deltas is read as variance 1e-2 (standard deviation 0.1)."""
+    rng = np.random.default_rng(seed)
+    f32 = np.float32
+    wrng = np.random.default_rng(12345)  # parameters are the same on every rank
+    x = dict(
+        mu_w=(wrng.standard_normal((N, K), dtype=f32) / f32(np.sqrt(K))),
+        var_w=(wrng.uniform(0.5, 1.5, (N, K)).astype(f32) / f32(K)),
+        mu_b=(wrng.standard_normal(N, dtype=f32) * f32(0.1)),
+        var_b=np.full(N, 1e-3, f32),
+        mu_a=rng.standard_normal((batch, K), dtype=f32),
+        var_a=rng.uniform(1e-3, 1e-1, (batch, K)).astype(f32),
+        jcb=rng.uniform(0, 1, (batch, K)).astype(f32),
+        dmu_z=(rng.standard_normal((batch, N), dtype=f32) * f32(0.1)),
+        dvar_z=(-rng.uniform(0, 1e-3, (batch, N))).astype(f32),
+    )
+    return x
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                 str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, t0, t1):
+        rows = [r for t, r in self.rows if t0 <= t <= t1 and len(r) >= 7] or [r for _, r in self.rows if len(r) >= 7]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        sm = sorted(float(r[0]) for r in rows)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in rows)]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(rows[0][1]), "reasons": reasons,
+                "power_w_max": max(float(r[2]) for r in rows), "samples": len(rows)}
+
+
+def cpu_arm(sample_rows, threads):
+    """The reference's CPU path on `sample_rows` batch rows of the workload. Returns (seconds, kind)."""
+    from oracle_lib import Oracle, RefLib
+    x = make_inputs(1, sample_rows)
+    if RefLib.available():
+        ref = RefLib()
+        t0 = time.perf_counter()
+        ref.linear_forward(x["mu_w"], x["var_w"], x["mu_b"], x["var_b"], x["mu_a"], x["var_a"], threads=threads)
+        ref.linear_backward(x["mu_w"], x["var_w"], x["var_b"], x["mu_a"], x["jcb"], x["dmu_z"], x["dvar_z"],
+                            threads=threads)
+        return time.perf_counter() - t0, "reference"
+    o = Oracle()
+    t0 = time.perf_counter()
+    o.linear_fwd(x["mu_w"], x["var_w"], x["mu_b"], x["var_b"], x["mu_a"], x["var_a"])
+    o.linear_bwd_state(x["mu_w"], x["jcb"], x["dmu_z"], x["dvar_z"])
+    o.linear_bwd_param(x["var_w"], x["var_b"], x["mu_a"], x["dmu_z"], x["dvar_z"])
+    return time.perf_counter() - t0, "port"
+
+
+def pick_sample_rows(threads, target_s):
+    """Batch rows for one CPU evaluation of about target_s seconds, from a 4-row probe."""
+    t, _ = cpu_arm(4, threads)
+    rows = int(max(4, min(B, 4 * target_s / max(t, 1e-3))))
+    return rows - rows % 4 if rows >= 8 else 4
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    rows = pick_sample_rows(threads, 4.0)
+    for _ in range(min(args.warmup, 1)):
+        cpu_arm(rows, threads)
+    t0 = time.perf_counter()
+    kind = "port"
+    for _ in range(args.steps):
+        _, kind = cpu_arm(rows, threads)
+    dt = time.perf_counter() - t0
+    tflops = 14.0 * rows * K * N * args.steps / dt / 1e12
+    sample = f"{rows} of {B} batch rows per step, full 4096x4096 weights"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": tflops, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps * (B / rows),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample, "ms_per_step_is": "scaled from the sample to 1024 rows"},
+        "cpu_baseline": {"value": tflops, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": tflops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0}))
+
+
+def run_b200(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    from cutagi_b200.capi import lib, IMPL_FFMA, IMPL_TF32X3
+
+    torch.cuda.set_device(local_rank)
+    devname = torch.cuda.get_device_name(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    x = make_inputs(100 + rank)
+    host = {k: torch.from_numpy(v).pin_memory() for k, v in x.items()}
+    d = {k: v.cuda(non_blocking=True) for k, v in host.items()}
+    out_shapes = dict(mu_z=(B, N), var_z=(B, N), dmu_a=(B, K), dvar_a=(B, K), dmu_w=(N, K), dvar_w=(N, K),
+                      dmu_b=(N,), dvar_b=(N,))
+    o = {k: torch.empty(s, dtype=torch.float32, device="cuda") for k, s in out_shapes.items()}
+    host_out = {k: torch.empty(s, dtype=torch.float32).pin_memory() for k, s in out_shapes.items()}
+    stream = torch.cuda.current_stream()
+    sp = stream.cuda_stream
+    p = {k: v.data_ptr() for k, v in {**d, **o}.items()}
+
+    def k_fwd():
+        lib.tagi_linear_fwd(p["mu_w"], p["var_w"], p["mu_b"], p["var_b"], p["mu_a"], p["var_a"], B, K, N, 1,
+                            p["mu_z"], p["var_z"], sp)
+
+    def k_state():
+        lib.tagi_linear_bwd_state(p["mu_w"], p["jcb"], p["dmu_z"], p["dvar_z"], B, K, N, p["dmu_a"], p["dvar_a"], sp)
+
+    def k_param():
+        lib.tagi_linear_bwd_param(p["var_w"], p["var_b"], p["mu_a"], p["dmu_z"], p["dvar_z"], B, K, N, 1,
+                                  p["dmu_w"], p["dvar_w"], p["dmu_b"], p["dvar_b"], sp)
+
+    def exchange():
+        if world > 1:
+            for k in ("dmu_w", "dvar_w", "dmu_b", "dvar_b"):
+                dist.all_reduce(o[k], op=dist.ReduceOp.AVG)
+
+    def step():
+        k_fwd()
+        k_state()
+        k_param()
+        exchange()
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(fn, n):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sync_all()
+        e0.record(stream)
+        for _ in range(n):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        sync_all()
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    for _ in range(args.warmup):
+        step()
+    t_begin = time.time()
+    ms_total = timed(step, args.steps)
+    t_end = time.time()
+    ms_step = ms_total / args.steps
+    value = FLOP_STEP * world / (ms_step * 1e-3) / 1e12
+
+    # per-kernel durations (same stream, CUDA events); each kernel's operands exceed the 126 MB L2
+    kt = {}
+    for name, fn in (("tagi_linear_fwd", k_fwd), ("tagi_linear_bwd_state", k_state), ("tagi_linear_bwd_param", k_param)):
+        fn()
+        kt[name] = timed(fn, args.steps) / args.steps
+
+    # end to end: pinned host inputs -> device, three calls, results -> pinned host, all inside the timed region
+    h2d = sum(v.numel() * 4 for v in host.values())
+    d2h = sum(v.numel() * 4 for v in host_out.values())
+
+    def e2e_step():
+        for k_, v in host.items():
+            d[k_].copy_(v, non_blocking=True)
+        step()
+        for k_, v in host_out.items():
+            v.copy_(o[k_], non_blocking=True)
+
+    e2e_step()
+    ms_e2e = timed(e2e_step, max(2, args.steps // 2)) / max(2, args.steps // 2)
+    e2e_value = FLOP_STEP * world / (ms_e2e * 1e-3) / 1e12
+    clocks = None
+    if rank == 0:
+        sampler.stop()
+        clocks = sampler.summary(t_begin, t_end)
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    impl = lib.tagi_get_impl()
+    flops = {"tagi_linear_fwd": FLOP_FWD, "tagi_linear_bwd_state": FLOP_STATE, "tagi_linear_bwd_param": FLOP_PARAM}
+    dom = max(kt, key=kt.get)
+    achieved = flops[dom] / (kt[dom] * 1e-3) / 1e12
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except OSError:
+        pass
+    if impl == IMPL_TF32X3:
+        bf16 = peaks.get("bf16_tflops", 1590.0)
+        peak, bound = bf16 / 2.0 / 3.0, "tensor"
+        peak_note = ("measured dense bf16 %.0f TFLOP/s / 2 (tf32 rate) / 3 (three tf32 products per fp32 product), %s"
+                     % (bf16, "of measured" if peaks else "of fallback"))
+    else:
+        peak, bound = FP32_NOMINAL_TFLOPS, "fp32"
+        peak_note = ("FP32 FFMA path: 148 SMs x 128 lanes x 2 x 1.965 GHz, of nominal "
+                     "(MEASURED_PEAKS.json holds no FP32 figure)")
+    roofline = {"bound": bound, "kernel": dom, "achieved": achieved, "peak": peak, "unit": UNIT,
+                "frac": achieved / peak, "traffic": None, "peak_note": peak_note,
+                "per_kernel_ms": kt,
+                "per_kernel_tflops": {k_: flops[k_] / (v * 1e-3) / 1e12 for k_, v in kt.items()}}
+
+    cpu_baseline = None
+    if world == 1 and not args.no_cpu:
+        threads = os.cpu_count() or 1
+        rows = pick_sample_rows(threads, 6.0)
+        t, kind = cpu_arm(rows, threads)
+        cpu_baseline = {"value": 14.0 * rows * K * N / t / 1e12, "unit": UNIT, "cores": threads, "kind": kind,
+                        "sample": f"{rows} of {B} batch rows, full 4096x4096 weights, {t:.1f} s"}
+
+    print(json.dumps({
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "impl": {0: "auto", 1: "ffma", 2: "tf32x3"}.get(impl, str(impl)),
+                   "device": devname, "l2": "inputs (604 MB per step) exceed the 126 MB L2; no flush",
+                   "exchange": "allreduce(avg) of parameter deltas, NCCL" if world > 1 else "none (1 GPU)"},
+        "roofline": roofline, "cpu_baseline": cpu_baseline,
+        "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h},
+        "gpu_launches": 4 * args.steps, "clocks": clocks}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    if args.impl == "reference":
+        run_reference(args, rank)
+    else:
+        run_b200(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

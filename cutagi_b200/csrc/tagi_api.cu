@@ -1,0 +1,207 @@
+// C-ABI entry points (include/tagi_b200.h): argument checks, implementation choice, status codes.
+#include <cstdlib>
+#include <cstring>
+
+#include "tagi_common.h"
+
+namespace tagi {
+
+std::string &last_error() {
+    static thread_local std::string s;
+    return s;
+}
+int fail(int code, const std::string &msg) {
+    last_error() = msg;
+    return code;
+}
+int cuda_fail(cudaError_t e, const char *where) {
+    last_error() = std::string(where) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")";
+    return TAGI_ERR_CUDA;
+}
+
+namespace {
+int g_impl = -1;
+int impl_from_env() {
+    const char *v = std::getenv("TAGI_B200_IMPL");
+    if (!v) return TAGI_IMPL_AUTO;
+    if (!std::strcmp(v, "ffma")) return TAGI_IMPL_FFMA;
+    if (!std::strcmp(v, "tf32x3")) return TAGI_IMPL_TF32X3;
+    return TAGI_IMPL_AUTO;
+}
+}  // namespace
+int current_impl() {
+    if (g_impl < 0) g_impl = impl_from_env();
+    return g_impl;
+}
+
+}  // namespace tagi
+
+using namespace tagi;
+
+extern "C" {
+
+const char *tagi_last_error_string(void) { return last_error().c_str(); }
+int tagi_version(void) { return 100; }
+
+int tagi_set_impl(int impl) {
+    TAGI_REQUIRE(impl >= TAGI_IMPL_AUTO && impl <= TAGI_IMPL_TF32X3, "unknown implementation id");
+    g_impl = impl;
+    return TAGI_OK;
+}
+int tagi_get_impl(void) { return current_impl(); }
+
+#define TAGI_PTR(p) TAGI_REQUIRE((p) != nullptr && aligned4(p), #p " is null or not 4-byte aligned")
+#define TAGI_DIMS()                                                                            \
+    TAGI_REQUIRE(B > 0 && K > 0 && N > 0, "B, K and N must be positive");                        \
+    TAGI_REQUIRE((long)B * K < (1L << 31) && (long)B * N < (1L << 31) && (long)K * N < (1L << 31), \
+                 "tensor extent exceeds 2^31 elements")
+
+int tagi_linear_fwd(const float *mu_w, const float *var_w, const float *mu_b, const float *var_b, const float *mu_a,
+                    const float *var_a, int B, int K, int N, int has_bias, float *mu_z, float *var_z, void *stream) {
+    TAGI_DIMS();
+    TAGI_PTR(mu_w);
+    TAGI_PTR(var_w);
+    TAGI_PTR(mu_a);
+    TAGI_PTR(var_a);
+    TAGI_PTR(mu_z);
+    TAGI_PTR(var_z);
+    if (has_bias) {
+        TAGI_PTR(mu_b);
+        TAGI_PTR(var_b);
+    } else {
+        mu_b = var_b = nullptr;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (current_impl() == TAGI_IMPL_TF32X3)
+        return fail(TAGI_ERR_UNSUPPORTED, "tagi_linear_fwd: TF32X3 cannot run this shape");
+    return linear_fwd_ffma(mu_w, var_w, mu_b, var_b, mu_a, var_a, B, K, N, mu_z, var_z, st);
+}
+
+int tagi_linear_bwd_state(const float *mu_w, const float *jcb, const float *dmu_z, const float *dvar_z, int B, int K,
+                          int N, float *dmu_a, float *dvar_a, void *stream) {
+    TAGI_DIMS();
+    TAGI_PTR(mu_w);
+    TAGI_PTR(jcb);
+    TAGI_PTR(dmu_z);
+    TAGI_PTR(dvar_z);
+    TAGI_PTR(dmu_a);
+    TAGI_PTR(dvar_a);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (current_impl() == TAGI_IMPL_TF32X3)
+        return fail(TAGI_ERR_UNSUPPORTED, "tagi_linear_bwd_state: TF32X3 cannot run this shape");
+    return linear_bwd_state_ffma(mu_w, jcb, dmu_z, dvar_z, B, K, N, dmu_a, dvar_a, st);
+}
+
+int tagi_linear_bwd_param(const float *var_w, const float *var_b, const float *mu_a, const float *dmu_z,
+                          const float *dvar_z, int B, int K, int N, int has_bias, float *dmu_w, float *dvar_w,
+                          float *dmu_b, float *dvar_b, void *stream) {
+    TAGI_DIMS();
+    TAGI_PTR(var_w);
+    TAGI_PTR(mu_a);
+    TAGI_PTR(dmu_z);
+    TAGI_PTR(dvar_z);
+    TAGI_PTR(dmu_w);
+    TAGI_PTR(dvar_w);
+    if (has_bias) {
+        TAGI_PTR(var_b);
+        TAGI_PTR(dmu_b);
+        TAGI_PTR(dvar_b);
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (current_impl() == TAGI_IMPL_TF32X3)
+        return fail(TAGI_ERR_UNSUPPORTED, "tagi_linear_bwd_param: TF32X3 cannot run this shape");
+    int rc = linear_bwd_param_ffma(var_w, mu_a, dmu_z, dvar_z, B, K, N, dmu_w, dvar_w, st);
+    if (rc != TAGI_OK) return rc;
+    if (has_bias) rc = linear_bias_delta(var_b, dmu_z, dvar_z, B, N, dmu_b, dvar_b, st);
+    return rc;
+}
+
+/* ------------------------------------------------------------------ Conv2d */
+
+int tagi_conv2d_out_size(int k, int stride, int wi, int hi, int pad, int pad_type, int *wo, int *ho) {
+    TAGI_REQUIRE(wo && ho, "null output pointer");
+    TAGI_REQUIRE(k > 0 && stride > 0 && wi > 0 && hi > 0 && pad >= 0, "non-positive kernel, stride or image size");
+    int nw, nh;
+    if (pad_type == 1) {
+        nw = wi - k + 2 * pad, nh = hi - k + 2 * pad;
+    } else if (pad_type == 2) {
+        nw = wi - k + pad, nh = hi - k + pad;
+    } else {
+        nw = wi - k, nh = hi - k;
+    }
+    TAGI_REQUIRE(nw >= 0 && nh >= 0 && nw % stride == 0 && nh % stride == 0,
+                 "invalid hyperparameters for conv2d layer: wi=" + std::to_string(wi) + ", hi=" + std::to_string(hi) +
+                     ", kernel=" + std::to_string(k) + ", stride=" + std::to_string(stride));
+    *wo = nw / stride + 1;
+    *ho = nh / stride + 1;
+    return TAGI_OK;
+}
+
+static int check_geom(const tagi_conv2d_geom *g) {
+    TAGI_REQUIRE(g != nullptr, "null geometry");
+    TAGI_REQUIRE(g->B > 0 && g->fi > 0 && g->fo > 0, "B, fi and fo must be positive");
+    int wo = 0, ho = 0;
+    int rc = tagi_conv2d_out_size(g->k, g->stride, g->wi, g->hi, g->pad, g->pad_type, &wo, &ho);
+    if (rc != TAGI_OK) return rc;
+    TAGI_REQUIRE(wo == g->wo && ho == g->ho, "ho / wo do not match the kernel, stride and padding");
+    const long lim = 1L << 31;
+    TAGI_REQUIRE((long)g->B * g->fi * g->hi * g->wi < lim && (long)g->B * g->fo * g->ho * g->wo < lim &&
+                     (long)g->fo * g->fi * g->k * g->k < lim,
+                 "tensor extent exceeds 2^31 elements");
+    return TAGI_OK;
+}
+
+int tagi_conv2d_fwd(const tagi_conv2d_geom *g, const float *mu_w, const float *var_w, const float *mu_b,
+                    const float *var_b, const float *mu_a, const float *var_a, float *mu_z, float *var_z,
+                    void *stream) {
+    int rc = check_geom(g);
+    if (rc != TAGI_OK) return rc;
+    TAGI_PTR(mu_w);
+    TAGI_PTR(var_w);
+    TAGI_PTR(mu_a);
+    TAGI_PTR(var_a);
+    TAGI_PTR(mu_z);
+    TAGI_PTR(var_z);
+    if (g->has_bias) {
+        TAGI_PTR(mu_b);
+        TAGI_PTR(var_b);
+    } else {
+        mu_b = var_b = nullptr;
+    }
+    return conv2d_fwd_ffma(*g, mu_w, var_w, mu_b, var_b, mu_a, var_a, mu_z, var_z, static_cast<cudaStream_t>(stream));
+}
+
+int tagi_conv2d_bwd_state(const tagi_conv2d_geom *g, const float *mu_w, const float *jcb, const float *dmu_z,
+                          const float *dvar_z, float *dmu_a, float *dvar_a, void *stream) {
+    int rc = check_geom(g);
+    if (rc != TAGI_OK) return rc;
+    TAGI_PTR(mu_w);
+    TAGI_PTR(jcb);
+    TAGI_PTR(dmu_z);
+    TAGI_PTR(dvar_z);
+    TAGI_PTR(dmu_a);
+    TAGI_PTR(dvar_a);
+    return conv2d_bwd_state_ffma(*g, mu_w, jcb, dmu_z, dvar_z, dmu_a, dvar_a, static_cast<cudaStream_t>(stream));
+}
+
+int tagi_conv2d_bwd_param(const tagi_conv2d_geom *g, const float *var_w, const float *var_b, const float *mu_a,
+                          const float *dmu_z, const float *dvar_z, float *dmu_w, float *dvar_w, float *dmu_b,
+                          float *dvar_b, void *stream) {
+    int rc = check_geom(g);
+    if (rc != TAGI_OK) return rc;
+    TAGI_PTR(var_w);
+    TAGI_PTR(mu_a);
+    TAGI_PTR(dmu_z);
+    TAGI_PTR(dvar_z);
+    TAGI_PTR(dmu_w);
+    TAGI_PTR(dvar_w);
+    if (g->has_bias) {
+        TAGI_PTR(var_b);
+        TAGI_PTR(dmu_b);
+        TAGI_PTR(dvar_b);
+    }
+    return conv2d_bwd_param_ffma(*g, var_w, var_b, mu_a, dmu_z, dvar_z, dmu_w, dvar_w, dmu_b, dvar_b,
+                                 static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

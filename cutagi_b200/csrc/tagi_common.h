@@ -1,0 +1,55 @@
+// Shared host-side helpers of the C-ABI translation units: status codes, the per-thread error
+// string and argument checks.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <string>
+
+#include "../../include/tagi_b200.h"
+
+namespace tagi {
+
+std::string &last_error();  // thread-local
+int fail(int code, const std::string &msg);
+int cuda_fail(cudaError_t e, const char *where);
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline bool aligned4(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 3u) == 0; }
+
+#define TAGI_REQUIRE(cond, msg) \
+    do {                        \
+        if (!(cond)) return ::tagi::fail(TAGI_ERR_INVALID_ARGUMENT, std::string(__func__) + ": " + (msg)); \
+    } while (0)
+
+#define TAGI_CUDA(expr)                                                  \
+    do {                                                                 \
+        cudaError_t e__ = (expr);                                        \
+        if (e__ != cudaSuccess) return ::tagi::cuda_fail(e__, #expr);    \
+    } while (0)
+
+int current_impl();  // TAGI_IMPL_*
+
+// FFMA implementations (tagi_linear_ffma.cu)
+int linear_fwd_ffma(const float *mu_w, const float *var_w, const float *mu_b, const float *var_b, const float *mu_a,
+                    const float *var_a, int B, int K, int N, float *mu_z, float *var_z, cudaStream_t st);
+int linear_bwd_state_ffma(const float *mu_w, const float *jcb, const float *dmu_z, const float *dvar_z, int B, int K,
+                          int N, float *dmu_a, float *dvar_a, cudaStream_t st);
+int linear_bwd_param_ffma(const float *var_w, const float *mu_a, const float *dmu_z, const float *dvar_z, int B,
+                          int K, int N, float *dmu_w, float *dvar_w, cudaStream_t st);
+// column sums of the [B][N] deltas scaled by var_b, var_b^2
+int linear_bias_delta(const float *var_b, const float *dmu_z, const float *dvar_z, int B, int N, float *dmu_b,
+                      float *dvar_b, cudaStream_t st);
+
+// Conv2d on the FFMA engine (tagi_conv_ffma.cu)
+int conv2d_fwd_ffma(const tagi_conv2d_geom &g, const float *mu_w, const float *var_w, const float *mu_b,
+                    const float *var_b, const float *mu_a, const float *var_a, float *mu_z, float *var_z,
+                    cudaStream_t st);
+int conv2d_bwd_state_ffma(const tagi_conv2d_geom &g, const float *mu_w, const float *jcb, const float *dmu_z,
+                          const float *dvar_z, float *dmu_a, float *dvar_a, cudaStream_t st);
+int conv2d_bwd_param_ffma(const tagi_conv2d_geom &g, const float *var_w, const float *var_b, const float *mu_a,
+                          const float *dmu_z, const float *dvar_z, float *dmu_w, float *dvar_w, float *dmu_b,
+                          float *dvar_b, cudaStream_t st);
+
+}  // namespace tagi

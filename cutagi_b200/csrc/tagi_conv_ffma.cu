@@ -1,0 +1,393 @@
+// TAGI Conv2d as implicit GEMM on the FP32 FFMA tile engine: the receptive-field gather is computed
+// from the geometry while a tile is staged, so there are no index tables, no im2col buffer and no
+// permuted copies of the Jacobian or of the deltas. Arithmetic follows the reference's CPU
+// definitions (src/conv2d_layer.cpp:274-322, 363-403, 459-494, 538-556 of cuTAGI) with the
+// receptive-field rule of src/indices.cpp:63-104, 163-194.
+//
+// GEMM views (rows x columns x contraction):
+//   forward          fo x (B*ho*wo) x (fi*k*k)      A = weights,          B = gathered activations
+//   state backward   fi x (B*hi*wi) x (fo*k*k)      A = gathered weights, B = gathered output deltas
+//   parameter bwd    fo x (fi*k*k)  x (B*ho*wo)     A = output deltas,    B = gathered activations
+// The columns are the memory-contiguous index of each output tensor.
+#include <mutex>
+
+#include "tagi_common.h"
+#include "tagi_ffma.cuh"
+
+namespace tagi {
+namespace {
+
+struct Geom {
+    int B, fi, hi, wi, fo, ho, wo, k, stride, off;
+    int k2, Kc, woho, wihi;
+};
+Geom make_geom(const tagi_conv2d_geom &g) {
+    Geom q;
+    q.B = g.B, q.fi = g.fi, q.hi = g.hi, q.wi = g.wi, q.fo = g.fo, q.ho = g.ho, q.wo = g.wo, q.k = g.k;
+    q.stride = g.stride;
+    q.off = g.pad_type == 1 ? g.pad : 0;
+    q.k2 = g.k * g.k, q.Kc = q.k2 * g.fi, q.woho = g.wo * g.ho, q.wihi = g.wi * g.hi;
+    return q;
+}
+
+// Activations seen by output pixel n = (b, oy, ox) through tap kc = (ci, ky, kx); zero outside the image.
+template <int D>
+struct ActForOutputPixel {
+    static constexpr int NSRC = DeriveTraits<D>::NSRC, NSM = DeriveTraits<D>::NSM, DER = D;
+    const float *src0, *src1;
+    Geom g;
+    int rows, kdim;
+    struct Ctx {
+        long base;
+        int y0, x0;
+        bool ok;
+    };
+    __device__ __forceinline__ Ctx row_ctx(int n) const {
+        const int b = n / g.woho, p = n - b * g.woho, oy = p / g.wo, ox = p - oy * g.wo;
+        return {(long)b * g.fi * g.wihi, oy * g.stride - g.off, ox * g.stride - g.off, n < rows};
+    }
+    __device__ __forceinline__ void load(const Ctx &c, int kc, float (&v)[NSM]) const {
+        float x0 = 0.f, x1 = 0.f;
+        if (c.ok && kc < kdim) {
+            const int ci = kc / g.k2, t = kc - ci * g.k2, ky = t / g.k, kx = t - ky * g.k;
+            const int y = c.y0 + ky, x = c.x0 + kx;
+            if ((unsigned)y < (unsigned)g.hi && (unsigned)x < (unsigned)g.wi) {
+                const long i = c.base + (long)ci * g.wihi + y * g.wi + x;
+                x0 = __ldg(src0 + i);
+                if (NSRC == 2) x1 = __ldg(src1 + i);
+            }
+        }
+        derive<D>(x0, x1, v);
+    }
+};
+
+// Same gather with the roles swapped for the parameter pass: row i = (ci, ky, kx), contraction kk = (b, oy, ox).
+template <int D>
+struct ActForTap {
+    static constexpr int NSRC = DeriveTraits<D>::NSRC, NSM = DeriveTraits<D>::NSM, DER = D;
+    const float *src0, *src1;
+    Geom g;
+    int rows, kdim;
+    struct Ctx {
+        long base;
+        int dy, dx;
+        bool ok;
+    };
+    __device__ __forceinline__ Ctx row_ctx(int i) const {
+        const int ci = i / g.k2, t = i - ci * g.k2, ky = t / g.k, kx = t - ky * g.k;
+        return {(long)ci * g.wihi, ky - g.off, kx - g.off, i < rows};
+    }
+    __device__ __forceinline__ void load(const Ctx &c, int kk, float (&v)[NSM]) const {
+        float x0 = 0.f, x1 = 0.f;
+        if (c.ok && kk < kdim) {
+            const int b = kk / g.woho, p = kk - b * g.woho, oy = p / g.wo, ox = p - oy * g.wo;
+            const int y = oy * g.stride + c.dy, x = ox * g.stride + c.dx;
+            if ((unsigned)y < (unsigned)g.hi && (unsigned)x < (unsigned)g.wi) {
+                const long i = (long)b * g.fi * g.wihi + c.base + y * g.wi + x;
+                x0 = __ldg(src0 + i);
+                if (NSRC == 2) x1 = __ldg(src1 + i);
+            }
+        }
+        derive<D>(x0, x1, v);
+    }
+};
+
+// Weights seen from input channel ci through kk = (co, ky, kx): mu_w[co][ci][ky][kx].
+template <int D>
+struct WeightForInputChannel {
+    static constexpr int NSRC = DeriveTraits<D>::NSRC, NSM = DeriveTraits<D>::NSM, DER = D;
+    const float *src0, *src1;
+    Geom g;
+    int rows, kdim;
+    struct Ctx {
+        long base;
+        bool ok;
+    };
+    __device__ __forceinline__ Ctx row_ctx(int ci) const { return {(long)ci * g.k2, ci < rows}; }
+    __device__ __forceinline__ void load(const Ctx &c, int kk, float (&v)[NSM]) const {
+        float x0 = 0.f, x1 = 0.f;
+        if (c.ok && kk < kdim) {
+            const int co = kk / g.k2, t = kk - co * g.k2;
+            const long i = (long)co * g.Kc + c.base + t;
+            x0 = __ldg(src0 + i);
+            if (NSRC == 2) x1 = __ldg(src1 + i);
+        }
+        derive<D>(x0, x1, v);
+    }
+};
+
+// Output deltas that input pixel n = (b, y, x) receives through kk = (co, ky, kx): the output pixel
+// ((y + off - ky) / stride, (x + off - kx) / stride) when that division is exact and inside the output.
+template <int D>
+struct DeltaForInputPixel {
+    static constexpr int NSRC = DeriveTraits<D>::NSRC, NSM = DeriveTraits<D>::NSM, DER = D;
+    const float *src0, *src1;
+    Geom g;
+    int rows, kdim;
+    struct Ctx {
+        long base;
+        int y, x;
+        bool ok;
+    };
+    __device__ __forceinline__ Ctx row_ctx(int n) const {
+        const int b = n / g.wihi, q = n - b * g.wihi, y = q / g.wi, x = q - y * g.wi;
+        return {(long)b * g.fo * g.woho, y + g.off, x + g.off, n < rows};
+    }
+    __device__ __forceinline__ void load(const Ctx &c, int kk, float (&v)[NSM]) const {
+        float x0 = 0.f, x1 = 0.f;
+        if (c.ok && kk < kdim) {
+            const int co = kk / g.k2, t = kk - co * g.k2, ky = t / g.k, kx = t - ky * g.k;
+            const int ty = c.y - ky, tx = c.x - kx;
+            if (ty >= 0 && tx >= 0) {
+                const int oy = ty / g.stride, ox = tx / g.stride;
+                if (oy * g.stride == ty && ox * g.stride == tx && oy < g.ho && ox < g.wo) {
+                    const long i = c.base + (long)co * g.woho + oy * g.wo + ox;
+                    x0 = __ldg(src0 + i);
+                    if (NSRC == 2) x1 = __ldg(src1 + i);
+                }
+            }
+        }
+        derive<D>(x0, x1, v);
+    }
+};
+
+// Output deltas of channel co over kk = (b, p): delta[b][co][p].
+template <int D>
+struct DeltaForChannel {
+    static constexpr int NSRC = DeriveTraits<D>::NSRC, NSM = DeriveTraits<D>::NSM, DER = D;
+    const float *src0, *src1;
+    Geom g;
+    int rows, kdim;
+    struct Ctx {
+        long base;
+        bool ok;
+    };
+    __device__ __forceinline__ Ctx row_ctx(int co) const { return {(long)co * g.woho, co < rows}; }
+    __device__ __forceinline__ void load(const Ctx &c, int kk, float (&v)[NSM]) const {
+        float x0 = 0.f, x1 = 0.f;
+        if (c.ok && kk < kdim) {
+            const int b = kk / g.woho, p = kk - b * g.woho;
+            const long i = (long)b * g.fo * g.woho + c.base + p;
+            x0 = __ldg(src0 + i);
+            if (NSRC == 2) x1 = __ldg(src1 + i);
+        }
+        derive<D>(x0, x1, v);
+    }
+};
+
+// Output tensors [b][chan][pix] written from GEMM coordinates (m = chan, n = b * npix + pix).
+// bias: out = c + bias[m] (forward). scale: out1 = c1 * s, out2 = c2 * s * s with s = scale[same index].
+struct EpiChanPix {
+    float *out1, *out2;
+    const float *bias1, *bias2;  // forward, may be null
+    const float *scale;          // state backward (Jacobian), may be null
+    int nchan, npix;
+    bool vec_ok;  // npix % 4 == 0 and 16-byte aligned bases: four consecutive n stay inside one image
+    __device__ __forceinline__ long index(int m, int n) const {
+        const int b = n / npix, p = n - b * npix;
+        return ((long)b * nchan + m) * npix + p;
+    }
+    __device__ __forceinline__ void store(int m, int n, int, float c1, float c2) const {
+        const long i = index(m, n);
+        if (bias1) {
+            c1 += __ldg(bias1 + m);
+            c2 += __ldg(bias2 + m);
+        }
+        if (scale) {
+            const float s = __ldg(scale + i);
+            c1 *= s;
+            c2 = c2 * s * s;
+        }
+        out1[i] = c1;
+        out2[i] = c2;
+    }
+    __device__ __forceinline__ void store4(int m, int n, int, float4 c1, float4 c2) const {
+        const long i = index(m, n);
+        if (bias1) {
+            const float b1 = __ldg(bias1 + m), b2 = __ldg(bias2 + m);
+            c1.x += b1, c1.y += b1, c1.z += b1, c1.w += b1;
+            c2.x += b2, c2.y += b2, c2.z += b2, c2.w += b2;
+        }
+        if (scale) {
+            const float4 s = __ldg(reinterpret_cast<const float4 *>(scale + i));
+            c1.x *= s.x, c1.y *= s.y, c1.z *= s.z, c1.w *= s.w;
+            c2.x = c2.x * s.x * s.x, c2.y = c2.y * s.y * s.y, c2.z = c2.z * s.z * s.z, c2.w = c2.w * s.w * s.w;
+        }
+        __stcs(reinterpret_cast<float4 *>(out1 + i), c1);
+        __stcs(reinterpret_cast<float4 *>(out2 + i), c2);
+    }
+};
+
+// Sum of the split-K slices in slice order, then the var_w scaling of the parameter pass.
+__global__ void __launch_bounds__(256) reduce_slices_scale_kernel(const float *__restrict__ part1,
+                                                                  const float *__restrict__ part2,
+                                                                  const float *__restrict__ scale, long n, int slices,
+                                                                  float *__restrict__ out1,
+                                                                  float *__restrict__ out2) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float a1 = 0.f, a2 = 0.f;
+    for (int z = 0; z < slices; z++) {
+        a1 += part1[(long)z * n + i];
+        a2 += part2[(long)z * n + i];
+    }
+    const float s = __ldg(scale + i);
+    out1[i] = a1 * s;
+    out2[i] = a2 * s * s;
+}
+
+// Bias deltas: per output channel the sum over (b, pixel) of the deltas, one CTA per channel,
+// fixed-order tree so the result does not depend on scheduling.
+__global__ void __launch_bounds__(256) conv_bias_delta_kernel(const float *__restrict__ var_b,
+                                                              const float *__restrict__ dmu_z,
+                                                              const float *__restrict__ dvar_z, int B, int fo,
+                                                              int woho, float *__restrict__ dmu_b,
+                                                              float *__restrict__ dvar_b) {
+    __shared__ float s1[256], s2[256];
+    const int co = blockIdx.x;
+    float a1 = 0.f, a2 = 0.f;
+    const long total = (long)B * woho;
+    for (long t = threadIdx.x; t < total; t += 256) {
+        const long b = t / woho, p = t - b * woho;
+        const long i = (b * fo + co) * woho + p;
+        a1 += __ldg(dmu_z + i);
+        a2 += __ldg(dvar_z + i);
+    }
+    s1[threadIdx.x] = a1;
+    s2[threadIdx.x] = a2;
+    __syncthreads();
+    for (int w = 128; w > 0; w >>= 1) {
+        if (threadIdx.x < w) {
+            s1[threadIdx.x] += s1[threadIdx.x + w];
+            s2[threadIdx.x] += s2[threadIdx.x + w];
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        const float vb = __ldg(var_b + co);
+        dmu_b[co] = s1[0] * vb;
+        dvar_b[co] = s2[0] * vb * vb;
+    }
+}
+
+inline int done(cudaError_t e, const char *what) { return e == cudaSuccess ? TAGI_OK : cuda_fail(e, what); }
+
+}  // namespace
+
+int conv2d_fwd_ffma(const tagi_conv2d_geom &cg, const float *mu_w, const float *var_w, const float *mu_b,
+                    const float *var_b, const float *mu_a, const float *var_a, float *mu_z, float *var_z,
+                    cudaStream_t st) {
+    const Geom g = make_geom(cg);
+    const int M = g.fo, N = g.B * g.woho, Kd = g.Kc;
+    StridedOperand<DER_MEAN_VAR_W> W{mu_w, var_w, (long)g.Kc, 1, g.fo, g.Kc};
+    ActForOutputPixel<DER_MEAN_VAR_ACT> X{mu_a, var_a, g, N, Kd};
+    EpiChanPix epi{mu_z, var_z, mu_b, var_b, nullptr, g.fo, g.woho,
+                   g.woho % 4 == 0 && aligned16(mu_z) && aligned16(var_z)};
+    return done(dispatch_ffma<decltype(W), decltype(X), EpiChanPix, LOAD_K_VEC4, LOAD_K_SCALAR, LOAD_R_SCALAR,
+                              LOAD_R_SCALAR>(W, X, epi, M, N, Kd, g.Kc % 4 == 0 && aligned16(mu_w) && aligned16(var_w),
+                                             false, st),
+                "conv2d forward launch");
+}
+
+int conv2d_bwd_state_ffma(const tagi_conv2d_geom &cg, const float *mu_w, const float *jcb, const float *dmu_z,
+                          const float *dvar_z, float *dmu_a, float *dvar_a, cudaStream_t st) {
+    const Geom g = make_geom(cg);
+    const int M = g.fi, N = g.B * g.wihi, Kd = g.fo * g.k2;
+    WeightForInputChannel<DER_SQUARE> W{mu_w, nullptr, g, g.fi, Kd};
+    DeltaForInputPixel<DER_PAIR> D{dmu_z, dvar_z, g, N, Kd};
+    EpiChanPix epi{dmu_a, dvar_a, nullptr, nullptr, jcb, g.fi, g.wihi,
+                   g.wihi % 4 == 0 && aligned16(dmu_a) && aligned16(dvar_a) && aligned16(jcb)};
+    return done(dispatch_ffma<decltype(W), decltype(D), EpiChanPix, LOAD_K_SCALAR, LOAD_K_SCALAR, LOAD_R_SCALAR,
+                              LOAD_R_SCALAR>(W, D, epi, M, N, Kd, false, false, st),
+                "conv2d state backward launch");
+}
+
+// Scratch for the split-K partial sums of the parameter pass: one grow-only buffer per device, owned by
+// the library. Calls that use it are ordered by the stream they run on; calls on different streams of
+// one device that both need scratch must not overlap.
+namespace {
+struct Scratch {
+    float *ptr = nullptr;
+    size_t bytes = 0;
+};
+Scratch g_scratch[64];
+std::mutex g_scratch_mu;
+
+int get_scratch(size_t bytes, float **out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (dev < 0 || dev >= 64) return fail(TAGI_ERR_UNSUPPORTED, "device index out of range");
+    std::lock_guard<std::mutex> lk(g_scratch_mu);
+    Scratch &s = g_scratch[dev];
+    if (s.bytes < bytes) {
+        if (s.ptr) {
+            e = cudaDeviceSynchronize();  // earlier calls may still be using the old buffer
+            if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceSynchronize");
+            cudaFree(s.ptr);
+            s.ptr = nullptr;
+            s.bytes = 0;
+        }
+        const size_t want = bytes + bytes / 2;
+        e = cudaMalloc(&s.ptr, want);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(split-K scratch)");
+        s.bytes = want;
+    }
+    *out = s.ptr;
+    return TAGI_OK;
+}
+}  // namespace
+
+int conv2d_bwd_param_ffma(const tagi_conv2d_geom &cg, const float *var_w, const float *var_b, const float *mu_a,
+                          const float *dmu_z, const float *dvar_z, float *dmu_w, float *dvar_w, float *dmu_b,
+                          float *dvar_b, cudaStream_t st) {
+    const Geom g = make_geom(cg);
+    const int M = g.fo, N = g.Kc, Kd = g.B * g.woho;
+    DeltaForChannel<DER_PAIR> D{dmu_z, dvar_z, g, g.fo, Kd};
+    ActForTap<DER_SQUARE> X{mu_a, nullptr, g, g.Kc, Kd};
+
+    // The output (fo x fi*k*k) is small and the contraction (B*ho*wo) long: slice the contraction so that
+    // about two CTAs per SM are in flight.
+    const bool big = M >= 128 && N >= 128;
+    const int tm = big ? 128 : 64;
+    const long tiles = (long)((M + tm - 1) / tm) * ((N + tm - 1) / tm);
+    int splits = (int)((2 * 148 + tiles - 1) / tiles);
+    const int max_splits = (Kd + 255) / 256;  // keep at least 256 contraction steps per slice
+    if (splits > max_splits) splits = max_splits;
+    if (splits < 1) splits = 1;
+
+    int rc;
+    if (splits == 1) {
+        EpiRowScale epi{dmu_w, dvar_w, var_w, (long)N,
+                        N % 4 == 0 && aligned16(dmu_w) && aligned16(dvar_w) && aligned16(var_w)};
+        rc = done(dispatch_ffma<decltype(D), decltype(X), EpiRowScale, LOAD_K_SCALAR, LOAD_K_SCALAR, LOAD_K_SCALAR,
+                                LOAD_K_SCALAR>(D, X, epi, M, N, Kd, false, false, st),
+                  "conv2d parameter backward launch");
+    } else {
+        const long slice = (long)M * N;
+        float *ws = nullptr;
+        rc = get_scratch((size_t)2 * splits * slice * sizeof(float), &ws);
+        if (rc != TAGI_OK) return rc;
+        EpiPartial epi{ws, ws + (long)splits * slice, (long)N, slice, N % 4 == 0};
+        // the kernel may use fewer slices than asked for (slice length is rounded up); it reports through the grid,
+        // so recompute the same rounding here
+        const int bk = use_large_tile(M, N, splits) ? TileL::BK : TileS::BK;
+        const int k_chunk = ((Kd + splits - 1) / splits + bk - 1) / bk * bk;
+        const int slices = (Kd + k_chunk - 1) / k_chunk;
+        rc = done(dispatch_ffma<decltype(D), decltype(X), EpiPartial, LOAD_K_SCALAR, LOAD_K_SCALAR, LOAD_K_SCALAR,
+                                LOAD_K_SCALAR>(D, X, epi, M, N, Kd, false, false, st, splits),
+                  "conv2d parameter backward launch");
+        if (rc != TAGI_OK) return rc;
+        reduce_slices_scale_kernel<<<(unsigned)((slice + 255) / 256), 256, 0, st>>>(
+            ws, ws + (long)splits * slice, var_w, slice, slices, dmu_w, dvar_w);
+        rc = done(cudaGetLastError(), "reduce_slices_scale_kernel launch");
+    }
+    if (rc != TAGI_OK) return rc;
+    if (cg.has_bias) {
+        conv_bias_delta_kernel<<<g.fo, 256, 0, st>>>(var_b, dmu_z, dvar_z, g.B, g.fo, g.woho, dmu_b, dvar_b);
+        rc = done(cudaGetLastError(), "conv_bias_delta_kernel launch");
+    }
+    return rc;
+}
+
+}  // namespace tagi

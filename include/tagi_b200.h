@@ -1,0 +1,116 @@
+/* tagi_b200.h - C ABI of the B200 (sm_100a) TAGI Linear / Conv2d hot path.
+ *
+ * Every entry point takes plain pointers and sizes, returns an int status
+ * (TAGI_OK = 0) and never exits or throws; tagi_last_error_string() gives the
+ * reason for the last non-zero status on the calling thread. Unless an entry
+ * point says "host", pointers are DEVICE pointers owned by the caller, `stream`
+ * is a cudaStream_t passed as void* (NULL = the legacy default stream, which
+ * is what the reference's launchers use) and the call is asynchronous.
+ * Inputs and outputs of one call must not alias. Outputs are fully overwritten
+ * for the live extent (B x features) and nothing beyond it is touched.
+ *
+ * Layouts (row-major, flat FP32, as in the reference):
+ *   activations / deltas  [B][features]        (src/linear_layer.cpp:44-54)
+ *   Linear weights        [N][K]               (src/linear_layer.cpp:46)
+ *   conv activations      [B][C][H][W], weights [fo][fi][k][k],
+ *   conv outputs          [B][fo][ho*wo]       (src/conv2d_layer.cpp:297-314)
+ *
+ * File:line citations name the reference interface that each entry point
+ * replaces (paths inside the cuTAGI source tree).
+ */
+#ifndef TAGI_B200_H
+#define TAGI_B200_H
+#include <stddef.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    TAGI_OK = 0,
+    TAGI_ERR_INVALID_ARGUMENT = 1, /* null pointer, non-positive size, misaligned pointer, bad geometry */
+    TAGI_ERR_CUDA = 2,             /* a CUDA runtime / driver call failed */
+    TAGI_ERR_UNSUPPORTED = 3,      /* requested implementation cannot run this shape */
+    TAGI_ERR_COMM = 4              /* NCCL / rendezvous failure */
+};
+
+/* Which arithmetic the three Linear entry points use.
+ *   AUTO   : the measured-faster variant that supports the shape (default)
+ *   FFMA   : FP32 fused multiply-add on the CUDA cores, any shape
+ *   TF32X3 : tcgen05 tensor-core MMA, each FP32 product split into three TF32 products
+ *            (hi*hi + hi*lo + lo*hi) accumulated in FP32 in tensor memory;
+ *            shapes it cannot run return TAGI_ERR_UNSUPPORTED under this setting. */
+enum { TAGI_IMPL_AUTO = 0, TAGI_IMPL_FFMA = 1, TAGI_IMPL_TF32X3 = 2 };
+int tagi_set_impl(int impl);
+int tagi_get_impl(void);
+
+const char *tagi_last_error_string(void);
+/* Library version as major*10000 + minor*100 + patch. */
+int tagi_version(void);
+
+/* ------------------------------------------------------------------ Linear */
+
+/* mu_z = mu_a.mu_w^T + mu_b ; var_z = var_a.(mu_w^2+var_w)^T + mu_a^2.var_w^T + var_b.
+ * Replaces linear_forward_cuda (src/linear_layer_cuda.cu:12-73) and its kernels
+ * linear_fwd_mean_var_v4/v3/v1 (include/linear_cuda_kernel.cuh:375,246,50); the CPU definition is
+ * linear_fwd_mean_var (src/linear_layer.cpp:10-60). mu_b/var_b may be NULL when has_bias == 0. */
+int tagi_linear_fwd(const float *mu_w, const float *var_w, const float *mu_b, const float *var_b,
+                    const float *mu_a, const float *var_a, int B, int K, int N, int has_bias,
+                    float *mu_z, float *var_z, void *stream);
+
+/* dmu_a = jcb * (dmu_z.mu_w) ; dvar_a = jcb^2 * (dvar_z.mu_w^2).
+ * Replaces linear_state_backward_cuda (src/linear_layer_cuda.cu:75-121), kernels linear_bwd_delta_z_v4/v3
+ * (include/linear_cuda_kernel.cuh:894,776); CPU definition linear_bwd_fc_delta_z (src/linear_layer.cpp:245-272).
+ * jcb is the Jacobian saved by the forward pass (bwd_states->jcb), [B][K]. */
+int tagi_linear_bwd_state(const float *mu_w, const float *jcb, const float *dmu_z, const float *dvar_z,
+                          int B, int K, int N, float *dmu_a, float *dvar_a, void *stream);
+
+/* dmu_w = var_w * (dmu_z^T.mu_a) ; dvar_w = var_w^2 * (dvar_z^T.mu_a^2) ;
+ * dmu_b = var_b * sum_b dmu_z ; dvar_b = var_b^2 * sum_b dvar_z  (bias part only when has_bias != 0).
+ * Replaces linear_weight_backward_cuda (src/linear_layer_cuda.cu:123-168), kernels linear_bwd_delta_w_v4/v3
+ * (include/linear_cuda_kernel.cuh:1320,1200) and the linear_bwd_delta_b launch (src/linear_layer_cuda.cu:311-321);
+ * CPU definitions linear_bwd_fc_delta_w / _delta_b (src/linear_layer.cpp:314-349, 391-423).
+ * mu_a is the input mean saved by the forward pass (bwd_states->mu_a), [B][K]. */
+int tagi_linear_bwd_param(const float *var_w, const float *var_b, const float *mu_a, const float *dmu_z,
+                          const float *dvar_z, int B, int K, int N, int has_bias, float *dmu_w, float *dvar_w,
+                          float *dmu_b, float *dvar_b, void *stream);
+
+/* ------------------------------------------------------------------ Conv2d */
+
+/* Geometry of one Conv2d call. The receptive field of output pixel (oy, ox), tap (ky, kx) is input pixel
+ * (oy*stride - off + ky, ox*stride - off + kx), off = pad for pad_type 1, off = 0 (padding on the bottom / right
+ * only) for pad_type 2 and for no padding; taps outside the image contribute nothing (src/indices.cpp:63-104,
+ * 163-194; src/conv2d_layer.cpp:299). ho / wo must equal tagi_conv2d_out_size()'s result. No index tables and
+ * no temporary buffers are needed: the kernels compute the gather arithmetically. */
+typedef struct tagi_conv2d_geom {
+    int B, fi, hi, wi, fo, ho, wo, k, stride, pad, pad_type, has_bias;
+} tagi_conv2d_geom;
+
+/* Host helper. Output extent by the reference's rule (compute_downsample_img_size_v2, src/conv2d_layer.cpp:581-628):
+ * pad_type 1: (w - k + 2*pad)/stride + 1 ; 2: (w - k + pad)/stride + 1 ; else (w - k)/stride + 1.
+ * TAGI_ERR_INVALID_ARGUMENT where the reference raises (numerator not divisible by the stride). */
+int tagi_conv2d_out_size(int k, int stride, int wi, int hi, int pad, int pad_type, int *wo, int *ho);
+
+/* Replaces conv2d_forward_cuda (src/conv2d_layer_cuda.cu:22-88), kernels conv2d_fwd_mean_var_cuda_v3/v2/v1
+ * (include/conv2d_cuda_kernel.cuh:491,351,260); CPU definition conv2d_fwd_mean_var (src/conv2d_layer.cpp:274-322). */
+int tagi_conv2d_fwd(const tagi_conv2d_geom *g, const float *mu_w, const float *var_w, const float *mu_b,
+                    const float *var_b, const float *mu_a, const float *var_a, float *mu_z, float *var_z,
+                    void *stream);
+
+/* Replaces conv2d_state_backward_cuda (src/conv2d_layer_cuda.cu:90-147), kernels conv2d_bwd_delta_z_cuda_v2/v1
+ * (include/conv2d_cuda_kernel.cuh:948,864) and the Jacobian permute launch (src/conv2d_layer_cuda.cu:504-511);
+ * CPU definition conv2d_bwd_delta_z (src/conv2d_layer.cpp:363-403). jcb is in the natural [B][fi][hi*wi] layout. */
+int tagi_conv2d_bwd_state(const tagi_conv2d_geom *g, const float *mu_w, const float *jcb, const float *dmu_z,
+                          const float *dvar_z, float *dmu_a, float *dvar_a, void *stream);
+
+/* Replaces conv2d_param_backward_cuda (src/conv2d_layer_cuda.cu:149-227), kernels conv2d_bwd_delta_w_cuda_v3/v2/v1
+ * (include/conv2d_cuda_kernel.cuh:1333,1199,1109), permute_delta_cuda (:241) and the bias reduction
+ * conv2d_bwd_delta_b_dual_sum_reduction (include/conv2d_cuda_kernel.cuh:812-860); CPU definitions conv2d_bwd_delta_w /
+ * _delta_b (src/conv2d_layer.cpp:459-494, 538-556). Deltas are in the natural [B][fo][ho*wo] layout. */
+int tagi_conv2d_bwd_param(const tagi_conv2d_geom *g, const float *var_w, const float *var_b, const float *mu_a,
+                          const float *dmu_z, const float *dvar_z, float *dmu_w, float *dvar_w, float *dmu_b,
+                          float *dvar_b, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TAGI_B200_H */

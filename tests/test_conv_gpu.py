@@ -1,0 +1,104 @@
+"""GPU parity of the Conv2d entry points (through the C ABI) against the CPU oracle and the golden fixtures."""
+import ctypes as C
+
+import numpy as np
+import pytest
+from oracle_lib import ConvGeom
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def G():
+    import gpu_util
+    return gpu_util
+
+
+def _run_all(G, oracle, g, x):
+    mz, vz = G.conv_fwd(g, x["mu_w"], x["var_w"], x["mu_b"], x["var_b"], x["mu_a"], x["var_a"])
+    rmz, rvz = oracle.conv2d_fwd(g, x["mu_w"], x["var_w"], x["mu_b"], x["var_b"], x["mu_a"], x["var_a"])
+    G.check("mu_z", mz, rmz, G.RTOL_MU)
+    G.check("var_z", vz, rvz, G.RTOL_VAR)
+    da, dv = G.conv_bwd_state(g, x["mu_w"], x["jcb"], x["dmu_z"], x["dvar_z"])
+    rda, rdv = oracle.conv2d_bwd_state(g, x["mu_w"], x["jcb"], x["dmu_z"], x["dvar_z"])
+    G.check("dmu_a", da, rda, G.RTOL_MU)
+    G.check("dvar_a", dv, rdv, G.RTOL_VAR)
+    dmw, dvw, dmb, dvb = G.conv_bwd_param(g, x["var_w"], x["var_b"], x["mu_a"], x["dmu_z"], x["dvar_z"])
+    r = oracle.conv2d_bwd_param(g, x["var_w"], x["var_b"], x["mu_a"], x["dmu_z"], x["dvar_z"])
+    G.check("dmu_w", dmw, r[0], G.RTOL_MU)
+    G.check("dvar_w", dvw, r[1], G.RTOL_VAR)
+    if g.has_bias:
+        G.check("dmu_b", dmb, r[2], G.RTOL_MU)
+        G.check("dvar_b", dvb, r[3], G.RTOL_VAR)
+
+
+@pytest.mark.parametrize("i", range(8))
+def test_golden_cases(G, golden, i):
+    p = f"conv{i}_"
+    x = {k[len(p):]: np.ascontiguousarray(golden[k]) for k in golden.files if k.startswith(p)}
+    B, fi, hi, wi, fo, k, stride, pad, pad_type, has_bias, ho, wo = [int(v) for v in x["geom"]]
+    g = ConvGeom(B=B, fi=fi, hi=hi, wi=wi, fo=fo, k=k, stride=stride, pad=pad, pad_type=pad_type, has_bias=has_bias)
+    mz, vz = G.conv_fwd(g, x["mu_w"], x["var_w"], x.get("mu_b"), x.get("var_b"), x["mu_a"], x["var_a"])
+    G.check("mu_z", mz, x["mu_z"], G.RTOL_MU)
+    G.check("var_z", vz, x["var_z"], G.RTOL_VAR)
+    da, dv = G.conv_bwd_state(g, x["mu_w"], x["jcb"], x["dmu_z"], x["dvar_z"])
+    G.check("dmu_a", da, x["dmu_a"], G.RTOL_MU)
+    G.check("dvar_a", dv, x["dvar_a"], G.RTOL_VAR)
+    dmw, dvw, dmb, dvb = G.conv_bwd_param(g, x["var_w"], x.get("var_b"), x["mu_a"], x["dmu_z"], x["dvar_z"])
+    G.check("dmu_w", dmw, x["dmu_w"], G.RTOL_MU)
+    G.check("dvar_w", dvw, x["dvar_w"], G.RTOL_VAR)
+    if has_bias:
+        G.check("dmu_b", dmb, x["dmu_b"], G.RTOL_MU)
+        G.check("dvar_b", dvb, x["dvar_b"], G.RTOL_VAR)
+
+
+# the layer geometries of the CIFAR-shaped CNN and of ResNet-18 at reduced batch / image extent, plus odd ones
+GEOMS = [
+    dict(B=4, fi=3, hi=32, wi=32, fo=32, k=3, stride=1, pad=1, pad_type=1, has_bias=1),     # CNN conv1
+    dict(B=4, fi=32, hi=16, wi=16, fo=64, k=3, stride=1, pad=1, pad_type=1, has_bias=1),    # CNN conv2
+    dict(B=4, fi=64, hi=8, wi=8, fo=128, k=3, stride=1, pad=1, pad_type=1, has_bias=1),     # CNN conv3
+    dict(B=2, fi=3, hi=32, wi=32, fo=64, k=6, stride=2, pad=2, pad_type=1, has_bias=0),     # ResNet stem (k6 s2 p2)
+    dict(B=2, fi=64, hi=14, wi=14, fo=64, k=3, stride=1, pad=1, pad_type=1, has_bias=0),    # layer1 block conv
+    dict(B=2, fi=64, hi=14, wi=14, fo=128, k=3, stride=2, pad=1, pad_type=2, has_bias=0),   # down-sampling conv
+    dict(B=2, fi=64, hi=14, wi=14, fo=128, k=2, stride=2, pad=0, pad_type=0, has_bias=0),   # projection shortcut
+    dict(B=3, fi=128, hi=7, wi=7, fo=256, k=3, stride=1, pad=1, pad_type=1, has_bias=0),
+    dict(B=1, fi=5, hi=9, wi=9, fo=7, k=5, stride=2, pad=2, pad_type=1, has_bias=1),
+    dict(B=2, fi=1, hi=5, wi=5, fo=1, k=1, stride=1, pad=0, pad_type=0, has_bias=1),
+    dict(B=5, fi=2, hi=6, wi=6, fo=130, k=3, stride=1, pad=0, pad_type=0, has_bias=1),
+]
+
+
+@pytest.mark.parametrize("kw", GEOMS, ids=lambda k: "fi{fi}_fo{fo}_h{hi}_k{k}_s{stride}_p{pad}t{pad_type}".format(**k))
+def test_layer_geometries(G, oracle, kw):
+    g = ConvGeom(**kw)
+    rng = np.random.default_rng(g.fi * 131 + g.fo * 7 + g.hi)
+    _run_all(G, oracle, g, G.conv_inputs(rng, g))
+
+
+def test_split_contraction_parameter_pass(G, oracle):
+    """Long contraction (B*ho*wo) with a small weight tensor: the parameter pass slices the contraction and sums
+    the slices in a fixed order; check parity and run-to-run bit equality."""
+    g = ConvGeom(B=16, fi=16, hi=28, wi=28, fo=32, k=3, stride=1, pad=1, pad_type=1, has_bias=1)
+    rng = np.random.default_rng(17)
+    x = G.conv_inputs(rng, g)
+    a = G.conv_bwd_param(g, x["var_w"], x["var_b"], x["mu_a"], x["dmu_z"], x["dvar_z"])
+    b = G.conv_bwd_param(g, x["var_w"], x["var_b"], x["mu_a"], x["dmu_z"], x["dvar_z"])
+    r = oracle.conv2d_bwd_param(g, x["var_w"], x["var_b"], x["mu_a"], x["dmu_z"], x["dvar_z"])
+    for name, u, v, w, tol in zip(("dmu_w", "dvar_w", "dmu_b", "dvar_b"), a, b, r,
+                                  (G.RTOL_MU, G.RTOL_VAR, G.RTOL_MU, G.RTOL_VAR)):
+        assert np.array_equal(u, v)
+        G.check(name, u, w, tol)
+
+
+def test_geometry_errors(G):
+    from cutagi_b200.capi import ConvGeom as CG, TagiError, conv_out_size, lib
+    assert conv_out_size(6, 2, 224, 224, 2, 1) == (112, 112)
+    assert conv_out_size(3, 2, 56, 56, 1, 2) == (28, 28)
+    with pytest.raises(TagiError) as e:
+        conv_out_size(3, 2, 8, 8, 0, 0)   # the reference raises for a stride that does not divide
+    assert e.value.code == 1 and "invalid hyperparameters" in str(e.value).lower()
+    import torch
+    q = torch.zeros(4096, device="cuda").data_ptr()
+    bad = CG(1, 1, 8, 8, 1, 5, 5, 3, 1, 0, 0, 0)   # ho / wo inconsistent (should be 6)
+    with pytest.raises(TagiError):
+        lib.tagi_conv2d_fwd(C.byref(bad), q, q, q, q, q, q, q, q, None)

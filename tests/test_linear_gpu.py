@@ -1,0 +1,141 @@
+"""GPU parity of the Linear entry points (through the C ABI) against the CPU oracle and the golden fixtures."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def G():
+    import gpu_util
+    return gpu_util
+
+
+def _run_all(G, oracle, x, misalign=0, tag=""):
+    mz, vz = G.linear_fwd(x["mu_w"], x["var_w"], x["mu_b"], x["var_b"], x["mu_a"], x["var_a"], misalign)
+    rmz, rvz = oracle.linear_fwd(x["mu_w"], x["var_w"], x["mu_b"], x["var_b"], x["mu_a"], x["var_a"])
+    G.check(tag + "mu_z", mz, rmz, G.RTOL_MU)
+    G.check(tag + "var_z", vz, rvz, G.RTOL_VAR)
+    da, dv = G.linear_bwd_state(x["mu_w"], x["jcb"], x["dmu_z"], x["dvar_z"], misalign)
+    rda, rdv = oracle.linear_bwd_state(x["mu_w"], x["jcb"], x["dmu_z"], x["dvar_z"])
+    G.check(tag + "dmu_a", da, rda, G.RTOL_MU)
+    G.check(tag + "dvar_a", dv, rdv, G.RTOL_VAR)
+    dmw, dvw, dmb, dvb = G.linear_bwd_param(x["var_w"], x["var_b"], x["mu_a"], x["dmu_z"], x["dvar_z"], misalign)
+    r = oracle.linear_bwd_param(x["var_w"], x["var_b"], x["mu_a"], x["dmu_z"], x["dvar_z"])
+    G.check(tag + "dmu_w", dmw, r[0], G.RTOL_MU)
+    G.check(tag + "dvar_w", dvw, r[1], G.RTOL_VAR)
+    if x["var_b"] is not None:
+        G.check(tag + "dmu_b", dmb, r[2], G.RTOL_MU)
+        G.check(tag + "dvar_b", dvb, r[3], G.RTOL_VAR)
+
+
+@pytest.mark.parametrize("i", range(8))
+def test_golden_cases(G, golden, i):
+    p = f"lin{i}_"
+    g = {k[len(p):]: np.ascontiguousarray(golden[k]) for k in golden.files if k.startswith(p)}
+    mz, vz = G.linear_fwd(g["mu_w"], g["var_w"], g.get("mu_b"), g.get("var_b"), g["mu_a"], g["var_a"])
+    G.check("mu_z", mz, g["mu_z"], G.RTOL_MU)
+    G.check("var_z", vz, g["var_z"], G.RTOL_VAR)
+    da, dv = G.linear_bwd_state(g["mu_w"], g["jcb"], g["dmu_z"], g["dvar_z"])
+    G.check("dmu_a", da, g["dmu_a"], G.RTOL_MU)
+    G.check("dvar_a", dv, g["dvar_a"], G.RTOL_VAR)
+    dmw, dvw, dmb, dvb = G.linear_bwd_param(g["var_w"], g.get("var_b"), g["mu_a"], g["dmu_z"], g["dvar_z"])
+    G.check("dmu_w", dmw, g["dmu_w"], G.RTOL_MU)
+    G.check("dvar_w", dvw, g["dvar_w"], G.RTOL_VAR)
+    if "var_b" in g:
+        G.check("dmu_b", dmb, g["dmu_b"], G.RTOL_MU)
+        G.check("dvar_b", dvb, g["dvar_b"], G.RTOL_VAR)
+
+
+# every tile-edge residue of the 64- and 128-wide tiles, vector and scalar load paths, with and without bias
+EDGE = [(1, 1, 1), (3, 5, 11), (4, 4, 4), (5, 3, 1), (11, 63, 65), (63, 64, 127), (64, 65, 128), (65, 127, 129),
+        (127, 128, 64), (128, 129, 63), (129, 11, 5), (32, 784, 128), (32, 128, 11), (16, 785, 6), (130, 260, 132),
+        (256, 8, 256), (7, 1, 300), (300, 300, 1)]
+
+
+@pytest.mark.parametrize("B,K,N", EDGE)
+@pytest.mark.parametrize("bias", [True, False])
+def test_edge_shapes(G, oracle, B, K, N, bias):
+    rng = np.random.default_rng(B * 1000003 + K * 1009 + N)
+    _run_all(G, oracle, G.linear_inputs(rng, B, K, N, bias))
+
+
+@pytest.mark.parametrize("B,K,N", [(8, 64, 64), (33, 128, 96), (130, 256, 132)])
+def test_misaligned_pointers(G, oracle, B, K, N):
+    """Buffers that start 4 bytes past a 16-byte boundary must take the scalar paths and still be exact."""
+    rng = np.random.default_rng(99 + B)
+    _run_all(G, oracle, G.linear_inputs(rng, B, K, N), misalign=1)
+
+
+@pytest.mark.parametrize("B,K,N", [(256, 1024, 1024), (1024, 512, 1536), (2048, 256, 1280)])
+def test_large_tile_path(G, oracle, B, K, N):
+    rng = np.random.default_rng(5 + B)
+    _run_all(G, oracle, G.linear_inputs(rng, B, K, N))
+
+
+def test_benchmark_shape_sampled(G, oracle):
+    """B=1024, 4096 -> 4096: the CPU oracle on this shape takes minutes, so rows are sampled. Forward and state
+    backward outputs of a batch row depend on that row only; parameter deltas of an output feature depend on that
+    feature's delta column only."""
+    rng = np.random.default_rng(2024)
+    B, K, N = 1024, 4096, 4096
+    x = G.linear_inputs(rng, B, K, N)
+    rows = np.sort(rng.choice(B, 6, replace=False))
+    feats = np.sort(rng.choice(N, 6, replace=False))
+    mz, vz = G.linear_fwd(x["mu_w"], x["var_w"], x["mu_b"], x["var_b"], x["mu_a"], x["var_a"])
+    rmz, rvz = oracle.linear_fwd(x["mu_w"], x["var_w"], x["mu_b"], x["var_b"],
+                                 np.ascontiguousarray(x["mu_a"][rows]), np.ascontiguousarray(x["var_a"][rows]))
+    G.check("mu_z", mz[rows], rmz, G.RTOL_MU)
+    G.check("var_z", vz[rows], rvz, G.RTOL_VAR)
+    da, dv = G.linear_bwd_state(x["mu_w"], x["jcb"], x["dmu_z"], x["dvar_z"])
+    rda, rdv = oracle.linear_bwd_state(x["mu_w"], np.ascontiguousarray(x["jcb"][rows]),
+                                       np.ascontiguousarray(x["dmu_z"][rows]), np.ascontiguousarray(x["dvar_z"][rows]))
+    G.check("dmu_a", da[rows], rda, G.RTOL_MU)
+    G.check("dvar_a", dv[rows], rdv, G.RTOL_VAR)
+    dmw, dvw, dmb, dvb = G.linear_bwd_param(x["var_w"], x["var_b"], x["mu_a"], x["dmu_z"], x["dvar_z"])
+    r = oracle.linear_bwd_param(np.ascontiguousarray(x["var_w"][feats]), np.ascontiguousarray(x["var_b"][feats]),
+                                x["mu_a"], np.ascontiguousarray(x["dmu_z"][:, feats]),
+                                np.ascontiguousarray(x["dvar_z"][:, feats]))
+    G.check("dmu_w", dmw[feats], r[0], G.RTOL_MU)
+    G.check("dvar_w", dvw[feats], r[1], G.RTOL_VAR)
+    G.check("dmu_b", dmb[feats], r[2], G.RTOL_MU)
+    G.check("dvar_b", dvb[feats], r[3], G.RTOL_VAR)
+    # size-independent properties: variances are positive, variance deltas non-positive
+    assert vz.min() > 0 and dv.max() <= 0 and dvw.max() <= 0
+
+
+def test_forward_closer_to_exact_than_tolerance(G, oracle):
+    """Arbitration against FP64: the GPU result is within the stated tolerance of the exactly-rounded value too."""
+    rng = np.random.default_rng(11)
+    x = G.linear_inputs(rng, 64, 2048, 192)
+    mz, vz = G.linear_fwd(x["mu_w"], x["var_w"], x["mu_b"], x["var_b"], x["mu_a"], x["var_a"])
+    m64, v64 = oracle.linear_fwd(x["mu_w"], x["var_w"], x["mu_b"], x["var_b"], x["mu_a"], x["var_a"], f64=True)
+    G.check("mu_z vs f64", mz, m64, G.RTOL_MU)
+    G.check("var_z vs f64", vz, v64, G.RTOL_VAR)
+
+
+def test_error_statuses(G):
+    import torch
+    from cutagi_b200.capi import TagiError, lib
+    t = torch.zeros(64, device="cuda")
+    q = t.data_ptr()
+    with pytest.raises(TagiError) as e:
+        lib.tagi_linear_fwd(q, q, q, q, q, q, 0, 4, 4, 1, q, q, None)
+    assert e.value.code == 1 and "positive" in str(e.value)
+    with pytest.raises(TagiError) as e:
+        lib.tagi_linear_fwd(None, q, q, q, q, q, 2, 4, 4, 1, q, q, None)
+    assert e.value.code == 1 and "mu_w" in str(e.value)
+    with pytest.raises(TagiError):
+        lib.tagi_linear_bwd_param(q, None, q, q, q, 2, 4, 4, 1, q, q, q, q, None)
+    # a failed call leaves the context usable
+    lib.tagi_linear_fwd(q, q, q, q, q, q, 2, 4, 4, 1, q, q, None)
+    torch.cuda.synchronize()
+
+
+def test_deterministic(G):
+    rng = np.random.default_rng(3)
+    x = G.linear_inputs(rng, 96, 320, 200)
+    a = G.linear_bwd_param(x["var_w"], x["var_b"], x["mu_a"], x["dmu_z"], x["dvar_z"])
+    b = G.linear_bwd_param(x["var_w"], x["var_b"], x["mu_a"], x["dmu_z"], x["dvar_z"])
+    for u, v in zip(a, b):
+        assert np.array_equal(u, v)
