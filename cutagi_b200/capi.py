@@ -27,6 +27,8 @@ _SIGNATURES = {
     "tagi_set_impl": [_i],
     "tagi_get_impl": [],
     "tagi_version": [],
+    "tagi_tc_status": [C.POINTER(_i), _i],
+    "tagi_tc_set_chunked": [_i],
     "tagi_linear_fwd": [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _p],
     "tagi_linear_bwd_state": [_p, _p, _p, _p, _i, _i, _i, _p, _p, _p],
     "tagi_linear_bwd_param": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _p, _p, _p],
@@ -75,6 +77,13 @@ class _Lib:
 
 
 lib = _Lib()
+
+
+def tc_status(reset=True):
+    """Status word of the TF32X3 kernels on the current device (0 = no bounded wait ever ran out)."""
+    s = _i(0)
+    lib.tagi_tc_status(C.byref(s), int(reset))
+    return s.value
 
 
 def conv_out_size(k, stride, wi, hi, pad, pad_type):

@@ -50,6 +50,27 @@ int tagi_set_impl(int impl) {
 }
 int tagi_get_impl(void) { return current_impl(); }
 
+int tagi_tc_status(int *status, int reset) {
+    TAGI_REQUIRE(status != nullptr, "null status pointer");
+    return linear_tc_status(status, reset);
+}
+int tagi_tc_set_chunked(int on) { return linear_tc_set_chunked(on); }
+
+// true -> run the tensor-core kernel; sets rc when the forced implementation cannot take the shape
+static bool pick_tc(const char *who, int B, int K, int N, std::initializer_list<const void *> ptrs, int *rc) {
+    *rc = TAGI_OK;
+    const int impl = current_impl();
+    if (impl == TAGI_IMPL_FFMA) return false;
+    const bool ok = linear_tc_supported(B, K, N, ptrs);
+    if (impl == TAGI_IMPL_TF32X3) {
+        if (!ok)
+            *rc = fail(TAGI_ERR_UNSUPPORTED, std::string(who) + ": TF32X3 needs 16-byte aligned tensors and B, K, N "
+                                                               "that are multiples of 4");
+        return ok;
+    }
+    return ok && linear_tc_profitable(B, K, N);
+}
+
 #define TAGI_PTR(p) TAGI_REQUIRE((p) != nullptr && aligned4(p), #p " is null or not 4-byte aligned")
 #define TAGI_DIMS()                                                                            \
     TAGI_REQUIRE(B > 0 && K > 0 && N > 0, "B, K and N must be positive");                        \
@@ -72,8 +93,10 @@ int tagi_linear_fwd(const float *mu_w, const float *var_w, const float *mu_b, co
         mu_b = var_b = nullptr;
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (current_impl() == TAGI_IMPL_TF32X3)
-        return fail(TAGI_ERR_UNSUPPORTED, "tagi_linear_fwd: TF32X3 cannot run this shape");
+    int rc;
+    if (pick_tc(__func__, B, K, N, {mu_w, var_w, mu_b, var_b, mu_a, var_a, mu_z, var_z}, &rc))
+        return linear_fwd_tc(mu_w, var_w, mu_b, var_b, mu_a, var_a, B, K, N, mu_z, var_z, st);
+    if (rc != TAGI_OK) return rc;
     return linear_fwd_ffma(mu_w, var_w, mu_b, var_b, mu_a, var_a, B, K, N, mu_z, var_z, st);
 }
 
@@ -87,8 +110,10 @@ int tagi_linear_bwd_state(const float *mu_w, const float *jcb, const float *dmu_
     TAGI_PTR(dmu_a);
     TAGI_PTR(dvar_a);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (current_impl() == TAGI_IMPL_TF32X3)
-        return fail(TAGI_ERR_UNSUPPORTED, "tagi_linear_bwd_state: TF32X3 cannot run this shape");
+    int rc;
+    if (pick_tc(__func__, B, K, N, {mu_w, jcb, dmu_z, dvar_z, dmu_a, dvar_a}, &rc))
+        return linear_bwd_state_tc(mu_w, jcb, dmu_z, dvar_z, B, K, N, dmu_a, dvar_a, st);
+    if (rc != TAGI_OK) return rc;
     return linear_bwd_state_ffma(mu_w, jcb, dmu_z, dvar_z, B, K, N, dmu_a, dvar_a, st);
 }
 
@@ -108,9 +133,11 @@ int tagi_linear_bwd_param(const float *var_w, const float *var_b, const float *m
         TAGI_PTR(dvar_b);
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (current_impl() == TAGI_IMPL_TF32X3)
-        return fail(TAGI_ERR_UNSUPPORTED, "tagi_linear_bwd_param: TF32X3 cannot run this shape");
-    int rc = linear_bwd_param_ffma(var_w, mu_a, dmu_z, dvar_z, B, K, N, dmu_w, dvar_w, st);
+    int rc;
+    if (pick_tc(__func__, B, K, N, {var_w, mu_a, dmu_z, dvar_z, dmu_w, dvar_w}, &rc))
+        rc = linear_bwd_param_tc(var_w, mu_a, dmu_z, dvar_z, B, K, N, dmu_w, dvar_w, st);
+    else if (rc == TAGI_OK)
+        rc = linear_bwd_param_ffma(var_w, mu_a, dmu_z, dvar_z, B, K, N, dmu_w, dvar_w, st);
     if (rc != TAGI_OK) return rc;
     if (has_bias) rc = linear_bias_delta(var_b, dmu_z, dvar_z, B, N, dmu_b, dvar_b, st);
     return rc;

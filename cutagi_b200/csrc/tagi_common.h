@@ -5,6 +5,7 @@
 
 #include <cstdint>
 #include <cstdio>
+#include <initializer_list>
 #include <string>
 
 #include "../../include/tagi_b200.h"
@@ -41,6 +42,18 @@ int linear_bwd_param_ffma(const float *var_w, const float *mu_a, const float *dm
 // column sums of the [B][N] deltas scaled by var_b, var_b^2
 int linear_bias_delta(const float *var_b, const float *dmu_z, const float *dvar_z, int B, int N, float *dmu_b,
                       float *dvar_b, cudaStream_t st);
+
+// tcgen05 / 3xTF32 implementations (tagi_linear_tc.cu)
+bool linear_tc_supported(int B, int K, int N, std::initializer_list<const void *> ptrs);
+bool linear_tc_profitable(int B, int K, int N);
+int linear_tc_set_chunked(int on);
+int linear_tc_status(int *out, int reset);
+int linear_fwd_tc(const float *mu_w, const float *var_w, const float *mu_b, const float *var_b, const float *mu_a,
+                  const float *var_a, int B, int K, int N, float *mu_z, float *var_z, cudaStream_t st);
+int linear_bwd_state_tc(const float *mu_w, const float *jcb, const float *dmu_z, const float *dvar_z, int B, int K,
+                        int N, float *dmu_a, float *dvar_a, cudaStream_t st);
+int linear_bwd_param_tc(const float *var_w, const float *mu_a, const float *dmu_z, const float *dvar_z, int B, int K,
+                        int N, float *dmu_w, float *dvar_w, cudaStream_t st);
 
 // Conv2d on the FFMA engine (tagi_conv_ffma.cu)
 int conv2d_fwd_ffma(const tagi_conv2d_geom &g, const float *mu_w, const float *var_w, const float *mu_b,

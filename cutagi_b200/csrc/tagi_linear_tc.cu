@@ -1,0 +1,475 @@
+// TAGI Linear on the 5th-generation tensor cores (tcgen05, sm_100a) with 3xTF32 splitting.
+//
+// Every FP32 product x*y of the three Linear contractions is evaluated as
+//     hi(x)*hi(y) + hi(x)*lo(y) + lo(x)*hi(y),   hi(x) = x with the low 13 mantissa bits cleared,
+//                                                 lo(x) = x - hi(x)  (exact in FP32)
+// by three kind::tf32 MMAs that accumulate in FP32 in tensor memory. The tensor core reads the
+// upper 19 bits of each 32-bit operand, so the raw FP32 tile that TMA lands in shared memory
+// already is the hi operand; only the lo tiles and the derived tiles (mu^2 + var, mu^2, and their
+// lo parts) are produced, by a group of converter warps, elementwise at the same swizzled
+// shared-memory offsets as the raw tiles. Nothing derived is ever written to HBM.
+//
+// One CTA computes a 128 x 128 tile of both outputs (mean-like D1, variance-like D2):
+//   warp 0      TMA producer: raw operand tiles, K-slab of 16, multi-stage ring
+//   warp 1      MMA issuer (one thread): 6 or 9 tf32 products per 8-wide k step; owns tensor memory
+//   warps 2-9   converters; they also add finished chunks (tcgen05.ld) to register sums and run the epilogue
+//               (bias / scale -> HBM)
+// Operands whose contraction index is contiguous in memory are staged K-major (64-byte swizzle);
+// the others (mu_w in the state pass, both operands of the parameter pass) are staged MN-major
+// (128-byte swizzle), which kind::tf32 accepts, so no transpose pass exists anywhere.
+//
+// The tensor core's FP32 accumulation loses a little on every MMA (its error grows with the number of
+// MMAs chained into one accumulator and with the accumulator's magnitude), which over thousands of k
+// steps would exceed the 1e-5 / 1e-4 tolerance. The contraction is therefore cut into chunks of 256:
+// each chunk accumulates from zero in one of two tensor-memory accumulator sets, and while the next
+// chunk runs in the other set the converter warps add the finished chunk to running sums that they
+// keep in registers (plain FP32 adds, one per chunk).
+#include <cuda.h>
+
+#include <mutex>
+
+#include "tagi_common.h"
+#include "tagi_tc_ptx.cuh"
+
+namespace tagi {
+namespace {
+
+using namespace ptx;
+
+constexpr int TM = 128, TN = 128, BK = 16;
+constexpr int TILE_BYTES = 128 * BK * 4;  // 8 KiB per operand tile
+constexpr int NCONV_WARPS = 8;
+constexpr int NTHREADS = 32 * (2 + NCONV_WARPS);
+constexpr int CHUNKS = TILE_BYTES / 16;  // 16-byte chunks per tile
+
+enum { OP_FWD = 0, OP_BWD_STATE = 1, OP_BWD_PARAM = 2 };
+
+template <int OP> struct OpTraits;
+// tiles per stage: forward A0 A1 A0l A1l S Sl | B0 B1 B0l B1l Q Ql ; backward A0 A1 A0l A1l | W Wl Q Ql
+template <> struct OpTraits<OP_FWD> { static constexpr int NTILES = 12, STAGES = 2, A_MN = 0, B_MN = 0, B_BASE = 6, NRAW = 4; };
+template <> struct OpTraits<OP_BWD_STATE> { static constexpr int NTILES = 8, STAGES = 3, A_MN = 0, B_MN = 1, B_BASE = 4, NRAW = 3; };
+template <> struct OpTraits<OP_BWD_PARAM> { static constexpr int NTILES = 8, STAGES = 3, A_MN = 1, B_MN = 1, B_BASE = 4, NRAW = 3; };
+
+template <int OP>
+constexpr size_t tc_smem_bytes() {
+    return (size_t)OpTraits<OP>::STAGES * OpTraits<OP>::NTILES * TILE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+}
+
+struct TcEpilogue {
+    float *out1, *out2;
+    const float *aux1, *aux2;  // forward: bias vectors (may be null); backward: aux1 = scale matrix
+    long ld;
+    int rows, cols;
+};
+
+__device__ __forceinline__ float lo_part(float x) { return x - __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
+__device__ __forceinline__ float4 lo_part(float4 v) {
+    return make_float4(lo_part(v.x), lo_part(v.y), lo_part(v.z), lo_part(v.w));
+}
+__device__ __forceinline__ float4 lds128(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, float4 v) {
+    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                 : "memory");
+}
+
+// K-major tile [128 rows][16 k], 64-byte swizzle: one box. MN-major tile: four boxes of [16 k][32 rows], 2 KiB
+// apart, in the 128-byte swizzle with 32-byte atoms, which is the only MN-major layout kind::tf32 reads
+// (swizzle pattern repeats every 4 k rows = 512 bytes).
+template <int MN>
+__device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap *tm, int row0, int k0, uint64_t *bar) {
+    if (MN) {
+#pragma unroll
+        for (int g = 0; g < 4; g++) tma_load_2d(dst + g * 2048, tm, row0 + 32 * g, k0, bar);
+    } else {
+        tma_load_2d(dst, tm, k0, row0, bar);
+    }
+}
+// descriptor of the 8-wide k step j (0 or 1) of a tile
+template <int MN>
+__device__ __forceinline__ uint64_t tile_desc(uint32_t addr, int j) {
+    return MN ? make_smem_desc(addr + j * 1024, 2048, 512, SWZ_128B_BASE32B)
+              : make_smem_desc(addr + j * 32, 16, 512, SWZ_64B);
+}
+
+// Contraction chunk: CHUNK_STAGES k-slabs (256 k) accumulate in one tensor-memory set before they are
+// added to the register sums. CHUNK_STAGES == 0 (template) means a single chunk: everything stays in set 0.
+constexpr int CHUNK_STAGES = 16;
+
+template <int OP, int CH>
+__global__ void __launch_bounds__(NTHREADS, 1)
+tagi_tc_linear_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
+                      const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
+                      const TcEpilogue epi, const int kdim, int *status) {
+    using T = OpTraits<OP>;
+    constexpr int STAGES = T::STAGES, NTILES = T::NTILES;
+    constexpr uint32_t NCOLS = 512;  // two accumulator sets of (D1, D2), 128 columns each
+    constexpr uint32_t IDESC = make_idesc_tf32(TM, TN, T::A_MN, T::B_MN);
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
+    uint8_t *aligned = smem_raw + (smem_base - smem_u32(smem_raw));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(aligned + (size_t)STAGES * NTILES * TILE_BYTES);
+    uint64_t *raw_full = bars, *conv_done = bars + STAGES, *empty = bars + 2 * STAGES;
+    uint64_t *acc_full = bars + 3 * STAGES, *acc_empty = bars + 3 * STAGES + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * STAGES + 4);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row0 = blockIdx.y * TM, col0 = blockIdx.x * TN;
+    const int nk = (kdim + BK - 1) / BK;
+    const int chunk_len = CH > 0 ? CH : nk;  // stages per chunk
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(raw_full + s, 1);
+            mbar_init(conv_done + s, NCONV_WARPS);
+            mbar_init(empty + s, 1);
+        }
+        for (int s = 0; s < 2; s++) {
+            mbar_init(acc_full + s, 1);
+            mbar_init(acc_empty + s, NCONV_WARPS);
+        }
+        *abort_flag = 0;
+        mbar_init_fence();
+        prefetch_tmap(&tmA0);
+        prefetch_tmap(&tmA1);
+        prefetch_tmap(&tmB0);
+        if (OP == OP_FWD) prefetch_tmap(&tmB1);
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, NCOLS);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            for (int it = 0; it < nk; it++) {
+                const int s = it % STAGES;
+                if (!mbar_wait(empty + s, ((it / STAGES) & 1) ^ 1, abort_flag, status, ST_TIMEOUT_EMPTY)) break;
+                mbar_arrive_expect_tx(raw_full + s, T::NRAW * TILE_BYTES);
+                const uint32_t st = smem_base + s * NTILES * TILE_BYTES;
+                const int k0 = it * BK;
+                load_tile<T::A_MN>(st + 0 * TILE_BYTES, &tmA0, row0, k0, raw_full + s);
+                load_tile<T::A_MN>(st + 1 * TILE_BYTES, &tmA1, row0, k0, raw_full + s);
+                load_tile<T::B_MN>(st + T::B_BASE * TILE_BYTES, &tmB0, col0, k0, raw_full + s);
+                if (OP == OP_FWD) load_tile<T::B_MN>(st + (T::B_BASE + 1) * TILE_BYTES, &tmB1, col0, k0, raw_full + s);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            uint32_t f1 = 0, f2 = 0;  // accumulate flags of the current chunk's D1, D2
+            uint32_t d1 = tmem, d2 = tmem + 128;
+            bool ok = true;
+            for (int it = 0; it < nk && ok; it++) {
+                const int s = it % STAGES;
+                if (it % chunk_len == 0) {
+                    // a new chunk starts from zero in the other accumulator set, once the converters have drained it
+                    const int c = it / chunk_len, set = c & 1;
+                    ok = mbar_wait(acc_empty + set, ((c >> 1) & 1) ^ 1, abort_flag, status, ST_TIMEOUT_ACC);
+                    if (!ok) break;
+                    d1 = tmem + set * 256, d2 = d1 + 128;
+                    f1 = f2 = 0;
+                }
+                ok = mbar_wait(conv_done + s, (it / STAGES) & 1, abort_flag, status, ST_TIMEOUT_CONV);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t st = smem_base + s * NTILES * TILE_BYTES;
+#define TILE(i) (st + (i) * TILE_BYTES)
+#define DA(i) tile_desc<T::A_MN>(TILE(i), j)
+#define DB(i) tile_desc<T::B_MN>(TILE(i), j)
+#pragma unroll
+                for (int j = 0; j < BK / 8; j++) {
+                    if (OP == OP_FWD) {
+                        // D1 = mu_a . mu_w ; D2 = (mu_a^2 + var_a) . var_w + var_a . mu_w^2
+                        mma_tf32_ss(d1, DA(0), DB(6), IDESC, f1);
+                        f1 = 1;
+                        mma_tf32_ss(d1, DA(0), DB(8), IDESC, 1);
+                        mma_tf32_ss(d1, DA(2), DB(6), IDESC, 1);
+                        mma_tf32_ss(d2, DA(4), DB(7), IDESC, f2);
+                        f2 = 1;
+                        mma_tf32_ss(d2, DA(1), DB(10), IDESC, 1);
+                        mma_tf32_ss(d2, DA(4), DB(9), IDESC, 1);
+                        mma_tf32_ss(d2, DA(5), DB(7), IDESC, 1);
+                        mma_tf32_ss(d2, DA(1), DB(11), IDESC, 1);
+                        mma_tf32_ss(d2, DA(3), DB(10), IDESC, 1);
+                    } else {
+                        // D1 = a0 . w ; D2 = a1 . w^2
+                        mma_tf32_ss(d1, DA(0), DB(4), IDESC, f1);
+                        f1 = 1;
+                        mma_tf32_ss(d1, DA(0), DB(5), IDESC, 1);
+                        mma_tf32_ss(d1, DA(2), DB(4), IDESC, 1);
+                        mma_tf32_ss(d2, DA(1), DB(6), IDESC, f2);
+                        f2 = 1;
+                        mma_tf32_ss(d2, DA(1), DB(7), IDESC, 1);
+                        mma_tf32_ss(d2, DA(3), DB(6), IDESC, 1);
+                    }
+                }
+#undef TILE
+#undef DA
+#undef DB
+                mma_commit(empty + s);  // the stage may be refilled once these MMAs have read it
+                if (it % chunk_len == chunk_len - 1 || it == nk - 1) mma_commit(acc_full + ((it / chunk_len) & 1));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ converters + accumulation + epilogue
+        const int ct = threadIdx.x - 64;
+        const int q = warp & 3;         // tensor-memory lane quadrant this warp may read
+        const int h = (warp - 2) >> 2;  // which half of the 128 columns
+        const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16) + h * 64;
+        float sum1[64], sum2[64];
+#pragma unroll
+        for (int i = 0; i < 64; i++) sum1[i] = sum2[i] = 0.f;
+
+        // adds chunk c (columns h*64 .. +63 of D1 and D2 of its set) to the register sums and frees the set
+        auto drain = [&](int c) -> bool {
+            const int set = c & 1;
+            if (!mbar_wait(acc_full + set, (c >> 1) & 1, abort_flag, status, ST_TIMEOUT_ACC)) return false;
+            tc_fence_after_sync();
+#pragma unroll
+            for (int blk = 0; blk < 2; blk++) {
+                float v[32];
+                tmem_ld_32x32(lane_base + set * 256 + blk * 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; i++) sum1[blk * 32 + i] += v[i];
+                tmem_ld_32x32(lane_base + set * 256 + 128 + blk * 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; i++) sum2[blk * 32 + i] += v[i];
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty + set);
+            return true;
+        };
+
+        bool ok = true;
+        int pending = -1;  // chunk whose MMAs have been issued but which has not been added yet
+        for (int it = 0; it < nk && ok; it++) {
+            const int s = it % STAGES;
+            ok = mbar_wait(raw_full + s, (it / STAGES) & 1, abort_flag, status, ST_TIMEOUT_RAW);
+            if (!ok) break;
+            const uint32_t st = smem_base + s * NTILES * TILE_BYTES;
+#pragma unroll
+            for (int c = ct; c < CHUNKS; c += 32 * NCONV_WARPS) {
+                const uint32_t o = c * 16;
+                const float4 a0 = lds128(st + 0 * TILE_BYTES + o), a1 = lds128(st + 1 * TILE_BYTES + o);
+                sts128(st + 2 * TILE_BYTES + o, lo_part(a0));
+                sts128(st + 3 * TILE_BYTES + o, lo_part(a1));
+                if (OP == OP_FWD) {
+                    const float4 sq = make_float4(fmaf(a0.x, a0.x, a1.x), fmaf(a0.y, a0.y, a1.y),
+                                                  fmaf(a0.z, a0.z, a1.z), fmaf(a0.w, a0.w, a1.w));
+                    sts128(st + 4 * TILE_BYTES + o, sq);
+                    sts128(st + 5 * TILE_BYTES + o, lo_part(sq));
+                    const float4 b0 = lds128(st + 6 * TILE_BYTES + o), b1 = lds128(st + 7 * TILE_BYTES + o);
+                    const float4 qq = make_float4(b0.x * b0.x, b0.y * b0.y, b0.z * b0.z, b0.w * b0.w);
+                    sts128(st + 8 * TILE_BYTES + o, lo_part(b0));
+                    sts128(st + 9 * TILE_BYTES + o, lo_part(b1));
+                    sts128(st + 10 * TILE_BYTES + o, qq);
+                    sts128(st + 11 * TILE_BYTES + o, lo_part(qq));
+                } else {
+                    const float4 w = lds128(st + 4 * TILE_BYTES + o);
+                    const float4 qq = make_float4(w.x * w.x, w.y * w.y, w.z * w.z, w.w * w.w);
+                    sts128(st + 5 * TILE_BYTES + o, lo_part(w));
+                    sts128(st + 6 * TILE_BYTES + o, qq);
+                    sts128(st + 7 * TILE_BYTES + o, lo_part(qq));
+                }
+            }
+            fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core's async proxy
+            __syncwarp();
+            if (lane == 0) mbar_arrive(conv_done + s);
+            // The previous chunk is added one stage late, after the first stage of the next chunk has been handed
+            // to the MMA warp, so that the tensor core keeps running while the sums are updated.
+            if (pending >= 0) {
+                ok = drain(pending);
+                pending = -1;
+            }
+            if (it % chunk_len == chunk_len - 1 || it == nk - 1) pending = it / chunk_len;
+        }
+        if (ok && pending >= 0) ok = drain(pending);
+
+        if (ok) {
+            const int row = row0 + q * 32 + lane;
+            if (row < epi.rows) {
+#pragma unroll
+                for (int i = 0; i < 64; i += 4) {
+                    const int col = col0 + h * 64 + i;
+                    if (col >= epi.cols) break;  // cols is a multiple of 4 on this path
+                    const long idx = (long)row * epi.ld + col;
+                    float4 o1 = make_float4(sum1[i], sum1[i + 1], sum1[i + 2], sum1[i + 3]);
+                    float4 o2 = make_float4(sum2[i], sum2[i + 1], sum2[i + 2], sum2[i + 3]);
+                    if (OP == OP_FWD) {
+                        if (epi.aux1) {
+                            const float4 b1 = __ldg(reinterpret_cast<const float4 *>(epi.aux1 + col));
+                            const float4 b2 = __ldg(reinterpret_cast<const float4 *>(epi.aux2 + col));
+                            o1.x += b1.x, o1.y += b1.y, o1.z += b1.z, o1.w += b1.w;
+                            o2.x += b2.x, o2.y += b2.y, o2.z += b2.z, o2.w += b2.w;
+                        }
+                    } else {
+                        const float4 sc = __ldg(reinterpret_cast<const float4 *>(epi.aux1 + idx));
+                        o1.x *= sc.x, o1.y *= sc.y, o1.z *= sc.z, o1.w *= sc.w;
+                        o2.x = o2.x * sc.x * sc.x, o2.y = o2.y * sc.y * sc.y;
+                        o2.z = o2.z * sc.z * sc.z, o2.w = o2.w * sc.w * sc.w;
+                    }
+                    __stcs(reinterpret_cast<float4 *>(epi.out1 + idx), o1);
+                    __stcs(reinterpret_cast<float4 *>(epi.out2 + idx), o2);
+                }
+            }
+        }
+    }
+    __syncwarp();
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        if (*abort_flag) {
+            // give copies and MMAs that are still in flight time to land before the memory is released
+            const long long t0 = clock64();
+            while (clock64() - t0 < 4000000LL) {
+            }
+        }
+        tmem_dealloc(tmem, NCOLS);
+    }
+}
+
+// ------------------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// Tensor map over a row-major FP32 matrix [outer][inner]. K-major operand tiles: box 16 x 128, 64-byte
+// swizzle; MN-major: box 32 x 16, 128-byte swizzle with 32-byte atoms.
+int make_tmap(CUtensorMap *tm, const float *ptr, uint64_t inner, uint64_t outer, bool mn_major) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(TAGI_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {inner * sizeof(float)};
+    cuuint32_t box[2] = {mn_major ? 32u : (cuuint32_t)BK, mn_major ? (cuuint32_t)BK : 128u};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_64B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(TAGI_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+    return TAGI_OK;
+}
+
+int *status_word() {
+    static int *ptr[64] = {};
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lk(mu);
+    if (!ptr[dev]) {
+        if (cudaMalloc(&ptr[dev], sizeof(int)) != cudaSuccess) return nullptr;
+        cudaMemset(ptr[dev], 0, sizeof(int));
+    }
+    return ptr[dev];
+}
+
+int g_chunked = 1;  // 1: contraction accumulated in chunks of 256 (default); 0: one accumulation chain (diagnostic)
+
+template <int OP>
+int launch(const CUtensorMap &a0, const CUtensorMap &a1, const CUtensorMap &b0, const CUtensorMap &b1,
+           const TcEpilogue &epi, int kdim, cudaStream_t st) {
+    int *status = status_word();
+    if (!status) return fail(TAGI_ERR_CUDA, "cannot allocate the tensor-core status word");
+    constexpr size_t smem = tc_smem_bytes<OP>();
+    dim3 grid((epi.cols + TN - 1) / TN, (epi.rows + TM - 1) / TM);
+    cudaError_t e;
+    if (g_chunked) {
+        auto k = tagi_tc_linear_kernel<OP, CHUNK_STAGES>;
+        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");
+        k<<<grid, NTHREADS, smem, st>>>(a0, a1, b0, b1, epi, kdim, status);
+    } else {
+        auto k = tagi_tc_linear_kernel<OP, 0>;
+        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");
+        k<<<grid, NTHREADS, smem, st>>>(a0, a1, b0, b1, epi, kdim, status);
+    }
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "tensor-core Linear kernel launch");
+    return TAGI_OK;
+}
+
+}  // namespace
+
+// Shapes the tensor-core path takes: 16-byte aligned tensors, every dimension a multiple of 4 (TMA pitches
+// and vector stores), and large enough for 128 x 128 tiles to make sense.
+bool linear_tc_supported(int B, int K, int N, std::initializer_list<const void *> ptrs) {
+    if (B % 4 || K % 4 || N % 4) return false;
+    for (const void *p : ptrs)
+        if (p && !aligned16(p)) return false;
+    return true;
+}
+bool linear_tc_profitable(int B, int K, int N) { return B >= 128 && K >= 128 && N >= 128; }
+
+int linear_tc_set_chunked(int on) {
+    g_chunked = on ? 1 : 0;
+    return TAGI_OK;
+}
+
+int linear_tc_status(int *out, int reset) {
+    int *w = status_word();
+    if (!w) return fail(TAGI_ERR_CUDA, "no status word");
+    cudaError_t e = cudaMemcpy(out, w, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpy(status)");
+    if (reset && *out) cudaMemset(w, 0, sizeof(int));
+    return TAGI_OK;
+}
+
+int linear_fwd_tc(const float *mu_w, const float *var_w, const float *mu_b, const float *var_b, const float *mu_a,
+                  const float *var_a, int B, int K, int N, float *mu_z, float *var_z, cudaStream_t st) {
+    CUtensorMap a0, a1, b0, b1;
+    int rc;
+    if ((rc = make_tmap(&a0, mu_a, K, B, false))) return rc;
+    if ((rc = make_tmap(&a1, var_a, K, B, false))) return rc;
+    if ((rc = make_tmap(&b0, mu_w, K, N, false))) return rc;
+    if ((rc = make_tmap(&b1, var_w, K, N, false))) return rc;
+    TcEpilogue epi{mu_z, var_z, mu_b, var_b, (long)N, B, N};
+    return launch<OP_FWD>(a0, a1, b0, b1, epi, K, st);
+}
+
+int linear_bwd_state_tc(const float *mu_w, const float *jcb, const float *dmu_z, const float *dvar_z, int B, int K,
+                        int N, float *dmu_a, float *dvar_a, cudaStream_t st) {
+    // rows = batch, columns = input features, contraction over output features; mu_w [N][K] is MN-major here
+    CUtensorMap a0, a1, b0;
+    int rc;
+    if ((rc = make_tmap(&a0, dmu_z, N, B, false))) return rc;
+    if ((rc = make_tmap(&a1, dvar_z, N, B, false))) return rc;
+    if ((rc = make_tmap(&b0, mu_w, K, N, true))) return rc;
+    TcEpilogue epi{dmu_a, dvar_a, jcb, nullptr, (long)K, B, K};
+    return launch<OP_BWD_STATE>(a0, a1, b0, b0, epi, N, st);
+}
+
+int linear_bwd_param_tc(const float *var_w, const float *mu_a, const float *dmu_z, const float *dvar_z, int B, int K,
+                        int N, float *dmu_w, float *dvar_w, cudaStream_t st) {
+    // rows = output features, columns = input features, contraction over the batch; both operands MN-major
+    CUtensorMap a0, a1, b0;
+    int rc;
+    if ((rc = make_tmap(&a0, dmu_z, N, B, true))) return rc;
+    if ((rc = make_tmap(&a1, dvar_z, N, B, true))) return rc;
+    if ((rc = make_tmap(&b0, mu_a, K, B, true))) return rc;
+    TcEpilogue epi{dmu_w, dvar_w, var_w, nullptr, (long)K, N, K};
+    return launch<OP_BWD_PARAM>(a0, a1, b0, b0, epi, B, st);
+}
+
+}  // namespace tagi

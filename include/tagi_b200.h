@@ -43,6 +43,16 @@ enum { TAGI_IMPL_AUTO = 0, TAGI_IMPL_FFMA = 1, TAGI_IMPL_TF32X3 = 2 };
 int tagi_set_impl(int impl);
 int tagi_get_impl(void);
 
+/* Diagnostics of the TF32X3 kernels. Their device-side waits (on TMA and MMA completion barriers) are bounded; a wait
+ * that runs out makes the kernel stop, release its tensor memory and record a non-zero code here instead of hanging.
+ * tagi_tc_status copies the current device's status word to *status (0 = no wait ever ran out) and clears it when
+ * `reset` is non-zero; it synchronises with the device. */
+int tagi_tc_status(int *status, int reset);
+/* Diagnostic switch of the TF32X3 kernels. on != 0 (default): the contraction is accumulated in tensor memory in
+ * chunks of 256 that are summed in FP32 registers, which keeps the tensor core's accumulation error far below the
+ * 1e-5 / 1e-4 tolerance. on == 0: one accumulation chain over the whole contraction (less accurate; for measurement). */
+int tagi_tc_set_chunked(int on);
+
 const char *tagi_last_error_string(void);
 /* Library version as major*10000 + minor*100 + patch. */
 int tagi_version(void);

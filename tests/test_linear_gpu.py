@@ -139,3 +139,82 @@ def test_deterministic(G):
     b = G.linear_bwd_param(x["var_w"], x["var_b"], x["mu_a"], x["dmu_z"], x["dvar_z"])
     for u, v in zip(a, b):
         assert np.array_equal(u, v)
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# The same parity bar for each implementation explicitly (FFMA on the CUDA cores, 3xTF32 on the tensor cores)
+# ------------------------------------------------------------------------------------------------------------------
+@pytest.fixture
+def force_impl():
+    from cutagi_b200.capi import lib
+    yield lambda i: lib.tagi_set_impl(i)
+    lib.tagi_set_impl(0)
+
+
+TC_SHAPES = [(128, 64, 128), (4, 8, 12), (132, 200, 260), (256, 256, 384), (512, 2048, 512), (384, 1024, 640),
+             (260, 516, 132), (64, 4096, 128)]
+
+
+@pytest.mark.parametrize("B,K,N", TC_SHAPES)
+def test_tensor_core_path(G, oracle, force_impl, B, K, N):
+    """TF32X3 forced: every shape with 16-byte aligned rows runs on tcgen05, including ragged tile edges."""
+    from cutagi_b200 import capi
+    force_impl(capi.IMPL_TF32X3)
+    capi.tc_status()
+    rng = np.random.default_rng(B * 7 + K * 3 + N)
+    _run_all(G, oracle, G.linear_inputs(rng, B, K, N), tag="tc ")
+    assert capi.tc_status() == 0, "a bounded device-side wait ran out"
+
+
+@pytest.mark.parametrize("B,K,N", [(512, 2048, 512), (130, 260, 132)])
+def test_ffma_path(G, oracle, force_impl, B, K, N):
+    from cutagi_b200 import capi
+    force_impl(capi.IMPL_FFMA)
+    rng = np.random.default_rng(B + K + N)
+    _run_all(G, oracle, G.linear_inputs(rng, B, K, N), tag="ffma ")
+
+
+def test_tensor_core_rejects_unaligned(G, force_impl):
+    import torch
+    from cutagi_b200 import capi
+    from cutagi_b200.capi import TagiError, lib
+    force_impl(capi.IMPL_TF32X3)
+    q = torch.zeros(1 << 16, device="cuda").data_ptr()
+    with pytest.raises(TagiError) as e:
+        lib.tagi_linear_fwd(q, q, q, q, q, q, 8, 6, 8, 1, q, q, None)   # K not a multiple of 4
+    assert e.value.code == 3
+    with pytest.raises(TagiError):
+        lib.tagi_linear_fwd(q + 4, q, q, q, q, q, 8, 8, 8, 1, q, q, None)   # misaligned pointer
+    force_impl(capi.IMPL_AUTO)
+    lib.tagi_linear_fwd(q, q, q, q, q, q, 8, 6, 8, 1, q, q, None)   # AUTO falls back to FFMA
+    torch.cuda.synchronize()
+
+
+def test_tensor_core_constant_variance_weights(G, oracle, force_impl):
+    """TAGI's initialisation gives every weight the same variance (1 / fan_in): operand rounding errors do not
+    average out for such inputs, which is what a single-TF32 product would fail on."""
+    from cutagi_b200 import capi
+    force_impl(capi.IMPL_TF32X3)
+    rng = np.random.default_rng(42)
+    B, K, N = 256, 1536, 256
+    x = G.linear_inputs(rng, B, K, N)
+    x["var_w"] = np.full((N, K), 1.0 / K, np.float32)
+    x["var_a"] = np.full((B, K), 0.0123, np.float32)
+    x["mu_a"] = np.abs(x["mu_a"])
+    _run_all(G, oracle, x, tag="tc const ")
+    assert capi.tc_status() == 0
+
+
+def test_benchmark_shape_is_tensor_core_and_in_tolerance_vs_f64(G, oracle, force_impl):
+    from cutagi_b200 import capi
+    force_impl(capi.IMPL_TF32X3)
+    rng = np.random.default_rng(77)
+    B, K, N = 1024, 4096, 4096
+    x = G.linear_inputs(rng, B, K, N)
+    rows = np.sort(rng.choice(B, 4, replace=False))
+    mz, vz = G.linear_fwd(x["mu_w"], x["var_w"], x["mu_b"], x["var_b"], x["mu_a"], x["var_a"])
+    m64, v64 = oracle.linear_fwd(x["mu_w"], x["var_w"], x["mu_b"], x["var_b"],
+                                 np.ascontiguousarray(x["mu_a"][rows]), np.ascontiguousarray(x["var_a"][rows]), f64=True)
+    G.check("mu_z vs f64", mz[rows], m64, G.RTOL_MU)
+    G.check("var_z vs f64", vz[rows], v64, G.RTOL_VAR)
+    assert capi.tc_status() == 0
