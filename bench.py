@@ -155,9 +155,10 @@ def run_reference(args, rank):
 def run_b200(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
-    from cutagi_b200.capi import lib, IMPL_FFMA, IMPL_TF32X3
+    from cutagi_b200.capi import lib, IMPL_FFMA, IMPL_TF32X3, tc_status as capi_tc_status
 
     torch.cuda.set_device(local_rank)
+    lib.tagi_set_impl({"auto": 0, "ffma": 1, "tf32x3": 2}[args.kernel_impl])
     devname = torch.cuda.get_device_name(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
@@ -244,8 +245,11 @@ def run_b200(args, rank, world, local_rank):
         for k_, v in host_out.items():
             v.copy_(o[k_], non_blocking=True)
 
-    e2e_step()
-    ms_e2e = timed(e2e_step, max(2, args.steps // 2)) / max(2, args.steps // 2)
+    if args.profile:
+        ms_e2e = float("nan")
+    else:
+        e2e_step()
+        ms_e2e = timed(e2e_step, max(2, args.steps // 2)) / max(2, args.steps // 2)
     e2e_value = FLOP_STEP * world / (ms_e2e * 1e-3) / 1e12
     clocks = None
     if rank == 0:
@@ -257,6 +261,9 @@ def run_b200(args, rank, world, local_rank):
         return
 
     impl = lib.tagi_get_impl()
+    if impl == 0:  # AUTO resolves to the tensor-core kernels for this shape (aligned, every dimension >= 128)
+        impl = IMPL_TF32X3
+    tc_status = capi_tc_status()
     flops = {"tagi_linear_fwd": FLOP_FWD, "tagi_linear_bwd_state": FLOP_STATE, "tagi_linear_bwd_param": FLOP_PARAM}
     dom = max(kt, key=kt.get)
     achieved = flops[dom] / (kt[dom] * 1e-3) / 1e12
@@ -291,13 +298,14 @@ def run_b200(args, rank, world, local_rank):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": WORKLOAD, "impl": {0: "auto", 1: "ffma", 2: "tf32x3"}.get(impl, str(impl)),
+        "config": {"workload": WORKLOAD, "impl": {1: "ffma (FP32 CUDA cores)", 2: "tf32x3 (tcgen05, 3 TF32 products per "
+                                                  "FP32 product, FP32 accumulation)"}.get(impl, str(impl)),
                    "device": devname, "l2": "inputs (604 MB per step) exceed the 126 MB L2; no flush",
                    "exchange": "allreduce(avg) of parameter deltas, NCCL" if world > 1 else "none (1 GPU)"},
         "roofline": roofline, "cpu_baseline": cpu_baseline,
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h},
-        "gpu_launches": 4 * args.steps, "clocks": clocks}))
+        "gpu_launches": 4 * args.steps, "tc_status": tc_status, "clocks": clocks}))
     if world > 1:
         dist.destroy_process_group()
 
@@ -309,8 +317,16 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--profile", action="store_true",
+                    help="for captures under ncu: one warm-up step, no end-to-end and no CPU leg (numbers printed "
+                         "in this mode are not benchmark values)")
+    ap.add_argument("--kernel-impl", default="auto", choices=["auto", "ffma", "tf32x3"],
+                    help="arithmetic of the Linear kernels (tagi_set_impl)")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.profile:
+        args.warmup, args.no_cpu = 1, True
+    else:
+        args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

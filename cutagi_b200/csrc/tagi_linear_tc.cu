@@ -103,11 +103,12 @@ template <int OP, int CH>
 __global__ void __launch_bounds__(NTHREADS, 1)
 tagi_tc_linear_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
                       const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
-                      const TcEpilogue epi, const int kdim, int *status) {
+                      const TcEpilogue epi, const int kdim, const int bn, int *status) {
     using T = OpTraits<OP>;
     constexpr int STAGES = T::STAGES, NTILES = T::NTILES;
     constexpr uint32_t NCOLS = 512;  // two accumulator sets of (D1, D2), 128 columns each
-    constexpr uint32_t IDESC = make_idesc_tf32(TM, TN, T::A_MN, T::B_MN);
+    // bn = columns per tile (a multiple of 16, at most 128): the MMA's N. Operand tiles are always staged 128 wide.
+    const uint32_t IDESC = make_idesc_tf32(TM, bn, T::A_MN, T::B_MN);
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
@@ -119,7 +120,7 @@ tagi_tc_linear_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row0 = blockIdx.y * TM, col0 = blockIdx.x * TN;
+    const int row0 = blockIdx.y * TM, col0 = blockIdx.x * bn;
     const int nk = (kdim + BK - 1) / BK;
     const int chunk_len = CH > 0 ? CH : nk;  // stages per chunk
 
@@ -300,7 +301,7 @@ tagi_tc_linear_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
 #pragma unroll
                 for (int i = 0; i < 64; i += 4) {
                     const int col = col0 + h * 64 + i;
-                    if (col >= epi.cols) break;  // cols is a multiple of 4 on this path
+                    if (h * 64 + i >= bn || col >= epi.cols) break;  // bn and cols are multiples of 4 on this path
                     const long idx = (long)row * epi.ld + col;
                     float4 o1 = make_float4(sum1[i], sum1[i + 1], sum1[i + 2], sum1[i + 3]);
                     float4 o2 = make_float4(sum2[i], sum2[i + 1], sum2[i + 2], sum2[i + 3]);
@@ -329,6 +330,315 @@ tagi_tc_linear_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
     if (warp == 1) {
         if (*abort_flag) {
             // give copies and MMAs that are still in flight time to land before the memory is released
+            const long long t0 = clock64();
+            while (clock64() - t0 < 4000000LL) {
+            }
+        }
+        tmem_dealloc(tmem, NCOLS);
+    }
+}
+
+// =====================================================================================================
+// Variant "ts": the A-side operand tiles live in tensor memory instead of shared memory.
+//
+// The all-shared-memory kernel above is bound by shared-memory bandwidth: per k-slab the tensor core reads
+// 18 x 8 KiB of operands while the converters read 32 KiB and write 64 KiB. Here the converters write the six
+// (forward) or four (backward) A-side tiles straight into tensor memory with tcgen05.st (lane = row, one tf32
+// per column) and the MMAs take A from there, which halves the tensor core's shared-memory reads and removes
+// the A-side converter writes. Raw tiles and derived B tiles use separate rings so that TMA can run four
+// slabs ahead. Tensor memory: columns [0,256) = D1, D2 (one accumulator set; the MMA warp pauses while a
+// finished 256-wide contraction chunk is added to the register sums), [256, 256 + 2 x 16 x NA) = A tiles.
+// =====================================================================================================
+template <int OP> struct TsTraits;
+// raw ring slot: A0 A1 B0 B1 (forward) / A0 A1 W (backward); derived slot: B0l B1l Q Ql / Wl Q Ql
+template <> struct TsTraits<OP_FWD> { static constexpr int NRAW = 4, NDER = 4, NA = 6; };
+template <> struct TsTraits<OP_BWD_STATE> { static constexpr int NRAW = 3, NDER = 3, NA = 4; };
+template <> struct TsTraits<OP_BWD_PARAM> { static constexpr int NRAW = 3, NDER = 3, NA = 4; };
+
+// RS raw-ring slots, DS derived-ring slots (shared memory for B, tensor memory for A)
+template <int OP, int RS, int DS>
+constexpr size_t ts_smem_bytes() {
+    return (size_t)(RS * TsTraits<OP>::NRAW + DS * TsTraits<OP>::NDER) * TILE_BYTES + 1024 + 256;
+}
+
+__device__ __forceinline__ float hi_part(float x) { return __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
+
+template <int OP, int CH, int RS, int DS>
+// 10 warps: three share one SM sub-partition (16 K registers), which caps a thread at 168 registers
+__global__ void __launch_bounds__(NTHREADS, 1)
+tagi_tc_linear_ts_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
+                         const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
+                         const TcEpilogue epi, const int kdim, const int bn, int *status) {
+    using T = OpTraits<OP>;
+    using S = TsTraits<OP>;
+    constexpr int NRAW = S::NRAW, NDER = S::NDER, NA = S::NA;
+    constexpr uint32_t NCOLS = 512;
+    // tensor-memory columns: D1 at 0, D2 at acc_stride, A tiles from 2 * acc_stride on (DS slots of NA * 16 columns)
+    const uint32_t acc_stride = (512 - DS * NA * BK) / 2 >= 128 ? 128 : 112;
+    const uint32_t A_COL0 = 2 * acc_stride;
+    const uint32_t IDESC = make_idesc_tf32(TM, bn, 0, T::B_MN);
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *aligned = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t raw_base = smem_base, der_base = smem_base + RS * NRAW * TILE_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(aligned + (size_t)(RS * NRAW + DS * NDER) * TILE_BYTES);
+    uint64_t *raw_full = bars, *raw_empty = bars + RS, *conv_done = bars + 2 * RS, *der_empty = bars + 2 * RS + DS;
+    uint64_t *acc_full = bars + 2 * RS + 2 * DS, *acc_empty = acc_full + 1;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 1);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row0 = blockIdx.y * TM, col0 = blockIdx.x * bn;
+    const int nk = (kdim + BK - 1) / BK;
+    const int chunk_len = CH > 0 ? CH : nk;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < RS; s++) {
+            mbar_init(raw_full + s, 1);
+            mbar_init(raw_empty + s, 1);
+        }
+        for (int s = 0; s < DS; s++) {
+            mbar_init(conv_done + s, NCONV_WARPS);
+            mbar_init(der_empty + s, 1);
+        }
+        mbar_init(acc_full, 1);
+        mbar_init(acc_empty, NCONV_WARPS);
+        *abort_flag = 0;
+        mbar_init_fence();
+        prefetch_tmap(&tmA0);
+        prefetch_tmap(&tmA1);
+        prefetch_tmap(&tmB0);
+        if (OP == OP_FWD) prefetch_tmap(&tmB1);
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, NCOLS);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            for (int it = 0; it < nk; it++) {
+                const int r = it % RS;
+                if (!mbar_wait(raw_empty + r, ((it / RS) & 1) ^ 1, abort_flag, status, ST_TIMEOUT_EMPTY)) break;
+                mbar_arrive_expect_tx(raw_full + r, NRAW * TILE_BYTES);
+                const uint32_t st = raw_base + r * NRAW * TILE_BYTES;
+                const int k0 = it * BK;
+                load_tile<T::A_MN>(st + 0 * TILE_BYTES, &tmA0, row0, k0, raw_full + r);
+                load_tile<T::A_MN>(st + 1 * TILE_BYTES, &tmA1, row0, k0, raw_full + r);
+                load_tile<T::B_MN>(st + 2 * TILE_BYTES, &tmB0, col0, k0, raw_full + r);
+                if (OP == OP_FWD) load_tile<T::B_MN>(st + 3 * TILE_BYTES, &tmB1, col0, k0, raw_full + r);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t d1 = tmem, d2 = tmem + acc_stride;
+            uint32_t f1 = 0, f2 = 0;
+            bool ok = true;
+            for (int it = 0; it < nk && ok; it++) {
+                const int r = it % RS, d = it % DS;
+                if (it > 0 && it % chunk_len == 0) {
+                    // the previous chunk must have been added to the register sums before it is overwritten
+                    const int c = it / chunk_len;
+                    ok = mbar_wait(acc_empty, (c - 1) & 1, abort_flag, status, ST_TIMEOUT_ACC);
+                    if (!ok) break;
+                    f1 = f2 = 0;
+                }
+                ok = mbar_wait(conv_done + d, (it / DS) & 1, abort_flag, status, ST_TIMEOUT_CONV);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t rs = raw_base + r * NRAW * TILE_BYTES, ds = der_base + d * NDER * TILE_BYTES;
+                const uint32_t at = tmem + A_COL0 + d * (NA * BK);
+#define AT(i) (at + (i) * BK + j * 8)
+#define RB(i) tile_desc<T::B_MN>(rs + (i) * TILE_BYTES, j)
+#define DB(i) tile_desc<T::B_MN>(ds + (i) * TILE_BYTES, j)
+#pragma unroll
+                for (int j = 0; j < BK / 8; j++) {
+                    if (OP == OP_FWD) {
+                        // A tiles: 0 mu_a, 1 var_a, 2 mu_a lo, 3 var_a lo, 4 S = mu_a^2 + var_a, 5 S lo
+                        // raw B: 2 mu_w, 3 var_w ; derived B: 0 mu_w lo, 1 var_w lo, 2 Q = mu_w^2, 3 Q lo
+                        mma_tf32_ts(d1, AT(0), RB(2), IDESC, f1);
+                        f1 = 1;
+                        mma_tf32_ts(d1, AT(0), DB(0), IDESC, 1);
+                        mma_tf32_ts(d1, AT(2), RB(2), IDESC, 1);
+                        mma_tf32_ts(d2, AT(4), RB(3), IDESC, f2);
+                        f2 = 1;
+                        mma_tf32_ts(d2, AT(1), DB(2), IDESC, 1);
+                        mma_tf32_ts(d2, AT(4), DB(1), IDESC, 1);
+                        mma_tf32_ts(d2, AT(5), RB(3), IDESC, 1);
+                        mma_tf32_ts(d2, AT(1), DB(3), IDESC, 1);
+                        mma_tf32_ts(d2, AT(3), DB(2), IDESC, 1);
+                    } else {
+                        // A tiles: 0 a0, 1 a1, 2 a0 lo, 3 a1 lo ; raw B: 2 w ; derived B: 0 w lo, 1 Q = w^2, 2 Q lo
+                        mma_tf32_ts(d1, AT(0), RB(2), IDESC, f1);
+                        f1 = 1;
+                        mma_tf32_ts(d1, AT(0), DB(0), IDESC, 1);
+                        mma_tf32_ts(d1, AT(2), RB(2), IDESC, 1);
+                        mma_tf32_ts(d2, AT(1), DB(1), IDESC, f2);
+                        f2 = 1;
+                        mma_tf32_ts(d2, AT(1), DB(2), IDESC, 1);
+                        mma_tf32_ts(d2, AT(3), DB(1), IDESC, 1);
+                    }
+                }
+#undef AT
+#undef RB
+#undef DB
+                mma_commit(raw_empty + r);
+                mma_commit(der_empty + d);
+                if (it % chunk_len == chunk_len - 1 || it == nk - 1) mma_commit(acc_full);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ converters + accumulation + epilogue
+        const int ct = threadIdx.x - 64;
+        const int q = warp & 3;         // tensor-memory lane quadrant of this warp
+        const int h = (warp - 2) >> 2;  // k step (A conversion) and column half (accumulation) of this warp
+        const int arow = q * 32 + lane;  // A-tile row this thread converts
+        const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16);
+        float sum1[64], sum2[64];
+#pragma unroll
+        for (int i = 0; i < 64; i++) sum1[i] = sum2[i] = 0.f;
+
+        auto drain = [&](int c) -> bool {
+            if (!mbar_wait(acc_full, c & 1, abort_flag, status, ST_TIMEOUT_ACC)) return false;
+            tc_fence_after_sync();
+#pragma unroll
+            for (int blk = 0; blk < 2; blk++) {
+                float v[32];
+                tmem_ld_32x32(lane_addr + h * 64 + blk * 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; i++) sum1[blk * 32 + i] += v[i];
+                tmem_ld_32x32(lane_addr + acc_stride + h * 64 + blk * 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; i++) sum2[blk * 32 + i] += v[i];
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty);
+            return true;
+        };
+
+        bool ok = true;
+        int pending = -1;
+        for (int it = 0; it < nk && ok; it++) {
+            const int r = it % RS, d = it % DS;
+            ok = mbar_wait(raw_full + r, (it / RS) & 1, abort_flag, status, ST_TIMEOUT_RAW) &&
+                 mbar_wait(der_empty + d, ((it / DS) & 1) ^ 1, abort_flag, status, ST_TIMEOUT_EMPTY);
+            if (!ok) break;
+            const uint32_t rs = raw_base + r * NRAW * TILE_BYTES, ds = der_base + d * NDER * TILE_BYTES;
+
+            // ---- A side: this thread's row, k step h (8 values) of both raw tiles -> tensor memory
+            float a0[8], a1[8];
+            if (T::A_MN) {
+                // [32-row group][16 k rows][128 B], 32-byte atoms XOR-swizzled with the k row
+                const uint32_t g = rs + q * 2048;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const int k = h * 8 + i;
+                    const uint32_t o = k * 128 + (((lane >> 3) ^ (k & 3)) << 5) + ((lane & 7) << 2);
+                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(a0[i]) : "r"(g + o));
+                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(a1[i]) : "r"(g + TILE_BYTES + o));
+                }
+            } else {
+                // [128 rows][64 B], 16-byte chunks XOR-swizzled with (row / 2) % 4
+                const uint32_t rowb = rs + arow * 64, sw = (arow >> 1) & 3;
+                const float4 x0 = lds128(rowb + (((2 * h) ^ sw) << 4)), x1 = lds128(rowb + (((2 * h + 1) ^ sw) << 4));
+                const float4 y0 = lds128(rowb + TILE_BYTES + (((2 * h) ^ sw) << 4));
+                const float4 y1 = lds128(rowb + TILE_BYTES + (((2 * h + 1) ^ sw) << 4));
+                a0[0] = x0.x, a0[1] = x0.y, a0[2] = x0.z, a0[3] = x0.w, a0[4] = x1.x, a0[5] = x1.y, a0[6] = x1.z, a0[7] = x1.w;
+                a1[0] = y0.x, a1[1] = y0.y, a1[2] = y0.z, a1[3] = y0.w, a1[4] = y1.x, a1[5] = y1.y, a1[6] = y1.z, a1[7] = y1.w;
+            }
+            {
+                const uint32_t at = lane_addr + A_COL0 + d * (NA * BK) + h * 8;
+                float t0[8], t1[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) t0[i] = hi_part(a0[i]), t1[i] = hi_part(a1[i]);
+                tmem_st_32x8(at + 0 * BK, t0);
+                tmem_st_32x8(at + 1 * BK, t1);
+#pragma unroll
+                for (int i = 0; i < 8; i++) t0[i] = a0[i] - t0[i], t1[i] = a1[i] - t1[i];
+                tmem_st_32x8(at + 2 * BK, t0);
+                tmem_st_32x8(at + 3 * BK, t1);
+                if (OP == OP_FWD) {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const float sq = fmaf(a0[i], a0[i], a1[i]);
+                        t0[i] = hi_part(sq);
+                        t1[i] = sq - t0[i];
+                    }
+                    tmem_st_32x8(at + 4 * BK, t0);
+                    tmem_st_32x8(at + 5 * BK, t1);
+                }
+            }
+            // ---- B side: elementwise on 16-byte chunks, derived tiles at the same swizzled offsets
+#pragma unroll
+            for (int c = ct; c < CHUNKS; c += 32 * NCONV_WARPS) {
+                const uint32_t o = c * 16;
+                if (OP == OP_FWD) {
+                    const float4 b0 = lds128(rs + 2 * TILE_BYTES + o), b1 = lds128(rs + 3 * TILE_BYTES + o);
+                    const float4 qq = make_float4(b0.x * b0.x, b0.y * b0.y, b0.z * b0.z, b0.w * b0.w);
+                    sts128(ds + 0 * TILE_BYTES + o, lo_part(b0));
+                    sts128(ds + 1 * TILE_BYTES + o, lo_part(b1));
+                    sts128(ds + 2 * TILE_BYTES + o, qq);
+                    sts128(ds + 3 * TILE_BYTES + o, lo_part(qq));
+                } else {
+                    const float4 w = lds128(rs + 2 * TILE_BYTES + o);
+                    const float4 qq = make_float4(w.x * w.x, w.y * w.y, w.z * w.z, w.w * w.w);
+                    sts128(ds + 0 * TILE_BYTES + o, lo_part(w));
+                    sts128(ds + 1 * TILE_BYTES + o, qq);
+                    sts128(ds + 2 * TILE_BYTES + o, lo_part(qq));
+                }
+            }
+            fence_proxy_async_smem();
+            tmem_wait_st();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(conv_done + d);
+            if (pending >= 0) {
+                ok = drain(pending);
+                pending = -1;
+            }
+            if (it % chunk_len == chunk_len - 1 || it == nk - 1) pending = it / chunk_len;
+        }
+        if (ok && pending >= 0) ok = drain(pending);
+
+        if (ok) {
+            const int row = row0 + q * 32 + lane;
+            if (row < epi.rows) {
+#pragma unroll
+                for (int i = 0; i < 64; i += 4) {
+                    const int col = col0 + h * 64 + i;
+                    if (h * 64 + i >= bn || col >= epi.cols) break;
+                    const long idx = (long)row * epi.ld + col;
+                    float4 o1 = make_float4(sum1[i], sum1[i + 1], sum1[i + 2], sum1[i + 3]);
+                    float4 o2 = make_float4(sum2[i], sum2[i + 1], sum2[i + 2], sum2[i + 3]);
+                    if (OP == OP_FWD) {
+                        if (epi.aux1) {
+                            const float4 b1 = __ldg(reinterpret_cast<const float4 *>(epi.aux1 + col));
+                            const float4 b2 = __ldg(reinterpret_cast<const float4 *>(epi.aux2 + col));
+                            o1.x += b1.x, o1.y += b1.y, o1.z += b1.z, o1.w += b1.w;
+                            o2.x += b2.x, o2.y += b2.y, o2.z += b2.z, o2.w += b2.w;
+                        }
+                    } else {
+                        const float4 sc = __ldg(reinterpret_cast<const float4 *>(epi.aux1 + idx));
+                        o1.x *= sc.x, o1.y *= sc.y, o1.z *= sc.z, o1.w *= sc.w;
+                        o2.x = o2.x * sc.x * sc.x, o2.y = o2.y * sc.y * sc.y;
+                        o2.z = o2.z * sc.z * sc.z, o2.w = o2.w * sc.w * sc.w;
+                    }
+                    __stcs(reinterpret_cast<float4 *>(epi.out1 + idx), o1);
+                    __stcs(reinterpret_cast<float4 *>(epi.out2 + idx), o2);
+                }
+            }
+        }
+    }
+    __syncwarp();
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        if (*abort_flag) {
             const long long t0 = clock64();
             while (clock64() - t0 < 4000000LL) {
             }
@@ -384,6 +694,8 @@ int *status_word() {
     return ptr[dev];
 }
 
+int g_deep = 0;     // deeper derived rings where tensor memory allows (diagnostic switch; measured: no gain)
+int g_variant = 1;  // 1: A-side tiles in tensor memory ("ts", default); 0: every operand tile in shared memory ("ss")
 int g_chunked = 1;  // 1: contraction accumulated in chunks of 256 (default); 0: one accumulation chain (diagnostic)
 
 template <int OP>
@@ -392,18 +704,54 @@ int launch(const CUtensorMap &a0, const CUtensorMap &a1, const CUtensorMap &b0, 
     int *status = status_word();
     if (!status) return fail(TAGI_ERR_CUDA, "cannot allocate the tensor-core status word");
     constexpr size_t smem = tc_smem_bytes<OP>();
-    dim3 grid((epi.cols + TN - 1) / TN, (epi.rows + TM - 1) / TM);
+    // Columns per tile: the width (a multiple of 16 up to 128) that minimises waves-of-148-CTAs x width, i.e. the
+    // tensor-core time of the slowest SM; e.g. 4096 columns x 8 row tiles run as 296 tiles of 112 (two full waves)
+    // rather than 256 tiles of 128 (two waves, the second 73 % full).
+    const long row_tiles = (epi.rows + TM - 1) / TM;
+    int bn = TN;
+    long best = -1;
+    for (int w = TN; w >= 64; w -= 16) {
+        const long tiles = row_tiles * ((epi.cols + w - 1) / w);
+        const long cost = ((tiles + 147) / 148) * (w + 16);  // + 16: per-tile work that does not shrink with the width
+        if (best < 0 || cost < best) best = cost, bn = w;
+    }
+    dim3 grid((epi.cols + bn - 1) / bn, (unsigned)row_tiles);
     cudaError_t e;
-    if (g_chunked) {
+    if (g_variant == 1) {
+        // ring depths: the backward passes have room for four derived slots; the forward pass for three when the
+        // tile is at most 112 columns wide (accumulators then take 2 x 112 tensor-memory columns), else two
+#define TAGI_TS_LAUNCH(CHV, RSV, DSV)                                                                          \
+    do {                                                                                                         \
+        auto k = tagi_tc_linear_ts_kernel<OP, CHV, RSV, DSV>;                                                    \
+        constexpr size_t sm = ts_smem_bytes<OP, RSV, DSV>();                                                     \
+        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);                       \
+        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");                                       \
+        k<<<grid, NTHREADS, sm, st>>>(a0, a1, b0, b1, epi, kdim, bn, status);                            \
+    } while (0)
+        if (OP == OP_FWD) {
+            if (bn <= 112 && g_deep) {
+                if (g_chunked) TAGI_TS_LAUNCH(CHUNK_STAGES, 3, 3); else TAGI_TS_LAUNCH(0, 3, 3);
+            } else {
+                if (g_chunked) TAGI_TS_LAUNCH(CHUNK_STAGES, 4, 2); else TAGI_TS_LAUNCH(0, 4, 2);
+            }
+        } else {
+            if (g_deep) {
+                if (g_chunked) TAGI_TS_LAUNCH(CHUNK_STAGES, 4, 4); else TAGI_TS_LAUNCH(0, 4, 4);
+            } else {
+                if (g_chunked) TAGI_TS_LAUNCH(CHUNK_STAGES, 4, 2); else TAGI_TS_LAUNCH(0, 4, 2);
+            }
+        }
+#undef TAGI_TS_LAUNCH
+    } else if (g_chunked) {
         auto k = tagi_tc_linear_kernel<OP, CHUNK_STAGES>;
         e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");
-        k<<<grid, NTHREADS, smem, st>>>(a0, a1, b0, b1, epi, kdim, status);
+        k<<<grid, NTHREADS, smem, st>>>(a0, a1, b0, b1, epi, kdim, bn, status);
     } else {
         auto k = tagi_tc_linear_kernel<OP, 0>;
         e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");
-        k<<<grid, NTHREADS, smem, st>>>(a0, a1, b0, b1, epi, kdim, status);
+        k<<<grid, NTHREADS, smem, st>>>(a0, a1, b0, b1, epi, kdim, bn, status);
     }
     e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "tensor-core Linear kernel launch");
@@ -422,6 +770,13 @@ bool linear_tc_supported(int B, int K, int N, std::initializer_list<const void *
 }
 bool linear_tc_profitable(int B, int K, int N) { return B >= 128 && K >= 128 && N >= 128; }
 
+int linear_tc_set_variant(int v) {
+    if (v < 0 || v > 2) return fail(TAGI_ERR_INVALID_ARGUMENT, "variant must be 0 (ss), 1 (ts) or 2 (ts, deeper rings)");
+    g_deep = v == 2;
+    if (v == 2) v = 1;
+    g_variant = v;
+    return TAGI_OK;
+}
 int linear_tc_set_chunked(int on) {
     g_chunked = on ? 1 : 0;
     return TAGI_OK;

@@ -54,13 +54,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
                                           int code) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
-    while (true) {
+    for (uint32_t spin = 1;; spin++) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (clock64() - t0 > 2000000000LL) {
-            *abort_flag = 1;
-            atomicCAS(status, 0, code);
-            return false;
+        // the abort flag lives in shared memory: look at it rarely so that polling does not eat LSU bandwidth
+        if ((spin & 255u) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > 2000000000LL) {
+                *abort_flag = 1;
+                atomicCAS(status, 0, code);
+                return false;
+            }
         }
     }
 }
@@ -112,6 +115,16 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, float (&v)[32]) {
     for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
 }
 
+// 32 lanes x 8 consecutive 32-bit columns written from registers: thread i of the warp writes row (lane base + i).
+__device__ __forceinline__ void tmem_st_32x8(uint32_t taddr, const float (&v)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
+                 "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+                 "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])),
+                 "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7]))
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
 // ----------------------------------------------------------------------------- descriptors
 // Shared-memory matrix descriptor (64 bit): start address, leading / stride byte offsets (all >> 4),
 // version 1 (bits 46-47), swizzle mode in bits 61-63.
@@ -142,6 +155,17 @@ __device__ __forceinline__ void mma_tf32_ss(uint32_t d_tmem, uint64_t a_desc, ui
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// D[tmem] (+)= A[tmem] * B[smem]: A is M x 8 in tensor memory (lane = row, one tf32 per 32-bit column).
+__device__ __forceinline__ void mma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 

@@ -52,6 +52,10 @@ int tagi_tc_status(int *status, int reset);
  * chunks of 256 that are summed in FP32 registers, which keeps the tensor core's accumulation error far below the
  * 1e-5 / 1e-4 tolerance. on == 0: one accumulation chain over the whole contraction (less accurate; for measurement). */
 int tagi_tc_set_chunked(int on);
+/* Diagnostic switch of the TF32X3 kernels. 1 (default): the A-side operand tiles are kept in tensor memory; 0: every
+ * operand tile is kept in shared memory (the simpler kernel, bound by shared-memory bandwidth); 2: as 1 with deeper
+ * rings of derived tiles. Same results in all three. */
+int tagi_tc_set_variant(int v);
 
 const char *tagi_last_error_string(void);
 /* Library version as major*10000 + minor*100 + patch. */
