@@ -37,6 +37,7 @@ _SIGNATURES = {
     "tagi_conv2d_fwd": [C.POINTER(ConvGeom), _p, _p, _p, _p, _p, _p, _p, _p, _p],
     "tagi_conv2d_bwd_state": [C.POINTER(ConvGeom), _p, _p, _p, _p, _p, _p, _p],
     "tagi_conv2d_bwd_param": [C.POINTER(ConvGeom), _p, _p, _p, _p, _p, _p, _p, _p, _p, _p],
+    "tagi_conv2d_bwd_param_noalloc": [C.POINTER(ConvGeom), _p, _p, _p, _p, _p, _p, _p, _p, _p, _p],
 }
 
 _lib = None

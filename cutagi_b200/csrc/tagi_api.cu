@@ -232,4 +232,24 @@ int tagi_conv2d_bwd_param(const tagi_conv2d_geom *g, const float *var_w, const f
                                  static_cast<cudaStream_t>(stream));
 }
 
+int tagi_conv2d_bwd_param_noalloc(const tagi_conv2d_geom *g, const float *var_w, const float *var_b, const float *mu_a,
+                                  const float *dmu_z, const float *dvar_z, float *dmu_w, float *dvar_w, float *dmu_b,
+                                  float *dvar_b, void *stream) {
+    int rc = check_geom(g);
+    if (rc != TAGI_OK) return rc;
+    TAGI_PTR(var_w);
+    TAGI_PTR(mu_a);
+    TAGI_PTR(dmu_z);
+    TAGI_PTR(dvar_z);
+    TAGI_PTR(dmu_w);
+    TAGI_PTR(dvar_w);
+    if (g->has_bias) {
+        TAGI_PTR(var_b);
+        TAGI_PTR(dmu_b);
+        TAGI_PTR(dvar_b);
+    }
+    return conv2d_bwd_param_noalloc(*g, var_w, var_b, mu_a, dmu_z, dvar_z, dmu_w, dvar_w, dmu_b, dvar_b,
+                                    static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

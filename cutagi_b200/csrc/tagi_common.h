@@ -65,5 +65,8 @@ int conv2d_bwd_state_ffma(const tagi_conv2d_geom &g, const float *mu_w, const fl
 int conv2d_bwd_param_ffma(const tagi_conv2d_geom &g, const float *var_w, const float *var_b, const float *mu_a,
                           const float *dmu_z, const float *dvar_z, float *dmu_w, float *dvar_w, float *dmu_b,
                           float *dvar_b, cudaStream_t st);
+int conv2d_bwd_param_noalloc(const tagi_conv2d_geom &g, const float *var_w, const float *var_b, const float *mu_a,
+                             const float *dmu_z, const float *dvar_z, float *dmu_w, float *dvar_w, float *dmu_b,
+                             float *dvar_b, cudaStream_t st);
 
 }  // namespace tagi

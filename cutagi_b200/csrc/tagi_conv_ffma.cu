@@ -390,4 +390,99 @@ int conv2d_bwd_param_ffma(const tagi_conv2d_geom &cg, const float *var_w, const 
     return rc;
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Parameter pass with statically reserved scratch (entry point tagi_conv2d_bwd_param_noalloc)
+// ---------------------------------------------------------------------------------------------------------
+// Some hosts of this library must not allocate device memory while they run: trainers that hand the whole GPU to their
+// own pool at start-up (a later cudaMalloc fails or fragments that pool), services whose memory budget is fixed when
+// they are admitted to a shared GPU, and code that runs while a thread of the process is capturing a stream in the
+// global capture mode, where cudaMalloc is not a permitted call. For them the split-contraction scratch lives in the
+// array below, which is part of the library image: every GPU that loads the library holds these 16 MiB until the
+// process exits, whether or not this entry point is ever called.
+//
+// In host code the array's name is only a handle for the runtime, not a device address; the address a kernel can use
+// comes from cudaGetSymbolAddress, asked once per device with that device current.
+constexpr size_t kStaticScratchFloats = (size_t)4 << 20;  // 4 Mi floats = 16 MiB
+constexpr long kNoAllocMaxWeights = (long)(kStaticScratchFloats / 4);  // two slices of both partial tensors must fit
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+
+namespace {
+float *g_static_scratch_addr[64] = {};
+std::mutex g_static_scratch_mu;
+
+// Device address of g_static_scratch on the current device. The first call on a device asks the runtime for it.
+int static_scratch(float **out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (dev < 0 || dev >= 64) return fail(TAGI_ERR_UNSUPPORTED, "device index out of range");
+    std::lock_guard<std::mutex> lk(g_static_scratch_mu);
+    if (!g_static_scratch_addr[dev]) {
+        float *ptr = nullptr;
+        e = cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_static_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static scratch)");
+        g_static_scratch_addr[dev] = ptr;
+    }
+    *out = g_static_scratch_addr[dev];
+    return TAGI_OK;
+}
+}  // namespace
+
+int conv2d_bwd_param_noalloc(const tagi_conv2d_geom &cg, const float *var_w, const float *var_b, const float *mu_a,
+                             const float *dmu_z, const float *dvar_z, float *dmu_w, float *dvar_w, float *dmu_b,
+                             float *dvar_b, cudaStream_t st) {
+    const Geom g = make_geom(cg);
+    const int M = g.fo, N = g.Kc, Kd = g.B * g.woho;
+    const long slice = (long)M * N;
+    if (slice > kNoAllocMaxWeights)
+        return fail(TAGI_ERR_UNSUPPORTED,
+                    "tagi_conv2d_bwd_param_noalloc: weight tensor of " + std::to_string(slice) +
+                        " elements exceeds the limit of " + std::to_string(kNoAllocMaxWeights) +
+                        " (16 MiB of static scratch); use tagi_conv2d_bwd_param");
+    DeltaForChannel<DER_PAIR> D{dmu_z, dvar_z, g, g.fo, Kd};
+    ActForTap<DER_SQUARE> X{mu_a, nullptr, g, g.Kc, Kd};
+
+    // same slicing rule as the allocating entry point, then as many slices as the static scratch holds
+    const bool big = M >= 128 && N >= 128;
+    const int tm = big ? 128 : 64;
+    const long tiles = (long)((M + tm - 1) / tm) * ((N + tm - 1) / tm);
+    int splits = (int)((2 * 148 + tiles - 1) / tiles);
+    const int max_splits = (Kd + 255) / 256;
+    if (splits > max_splits) splits = max_splits;
+    const long fit = (long)(kStaticScratchFloats / (2 * (size_t)slice));
+    if (splits > fit) splits = (int)fit;
+    if (splits < 1) splits = 1;
+
+    int rc;
+    if (splits == 1) {
+        EpiRowScale epi{dmu_w, dvar_w, var_w, (long)N,
+                        N % 4 == 0 && aligned16(dmu_w) && aligned16(dvar_w) && aligned16(var_w)};
+        rc = done(dispatch_ffma<decltype(D), decltype(X), EpiRowScale, LOAD_K_SCALAR, LOAD_K_SCALAR, LOAD_K_SCALAR,
+                                LOAD_K_SCALAR>(D, X, epi, M, N, Kd, false, false, st),
+                  "conv2d parameter backward launch");
+    } else {
+        float *ws = nullptr;
+        rc = static_scratch(&ws);
+        if (rc != TAGI_OK) return rc;
+        // every slice overwrites its whole M x N part of both partial tensors, so nothing has to start at zero
+        EpiPartial epi{ws, ws + (long)splits * slice, (long)N, slice, N % 4 == 0};
+        const int bk = use_large_tile(M, N, splits) ? TileL::BK : TileS::BK;
+        const int k_chunk = ((Kd + splits - 1) / splits + bk - 1) / bk * bk;
+        const int slices = (Kd + k_chunk - 1) / k_chunk;
+        rc = done(dispatch_ffma<decltype(D), decltype(X), EpiPartial, LOAD_K_SCALAR, LOAD_K_SCALAR, LOAD_K_SCALAR,
+                                LOAD_K_SCALAR>(D, X, epi, M, N, Kd, false, false, st, splits),
+                  "conv2d parameter backward launch");
+        if (rc != TAGI_OK) return rc;
+        reduce_slices_scale_kernel<<<(unsigned)((slice + 255) / 256), 256, 0, st>>>(
+            ws, ws + (long)splits * slice, var_w, slice, slices, dmu_w, dvar_w);
+        rc = done(cudaGetLastError(), "reduce_slices_scale_kernel launch");
+    }
+    if (rc != TAGI_OK) return rc;
+    if (cg.has_bias) {
+        conv_bias_delta_kernel<<<g.fo, 256, 0, st>>>(var_b, dmu_z, dvar_z, g.B, g.fo, g.woho, dmu_b, dvar_b);
+        rc = done(cudaGetLastError(), "conv_bias_delta_kernel launch");
+    }
+    return rc;
+}
+
 }  // namespace tagi

@@ -124,6 +124,24 @@ int tagi_conv2d_bwd_param(const tagi_conv2d_geom *g, const float *var_w, const f
                           const float *dmu_z, const float *dvar_z, float *dmu_w, float *dvar_w, float *dmu_b,
                           float *dvar_b, void *stream);
 
+/* Same result as tagi_conv2d_bwd_param, for callers that must not allocate device memory while they run: a trainer
+ * that gave the whole GPU to its own memory pool at start-up, a service with a fixed memory budget on a shared GPU, or
+ * code running while another thread of the process captures a stream in the global capture mode (cudaMalloc is not
+ * allowed then). This entry point has no counterpart in the reference. It never calls cudaMalloc, cudaFree or any
+ * allocating routine: the partial sums of the split contraction go to a 16 MiB array that is part of the library
+ * image (every GPU that loads the library holds it until the process exits).
+ *  - Limit: fo * fi * k * k <= 1048576 weights (two slices of both partial tensors must fit); larger layers return
+ *    TAGI_ERR_UNSUPPORTED with a message, use tagi_conv2d_bwd_param for them. Within the limit the contraction is cut
+ *    into as many slices as fit, so results can differ from tagi_conv2d_bwd_param in the last bits.
+ *  - The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that device current);
+ *    make that first call before any stream capture starts.
+ *  - All calls on a device share the array, which keeps whatever the previous call left; every call overwrites the part
+ *    it reads, so nothing depends on old contents. Two calls that overlap on the GPU (different streams) race: keep
+ *    calls of this entry point on one stream, or order them with events. */
+int tagi_conv2d_bwd_param_noalloc(const tagi_conv2d_geom *g, const float *var_w, const float *var_b,
+                                  const float *mu_a, const float *dmu_z, const float *dvar_z, float *dmu_w,
+                                  float *dvar_w, float *dmu_b, float *dvar_b, void *stream);
+
 #ifdef __cplusplus
 }
 #endif
