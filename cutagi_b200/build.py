@@ -15,6 +15,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(CSRC, "build")
 LIB = os.path.join(HERE, "libtagi_b200.so")
+COMM_SRC = os.path.join(HERE, "csrc_comm", "tagi_comm.cpp")
+COMM_LIB = os.path.join(HERE, "libtagi_b200_comm.so")
 NVCC = os.environ.get("NVCC", "nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
          "-Xptxas", "-v", "--expt-relaxed-constexpr"]
@@ -56,7 +58,19 @@ def build(force=False, verbose=False):
         r = subprocess.run([NVCC, "-shared", "-o", LIB, *objs, "-lcudart"], capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("link failed:\n" + r.stdout + r.stderr)
+    build_comm(force)
     return LIB
+
+
+def build_comm(force=False):
+    """libtagi_b200_comm.so: host-only C++ over NCCL (kept apart so that the kernel library does not depend on NCCL)."""
+    hdrs = glob.glob(os.path.join(os.path.dirname(HERE), "include", "*.h"))
+    if force or _newer(COMM_SRC, COMM_LIB) or any(_newer(h, COMM_LIB) for h in hdrs):
+        r = subprocess.run([NVCC, "-O2", "-std=c++17", "-Xcompiler", "-fPIC", "-shared", "-o", COMM_LIB, COMM_SRC,
+                            "-lnccl", "-lcudart"], capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("comm library build failed:\n" + r.stdout + r.stderr)
+    return COMM_LIB
 
 
 if __name__ == "__main__":

@@ -1,0 +1,316 @@
+// Data-parallel exchange of TAGI parameter deltas over NCCL (see include/tagi_b200_comm.h).
+// Host-only C++: the collectives are NCCL's; what this file adds is the MPI-free rendezvous, the bucket plan and the
+// event-ordered overlap with the backward pass.
+#include <cuda_runtime.h>
+#include <fcntl.h>
+#include <nccl.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <chrono>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "../../include/tagi_b200.h"
+#include "../../include/tagi_b200_comm.h"
+
+namespace {
+
+thread_local std::string g_err;
+int fail(int code, const std::string &m) {
+    g_err = m;
+    return code;
+}
+#define CU(expr)                                                                                   \
+    do {                                                                                           \
+        cudaError_t e__ = (expr);                                                                  \
+        if (e__ != cudaSuccess) return fail(TAGI_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(e__)); \
+    } while (0)
+#define NC(expr)                                                                                   \
+    do {                                                                                           \
+        ncclResult_t r__ = (expr);                                                                 \
+        if (r__ != ncclSuccess && r__ != ncclInProgress)                                           \
+            return fail(TAGI_ERR_COMM, std::string(#expr) + ": " + ncclGetErrorString(r__));       \
+    } while (0)
+
+struct Tensor {
+    float *ptr;
+    size_t count;
+    int bucket;
+};
+struct Bucket {
+    std::vector<int> tensors;
+    int ready = 0;       // tensors marked ready in this step
+    bool launched = false;
+    cudaEvent_t done = nullptr;
+};
+struct Comm {
+    ncclComm_t nccl = nullptr;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev = nullptr;  // compute -> comm ordering
+    int rank = 0, world = 1, device = 0;
+    bool finalized = false;
+    std::vector<Tensor> tensors;
+    std::vector<Bucket> buckets;
+    std::vector<char> ready;   // per tensor, this step
+};
+Comm *g = nullptr;
+
+int need_comm() { return g ? TAGI_OK : fail(TAGI_ERR_COMM, "communicator not initialised"); }
+
+int launch_bucket(Bucket &b, cudaStream_t compute, int average) {
+    if (b.launched) return TAGI_OK;
+    CU(cudaEventRecord(g->ev, compute));
+    CU(cudaStreamWaitEvent(g->stream, g->ev, 0));
+    NC(ncclGroupStart());
+    for (int t : b.tensors) {
+        Tensor &x = g->tensors[t];
+        NC(ncclAllReduce(x.ptr, x.ptr, x.count, ncclFloat32, average ? ncclAvg : ncclSum, g->nccl, g->stream));
+    }
+    NC(ncclGroupEnd());
+    CU(cudaEventRecord(b.done, g->stream));
+    b.launched = true;
+    return TAGI_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char *tagi_comm_last_error_string(void) { return g_err.c_str(); }
+
+// ------------------------------------------------------------------------------------------------ host-only pieces
+int tagi_rendezvous_publish(const char *path, const void *blob, size_t bytes) {
+    if (!path || !blob || bytes == 0) return fail(TAGI_ERR_INVALID_ARGUMENT, "rendezvous: null path or empty blob");
+    const std::string tmp = std::string(path) + ".tmp." + std::to_string((long)getpid());
+    FILE *f = std::fopen(tmp.c_str(), "wb");
+    if (!f) return fail(TAGI_ERR_COMM, "rendezvous: cannot create " + tmp);
+    const size_t w = std::fwrite(blob, 1, bytes, f);
+    std::fclose(f);
+    if (w != bytes) return fail(TAGI_ERR_COMM, "rendezvous: short write to " + tmp);
+    if (std::rename(tmp.c_str(), path) != 0) return fail(TAGI_ERR_COMM, std::string("rendezvous: cannot rename to ") + path);
+    return TAGI_OK;
+}
+
+int tagi_rendezvous_fetch(const char *path, void *blob, size_t bytes, int timeout_ms) {
+    if (!path || !blob || bytes == 0) return fail(TAGI_ERR_INVALID_ARGUMENT, "rendezvous: null path or empty blob");
+    const auto t0 = std::chrono::steady_clock::now();
+    while (true) {
+        FILE *f = std::fopen(path, "rb");
+        if (f) {
+            const size_t r = std::fread(blob, 1, bytes, f);
+            std::fclose(f);
+            if (r == bytes) return TAGI_OK;
+        }
+        const auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+        if (ms > timeout_ms)
+            return fail(TAGI_ERR_COMM, std::string("rendezvous: nothing published at ") + path + " within " +
+                                           std::to_string(timeout_ms) + " ms (did rank 0 start?)");
+        std::this_thread::sleep_for(std::chrono::milliseconds(5));
+    }
+}
+
+int tagi_comm_plan_buckets(const size_t *counts, int n, size_t bucket_bytes, int *bucket_of) {
+    if (!counts || !bucket_of || n < 0 || bucket_bytes == 0) {
+        fail(TAGI_ERR_INVALID_ARGUMENT, "plan_buckets: bad arguments");
+        return -TAGI_ERR_INVALID_ARGUMENT;
+    }
+    int bucket = 0;
+    size_t used = 0;
+    for (int i = 0; i < n; i++) {
+        const size_t bytes = counts[i] * sizeof(float);
+        if (used > 0 && used + bytes > bucket_bytes) {
+            bucket++;
+            used = 0;
+        }
+        bucket_of[i] = bucket;
+        used += bytes;
+    }
+    return n == 0 ? 0 : bucket + 1;
+}
+
+// ------------------------------------------------------------------------------------------------ communicator
+int tagi_comm_create_id(void *id) {
+    if (!id) return fail(TAGI_ERR_INVALID_ARGUMENT, "null id");
+    static_assert(sizeof(ncclUniqueId) == TAGI_COMM_ID_BYTES, "ncclUniqueId size");
+    ncclUniqueId u;
+    NC(ncclGetUniqueId(&u));
+    std::memcpy(id, &u, sizeof(u));
+    return TAGI_OK;
+}
+
+int tagi_comm_init(const void *id, int rank, int world_size, int device) {
+    if (g) return fail(TAGI_ERR_COMM, "communicator already initialised");
+    if (!id || world_size < 1 || rank < 0 || rank >= world_size)
+        return fail(TAGI_ERR_INVALID_ARGUMENT, "comm_init: bad id, rank or world size");
+    CU(cudaSetDevice(device));
+    Comm *c = new Comm;
+    c->rank = rank, c->world = world_size, c->device = device;
+    ncclUniqueId u;
+    std::memcpy(&u, id, sizeof(u));
+    ncclResult_t r = ncclCommInitRank(&c->nccl, world_size, u, rank);
+    if (r != ncclSuccess) {
+        delete c;
+        return fail(TAGI_ERR_COMM, std::string("ncclCommInitRank: ") + ncclGetErrorString(r));
+    }
+    cudaError_t e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev, cudaEventDisableTiming);
+    if (e != cudaSuccess) {
+        ncclCommAbort(c->nccl);
+        delete c;
+        return fail(TAGI_ERR_CUDA, std::string("comm stream/event: ") + cudaGetErrorString(e));
+    }
+    g = c;
+    return TAGI_OK;
+}
+
+int tagi_comm_init_file(const char *path, int rank, int world_size, int device, int timeout_ms) {
+    unsigned char id[TAGI_COMM_ID_BYTES];
+    int rc;
+    if (rank == 0) {
+        if ((rc = tagi_comm_create_id(id)) != TAGI_OK) return rc;
+        if ((rc = tagi_rendezvous_publish(path, id, sizeof(id))) != TAGI_OK) return rc;
+    } else {
+        if ((rc = tagi_rendezvous_fetch(path, id, sizeof(id), timeout_ms)) != TAGI_OK) return rc;
+    }
+    return tagi_comm_init(id, rank, world_size, device);
+}
+
+int tagi_comm_rank(void) { return g ? g->rank : 0; }
+int tagi_comm_world_size(void) { return g ? g->world : 1; }
+
+int tagi_comm_register(float *ptr, size_t count) {
+    if (need_comm() != TAGI_OK) return -TAGI_ERR_COMM;
+    if (g->finalized) {
+        fail(TAGI_ERR_COMM, "register after finalize_buckets");
+        return -TAGI_ERR_COMM;
+    }
+    if (!ptr || count == 0) {
+        fail(TAGI_ERR_INVALID_ARGUMENT, "register: null pointer or zero count");
+        return -TAGI_ERR_INVALID_ARGUMENT;
+    }
+    g->tensors.push_back({ptr, count, -1});
+    return (int)g->tensors.size() - 1;
+}
+
+int tagi_comm_finalize_buckets(size_t bucket_bytes) {
+    int rc = need_comm();
+    if (rc != TAGI_OK) return rc;
+    if (g->finalized) return fail(TAGI_ERR_COMM, "buckets already finalized");
+    const int n = (int)g->tensors.size();
+    std::vector<size_t> counts(n);
+    std::vector<int> of(n);
+    for (int i = 0; i < n; i++) counts[i] = g->tensors[i].count;
+    const int nb = tagi_comm_plan_buckets(counts.data(), n, bucket_bytes, of.data());
+    if (nb < 0) return -nb;
+    g->buckets.resize(nb);
+    for (int i = 0; i < n; i++) {
+        g->tensors[i].bucket = of[i];
+        g->buckets[of[i]].tensors.push_back(i);
+    }
+    for (auto &b : g->buckets) CU(cudaEventCreateWithFlags(&b.done, cudaEventDisableTiming));
+    g->ready.assign(n, 0);
+    g->finalized = true;
+    return TAGI_OK;
+}
+
+int tagi_comm_num_buckets(void) { return g ? (int)g->buckets.size() : 0; }
+int tagi_comm_bucket_of(int i) { return (g && i >= 0 && i < (int)g->tensors.size()) ? g->tensors[i].bucket : -1; }
+
+int tagi_comm_tensor_ready(int i, void *compute_stream, int average) {
+    int rc = need_comm();
+    if (rc != TAGI_OK) return rc;
+    if (!g->finalized) return fail(TAGI_ERR_COMM, "tensor_ready before finalize_buckets");
+    if (i < 0 || i >= (int)g->tensors.size()) return fail(TAGI_ERR_INVALID_ARGUMENT, "tensor index out of range");
+    if (g->ready[i]) return TAGI_OK;
+    g->ready[i] = 1;
+    Bucket &b = g->buckets[g->tensors[i].bucket];
+    if (++b.ready == (int)b.tensors.size()) return launch_bucket(b, static_cast<cudaStream_t>(compute_stream), average);
+    return TAGI_OK;
+}
+
+int tagi_comm_flush(void *compute_stream, int average) {
+    int rc = need_comm();
+    if (rc != TAGI_OK) return rc;
+    if (!g->finalized) return fail(TAGI_ERR_COMM, "flush before finalize_buckets");
+    for (auto &b : g->buckets)
+        if ((rc = launch_bucket(b, static_cast<cudaStream_t>(compute_stream), average)) != TAGI_OK) return rc;
+    return TAGI_OK;
+}
+
+int tagi_comm_wait(void *compute_stream) {
+    int rc = need_comm();
+    if (rc != TAGI_OK) return rc;
+    for (auto &b : g->buckets) {
+        if (b.launched) CU(cudaStreamWaitEvent(static_cast<cudaStream_t>(compute_stream), b.done, 0));
+        b.launched = false;
+        b.ready = 0;
+    }
+    std::fill(g->ready.begin(), g->ready.end(), 0);
+    return TAGI_OK;
+}
+
+int tagi_comm_allreduce(float *ptr, size_t count, int average, void *compute_stream) {
+    int rc = need_comm();
+    if (rc != TAGI_OK) return rc;
+    if (!ptr || count == 0) return fail(TAGI_ERR_INVALID_ARGUMENT, "allreduce: null pointer or zero count");
+    cudaStream_t cs = static_cast<cudaStream_t>(compute_stream);
+    CU(cudaEventRecord(g->ev, cs));
+    CU(cudaStreamWaitEvent(g->stream, g->ev, 0));
+    NC(ncclAllReduce(ptr, ptr, count, ncclFloat32, average ? ncclAvg : ncclSum, g->nccl, g->stream));
+    CU(cudaEventRecord(g->ev, g->stream));
+    CU(cudaStreamWaitEvent(cs, g->ev, 0));
+    return TAGI_OK;
+}
+
+int tagi_comm_broadcast(float *ptr, size_t count, int root, void *compute_stream) {
+    int rc = need_comm();
+    if (rc != TAGI_OK) return rc;
+    if (!ptr || count == 0 || root < 0 || root >= g->world)
+        return fail(TAGI_ERR_INVALID_ARGUMENT, "broadcast: bad pointer, count or root");
+    cudaStream_t cs = static_cast<cudaStream_t>(compute_stream);
+    CU(cudaEventRecord(g->ev, cs));
+    CU(cudaStreamWaitEvent(g->stream, g->ev, 0));
+    NC(ncclBroadcast(ptr, ptr, count, ncclFloat32, root, g->nccl, g->stream));
+    CU(cudaEventRecord(g->ev, g->stream));
+    CU(cudaStreamWaitEvent(cs, g->ev, 0));
+    return TAGI_OK;
+}
+
+int tagi_comm_check(void) {
+    int rc = need_comm();
+    if (rc != TAGI_OK) return rc;
+    ncclResult_t async = ncclSuccess;
+    ncclResult_t r = ncclCommGetAsyncError(g->nccl, &async);
+    if (r != ncclSuccess) return fail(TAGI_ERR_COMM, std::string("ncclCommGetAsyncError: ") + ncclGetErrorString(r));
+    if (async != ncclSuccess && async != ncclInProgress)
+        return fail(TAGI_ERR_COMM, std::string("NCCL asynchronous error: ") + ncclGetErrorString(async));
+    cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) return fail(TAGI_ERR_CUDA, std::string("CUDA error pending: ") + cudaGetErrorString(e));
+    return TAGI_OK;
+}
+
+int tagi_comm_barrier(void) {
+    int rc = need_comm();
+    if (rc != TAGI_OK) return rc;
+    CU(cudaStreamSynchronize(g->stream));
+    return TAGI_OK;
+}
+
+int tagi_comm_destroy(void) {
+    if (!g) return TAGI_OK;
+    cudaStreamSynchronize(g->stream);
+    for (auto &b : g->buckets)
+        if (b.done) cudaEventDestroy(b.done);
+    if (g->ev) cudaEventDestroy(g->ev);
+    if (g->stream) cudaStreamDestroy(g->stream);
+    if (g->nccl) ncclCommDestroy(g->nccl);
+    delete g;
+    g = nullptr;
+    return TAGI_OK;
+}
+
+}  // extern "C"
