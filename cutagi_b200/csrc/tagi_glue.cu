@@ -1,0 +1,159 @@
+// Elementwise neighbours of the hot path, so that whole TAGI training steps can run on the device through this
+// library alone: ReLU moments, output-layer innovation (plain and index-selected), capped parameter update.
+// Each follows the reference's CPU definition; the reference's CUDA counterparts are cited at the entry points.
+#include "tagi_common.h"
+
+namespace tagi {
+namespace {
+
+constexpr int BLOCK = 256;
+inline unsigned blocks_for(size_t n) { return (unsigned)((n + BLOCK - 1) / BLOCK); }
+
+// src/activation.cpp:7-29
+__global__ void relu_kernel(const float *__restrict__ mu_z, const float *__restrict__ var_z, size_t n,
+                            float *__restrict__ mu_a, float *__restrict__ var_a, float *__restrict__ jcb) {
+    const size_t i = (size_t)blockIdx.x * BLOCK + threadIdx.x;
+    if (i >= n) return;
+    const float t = fmaxf(mu_z[i], 0.f);
+    mu_a[i] = t;
+    if (t == 0.f) {
+        jcb[i] = 0.f;
+        var_a[i] = 0.f;
+    } else {
+        jcb[i] = 1.f;
+        var_a[i] = var_z[i];
+    }
+}
+
+// src/base_output_updater.cpp:8-29
+__global__ void output_delta_kernel(const float *__restrict__ mu_a, const float *__restrict__ var_a,
+                                    const float *__restrict__ jcb, const float *__restrict__ obs,
+                                    const float *__restrict__ var_obs, size_t n, float *__restrict__ dmu,
+                                    float *__restrict__ dvar) {
+    const size_t i = (size_t)blockIdx.x * BLOCK + threadIdx.x;
+    if (i >= n) return;
+    const float t = jcb[i] / (var_a[i] + var_obs[i]);
+    if (isinf(t) || isnan(t) || isnan(obs[i])) {
+        dmu[i] = 0.f;
+        dvar[i] = 0.f;
+    } else {
+        dmu[i] = t * (obs[i] - mu_a[i]);
+        dvar[i] = -t * jcb[i];
+    }
+}
+
+// src/base_output_updater.cpp:67-93; selected_idx is one-based within a sample
+__global__ void output_delta_selected_kernel(const float *__restrict__ mu_a, const float *__restrict__ var_a,
+                                             const float *__restrict__ jcb, const float *__restrict__ obs,
+                                             const float *__restrict__ var_obs, const int *__restrict__ sel, int n_sel,
+                                             int n_out, int n_enc, float *__restrict__ dmu,
+                                             float *__restrict__ dvar) {
+    const int c = blockIdx.x * BLOCK + threadIdx.x;
+    if (c >= n_sel) return;
+    const long idx = sel[c] + (long)(c / n_enc) * n_out - 1;
+    const float t = jcb[idx] / (var_a[idx] + var_obs[c]);
+    if (isinf(t) || isnan(t)) {
+        dmu[idx] = 0.f;
+        dvar[idx] = 0.f;
+    } else {
+        dmu[idx] = t * (obs[c] - mu_a[idx]);
+        dvar[idx] = -t * jcb[idx];
+    }
+}
+
+// src/base_layer.cpp:116-162
+__global__ void param_update_kernel(const float *__restrict__ dmu, const float *__restrict__ dvar, float cap, size_t n,
+                                    float *__restrict__ mu, float *__restrict__ var, int *__restrict__ neg) {
+    const size_t i = (size_t)blockIdx.x * BLOCK + threadIdx.x;
+    if (i >= n) return;
+    const float dm = dmu[i], dv = dvar[i];
+    const float sm = (float)((dm > 0.f) - (dm < 0.f)), sv = (float)((dv > 0.f) - (dv < 0.f));
+    float v = var[i];
+    const float bar = sqrtf(v) / cap;
+    mu[i] += sm * fminf(fabsf(dm), bar);
+    v += sv * fminf(fabsf(dv), bar);
+    if (v <= 0.f) {
+        v = 1e-5f;
+        if (neg) atomicAdd(neg, 1);
+    }
+    var[i] = v;
+}
+
+inline int launched(const char *what) {
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? TAGI_OK : cuda_fail(e, what);
+}
+
+}  // namespace
+}  // namespace tagi
+
+using namespace tagi;
+
+#define TAGI_PTR(p) TAGI_REQUIRE((p) != nullptr && aligned4(p), #p " is null or not 4-byte aligned")
+
+extern "C" {
+
+int tagi_relu_fwd(const float *mu_z, const float *var_z, size_t n, float *mu_a, float *var_a, float *jcb,
+                  void *stream) {
+    TAGI_REQUIRE(n > 0, "n must be positive");
+    TAGI_PTR(mu_z);
+    TAGI_PTR(var_z);
+    TAGI_PTR(mu_a);
+    TAGI_PTR(var_a);
+    TAGI_PTR(jcb);
+    relu_kernel<<<blocks_for(n), BLOCK, 0, static_cast<cudaStream_t>(stream)>>>(mu_z, var_z, n, mu_a, var_a, jcb);
+    return launched("relu_kernel launch");
+}
+
+int tagi_output_delta(const float *mu_a, const float *var_a, const float *jcb, const float *obs, const float *var_obs,
+                      size_t n, float *dmu, float *dvar, void *stream) {
+    TAGI_REQUIRE(n > 0, "n must be positive");
+    TAGI_PTR(mu_a);
+    TAGI_PTR(var_a);
+    TAGI_PTR(jcb);
+    TAGI_PTR(obs);
+    TAGI_PTR(var_obs);
+    TAGI_PTR(dmu);
+    TAGI_PTR(dvar);
+    output_delta_kernel<<<blocks_for(n), BLOCK, 0, static_cast<cudaStream_t>(stream)>>>(mu_a, var_a, jcb, obs, var_obs,
+                                                                                         n, dmu, dvar);
+    return launched("output_delta_kernel launch");
+}
+
+int tagi_output_delta_selected(const float *mu_a, const float *var_a, const float *jcb, const float *obs,
+                               const float *var_obs, const int *selected_idx, int B, int n_out, int n_enc, float *dmu,
+                               float *dvar, void *stream) {
+    TAGI_REQUIRE(B > 0 && n_out > 0 && n_enc > 0, "B, n_out and n_enc must be positive");
+    TAGI_PTR(mu_a);
+    TAGI_PTR(var_a);
+    TAGI_PTR(jcb);
+    TAGI_PTR(obs);
+    TAGI_PTR(var_obs);
+    TAGI_PTR(selected_idx);
+    TAGI_PTR(dmu);
+    TAGI_PTR(dvar);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t bytes = (size_t)B * n_out * sizeof(float);
+    TAGI_CUDA(cudaMemsetAsync(dmu, 0, bytes, st));
+    TAGI_CUDA(cudaMemsetAsync(dvar, 0, bytes, st));
+    const int n_sel = B * n_enc;
+    output_delta_selected_kernel<<<blocks_for(n_sel), BLOCK, 0, st>>>(mu_a, var_a, jcb, obs, var_obs, selected_idx,
+                                                                      n_sel, n_out, n_enc, dmu, dvar);
+    return launched("output_delta_selected_kernel launch");
+}
+
+int tagi_param_update(int batch_size, size_t n, float *mu, float *var, const float *dmu, const float *dvar,
+                      int *neg_var_count, void *stream) {
+    TAGI_REQUIRE(batch_size > 0 && n > 0, "batch_size and n must be positive");
+    TAGI_PTR(mu);
+    TAGI_PTR(var);
+    TAGI_PTR(dmu);
+    TAGI_PTR(dvar);
+    // cap factor: 0.1 for batch 1, 2 below 256, 3 from 256 on (src/base_layer.cpp:164-187)
+    const float cap = batch_size == 1 ? 0.1f : (batch_size < 256 ? 2.0f : 3.0f);
+    param_update_kernel<<<blocks_for(n), BLOCK, 0, static_cast<cudaStream_t>(stream)>>>(dmu, dvar, cap, n, mu, var,
+                                                                                        neg_var_count);
+    return launched("param_update_kernel launch");
+}
+
+}  // extern "C"

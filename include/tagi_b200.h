@@ -124,6 +124,35 @@ int tagi_conv2d_bwd_param(const tagi_conv2d_geom *g, const float *var_w, const f
                           const float *dmu_z, const float *dvar_z, float *dmu_w, float *dvar_w, float *dmu_b,
                           float *dvar_b, void *stream);
 
+/* ------------------------------------------------------------------ neighbours of the path
+ * Elementwise steps that sit between the calls above in a TAGI training step. They are memory-bound and outside the
+ * hot path; they are here so that whole steps can run on the device through this library alone. */
+
+/* ReLU moments: mu_a = max(mu_z, 0); where that is 0: jcb = 0, var_a = 0, else jcb = 1, var_a = var_z.
+ * CPU definition relu_mean_var (src/activation.cpp:7-29); replaces relu_mean_var_cuda (src/activation_cuda.cu:8-24). */
+int tagi_relu_fwd(const float *mu_z, const float *var_z, size_t n, float *mu_a, float *var_a, float *jcb, void *stream);
+
+/* Output-layer innovation, n entries: t = jcb / (var_a + var_obs); dmu = t * (obs - mu_a); dvar = -t * jcb; zero where t
+ * is not finite or obs is NaN. CPU definition compute_delta_z_output (src/base_output_updater.cpp:8-29); replaces
+ * update_delta_z_cuda (src/output_updater_cuda.cu:3-27). */
+int tagi_output_delta(const float *mu_a, const float *var_a, const float *jcb, const float *obs, const float *var_obs,
+                      size_t n, float *dmu, float *dvar, void *stream);
+
+/* Index-selected innovation (hierarchical softmax): dmu / dvar (B * n_out entries) are zeroed, then for each of the
+ * B * n_enc observations c the output unit selected_idx[c] (one-based within its sample) is updated as above.
+ * CPU definition compute_selected_delta_z_output (src/base_output_updater.cpp:67-93, zeroing :281,300); replaces
+ * update_delta_z_using_indices_cuda (src/output_updater_cuda.cu:29-60). selected_idx is a device array. */
+int tagi_output_delta_selected(const float *mu_a, const float *var_a, const float *jcb, const float *obs,
+                               const float *var_obs, const int *selected_idx, int B, int n_out, int n_enc, float *dmu,
+                               float *dvar, void *stream);
+
+/* Capped parameter update in place: mu += sign(dmu) * min(|dmu|, sqrt(var) / cap), var likewise, var <= 0 -> 1e-5;
+ * cap = 0.1, 2, 3 for batch size 1, < 256, >= 256. neg_var_count (device int, may be NULL) is incremented per reset.
+ * CPU definition BaseLayer::update_weights / update_biases (src/base_layer.cpp:116-187); replaces device_weight_update /
+ * device_bias_update (src/base_layer_cuda.cu:56-103). */
+int tagi_param_update(int batch_size, size_t n, float *mu, float *var, const float *dmu, const float *dvar,
+                      int *neg_var_count, void *stream);
+
 /* Same result as tagi_conv2d_bwd_param, for callers that must not allocate device memory while they run: a trainer
  * that gave the whole GPU to its own memory pool at start-up, a service with a fixed memory budget on a shared GPU, or
  * code running while another thread of the process captures a stream in the global capture mode (cudaMalloc is not
