@@ -39,7 +39,9 @@ using namespace ptx;
 constexpr int TM = 128, TN = 128, BK = 16;
 constexpr int TILE_BYTES = 128 * BK * 4;  // 8 KiB per operand tile
 constexpr int NCONV_WARPS = 8;
-constexpr int NTHREADS = 32 * (2 + NCONV_WARPS);
+constexpr int NTHREADS = 32 * (2 + NCONV_WARPS);       // all-shared-memory kernel: TMA, MMA, converters
+constexpr int NTHREADS2 = 32 * (3 + NCONV_WARPS);      // ts / pair kernels: TMA, two MMA issuers (warps 1, 10), converters
+constexpr int ISSUER2_WARP = 2 + NCONV_WARPS;
 constexpr int CHUNKS = TILE_BYTES / 16;  // 16-byte chunks per tile
 
 enum { OP_FWD = 0, OP_BWD_STATE = 1, OP_BWD_PARAM = 2 };
@@ -364,8 +366,8 @@ constexpr size_t ts_smem_bytes() {
 __device__ __forceinline__ float hi_part(float x) { return __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
 
 template <int OP, int CH, int RS, int DS>
-// 10 warps: three share one SM sub-partition (16 K registers), which caps a thread at 168 registers
-__global__ void __launch_bounds__(NTHREADS, 1)
+// 11 warps: three share one SM sub-partition (16 K registers), which caps a thread at 168 registers
+__global__ void __launch_bounds__(NTHREADS2, 1)
 tagi_tc_linear_ts_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
                          const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
                          const TcEpilogue epi, const int kdim, const int bn, int *status) {
@@ -383,8 +385,11 @@ tagi_tc_linear_ts_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_
     uint8_t *aligned = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t raw_base = smem_base, der_base = smem_base + RS * NRAW * TILE_BYTES;
     uint64_t *bars = reinterpret_cast<uint64_t *>(aligned + (size_t)(RS * NRAW + DS * NDER) * TILE_BYTES);
-    uint64_t *raw_full = bars, *raw_empty = bars + RS, *conv_done = bars + 2 * RS, *der_empty = bars + 2 * RS + DS;
-    uint64_t *acc_full = bars + 2 * RS + 2 * DS, *acc_empty = acc_full + 1;
+    // stage_done[it % L] completes when the MMAs of k-slab `it` have finished: one commit per slab releases both the
+    // raw slot (refilled RS slabs later) and the derived slot (overwritten DS slabs later)
+    constexpr int L = RS > DS ? RS : DS;
+    uint64_t *raw_full = bars, *stage_done = bars + RS, *conv_done = bars + RS + L;
+    uint64_t *acc_full = bars + RS + L + DS, *acc_empty = acc_full + 1;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
@@ -394,15 +399,10 @@ tagi_tc_linear_ts_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_
     const int chunk_len = CH > 0 ? CH : nk;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < RS; s++) {
-            mbar_init(raw_full + s, 1);
-            mbar_init(raw_empty + s, 1);
-        }
-        for (int s = 0; s < DS; s++) {
-            mbar_init(conv_done + s, NCONV_WARPS);
-            mbar_init(der_empty + s, 1);
-        }
-        mbar_init(acc_full, 1);
+        for (int s = 0; s < RS; s++) mbar_init(raw_full + s, 1);
+        for (int s = 0; s < L; s++) mbar_init(stage_done + s, 2);  // one commit from each MMA issuer
+        for (int s = 0; s < DS; s++) mbar_init(conv_done + s, NCONV_WARPS);
+        mbar_init(acc_full, 2);
         mbar_init(acc_empty, NCONV_WARPS);
         *abort_flag = 0;
         mbar_init_fence();
@@ -422,7 +422,9 @@ tagi_tc_linear_ts_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_
         if (lane == 0) {
             for (int it = 0; it < nk; it++) {
                 const int r = it % RS;
-                if (!mbar_wait(raw_empty + r, ((it / RS) & 1) ^ 1, abort_flag, status, ST_TIMEOUT_EMPTY)) break;
+                if (it >= RS && !mbar_spin(stage_done + (it - RS) % L, ((it - RS) / L) & 1, abort_flag, status,
+                                           ST_TIMEOUT_EMPTY))
+                    break;
                 mbar_arrive_expect_tx(raw_full + r, NRAW * TILE_BYTES);
                 const uint32_t st = raw_base + r * NRAW * TILE_BYTES;
                 const int k0 = it * BK;
@@ -432,62 +434,40 @@ tagi_tc_linear_ts_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_
                 if (OP == OP_FWD) load_tile<T::B_MN>(st + 3 * TILE_BYTES, &tmB1, col0, k0, raw_full + r);
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
+    } else if (warp == 1 || warp == ISSUER2_WARP) {
+        // ------------------------------------------------------------------ MMA issuers: warp 1 -> D1, warp 10 -> D2
         if (lane == 0) {
+            const bool chain1 = warp == 1;
             const uint32_t d1 = tmem, d2 = tmem + acc_stride;
-            uint32_t f1 = 0, f2 = 0;
+            uint32_t f = 0;
             bool ok = true;
             for (int it = 0; it < nk && ok; it++) {
                 const int r = it % RS, d = it % DS;
                 if (it > 0 && it % chunk_len == 0) {
                     // the previous chunk must have been added to the register sums before it is overwritten
                     const int c = it / chunk_len;
-                    ok = mbar_wait(acc_empty, (c - 1) & 1, abort_flag, status, ST_TIMEOUT_ACC);
+                    ok = mbar_spin(acc_empty, (c - 1) & 1, abort_flag, status, ST_TIMEOUT_ACC);
                     if (!ok) break;
-                    f1 = f2 = 0;
+                    f = 0;
                 }
-                ok = mbar_wait(conv_done + d, (it / DS) & 1, abort_flag, status, ST_TIMEOUT_CONV);
+                ok = mbar_spin(conv_done + d, (it / DS) & 1, abort_flag, status, ST_TIMEOUT_CONV);
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t rs = raw_base + r * NRAW * TILE_BYTES, ds = der_base + d * NDER * TILE_BYTES;
                 const uint32_t at = tmem + A_COL0 + d * (NA * BK);
-#define AT(i) (at + (i) * BK + j * 8)
-#define RB(i) tile_desc<T::B_MN>(rs + (i) * TILE_BYTES, j)
-#define DB(i) tile_desc<T::B_MN>(ds + (i) * TILE_BYTES, j)
-#pragma unroll
-                for (int j = 0; j < BK / 8; j++) {
-                    if (OP == OP_FWD) {
-                        // A tiles: 0 mu_a, 1 var_a, 2 mu_a lo, 3 var_a lo, 4 S = mu_a^2 + var_a, 5 S lo
-                        // raw B: 2 mu_w, 3 var_w ; derived B: 0 mu_w lo, 1 var_w lo, 2 Q = mu_w^2, 3 Q lo
-                        mma_tf32_ts(d1, AT(0), RB(2), IDESC, f1);
-                        f1 = 1;
-                        mma_tf32_ts(d1, AT(0), DB(0), IDESC, 1);
-                        mma_tf32_ts(d1, AT(2), RB(2), IDESC, 1);
-                        mma_tf32_ts(d2, AT(4), RB(3), IDESC, f2);
-                        f2 = 1;
-                        mma_tf32_ts(d2, AT(1), DB(2), IDESC, 1);
-                        mma_tf32_ts(d2, AT(4), DB(1), IDESC, 1);
-                        mma_tf32_ts(d2, AT(5), RB(3), IDESC, 1);
-                        mma_tf32_ts(d2, AT(1), DB(3), IDESC, 1);
-                        mma_tf32_ts(d2, AT(3), DB(2), IDESC, 1);
-                    } else {
-                        // A tiles: 0 a0, 1 a1, 2 a0 lo, 3 a1 lo ; raw B: 2 w ; derived B: 0 w lo, 1 Q = w^2, 2 Q lo
-                        mma_tf32_ts(d1, AT(0), RB(2), IDESC, f1);
-                        f1 = 1;
-                        mma_tf32_ts(d1, AT(0), DB(0), IDESC, 1);
-                        mma_tf32_ts(d1, AT(2), RB(2), IDESC, 1);
-                        mma_tf32_ts(d2, AT(1), DB(1), IDESC, f2);
-                        f2 = 1;
-                        mma_tf32_ts(d2, AT(1), DB(2), IDESC, 1);
-                        mma_tf32_ts(d2, AT(3), DB(1), IDESC, 1);
-                    }
+                // descriptor words of raw B tile 0 (third tile of the raw slot) and derived B tile 0; k step j adds KSTEP
+                constexpr uint32_t LBO = T::B_MN ? 2048 : 16, KSTEP = (T::B_MN ? 1024 : 32) >> 4;
+                constexpr uint32_t HI = desc_hi(512, T::B_MN ? SWZ_128B_BASE32B : SWZ_64B);
+                const uint32_t rbl = desc_lo(rs + 2 * TILE_BYTES, LBO), dsl = desc_lo(ds, LBO);
+                if (chain1) {
+                    mma_kstep_ts<OP == OP_FWD, 1>(d1, d2, at, rbl, dsl, HI, IDESC, f, f);
+                    mma_kstep_ts<OP == OP_FWD, 1>(d1, d2, at + 8, rbl + KSTEP, dsl + KSTEP, HI, IDESC, 1, 1);
+                } else {
+                    mma_kstep_ts<OP == OP_FWD, 2>(d1, d2, at, rbl, dsl, HI, IDESC, f, f);
+                    mma_kstep_ts<OP == OP_FWD, 2>(d1, d2, at + 8, rbl + KSTEP, dsl + KSTEP, HI, IDESC, 1, 1);
                 }
-#undef AT
-#undef RB
-#undef DB
-                mma_commit(raw_empty + r);
-                mma_commit(der_empty + d);
+                f = 1;
+                mma_commit(stage_done + it % L);
                 if (it % chunk_len == chunk_len - 1 || it == nk - 1) mma_commit(acc_full);
             }
         }
@@ -526,7 +506,8 @@ tagi_tc_linear_ts_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_
         for (int it = 0; it < nk && ok; it++) {
             const int r = it % RS, d = it % DS;
             ok = mbar_wait(raw_full + r, (it / RS) & 1, abort_flag, status, ST_TIMEOUT_RAW) &&
-                 mbar_wait(der_empty + d, ((it / DS) & 1) ^ 1, abort_flag, status, ST_TIMEOUT_EMPTY);
+                 (it < DS || mbar_wait(stage_done + (it - DS) % L, ((it - DS) / L) & 1, abort_flag, status,
+                                       ST_TIMEOUT_EMPTY));
             if (!ok) break;
             const uint32_t rs = raw_base + r * NRAW * TILE_BYTES, ds = der_base + d * NDER * TILE_BYTES;
 
@@ -647,6 +628,304 @@ tagi_tc_linear_ts_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_
     }
 }
 
+// =====================================================================================================
+// Variant "pair": as "ts", on CTA pairs (cta_group::2).
+//
+// The ts kernel still asks more of the shared-memory pipe per k-slab (tensor-core reads of B, converter traffic, TMA
+// writes: about 1300 cycles' worth) than the MMAs take (about 1000 cycles), so it runs at the speed of shared memory.
+// Here two CTAs of a cluster share one 256 x bn output tile: each keeps its own 128 rows of A (tensor memory) and of
+// the accumulators, and only HALF of the B rows (bn / 2) in its shared memory; every MMA is one
+// tcgen05.mma.cta_group::2 of 256 x bn x 8 issued by the even CTA, whose tensor cores on both SMs read each B half
+// once. Per CTA that halves the B traffic of TMA, converters and tensor core. Barriers: TMA and ring-slot barriers are
+// per CTA (the MMA's completion is multicast to both); "converted" and "accumulator drained" are counted in the
+// issuing CTA, the other CTA's warps arrive there through the cluster's shared-memory window.
+// =====================================================================================================
+constexpr int HALF_BYTES = TILE_BYTES / 2;  // B half tile: 64 rows x 16 k
+
+template <int OP> struct PairTraits;
+// raw slot: A0 A1 (8 KiB each) then B halves (4 KiB each); derived slot: B halves only
+template <> struct PairTraits<OP_FWD> { static constexpr int NRAW_B = 2, NDER = 4, NA = 6; };
+template <> struct PairTraits<OP_BWD_STATE> { static constexpr int NRAW_B = 1, NDER = 3, NA = 4; };
+template <> struct PairTraits<OP_BWD_PARAM> { static constexpr int NRAW_B = 1, NDER = 3, NA = 4; };
+
+template <int OP, int RS, int DS>
+constexpr size_t pair_smem_bytes() {
+    return (size_t)RS * (2 * TILE_BYTES + PairTraits<OP>::NRAW_B * HALF_BYTES) +
+           (size_t)DS * PairTraits<OP>::NDER * HALF_BYTES + 1024 + 256;
+}
+
+// B half tile: K-major one box of 64 rows; MN-major two boxes of 32 rows
+template <int MN>
+__device__ __forceinline__ void load_half_tile(uint32_t dst, const CUtensorMap *tm, int row0, int k0, uint64_t *bar) {
+    if (MN) {
+#pragma unroll
+        for (int g = 0; g < 2; g++) tma_load_2d(dst + g * 2048, tm, row0 + 32 * g, k0, bar);
+    } else {
+        tma_load_2d(dst, tm, k0, row0, bar);
+    }
+}
+
+template <int OP, int CH, int RS, int DS>
+__global__ void __launch_bounds__(NTHREADS2, 1)
+tagi_tc_linear_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
+                           const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
+                           const TcEpilogue epi, const int kdim, const int bn, int *status) {
+    using T = OpTraits<OP>;
+    using S = PairTraits<OP>;
+    constexpr int NRAW_B = S::NRAW_B, NDER = S::NDER, NA = S::NA;
+    constexpr uint32_t RAW_SLOT = 2 * TILE_BYTES + NRAW_B * HALF_BYTES, DER_SLOT = NDER * HALF_BYTES;
+    constexpr uint32_t NCOLS = 512;
+    // tensor-memory columns: D1 at 0, D2 at acc_stride, A tiles from 2 * acc_stride on (DS slots of NA * 16 columns)
+    constexpr uint32_t acc_stride = (512 - DS * NA * BK) / 2 >= 128 ? 128 : 112;
+    constexpr uint32_t A_COL0 = 2 * acc_stride;
+    const uint32_t IDESC = make_idesc_tf32(256, bn, 0, T::B_MN);
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *aligned = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t raw_base = smem_base, der_base = smem_base + RS * RAW_SLOT;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(aligned + (size_t)RS * RAW_SLOT + (size_t)DS * DER_SLOT);
+    constexpr int L = RS > DS ? RS : DS;  // stage_done ring, as in the one-CTA kernel; completion is multicast to both CTAs
+    uint64_t *raw_full = bars, *stage_done = bars + RS, *conv_done = bars + RS + L;
+    uint64_t *acc_full = bars + RS + L + DS, *acc_empty = acc_full + 1;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 1);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t cta = cluster_ctarank();  // 0 issues the MMAs
+    const int half = bn / 2;
+    const int row0 = blockIdx.y * 256 + (int)cta * 128;          // this CTA's 128 rows of A and of the output
+    const int col0 = (blockIdx.x >> 1) * bn;                      // the pair's columns
+    const int brow0 = col0 + (int)cta * half;                     // this CTA's half of the B rows
+    const int nk = (kdim + BK - 1) / BK;
+    const int chunk_len = CH > 0 ? CH : nk;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < RS; s++) mbar_init(raw_full + s, 1);
+        for (int s = 0; s < L; s++) mbar_init(stage_done + s, 2);  // one commit from each MMA issuer
+        for (int s = 0; s < DS; s++) mbar_init(conv_done + s, 2 * NCONV_WARPS);  // used in CTA 0: both CTAs' warps arrive
+        mbar_init(acc_full, 2);
+        mbar_init(acc_empty, 2 * NCONV_WARPS);          // used in CTA 0 only
+        *abort_flag = 0;
+        mbar_init_fence();
+        prefetch_tmap(&tmA0);
+        prefetch_tmap(&tmA1);
+        prefetch_tmap(&tmB0);
+        if (OP == OP_FWD) prefetch_tmap(&tmB1);
+    }
+    if (warp == 1) tmem_alloc_pair(tmem_slot, NCOLS);
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();  // the peer's barriers exist before anyone arrives on them
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (each CTA for itself)
+        if (lane == 0) {
+            for (int it = 0; it < nk; it++) {
+                const int r = it % RS;
+                if (it >= RS && !mbar_wait(stage_done + (it - RS) % L, ((it - RS) / L) & 1, abort_flag, status,
+                                           ST_TIMEOUT_EMPTY))
+                    break;
+                mbar_arrive_expect_tx(raw_full + r, RAW_SLOT);
+                const uint32_t st = raw_base + r * RAW_SLOT;
+                const int k0 = it * BK;
+                load_tile<T::A_MN>(st, &tmA0, row0, k0, raw_full + r);
+                load_tile<T::A_MN>(st + TILE_BYTES, &tmA1, row0, k0, raw_full + r);
+                load_half_tile<T::B_MN>(st + 2 * TILE_BYTES, &tmB0, brow0, k0, raw_full + r);
+                if (OP == OP_FWD) load_half_tile<T::B_MN>(st + 2 * TILE_BYTES + HALF_BYTES, &tmB1, brow0, k0, raw_full + r);
+            }
+        }
+    } else if (warp == 1 || warp == ISSUER2_WARP) {
+        // ------------------------------------------------------------------ MMA issuers (CTA 0): warp 1 -> D1, warp 10 -> D2
+        if (lane == 0 && cta == 0) {
+            const bool chain1 = warp == 1;
+            const uint32_t d1 = tmem, d2 = tmem + acc_stride;
+            uint32_t f = 0;
+            bool ok = true;
+            for (int it = 0; it < nk && ok; it++) {
+                const int r = it % RS, d = it % DS;
+                if (it > 0 && it % chunk_len == 0) {
+                    const int c = it / chunk_len;
+                    ok = mbar_wait_cluster(acc_empty, (c - 1) & 1, abort_flag, status, ST_TIMEOUT_ACC);
+                    if (!ok) break;
+                    f = 0;
+                }
+                ok = mbar_wait_cluster(conv_done + d, (it / DS) & 1, abort_flag, status, ST_TIMEOUT_CONV);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t rb = raw_base + r * RAW_SLOT + 2 * TILE_BYTES, ds = der_base + d * DER_SLOT;
+                const uint32_t at = tmem + A_COL0 + d * (NA * BK);
+                constexpr uint32_t LBO = T::B_MN ? 2048 : 16, KSTEP = (T::B_MN ? 1024 : 32) >> 4;
+                constexpr uint32_t HI = desc_hi(512, T::B_MN ? SWZ_128B_BASE32B : SWZ_64B);
+                const uint32_t rbl = desc_lo(rb, LBO), dsl = desc_lo(ds, LBO);
+                if (chain1) {
+                    mma_kstep_pair<OP == OP_FWD, 1>(d1, d2, at, rbl, dsl, HI, IDESC, f, f);
+                    mma_kstep_pair<OP == OP_FWD, 1>(d1, d2, at + 8, rbl + KSTEP, dsl + KSTEP, HI, IDESC, 1, 1);
+                } else {
+                    mma_kstep_pair<OP == OP_FWD, 2>(d1, d2, at, rbl, dsl, HI, IDESC, f, f);
+                    mma_kstep_pair<OP == OP_FWD, 2>(d1, d2, at + 8, rbl + KSTEP, dsl + KSTEP, HI, IDESC, 1, 1);
+                }
+                f = 1;
+                mma_commit_pair(stage_done + it % L);  // both CTAs may refill the raw slot and overwrite the derived one
+                if (it % chunk_len == chunk_len - 1 || it == nk - 1) mma_commit_pair(acc_full);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ converters + accumulation + epilogue
+        const int ct = threadIdx.x - 64;
+        const int q = warp & 3;
+        const int h = (warp - 2) >> 2;
+        const int arow = q * 32 + lane;
+        const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16);
+        float sum1[64], sum2[64];
+#pragma unroll
+        for (int i = 0; i < 64; i++) sum1[i] = sum2[i] = 0.f;
+
+        auto drain = [&](int c) -> bool {
+            if (!mbar_wait(acc_full, c & 1, abort_flag, status, ST_TIMEOUT_ACC)) return false;
+            tc_fence_after_sync();
+#pragma unroll
+            for (int blk = 0; blk < 2; blk++) {
+                float v[32];
+                tmem_ld_32x32(lane_addr + h * 64 + blk * 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; i++) sum1[blk * 32 + i] += v[i];
+                tmem_ld_32x32(lane_addr + acc_stride + h * 64 + blk * 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; i++) sum2[blk * 32 + i] += v[i];
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(acc_empty, 0);
+            return true;
+        };
+
+        bool ok = true;
+        int pending = -1;
+        for (int it = 0; it < nk && ok; it++) {
+            const int r = it % RS, d = it % DS;
+            ok = mbar_wait(raw_full + r, (it / RS) & 1, abort_flag, status, ST_TIMEOUT_RAW) &&
+                 (it < DS || mbar_wait(stage_done + (it - DS) % L, ((it - DS) / L) & 1, abort_flag, status,
+                                       ST_TIMEOUT_EMPTY));
+            if (!ok) break;
+            const uint32_t rs = raw_base + r * RAW_SLOT, rb = rs + 2 * TILE_BYTES, ds = der_base + d * DER_SLOT;
+
+            float a0[8], a1[8];
+            if (T::A_MN) {
+                const uint32_t g = rs + q * 2048;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const int k = h * 8 + i;
+                    const uint32_t o = k * 128 + (((lane >> 3) ^ (k & 3)) << 5) + ((lane & 7) << 2);
+                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(a0[i]) : "r"(g + o));
+                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(a1[i]) : "r"(g + TILE_BYTES + o));
+                }
+            } else {
+                const uint32_t rowb = rs + arow * 64, sw = (arow >> 1) & 3;
+                const float4 x0 = lds128(rowb + (((2 * h) ^ sw) << 4)), x1 = lds128(rowb + (((2 * h + 1) ^ sw) << 4));
+                const float4 y0 = lds128(rowb + TILE_BYTES + (((2 * h) ^ sw) << 4));
+                const float4 y1 = lds128(rowb + TILE_BYTES + (((2 * h + 1) ^ sw) << 4));
+                a0[0] = x0.x, a0[1] = x0.y, a0[2] = x0.z, a0[3] = x0.w, a0[4] = x1.x, a0[5] = x1.y, a0[6] = x1.z, a0[7] = x1.w;
+                a1[0] = y0.x, a1[1] = y0.y, a1[2] = y0.z, a1[3] = y0.w, a1[4] = y1.x, a1[5] = y1.y, a1[6] = y1.z, a1[7] = y1.w;
+            }
+            {
+                const uint32_t at = lane_addr + A_COL0 + d * (NA * BK) + h * 8;
+                float t0[8], t1[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) t0[i] = hi_part(a0[i]), t1[i] = hi_part(a1[i]);
+                tmem_st_32x8(at + 0 * BK, t0);
+                tmem_st_32x8(at + 1 * BK, t1);
+#pragma unroll
+                for (int i = 0; i < 8; i++) t0[i] = a0[i] - t0[i], t1[i] = a1[i] - t1[i];
+                tmem_st_32x8(at + 2 * BK, t0);
+                tmem_st_32x8(at + 3 * BK, t1);
+                if (OP == OP_FWD) {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const float sq = fmaf(a0[i], a0[i], a1[i]);
+                        t0[i] = hi_part(sq);
+                        t1[i] = sq - t0[i];
+                    }
+                    tmem_st_32x8(at + 4 * BK, t0);
+                    tmem_st_32x8(at + 5 * BK, t1);
+                }
+            }
+            // B halves: one 16-byte chunk per converter thread
+            {
+                const uint32_t o = ct * 16;
+                if (OP == OP_FWD) {
+                    const float4 b0 = lds128(rb + o), b1 = lds128(rb + HALF_BYTES + o);
+                    const float4 qq = make_float4(b0.x * b0.x, b0.y * b0.y, b0.z * b0.z, b0.w * b0.w);
+                    sts128(ds + 0 * HALF_BYTES + o, lo_part(b0));
+                    sts128(ds + 1 * HALF_BYTES + o, lo_part(b1));
+                    sts128(ds + 2 * HALF_BYTES + o, qq);
+                    sts128(ds + 3 * HALF_BYTES + o, lo_part(qq));
+                } else {
+                    const float4 w = lds128(rb + o);
+                    const float4 qq = make_float4(w.x * w.x, w.y * w.y, w.z * w.z, w.w * w.w);
+                    sts128(ds + 0 * HALF_BYTES + o, lo_part(w));
+                    sts128(ds + 1 * HALF_BYTES + o, qq);
+                    sts128(ds + 2 * HALF_BYTES + o, lo_part(qq));
+                }
+            }
+            fence_proxy_async_smem();
+            tmem_wait_st();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(conv_done + d, 0);
+            if (pending >= 0) {
+                ok = drain(pending);
+                pending = -1;
+            }
+            if (it % chunk_len == chunk_len - 1 || it == nk - 1) pending = it / chunk_len;
+        }
+        if (ok && pending >= 0) ok = drain(pending);
+
+        if (ok) {
+            const int row = row0 + q * 32 + lane;
+            if (row < epi.rows) {
+#pragma unroll
+                for (int i = 0; i < 64; i += 4) {
+                    const int col = col0 + h * 64 + i;
+                    if (h * 64 + i >= bn || col >= epi.cols) break;
+                    const long idx = (long)row * epi.ld + col;
+                    float4 o1 = make_float4(sum1[i], sum1[i + 1], sum1[i + 2], sum1[i + 3]);
+                    float4 o2 = make_float4(sum2[i], sum2[i + 1], sum2[i + 2], sum2[i + 3]);
+                    if (OP == OP_FWD) {
+                        if (epi.aux1) {
+                            const float4 b1 = __ldg(reinterpret_cast<const float4 *>(epi.aux1 + col));
+                            const float4 b2 = __ldg(reinterpret_cast<const float4 *>(epi.aux2 + col));
+                            o1.x += b1.x, o1.y += b1.y, o1.z += b1.z, o1.w += b1.w;
+                            o2.x += b2.x, o2.y += b2.y, o2.z += b2.z, o2.w += b2.w;
+                        }
+                    } else {
+                        const float4 sc = __ldg(reinterpret_cast<const float4 *>(epi.aux1 + idx));
+                        o1.x *= sc.x, o1.y *= sc.y, o1.z *= sc.z, o1.w *= sc.w;
+                        o2.x = o2.x * sc.x * sc.x, o2.y = o2.y * sc.y * sc.y;
+                        o2.z = o2.z * sc.z * sc.z, o2.w = o2.w * sc.w * sc.w;
+                    }
+                    __stcs(reinterpret_cast<float4 *>(epi.out1 + idx), o1);
+                    __stcs(reinterpret_cast<float4 *>(epi.out2 + idx), o2);
+                }
+            }
+        }
+    }
+    __syncwarp();
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();  // neither CTA leaves (or frees tensor memory) while the other may still signal or read it
+    if (warp == 1) {
+        if (*abort_flag) {
+            const long long t0 = clock64();
+            while (clock64() - t0 < 4000000LL) {
+            }
+        }
+        tmem_dealloc_pair(tmem, NCOLS);
+    }
+}
+
 // ------------------------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -666,12 +945,12 @@ EncodeTiledFn encode_fn() {
 
 // Tensor map over a row-major FP32 matrix [outer][inner]. K-major operand tiles: box 16 x 128, 64-byte
 // swizzle; MN-major: box 32 x 16, 128-byte swizzle with 32-byte atoms.
-int make_tmap(CUtensorMap *tm, const float *ptr, uint64_t inner, uint64_t outer, bool mn_major) {
+int make_tmap(CUtensorMap *tm, const float *ptr, uint64_t inner, uint64_t outer, bool mn_major, unsigned kmajor_rows = 128) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail(TAGI_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[2] = {inner, outer};
     cuuint64_t strides[1] = {inner * sizeof(float)};
-    cuuint32_t box[2] = {mn_major ? 32u : (cuuint32_t)BK, mn_major ? (cuuint32_t)BK : 128u};
+    cuuint32_t box[2] = {mn_major ? 32u : (cuuint32_t)BK, mn_major ? (cuuint32_t)BK : (cuuint32_t)kmajor_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(ptr), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -695,7 +974,9 @@ int *status_word() {
 }
 
 int g_deep = 0;     // deeper derived rings where tensor memory allows (diagnostic switch; measured: no gain)
-int g_variant = 1;  // 1: A-side tiles in tensor memory ("ts", default); 0: every operand tile in shared memory ("ss")
+int g_variant = 3;  // 3: CTA pairs (default; passes with < 256 output rows use 1); 1: one CTA, A-side tiles in tensor
+                    // memory ("ts"); 0: every operand tile in shared memory ("ss")
+int g_pair_bn = 0;  // forces the pair kernel's tile width (diagnostic); 0 = chosen per launch
 int g_chunked = 1;  // 1: contraction accumulated in chunks of 256 (default); 0: one accumulation chain (diagnostic)
 
 template <int OP>
@@ -717,7 +998,7 @@ int launch(const CUtensorMap &a0, const CUtensorMap &a1, const CUtensorMap &b0, 
     }
     dim3 grid((epi.cols + bn - 1) / bn, (unsigned)row_tiles);
     cudaError_t e;
-    if (g_variant == 1) {
+    if (g_variant == 1 || g_variant == 3) {
         // ring depths: the backward passes have room for four derived slots; the forward pass for three when the
         // tile is at most 112 columns wide (accumulators then take 2 x 112 tensor-memory columns), else two
 #define TAGI_TS_LAUNCH(CHV, RSV, DSV)                                                                          \
@@ -726,7 +1007,7 @@ int launch(const CUtensorMap &a0, const CUtensorMap &a1, const CUtensorMap &b0, 
         constexpr size_t sm = ts_smem_bytes<OP, RSV, DSV>();                                                     \
         e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);                       \
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");                                       \
-        k<<<grid, NTHREADS, sm, st>>>(a0, a1, b0, b1, epi, kdim, bn, status);                            \
+        k<<<grid, NTHREADS2, sm, st>>>(a0, a1, b0, b1, epi, kdim, bn, status);                            \
     } while (0)
         if (OP == OP_FWD) {
             if (bn <= 112 && g_deep) {
@@ -758,6 +1039,61 @@ int launch(const CUtensorMap &a0, const CUtensorMap &a1, const CUtensorMap &b0, 
     return TAGI_OK;
 }
 
+// CTA-pair variant: grid.x = 2 x column tiles (cluster of two along x), grid.y = 256-row tiles.
+template <int OP>
+int launch_pair(const CUtensorMap &a0, const CUtensorMap &a1, const CUtensorMap &b0, const CUtensorMap &b1,
+                const TcEpilogue &epi, int kdim, cudaStream_t st) {
+    int *status = status_word();
+    if (!status) return fail(TAGI_ERR_CUDA, "cannot allocate the tensor-core status word");
+    const long row_tiles = (epi.rows + 255) / 256;
+    int bn = TN;
+    long best = -1;
+    for (int w = TN; w >= 64; w -= 16) {  // 74 pairs run at a time
+        const long tiles = row_tiles * ((epi.cols + w - 1) / w);
+        const long cost = ((tiles + 73) / 74) * (w + 16);
+        if (best < 0 || cost < best) best = cost, bn = w;
+    }
+    if (g_pair_bn) bn = g_pair_bn;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (unsigned)((epi.cols + bn - 1) / bn), (unsigned)row_tiles);
+    cfg.blockDim = dim3(NTHREADS2);
+    cfg.stream = st;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    cudaError_t e;
+#define TAGI_PAIR_LAUNCH(CHV, RSV, DSV)                                                        \
+    do {                                                                                         \
+        auto k = tagi_tc_linear_pair_kernel<OP, CHV, RSV, DSV>;                                  \
+        constexpr size_t sm = pair_smem_bytes<OP, RSV, DSV>();                                   \
+        cfg.dynamicSmemBytes = sm;                                                               \
+        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);       \
+        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");                       \
+        e = cudaLaunchKernelEx(&cfg, k, a0, a1, b0, b1, epi, kdim, bn, status);                  \
+    } while (0)
+    // ring depths: hand-offs cross two SMs here, so the derived ring is as deep as tensor memory allows (backward:
+    // four slots; forward: three when the accumulators fit 2 x 112 columns, else two)
+    if (OP == OP_FWD) {
+        if (bn <= 112) {
+            if (g_chunked) TAGI_PAIR_LAUNCH(CHUNK_STAGES, 5, 3); else TAGI_PAIR_LAUNCH(0, 5, 3);
+        } else {
+            if (g_chunked) TAGI_PAIR_LAUNCH(CHUNK_STAGES, 5, 2); else TAGI_PAIR_LAUNCH(0, 5, 2);
+        }
+    } else {
+        if (g_chunked) TAGI_PAIR_LAUNCH(CHUNK_STAGES, 6, 4); else TAGI_PAIR_LAUNCH(0, 6, 4);
+    }
+#undef TAGI_PAIR_LAUNCH
+    if (e != cudaSuccess) return cuda_fail(e, "tensor-core Linear pair kernel launch");
+    return TAGI_OK;
+}
+
+// the pair kernel needs at least one full 256-row tile to pay off
+inline bool use_pair(int rows) { return g_variant == 3 && rows >= 256; }
+
 }  // namespace
 
 // Shapes the tensor-core path takes: 16-byte aligned tensors, every dimension a multiple of 4 (TMA pitches
@@ -771,7 +1107,14 @@ bool linear_tc_supported(int B, int K, int N, std::initializer_list<const void *
 bool linear_tc_profitable(int B, int K, int N) { return B >= 128 && K >= 128 && N >= 128; }
 
 int linear_tc_set_variant(int v) {
-    if (v < 0 || v > 2) return fail(TAGI_ERR_INVALID_ARGUMENT, "variant must be 0 (ss), 1 (ts) or 2 (ts, deeper rings)");
+    if (v < 0 || (v > 3 && v < 64) || v > 128 || (v >= 64 && v % 16))
+        return fail(TAGI_ERR_INVALID_ARGUMENT, "variant must be 0 (ss), 1 (ts), 2 (ts, deeper rings) or 3 (CTA pairs)");
+    if (v >= 64) {  // 64, 80, ..., 128: CTA pairs with this tile width (diagnostic)
+        g_pair_bn = v;
+        v = 3;
+    } else {
+        g_pair_bn = 0;
+    }
     g_deep = v == 2;
     if (v == 2) v = 1;
     g_variant = v;
@@ -797,9 +1140,11 @@ int linear_fwd_tc(const float *mu_w, const float *var_w, const float *mu_b, cons
     int rc;
     if ((rc = make_tmap(&a0, mu_a, K, B, false))) return rc;
     if ((rc = make_tmap(&a1, var_a, K, B, false))) return rc;
-    if ((rc = make_tmap(&b0, mu_w, K, N, false))) return rc;
-    if ((rc = make_tmap(&b1, var_w, K, N, false))) return rc;
+    const bool pair = use_pair(B);
+    if ((rc = make_tmap(&b0, mu_w, K, N, false, pair ? 64 : 128))) return rc;
+    if ((rc = make_tmap(&b1, var_w, K, N, false, pair ? 64 : 128))) return rc;
     TcEpilogue epi{mu_z, var_z, mu_b, var_b, (long)N, B, N};
+    if (pair) return launch_pair<OP_FWD>(a0, a1, b0, b1, epi, K, st);
     return launch<OP_FWD>(a0, a1, b0, b1, epi, K, st);
 }
 
@@ -812,6 +1157,7 @@ int linear_bwd_state_tc(const float *mu_w, const float *jcb, const float *dmu_z,
     if ((rc = make_tmap(&a1, dvar_z, N, B, false))) return rc;
     if ((rc = make_tmap(&b0, mu_w, K, N, true))) return rc;
     TcEpilogue epi{dmu_a, dvar_a, jcb, nullptr, (long)K, B, K};
+    if (use_pair(B)) return launch_pair<OP_BWD_STATE>(a0, a1, b0, b0, epi, N, st);
     return launch<OP_BWD_STATE>(a0, a1, b0, b0, epi, N, st);
 }
 
@@ -824,6 +1170,7 @@ int linear_bwd_param_tc(const float *var_w, const float *mu_a, const float *dmu_
     if ((rc = make_tmap(&a1, dvar_z, N, B, true))) return rc;
     if ((rc = make_tmap(&b0, mu_a, K, B, true))) return rc;
     TcEpilogue epi{dmu_w, dvar_w, var_w, nullptr, (long)K, N, K};
+    if (use_pair(N)) return launch_pair<OP_BWD_PARAM>(a0, a1, b0, b0, epi, B, st);
     return launch<OP_BWD_PARAM>(a0, a1, b0, b0, epi, B, st);
 }
 

@@ -45,6 +45,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Non-blocking test: for the single producer / issuer threads, whose wake-up latency paces the pipeline
+// (try_wait may park the thread for a while before it looks again).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 // Status codes written to the device status word when a wait runs out.
 enum { ST_OK = 0, ST_TIMEOUT_EMPTY = 1, ST_TIMEOUT_RAW = 2, ST_TIMEOUT_CONV = 3, ST_TIMEOUT_ACC = 4 };
 
@@ -58,6 +72,23 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
         if (mbar_try_wait(bar, parity)) return true;
         // the abort flag lives in shared memory: look at it rarely so that polling does not eat LSU bandwidth
         if ((spin & 255u) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > 2000000000LL) {
+                *abort_flag = 1;
+                atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+// Same bounded wait, spinning on test_wait (lowest wake-up latency; use from single threads only).
+__device__ __forceinline__ bool mbar_spin(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
+    if (mbar_test_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t spin = 1;; spin++) {
+        if (mbar_test_wait(bar, parity)) return true;
+        if ((spin & 1023u) == 0) {
             if (*abort_flag) return false;
             if (clock64() - t0 > 2000000000LL) {
                 *abort_flag = 1;
@@ -173,6 +204,147 @@ __device__ __forceinline__ void mma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, ui
 __device__ __forceinline__ void mma_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                  : "memory");
+}
+
+// ----------------------------------------------------------------------------- CTA pairs (cta_group::2)
+// Two CTAs of a cluster drive one tensor-core instruction of 256 rows: each holds 128 rows of A / D in its own tensor
+// memory and half of B's rows in its own shared memory. One thread of the even CTA issues; completion is signalled to
+// barriers in both CTAs.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// arrive on the barrier at the same shared-memory offset in CTA `cta` of the cluster (release at cluster scope)
+__device__ __forceinline__ void mbar_arrive_cluster(uint64_t *bar, uint32_t cta) {
+    asm volatile(
+        "{\n\t.reg .b32 ra;\n\t"
+        "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
+        "mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [ra];\n\t}"
+        ::"r"(smem_u32(bar)), "r"(cta)
+        : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.relaxed.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// bounded wait with cluster-scope acquire (the arrivals come from both CTAs of the pair)
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status,
+                                                  int code) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t spin = 1;; spin++) {
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+        if ((spin & 255u) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > 2000000000LL) {
+                *abort_flag = 1;
+                atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t *smem_slot, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)),
+                 "r"(ncols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// D[tmem, both CTAs] (+)= A[tmem, both CTAs] * B[smem halves of both CTAs]; M = 256
+__device__ __forceinline__ void mma_tf32_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// completion of every MMA issued so far -> arrive on the barrier at this offset in both CTAs of the pair
+__device__ __forceinline__ void mma_commit_pair(uint64_t *bar) {
+    const uint16_t mask = 3;
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(smem_u32(bar)), "h"(mask)
+        : "memory");
+}
+
+// ----------------------------------------------------------------------------- batched MMA issue
+// The thread that issues the MMAs is the pacemaker of the whole CTA: measured on the B200, building every
+// descriptor in C++ and issuing the MMAs one asm statement at a time cost ~90 cycles per MMA of issue time against
+// 56 cycles of tensor-core time. The groups below issue all MMAs of one 8-wide k step in a single asm block: the
+// high descriptor word is constant, the low word is a base plus a literal tile offset, the predicates are set once.
+//   at   : tensor-memory address of A tile 0 for this k step (tile i is 16 columns further)
+//   rbl  : low descriptor word of raw B tile 0 for this k step, dsl: of derived B tile 0; tile i is BS units of 16 bytes on
+//   hi   : high descriptor word (stride offset, version, swizzle)
+//   f1/f2: 0 -> the first MMA into D1 / D2 overwrites (start of an accumulation chunk), else accumulates
+#define TAGI_STR_(x) #x
+#define TAGI_STR(x) TAGI_STR_(x)
+#define TAGI_MMA_HEAD                                             \
+    "{\n\t.reg .pred p1, p2, pt;\n\t.reg .b32 ta, tb;\n\t.reg .b64 db;\n\t" \
+    "setp.ne.b32 p1, %7, 0;\n\tsetp.ne.b32 p2, %8, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
+// one MMA: D operand index, A tile, B base operand index (3 = raw, 4 = derived), B tile, predicate
+#define TAGI_MMA(CG, D, AT, BB, BT, BS, P)                                          \
+    "add.u32 ta, %2, " TAGI_STR(AT) " * 16;\n\t"                                    \
+    "add.u32 tb, %" #BB ", " TAGI_STR(BT) " * " TAGI_STR(BS) ";\n\t"                \
+    "mov.b64 db, {tb, %5};\n\t"                                                     \
+    "tcgen05.mma.cta_group::" #CG ".kind::tf32 [%" #D "], [ta], db, %6, " #P ";\n\t"
+#define TAGI_MMA_OPERANDS \
+    ::"r"(d1), "r"(d2), "r"(at), "r"(rbl), "r"(dsl), "r"(hi), "r"(idesc), "r"(f1), "r"(f2) : "memory"
+
+// Measured on the B200: one thread issues at most one tcgen05.mma per ~50-56 cycles whatever the MMA's size, and two
+// warps issue concurrently at twice that rate. A 128 x 112 x 8 MMA takes 56 tensor-core cycles, so a single issuing
+// thread has no slack for anything else; the MMAs are therefore split by accumulator between two issuing warps
+// (chain 1 = everything that accumulates into D1, chain 2 = D2), which also means no accumulator is shared between
+// issuers and no ordering between them is needed.
+// forward: A tiles 0 mu_a, 1 var_a, 2 mu_a lo, 3 var_a lo, 4 S, 5 S lo ; raw B 0 mu_w, 1 var_w ; derived B 0 mu_w lo,
+// 1 var_w lo, 2 Q, 3 Q lo.  D1 = mu_a.mu_w ; D2 = S.var_w + var_a.Q, each as hi*hi + hi*lo + lo*hi
+#define TAGI_MMA_D1(CG, BS) \
+    TAGI_MMA_HEAD TAGI_MMA(CG, 0, 0, 3, 0, BS, p1) TAGI_MMA(CG, 0, 0, 4, 0, BS, pt) TAGI_MMA(CG, 0, 2, 3, 0, BS, pt) "}"
+#define TAGI_MMA_FWD_D2(CG, BS)                                                                                   \
+    TAGI_MMA_HEAD TAGI_MMA(CG, 1, 4, 3, 1, BS, p2) TAGI_MMA(CG, 1, 1, 4, 2, BS, pt) TAGI_MMA(CG, 1, 4, 4, 1, BS, pt) \
+        TAGI_MMA(CG, 1, 5, 3, 1, BS, pt) TAGI_MMA(CG, 1, 1, 4, 3, BS, pt) TAGI_MMA(CG, 1, 3, 4, 2, BS, pt) "}"
+// backward: A tiles 0 a0, 1 a1, 2 a0 lo, 3 a1 lo ; raw B 0 w ; derived B 0 w lo, 1 Q = w^2, 2 Q lo.  D1 = a0.w (same
+// three MMAs as the forward D1) ; D2 = a1.Q
+#define TAGI_MMA_BWD_D2(CG, BS) \
+    TAGI_MMA_HEAD TAGI_MMA(CG, 1, 1, 4, 1, BS, p2) TAGI_MMA(CG, 1, 1, 4, 2, BS, pt) TAGI_MMA(CG, 1, 3, 4, 1, BS, pt) "}"
+
+// CHAIN 1 or 2; BS = 512: B tiles of 8 KiB (one CTA); BS = 256: B half tiles of 4 KiB (CTA pairs, cta_group::2)
+template <bool FWD, int CHAIN>
+__device__ __forceinline__ void mma_kstep_ts(uint32_t d1, uint32_t d2, uint32_t at, uint32_t rbl, uint32_t dsl, uint32_t hi,
+                                             uint32_t idesc, uint32_t f1, uint32_t f2) {
+    if (CHAIN == 1) asm volatile(TAGI_MMA_D1(1, 512) TAGI_MMA_OPERANDS);
+    else if (FWD) asm volatile(TAGI_MMA_FWD_D2(1, 512) TAGI_MMA_OPERANDS);
+    else asm volatile(TAGI_MMA_BWD_D2(1, 512) TAGI_MMA_OPERANDS);
+}
+template <bool FWD, int CHAIN>
+__device__ __forceinline__ void mma_kstep_pair(uint32_t d1, uint32_t d2, uint32_t at, uint32_t rbl, uint32_t dsl,
+                                               uint32_t hi, uint32_t idesc, uint32_t f1, uint32_t f2) {
+    if (CHAIN == 1) asm volatile(TAGI_MMA_D1(2, 256) TAGI_MMA_OPERANDS);
+    else if (FWD) asm volatile(TAGI_MMA_FWD_D2(2, 256) TAGI_MMA_OPERANDS);
+    else asm volatile(TAGI_MMA_BWD_D2(2, 256) TAGI_MMA_OPERANDS);
+}
+// low / high 32-bit words of a shared-memory matrix descriptor (see make_smem_desc)
+__device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+    return ((smem_addr >> 4) & 0x3fffu) | ((lbo_bytes >> 4) << 16);
+}
+__host__ __device__ constexpr uint32_t desc_hi(uint32_t sbo_bytes, uint32_t swizzle) {
+    return ((sbo_bytes >> 4) & 0x3fffu) | (1u << 14) | (swizzle << 29);
 }
 
 }  // namespace ptx

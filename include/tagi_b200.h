@@ -52,9 +52,11 @@ int tagi_tc_status(int *status, int reset);
  * chunks of 256 that are summed in FP32 registers, which keeps the tensor core's accumulation error far below the
  * 1e-5 / 1e-4 tolerance. on == 0: one accumulation chain over the whole contraction (less accurate; for measurement). */
 int tagi_tc_set_chunked(int on);
-/* Diagnostic switch of the TF32X3 kernels. 1 (default): the A-side operand tiles are kept in tensor memory; 0: every
- * operand tile is kept in shared memory (the simpler kernel, bound by shared-memory bandwidth); 2: as 1 with deeper
- * rings of derived tiles. Same results in all three. */
+/* Diagnostic switch of the TF32X3 kernels. 3 (default): CTA pairs (tcgen05 cta_group::2, 256-row tiles, A-side operand
+ * tiles in tensor memory, each CTA stages half of the B rows; passes with fewer than 256 output rows use variant 1);
+ * 1: one CTA per 128-row tile, A-side tiles in tensor memory; 2: as 1 with deeper rings of derived tiles; 0: every
+ * operand tile in shared memory (the simplest kernel, bound by shared-memory bandwidth); 64, 80, 96, 112 or 128: as 3
+ * with that tile width. Same results in all of them. */
 int tagi_tc_set_variant(int v);
 
 const char *tagi_last_error_string(void);

@@ -174,6 +174,43 @@ def test_ffma_path(G, oracle, force_impl, B, K, N):
     _run_all(G, oracle, G.linear_inputs(rng, B, K, N), tag="ffma ")
 
 
+PAIR_SHAPES = [(256, 64, 128), (260, 200, 260), (512, 2048, 512), (300, 516, 1000), (1024, 256, 112), (256, 4096, 256)]
+
+
+@pytest.mark.parametrize("B,K,N", PAIR_SHAPES)
+def test_tensor_core_cta_pair_variant(G, oracle, force_impl, B, K, N):
+    """tagi_tc_set_variant(3): the same kernels on CTA pairs (tcgen05 cta_group::2, 256-row tiles, each CTA staging
+    half of the B rows). Passes that have fewer than 256 output rows fall back to the one-CTA kernel."""
+    from cutagi_b200 import capi
+    from cutagi_b200.capi import lib
+    force_impl(capi.IMPL_TF32X3)
+    lib.tagi_tc_set_variant(3)
+    try:
+        capi.tc_status()
+        rng = np.random.default_rng(B * 5 + K * 3 + N)
+        _run_all(G, oracle, G.linear_inputs(rng, B, K, N), tag="pair ")
+        assert capi.tc_status() == 0, "a bounded device-side wait ran out"
+    finally:
+        lib.tagi_tc_set_variant(3)
+
+
+@pytest.mark.parametrize("variant", [0, 1])
+def test_tensor_core_one_cta_variants(G, oracle, force_impl, variant):
+    """The one-CTA kernels (1: A tiles in tensor memory, 0: every tile in shared memory) at shapes where the default
+    would use CTA pairs."""
+    from cutagi_b200 import capi
+    from cutagi_b200.capi import lib
+    force_impl(capi.IMPL_TF32X3)
+    lib.tagi_tc_set_variant(variant)
+    try:
+        rng = np.random.default_rng(21)
+        _run_all(G, oracle, G.linear_inputs(rng, 260, 516, 132), tag="one-cta ")
+        _run_all(G, oracle, G.linear_inputs(rng, 512, 1024, 384), tag="one-cta ")
+        assert capi.tc_status() == 0
+    finally:
+        lib.tagi_tc_set_variant(3)
+
+
 def test_tensor_core_rejects_unaligned(G, force_impl):
     import torch
     from cutagi_b200 import capi
