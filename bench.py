@@ -322,8 +322,13 @@ def run_b200(args, rank, world, local_rank):
         peak, bound = FP32_NOMINAL_TFLOPS, "fp32"
         peak_note = ("FP32 FFMA path: 148 SMs x 128 lanes x 2 x 1.965 GHz, of nominal "
                      "(MEASURED_PEAKS.json holds no FP32 figure)")
+    # DRAM traffic of one launch of each kernel, from the ncu capture summarised in
+    # profiles/tagi_tc_linear_pair_kernel_b1024_4096.md (dram__bytes_read.sum + dram__bytes_write.sum); the FFMA kernels
+    # have not been captured
+    ncu_traffic = {"tagi_linear_fwd": 327.9e6, "tagi_linear_bwd_state": 202.6e6, "tagi_linear_bwd_param": 219.9e6}
     roofline = {"bound": bound, "kernel": dom, "achieved": achieved, "peak": peak, "unit": UNIT,
-                "frac": achieved / peak, "traffic": None, "peak_note": peak_note,
+                "frac": achieved / peak, "traffic": ncu_traffic[dom] if impl == IMPL_TF32X3 else None,
+                "traffic_unit": "bytes per launch (ncu, dram read + write)", "peak_note": peak_note,
                 "per_kernel_ms": kt,
                 "per_kernel_tflops": {k_: flops[k_] / (v * 1e-3) / 1e12 for k_, v in kt.items()}}
 
