@@ -360,6 +360,68 @@ def run_b200(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+# Conv2d layer shapes of the CIFAR-shaped CNN (batch 128) and of the ResNet-18 configuration (batch 64, 224x224)
+CONV_LAYERS = [
+    ("CNN conv1", dict(B=128, fi=3, hi=32, wi=32, fo=32, k=3, stride=1, pad=1, pad_type=1, has_bias=1)),
+    ("CNN conv2", dict(B=128, fi=32, hi=16, wi=16, fo=64, k=3, stride=1, pad=1, pad_type=1, has_bias=1)),
+    ("CNN conv3", dict(B=128, fi=64, hi=8, wi=8, fo=128, k=3, stride=1, pad=1, pad_type=1, has_bias=1)),
+    ("ResNet-18 stem", dict(B=64, fi=3, hi=224, wi=224, fo=64, k=6, stride=2, pad=2, pad_type=1, has_bias=0)),
+    ("ResNet-18 layer1", dict(B=64, fi=64, hi=56, wi=56, fo=64, k=3, stride=1, pad=1, pad_type=1, has_bias=0)),
+    ("ResNet-18 down-sampling", dict(B=64, fi=64, hi=56, wi=56, fo=128, k=3, stride=2, pad=1, pad_type=2, has_bias=0)),
+    ("ResNet-18 shortcut", dict(B=64, fi=64, hi=56, wi=56, fo=128, k=2, stride=2, pad=0, pad_type=0, has_bias=0)),
+    ("ResNet-18 layer2", dict(B=64, fi=128, hi=28, wi=28, fo=128, k=3, stride=1, pad=1, pad_type=1, has_bias=0)),
+    ("ResNet-18 layer3", dict(B=64, fi=256, hi=14, wi=14, fo=256, k=3, stride=1, pad=1, pad_type=1, has_bias=0)),
+    ("ResNet-18 layer4", dict(B=64, fi=512, hi=7, wi=7, fo=512, k=3, stride=1, pad=1, pad_type=1, has_bias=0)),
+]
+
+
+def run_conv_layers(args):
+    """Side table, not the benchmark line: CUDA-event time of each Conv2d entry point per layer shape, inputs resident
+    in HBM, seeded synthetic tensors. P = B*ho*wo*fo*fi*k*k multiply-adds per product; algorithmic FLOP: forward 6P,
+    state backward 4P, parameter backward 4P."""
+    import ctypes as C
+    import torch
+    import gpu_util as G
+    from cutagi_b200 import capi
+    from cutagi_b200.capi import lib
+    from oracle_lib import ConvGeom
+    lib.tagi_set_impl({"auto": capi.IMPL_AUTO, "ffma": capi.IMPL_FFMA, "tf32x3": capi.IMPL_TF32X3}[args.kernel_impl])
+    torch.manual_seed(0)
+    P = lambda t: t.data_ptr()
+
+    def timed(fn, n):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    print("| layer (B, fi -> fo, image, k, stride) | P | forward | state backward | parameter backward |")
+    print("|---|---|---|---|---|")
+    for name, kw in CONV_LAYERS:
+        g = ConvGeom(**kw)
+        n_in, n_out, nw = g.B * g.n_in, g.B * g.n_out, g.fo * g.Kc
+        t = lambda n: torch.rand(n, device="cuda") * 0.1 + 0.01
+        mw, vw, mb, vb, ma, va, j, dm, dv = t(nw), t(nw), t(g.fo), t(g.fo), t(n_in), t(n_in), t(n_in), t(n_out), t(n_out)
+        mz, vz, da, dva, dw, dvw, db, dvb = t(n_out), t(n_out), t(n_in), t(n_in), t(nw), t(nw), t(g.fo), t(g.fo)
+        cg = G.cgeom(g)
+        tf = timed(lambda: lib.tagi_conv2d_fwd(C.byref(cg), P(mw), P(vw), P(mb), P(vb), P(ma), P(va), P(mz), P(vz),
+                                               None), args.steps)
+        ts = timed(lambda: lib.tagi_conv2d_bwd_state(C.byref(cg), P(mw), P(j), P(dm), P(dv), P(da), P(dva), None),
+                   args.steps)
+        tp = timed(lambda: lib.tagi_conv2d_bwd_param(C.byref(cg), P(vw), P(vb), P(ma), P(dm), P(dv), P(dw), P(dvw),
+                                                     P(db), P(dvb), None), args.steps)
+        pm = g.B * g.ho * g.wo * g.fo * g.Kc
+        print(f"| {name} ({g.B}, {g.fi} -> {g.fo}, {g.hi}x{g.wi}, k{g.k} s{g.stride}) | {pm:.2e} | "
+              f"{tf:.3f} ms, {6 * pm / tf / 1e9:.1f} TF/s | {ts:.3f} ms, {4 * pm / ts / 1e9:.1f} | "
+              f"{tp:.3f} ms, {4 * pm / tp / 1e9:.1f} |")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -371,8 +433,13 @@ def main():
                     help="for captures under ncu: one warm-up step, no end-to-end and no CPU leg (numbers printed "
                          "in this mode are not benchmark values)")
     ap.add_argument("--kernel-impl", default="auto", choices=["auto", "ffma", "tf32x3"],
-                    help="arithmetic of the Linear kernels (tagi_set_impl)")
+                    help="arithmetic of the kernels (tagi_set_impl)")
+    ap.add_argument("--conv-layers", action="store_true",
+                    help="print a per-layer timing table of the Conv2d entry points instead of the benchmark line")
     args = ap.parse_args()
+    if args.conv_layers:
+        args.steps = min(args.steps, 20)
+        return run_conv_layers(args)
     if args.profile:
         args.warmup, args.no_cpu = 1, True
     else:

@@ -165,6 +165,21 @@ int tagi_conv2d_out_size(int k, int stride, int wi, int hi, int pad, int pad_typ
     return TAGI_OK;
 }
 
+// true -> run Conv2d on the tensor-core kernels; sets rc when the forced implementation cannot take the layer
+static bool pick_conv_tc(const char *who, const tagi_conv2d_geom &g, std::initializer_list<const void *> ptrs, int *rc) {
+    *rc = TAGI_OK;
+    const int impl = current_impl();
+    if (impl == TAGI_IMPL_FFMA) return false;
+    const bool ok = conv_tc_supported(g, ptrs);
+    if (impl == TAGI_IMPL_TF32X3) {
+        if (!ok)
+            *rc = fail(TAGI_ERR_UNSUPPORTED, std::string(who) + ": TF32X3 needs 16-byte aligned tensors and fi, fo, "
+                                                               "fi*k*k, B*ho*wo and B*hi*wi that are multiples of 4");
+        return ok;
+    }
+    return ok && conv_tc_profitable(g);
+}
+
 static int check_geom(const tagi_conv2d_geom *g) {
     TAGI_REQUIRE(g != nullptr, "null geometry");
     TAGI_REQUIRE(g->B > 0 && g->fi > 0 && g->fo > 0, "B, fi and fo must be positive");
@@ -196,7 +211,11 @@ int tagi_conv2d_fwd(const tagi_conv2d_geom *g, const float *mu_w, const float *v
     } else {
         mu_b = var_b = nullptr;
     }
-    return conv2d_fwd_ffma(*g, mu_w, var_w, mu_b, var_b, mu_a, var_a, mu_z, var_z, static_cast<cudaStream_t>(stream));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (pick_conv_tc(__func__, *g, {mu_w, var_w, mu_b, var_b, mu_a, var_a, mu_z, var_z}, &rc))
+        return conv2d_fwd_tc(*g, mu_w, var_w, mu_b, var_b, mu_a, var_a, mu_z, var_z, st);
+    if (rc != TAGI_OK) return rc;
+    return conv2d_fwd_ffma(*g, mu_w, var_w, mu_b, var_b, mu_a, var_a, mu_z, var_z, st);
 }
 
 int tagi_conv2d_bwd_state(const tagi_conv2d_geom *g, const float *mu_w, const float *jcb, const float *dmu_z,
@@ -209,7 +228,11 @@ int tagi_conv2d_bwd_state(const tagi_conv2d_geom *g, const float *mu_w, const fl
     TAGI_PTR(dvar_z);
     TAGI_PTR(dmu_a);
     TAGI_PTR(dvar_a);
-    return conv2d_bwd_state_ffma(*g, mu_w, jcb, dmu_z, dvar_z, dmu_a, dvar_a, static_cast<cudaStream_t>(stream));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (pick_conv_tc(__func__, *g, {mu_w, jcb, dmu_z, dvar_z, dmu_a, dvar_a}, &rc))
+        return conv2d_bwd_state_tc(*g, mu_w, jcb, dmu_z, dvar_z, dmu_a, dvar_a, st);
+    if (rc != TAGI_OK) return rc;
+    return conv2d_bwd_state_ffma(*g, mu_w, jcb, dmu_z, dvar_z, dmu_a, dvar_a, st);
 }
 
 int tagi_conv2d_bwd_param(const tagi_conv2d_geom *g, const float *var_w, const float *var_b, const float *mu_a,
@@ -228,8 +251,14 @@ int tagi_conv2d_bwd_param(const tagi_conv2d_geom *g, const float *var_w, const f
         TAGI_PTR(dmu_b);
         TAGI_PTR(dvar_b);
     }
-    return conv2d_bwd_param_ffma(*g, var_w, var_b, mu_a, dmu_z, dvar_z, dmu_w, dvar_w, dmu_b, dvar_b,
-                                 static_cast<cudaStream_t>(stream));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (pick_conv_tc(__func__, *g, {var_w, mu_a, dmu_z, dvar_z, dmu_w, dvar_w}, &rc)) {
+        rc = conv2d_bwd_param_tc(*g, var_w, mu_a, dmu_z, dvar_z, dmu_w, dvar_w, st);
+        if (rc == TAGI_OK && g->has_bias) rc = conv_bias_delta(*g, var_b, dmu_z, dvar_z, dmu_b, dvar_b, st);
+        return rc;
+    }
+    if (rc != TAGI_OK) return rc;
+    return conv2d_bwd_param_ffma(*g, var_w, var_b, mu_a, dmu_z, dvar_z, dmu_w, dvar_w, dmu_b, dvar_b, st);
 }
 
 int tagi_conv2d_bwd_param_noalloc(const tagi_conv2d_geom *g, const float *var_w, const float *var_b, const float *mu_a,

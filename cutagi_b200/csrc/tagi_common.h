@@ -50,11 +50,13 @@ int linear_tc_set_chunked(int on);
 int linear_tc_set_variant(int v);
 int linear_tc_status(int *out, int reset);
 int linear_fwd_tc(const float *mu_w, const float *var_w, const float *mu_b, const float *var_b, const float *mu_a,
-                  const float *var_a, int B, int K, int N, float *mu_z, float *var_z, cudaStream_t st);
+                  const float *var_a, int B, int K, int N, float *mu_z, float *var_z, cudaStream_t st, int npix = 0);
 int linear_bwd_state_tc(const float *mu_w, const float *jcb, const float *dmu_z, const float *dvar_z, int B, int K,
-                        int N, float *dmu_a, float *dvar_a, cudaStream_t st);
+                        int N, float *dmu_a, float *dvar_a, cudaStream_t st, int npix = 0);
+// npix > 0: the rows are (image, pixel) pairs and outputs / the Jacobian are laid out [image][channel][pixel] (Conv2d)
 int linear_bwd_param_tc(const float *var_w, const float *mu_a, const float *dmu_z, const float *dvar_z, int B, int K,
-                        int N, float *dmu_w, float *dvar_w, cudaStream_t st);
+                        int N, float *dmu_w, float *dvar_w, cudaStream_t st, float *split_ws = nullptr, int slices = 1);
+int linear_bwd_param_tc_slices(int B, int K, int N);
 
 // Conv2d on the FFMA engine (tagi_conv_ffma.cu)
 int conv2d_fwd_ffma(const tagi_conv2d_geom &g, const float *mu_w, const float *var_w, const float *mu_b,
@@ -65,6 +67,19 @@ int conv2d_bwd_state_ffma(const tagi_conv2d_geom &g, const float *mu_w, const fl
 int conv2d_bwd_param_ffma(const tagi_conv2d_geom &g, const float *var_w, const float *var_b, const float *mu_a,
                           const float *dmu_z, const float *dvar_z, float *dmu_w, float *dvar_w, float *dmu_b,
                           float *dvar_b, cudaStream_t st);
+int conv_scratch(size_t bytes, float **out);  // library-owned, grow-only, per device
+int conv_bias_delta(const tagi_conv2d_geom &g, const float *var_b, const float *dmu_z, const float *dvar_z,
+                    float *dmu_b, float *dvar_b, cudaStream_t st);
+// Conv2d on the tensor-core Linear kernels (tagi_conv_tc.cu)
+bool conv_tc_supported(const tagi_conv2d_geom &g, std::initializer_list<const void *> ptrs);
+bool conv_tc_profitable(const tagi_conv2d_geom &g);
+int conv2d_fwd_tc(const tagi_conv2d_geom &g, const float *mu_w, const float *var_w, const float *mu_b,
+                  const float *var_b, const float *mu_a, const float *var_a, float *mu_z, float *var_z,
+                  cudaStream_t st);
+int conv2d_bwd_state_tc(const tagi_conv2d_geom &g, const float *mu_w, const float *jcb, const float *dmu_z,
+                        const float *dvar_z, float *dmu_a, float *dvar_a, cudaStream_t st);
+int conv2d_bwd_param_tc(const tagi_conv2d_geom &g, const float *var_w, const float *mu_a, const float *dmu_z,
+                        const float *dvar_z, float *dmu_w, float *dvar_w, cudaStream_t st);
 int conv2d_bwd_param_noalloc(const tagi_conv2d_geom &g, const float *var_w, const float *var_b, const float *mu_a,
                              const float *dmu_z, const float *dvar_z, float *dmu_w, float *dvar_w, float *dmu_b,
                              float *dvar_b, cudaStream_t st);

@@ -302,9 +302,9 @@ int conv2d_bwd_state_ffma(const tagi_conv2d_geom &cg, const float *mu_w, const f
                 "conv2d state backward launch");
 }
 
-// Scratch for the split-K partial sums of the parameter pass: one grow-only buffer per device, owned by
-// the library. Calls that use it are ordered by the stream they run on; calls on different streams of
-// one device that both need scratch must not overlap.
+// Scratch of the Conv2d implementations (split-contraction partial sums here, gathered matrices in the tensor-core
+// path): one grow-only buffer per device, owned by the library. Calls that use it are ordered by the stream they
+// run on; calls on different streams of one device that both need scratch must not overlap.
 namespace {
 struct Scratch {
     float *ptr = nullptr;
@@ -313,7 +313,15 @@ struct Scratch {
 Scratch g_scratch[64];
 std::mutex g_scratch_mu;
 
-int get_scratch(size_t bytes, float **out) {
+}  // namespace
+
+int conv_bias_delta(const tagi_conv2d_geom &cg, const float *var_b, const float *dmu_z, const float *dvar_z,
+                    float *dmu_b, float *dvar_b, cudaStream_t st) {
+    conv_bias_delta_kernel<<<cg.fo, 256, 0, st>>>(var_b, dmu_z, dvar_z, cg.B, cg.fo, cg.ho * cg.wo, dmu_b, dvar_b);
+    return done(cudaGetLastError(), "conv_bias_delta_kernel launch");
+}
+
+int conv_scratch(size_t bytes, float **out) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
@@ -336,7 +344,6 @@ int get_scratch(size_t bytes, float **out) {
     *out = s.ptr;
     return TAGI_OK;
 }
-}  // namespace
 
 int conv2d_bwd_param_ffma(const tagi_conv2d_geom &cg, const float *var_w, const float *var_b, const float *mu_a,
                           const float *dmu_z, const float *dvar_z, float *dmu_w, float *dvar_w, float *dmu_b,
@@ -366,7 +373,7 @@ int conv2d_bwd_param_ffma(const tagi_conv2d_geom &cg, const float *var_w, const 
     } else {
         const long slice = (long)M * N;
         float *ws = nullptr;
-        rc = get_scratch((size_t)2 * splits * slice * sizeof(float), &ws);
+        rc = conv_scratch((size_t)2 * splits * slice * sizeof(float), &ws);
         if (rc != TAGI_OK) return rc;
         EpiPartial epi{ws, ws + (long)splits * slice, (long)N, slice, N % 4 == 0};
         // the kernel may use fewer slices than asked for (slice length is rounded up); it reports through the grid,

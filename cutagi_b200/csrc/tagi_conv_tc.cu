@@ -1,0 +1,243 @@
+// TAGI Conv2d on the tensor-core Linear kernels.
+//
+// Each pass is a gather kernel that lays the receptive fields out as a matrix in scratch memory, followed by the
+// same tcgen05 3xTF32 kernel that Linear uses (tagi_linear_tc.cu), whose epilogue can write the [image][channel][pixel]
+// layout directly:
+//   forward         X = im2col(mu_a), im2col(var_a)  [(b, oy, ox)][ci*k*k]      -> Linear forward with the conv weights
+//   state backward  stride 1: Z = gather(dmu_z), gather(dvar_z) [(b, y, x)][(co, ky, kx)] -> Linear state pass with the
+//                   weights regrouped as [(co, ky, kx)][ci]
+//                   stride > 1 (most entries of Z would be zeros): C = D W, D = deltas regrouped as [(b, p)][co], written
+//                   as [b][(ci, ky, kx)][p], then each input pixel sums the taps that reach it and applies the Jacobian
+//   parameter bwd   X = im2col(mu_a), D = deltas regrouped as [(b, p)][co]     -> Linear parameter pass
+// The gathers follow the same receptive-field rule as the FFMA path (src/indices.cpp:63-104,163-194 of cuTAGI);
+// taps outside the image are written as zeros. The matrices are scratch: they are consumed by the next launch on the
+// same stream and never leave the device. Shapes that the tensor-core kernels cannot take (channel counts or
+// fi*k*k not multiples of 4) stay on the FFMA implicit-GEMM kernels.
+#include "tagi_common.h"
+
+namespace tagi {
+namespace {
+
+struct G {
+    int B, fi, hi, wi, fo, ho, wo, k, stride, off, k2, Kc, woho, wihi;
+};
+G geom_of(const tagi_conv2d_geom &g) {
+    G q;
+    q.B = g.B, q.fi = g.fi, q.hi = g.hi, q.wi = g.wi, q.fo = g.fo, q.ho = g.ho, q.wo = g.wo, q.k = g.k;
+    q.stride = g.stride, q.off = g.pad_type == 1 ? g.pad : 0;
+    q.k2 = g.k * g.k, q.Kc = q.k2 * g.fi, q.woho = g.wo * g.ho, q.wihi = g.wi * g.hi;
+    return q;
+}
+
+// X[(b, p)][kc] = a[b][ci][oy*s - off + ky][ox*s - off + kx]; one thread per element, kc fastest (coalesced writes,
+// reads of neighbouring taps hit the same cache lines). NSRC = 2 gathers mean and variance in one pass.
+template <int NSRC>
+__global__ void __launch_bounds__(256) im2col_kernel(const float *__restrict__ a0, const float *__restrict__ a1, G g,
+                                                     float *__restrict__ x0, float *__restrict__ x1) {
+    const long total = (long)g.B * g.woho * g.Kc;
+    for (long t = (long)blockIdx.x * 256 + threadIdx.x; t < total; t += (long)gridDim.x * 256) {
+        const int kc = (int)(t % g.Kc);
+        const long n = t / g.Kc;
+        const int b = (int)(n / g.woho), p = (int)(n - (long)b * g.woho);
+        const int oy = p / g.wo, ox = p - oy * g.wo;
+        const int ci = kc / g.k2, r = kc - ci * g.k2, ky = r / g.k, kx = r - ky * g.k;
+        const int y = oy * g.stride - g.off + ky, x = ox * g.stride - g.off + kx;
+        float v0 = 0.f, v1 = 0.f;
+        if ((unsigned)y < (unsigned)g.hi && (unsigned)x < (unsigned)g.wi) {
+            const long i = ((long)b * g.fi + ci) * g.wihi + (long)y * g.wi + x;
+            v0 = __ldg(a0 + i);
+            if (NSRC == 2) v1 = __ldg(a1 + i);
+        }
+        x0[t] = v0;
+        if (NSRC == 2) x1[t] = v1;
+    }
+}
+
+// Z[(b, q)][(co, ky, kx)] = delta[b][co][(y + off - ky) / s][(x + off - kx) / s] where that output pixel exists
+__global__ void __launch_bounds__(256) delta_gather_kernel(const float *__restrict__ d0, const float *__restrict__ d1, G g,
+                                                           float *__restrict__ z0, float *__restrict__ z1) {
+    const int kd = g.fo * g.k2;
+    const long total = (long)g.B * g.wihi * kd;
+    for (long t = (long)blockIdx.x * 256 + threadIdx.x; t < total; t += (long)gridDim.x * 256) {
+        const int kk = (int)(t % kd);
+        const long n = t / kd;
+        const int b = (int)(n / g.wihi), q = (int)(n - (long)b * g.wihi);
+        const int y = q / g.wi, x = q - y * g.wi;
+        const int co = kk / g.k2, r = kk - co * g.k2, ky = r / g.k, kx = r - ky * g.k;
+        const int ty = y + g.off - ky, tx = x + g.off - kx;
+        float v0 = 0.f, v1 = 0.f;
+        if (ty >= 0 && tx >= 0) {
+            const int oy = ty / g.stride, ox = tx / g.stride;
+            if (oy * g.stride == ty && ox * g.stride == tx && oy < g.ho && ox < g.wo) {
+                const long i = ((long)b * g.fo + co) * g.woho + (long)oy * g.wo + ox;
+                v0 = __ldg(d0 + i);
+                v1 = __ldg(d1 + i);
+            }
+        }
+        z0[t] = v0;
+        z1[t] = v1;
+    }
+}
+
+// W2[(co, tap)][ci] = w[co][ci][tap]: the weights with the input channel as the contiguous index
+__global__ void __launch_bounds__(256) weight_regroup_kernel(const float *__restrict__ w, G g, float *__restrict__ w2) {
+    const long total = (long)g.fo * g.Kc;
+    for (long t = (long)blockIdx.x * 256 + threadIdx.x; t < total; t += (long)gridDim.x * 256) {
+        const int ci = (int)(t % g.fi);
+        const long r = t / g.fi;
+        const int tap = (int)(r % g.k2), co = (int)(r / g.k2);
+        w2[t] = __ldg(w + (long)co * g.Kc + ci * g.k2 + tap);
+    }
+}
+
+// D[(b, p)][co] = delta[b][co][p], through a 32 x 32 shared-memory tile so that both sides are coalesced
+__global__ void __launch_bounds__(256) delta_regroup_kernel(const float *__restrict__ d0, const float *__restrict__ d1, G g,
+                                                            float *__restrict__ o0, float *__restrict__ o1) {
+    __shared__ float t0[32][33], t1[32][33];
+    const int b = blockIdx.z, p0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+    for (int j = ty; j < 32; j += 8) {
+        const int co = c0 + j, p = p0 + tx;
+        if (co < g.fo && p < g.woho) {
+            const long i = ((long)b * g.fo + co) * g.woho + p;
+            t0[j][tx] = __ldg(d0 + i);
+            t1[j][tx] = __ldg(d1 + i);
+        }
+    }
+    __syncthreads();
+    for (int j = ty; j < 32; j += 8) {
+        const int p = p0 + j, co = c0 + tx;
+        if (co < g.fo && p < g.woho) {
+            const long i = ((long)b * g.woho + p) * g.fo + co;
+            o0[i] = t0[tx][j];
+            o1[i] = t1[tx][j];
+        }
+    }
+}
+
+// dmu_a[b][ci][y][x] = J * sum over taps (ky, kx) whose output pixel ((y + off - ky) / s, (x + off - kx) / s) exists of
+// C[b][(ci, ky, kx)][that pixel]; the variance with J * J. One thread per input element, x fastest.
+__global__ void __launch_bounds__(256) col2im_kernel(const float *__restrict__ c0, const float *__restrict__ c1,
+                                                     const float *__restrict__ jcb, G g, float *__restrict__ o0,
+                                                     float *__restrict__ o1) {
+    const long total = (long)g.B * g.fi * g.wihi;
+    for (long t = (long)blockIdx.x * 256 + threadIdx.x; t < total; t += (long)gridDim.x * 256) {
+        const int q = (int)(t % g.wihi);
+        const long n = t / g.wihi;  // b * fi + ci
+        const int y = q / g.wi, x = q - y * g.wi;
+        float a0 = 0.f, a1 = 0.f;
+        for (int ky = 0; ky < g.k; ky++) {
+            const int ty = y + g.off - ky;
+            if (ty < 0) break;
+            const int oy = ty / g.stride;
+            if (oy * g.stride != ty || oy >= g.ho) continue;
+            for (int kx = 0; kx < g.k; kx++) {
+                const int tx = x + g.off - kx;
+                if (tx < 0) break;
+                const int ox = tx / g.stride;
+                if (ox * g.stride != tx || ox >= g.wo) continue;
+                const long i = (n * g.k2 + ky * g.k + kx) * g.woho + (long)oy * g.wo + ox;
+                a0 += __ldg(c0 + i);
+                a1 += __ldg(c1 + i);
+            }
+        }
+        const float j = __ldg(jcb + t);
+        o0[t] = a0 * j;
+        o1[t] = a1 * j * j;
+    }
+}
+
+inline unsigned grid_for(long total) {
+    long blocks = (total + 255) / 256;
+    return (unsigned)(blocks < 148L * 32 ? blocks : 148L * 32);
+}
+inline int ok_or(cudaError_t e, const char *what) { return e == cudaSuccess ? TAGI_OK : cuda_fail(e, what); }
+
+}  // namespace
+
+// Which Conv2d calls the tensor-core kernels take: 16-byte aligned tensors and every GEMM dimension a multiple of 4
+// (TMA row pitches, vector stores), and enough work for 128-row tiles.
+bool conv_tc_supported(const tagi_conv2d_geom &cg, std::initializer_list<const void *> ptrs) {
+    const G g = geom_of(cg);
+    if (g.fo % 4 || g.fi % 4 || g.Kc % 4) return false;
+    if (((long)g.B * g.woho) % 4 || ((long)g.B * g.wihi) % 4) return false;
+    for (const void *p : ptrs)
+        if (p && !aligned16(p)) return false;
+    return true;
+}
+bool conv_tc_profitable(const tagi_conv2d_geom &cg) {
+    const G g = geom_of(cg);
+    return g.fo >= 32 && g.fi >= 16 && (long)g.B * g.woho >= 256;
+}
+
+int conv2d_fwd_tc(const tagi_conv2d_geom &cg, const float *mu_w, const float *var_w, const float *mu_b,
+                  const float *var_b, const float *mu_a, const float *var_a, float *mu_z, float *var_z,
+                  cudaStream_t st) {
+    const G g = geom_of(cg);
+    const long rows = (long)g.B * g.woho;
+    float *ws = nullptr;
+    int rc = conv_scratch((size_t)2 * rows * g.Kc * sizeof(float), &ws);
+    if (rc != TAGI_OK) return rc;
+    float *x_mu = ws, *x_var = ws + rows * g.Kc;
+    im2col_kernel<2><<<grid_for(rows * g.Kc), 256, 0, st>>>(mu_a, var_a, g, x_mu, x_var);
+    if ((rc = ok_or(cudaGetLastError(), "im2col_kernel launch")) != TAGI_OK) return rc;
+    // rows = (image, output pixel), columns = output channels: exactly Linear's forward, written as [b][co][pixel]
+    return linear_fwd_tc(mu_w, var_w, mu_b, var_b, x_mu, x_var, (int)rows, g.Kc, g.fo, mu_z, var_z, st, g.woho);
+}
+
+int conv2d_bwd_state_tc(const tagi_conv2d_geom &cg, const float *mu_w, const float *jcb, const float *dmu_z,
+                        const float *dvar_z, float *dmu_a, float *dvar_a, cudaStream_t st) {
+    const G g = geom_of(cg);
+    float *ws = nullptr;
+    int rc;
+    if (g.stride > 1) {
+        const long rows = (long)g.B * g.woho;
+        if ((rc = conv_scratch(((size_t)2 * rows * g.fo + (size_t)2 * rows * g.Kc) * sizeof(float), &ws)) != TAGI_OK)
+            return rc;
+        float *d_mu = ws, *d_var = d_mu + rows * g.fo, *c_mu = d_var + rows * g.fo, *c_var = c_mu + rows * g.Kc;
+        dim3 grid((g.woho + 31) / 32, (g.fo + 31) / 32, g.B);
+        delta_regroup_kernel<<<grid, 256, 0, st>>>(dmu_z, dvar_z, g, d_mu, d_var);
+        if ((rc = ok_or(cudaGetLastError(), "delta_regroup_kernel launch")) != TAGI_OK) return rc;
+        // Linear's state pass without a Jacobian: C[(b, p)][kc] = sum over co of D[(b, p)][co] * w[co][kc] (and w * w for
+        // the variance), stored as [b][kc][p]
+        rc = linear_bwd_state_tc(mu_w, nullptr, d_mu, d_var, (int)rows, g.Kc, g.fo, c_mu, c_var, st, g.woho);
+        if (rc != TAGI_OK) return rc;
+        col2im_kernel<<<grid_for((long)g.B * g.fi * g.wihi), 256, 0, st>>>(c_mu, c_var, jcb, g, dmu_a, dvar_a);
+        return ok_or(cudaGetLastError(), "col2im_kernel launch");
+    }
+    const long rows = (long)g.B * g.wihi;
+    const int kd = g.fo * g.k2;
+    rc = conv_scratch(((size_t)2 * rows * kd + (size_t)g.fo * g.Kc) * sizeof(float), &ws);
+    if (rc != TAGI_OK) return rc;
+    float *z_mu = ws, *z_var = ws + rows * kd, *w2 = ws + 2 * rows * kd;
+    delta_gather_kernel<<<grid_for(rows * kd), 256, 0, st>>>(dmu_z, dvar_z, g, z_mu, z_var);
+    if ((rc = ok_or(cudaGetLastError(), "delta_gather_kernel launch")) != TAGI_OK) return rc;
+    weight_regroup_kernel<<<grid_for((long)g.fo * g.Kc), 256, 0, st>>>(mu_w, g, w2);
+    if ((rc = ok_or(cudaGetLastError(), "weight_regroup_kernel launch")) != TAGI_OK) return rc;
+    // Linear's state pass with "output features" = (co, tap) and "input features" = ci; Jacobian and outputs in
+    // [b][ci][pixel]
+    return linear_bwd_state_tc(w2, jcb, z_mu, z_var, (int)rows, g.fi, kd, dmu_a, dvar_a, st, g.wihi);
+}
+
+int conv2d_bwd_param_tc(const tagi_conv2d_geom &cg, const float *var_w, const float *mu_a, const float *dmu_z,
+                        const float *dvar_z, float *dmu_w, float *dvar_w, cudaStream_t st) {
+    const G g = geom_of(cg);
+    const long rows = (long)g.B * g.woho;
+    // small weight tensors with a long contraction (B * ho * wo): the contraction is cut into slices
+    const int slices = linear_bwd_param_tc_slices((int)rows, g.Kc, g.fo);
+    const size_t part = slices > 1 ? (size_t)2 * slices * g.fo * g.Kc : 0;
+    float *ws = nullptr;
+    int rc = conv_scratch(((size_t)rows * g.Kc + (size_t)2 * rows * g.fo + part) * sizeof(float), &ws);
+    if (rc != TAGI_OK) return rc;
+    float *x_mu = ws, *d_mu = ws + rows * g.Kc, *d_var = d_mu + rows * g.fo, *split_ws = d_var + rows * g.fo;
+    im2col_kernel<1><<<grid_for(rows * g.Kc), 256, 0, st>>>(mu_a, nullptr, g, x_mu, nullptr);
+    if ((rc = ok_or(cudaGetLastError(), "im2col_kernel launch")) != TAGI_OK) return rc;
+    dim3 grid((g.woho + 31) / 32, (g.fo + 31) / 32, g.B);
+    delta_regroup_kernel<<<grid, 256, 0, st>>>(dmu_z, dvar_z, g, d_mu, d_var);
+    if ((rc = ok_or(cudaGetLastError(), "delta_regroup_kernel launch")) != TAGI_OK) return rc;
+    // Linear's parameter pass with batch = (image, output pixel): dmu_w[co][kc] = var_w * sum D[.][co] X[.][kc]
+    return linear_bwd_param_tc(var_w, x_mu, d_mu, d_var, (int)rows, g.Kc, g.fo, dmu_w, dvar_w, st,
+                               slices > 1 ? split_ws : nullptr, slices);
+}
+
+}  // namespace tagi

@@ -62,6 +62,13 @@ struct TcEpilogue {
     const float *aux1, *aux2;  // forward: bias vectors (may be null); backward: aux1 = scale matrix
     long ld;
     int rows, cols;
+    // 0: outputs are row-major [rows][ld]. > 0: rows are (image, pixel) pairs with npix pixels per image, columns are
+    // channels, and outputs (and the scale matrix) are laid out [image][channel][pixel] as Conv2d wants them
+    int npix;
+    // Split contraction: slice z = blockIdx.z covers k-slabs [z * slabs_per_slice, ...) and writes its sums at
+    // out + z * slice_elems (0 slabs_per_slice: the whole contraction in one slice)
+    int slabs_per_slice;
+    long slice_elems;
 };
 
 __device__ __forceinline__ float lo_part(float x) { return x - __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
@@ -76,6 +83,62 @@ __device__ __forceinline__ float4 lds128(uint32_t addr) {
 __device__ __forceinline__ void sts128(uint32_t addr, float4 v) {
     asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
                  : "memory");
+}
+
+// One thread's 64 columns (starting at column c0, `valid` of them inside the tile) of output row `row`:
+// forward adds the bias of the column, the backward passes scale by the matrix entry (s and s*s).
+template <int OP>
+__device__ __forceinline__ void store_tile(const TcEpilogue &epi, int row, int c0, int valid, const float (&sum1)[64],
+                                           const float (&sum2)[64]) {
+    if (row >= epi.rows) return;
+    if (epi.npix > 0) {
+        // [image][channel][pixel]: consecutive lanes hold consecutive pixels, so each channel's store is coalesced
+        const int img = row / epi.npix, pix = row - img * epi.npix;
+        const long base = (long)img * epi.cols * epi.npix + pix;
+#pragma unroll
+        for (int i = 0; i < 64; i++) {
+            const int col = c0 + i;
+            if (i >= valid || col >= epi.cols) break;
+            const long idx = base + (long)col * epi.npix;
+            float o1 = sum1[i], o2 = sum2[i];
+            if (OP == OP_FWD) {
+                if (epi.aux1) {
+                    o1 += __ldg(epi.aux1 + col);
+                    o2 += __ldg(epi.aux2 + col);
+                }
+            } else if (epi.aux1) {
+                const float sc = __ldg(epi.aux1 + idx);
+                o1 *= sc;
+                o2 = o2 * sc * sc;
+            }
+            __stcs(epi.out1 + idx, o1);
+            __stcs(epi.out2 + idx, o2);
+        }
+        return;
+    }
+#pragma unroll
+    for (int i = 0; i < 64; i += 4) {
+        const int col = c0 + i;
+        if (i >= valid || col >= epi.cols) break;  // tile widths and cols are multiples of 4 on this path
+        const long idx = (long)row * epi.ld + col;
+        float4 o1 = make_float4(sum1[i], sum1[i + 1], sum1[i + 2], sum1[i + 3]);
+        float4 o2 = make_float4(sum2[i], sum2[i + 1], sum2[i + 2], sum2[i + 3]);
+        if (OP == OP_FWD) {
+            if (epi.aux1) {
+                const float4 b1 = __ldg(reinterpret_cast<const float4 *>(epi.aux1 + col));
+                const float4 b2 = __ldg(reinterpret_cast<const float4 *>(epi.aux2 + col));
+                o1.x += b1.x, o1.y += b1.y, o1.z += b1.z, o1.w += b1.w;
+                o2.x += b2.x, o2.y += b2.y, o2.z += b2.z, o2.w += b2.w;
+            }
+        } else if (epi.aux1) {  // no scale matrix: raw partial sums of a split contraction
+            const float4 sc = __ldg(reinterpret_cast<const float4 *>(epi.aux1 + idx));
+            o1.x *= sc.x, o1.y *= sc.y, o1.z *= sc.z, o1.w *= sc.w;
+            o2.x = o2.x * sc.x * sc.x, o2.y = o2.y * sc.y * sc.y;
+            o2.z = o2.z * sc.z * sc.z, o2.w = o2.w * sc.w * sc.w;
+        }
+        __stcs(reinterpret_cast<float4 *>(epi.out1 + idx), o1);
+        __stcs(reinterpret_cast<float4 *>(epi.out2 + idx), o2);
+    }
 }
 
 // K-major tile [128 rows][16 k], 64-byte swizzle: one box. MN-major tile: four boxes of [16 k][32 rows], 2 KiB
@@ -299,31 +362,7 @@ tagi_tc_linear_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
 
         if (ok) {
             const int row = row0 + q * 32 + lane;
-            if (row < epi.rows) {
-#pragma unroll
-                for (int i = 0; i < 64; i += 4) {
-                    const int col = col0 + h * 64 + i;
-                    if (h * 64 + i >= bn || col >= epi.cols) break;  // bn and cols are multiples of 4 on this path
-                    const long idx = (long)row * epi.ld + col;
-                    float4 o1 = make_float4(sum1[i], sum1[i + 1], sum1[i + 2], sum1[i + 3]);
-                    float4 o2 = make_float4(sum2[i], sum2[i + 1], sum2[i + 2], sum2[i + 3]);
-                    if (OP == OP_FWD) {
-                        if (epi.aux1) {
-                            const float4 b1 = __ldg(reinterpret_cast<const float4 *>(epi.aux1 + col));
-                            const float4 b2 = __ldg(reinterpret_cast<const float4 *>(epi.aux2 + col));
-                            o1.x += b1.x, o1.y += b1.y, o1.z += b1.z, o1.w += b1.w;
-                            o2.x += b2.x, o2.y += b2.y, o2.z += b2.z, o2.w += b2.w;
-                        }
-                    } else {
-                        const float4 sc = __ldg(reinterpret_cast<const float4 *>(epi.aux1 + idx));
-                        o1.x *= sc.x, o1.y *= sc.y, o1.z *= sc.z, o1.w *= sc.w;
-                        o2.x = o2.x * sc.x * sc.x, o2.y = o2.y * sc.y * sc.y;
-                        o2.z = o2.z * sc.z * sc.z, o2.w = o2.w * sc.w * sc.w;
-                    }
-                    __stcs(reinterpret_cast<float4 *>(epi.out1 + idx), o1);
-                    __stcs(reinterpret_cast<float4 *>(epi.out2 + idx), o2);
-                }
-            }
+            store_tile<OP>(epi, row, col0 + h * 64, bn - h * 64, sum1, sum2);
         }
     }
     __syncwarp();
@@ -395,7 +434,9 @@ tagi_tc_linear_ts_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row0 = blockIdx.y * TM, col0 = blockIdx.x * bn;
-    const int nk = (kdim + BK - 1) / BK;
+    const int nk_all = (kdim + BK - 1) / BK;
+    const int kb = epi.slabs_per_slice > 0 ? (int)blockIdx.z * epi.slabs_per_slice : 0;  // first k-slab of this slice
+    const int nk = epi.slabs_per_slice > 0 ? min(nk_all - kb, epi.slabs_per_slice) : nk_all;
     const int chunk_len = CH > 0 ? CH : nk;
 
     if (threadIdx.x == 0) {
@@ -427,7 +468,7 @@ tagi_tc_linear_ts_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_
                     break;
                 mbar_arrive_expect_tx(raw_full + r, NRAW * TILE_BYTES);
                 const uint32_t st = raw_base + r * NRAW * TILE_BYTES;
-                const int k0 = it * BK;
+                const int k0 = (kb + it) * BK;
                 load_tile<T::A_MN>(st + 0 * TILE_BYTES, &tmA0, row0, k0, raw_full + r);
                 load_tile<T::A_MN>(st + 1 * TILE_BYTES, &tmA1, row0, k0, raw_full + r);
                 load_tile<T::B_MN>(st + 2 * TILE_BYTES, &tmB0, col0, k0, raw_full + r);
@@ -588,31 +629,10 @@ tagi_tc_linear_ts_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_
 
         if (ok) {
             const int row = row0 + q * 32 + lane;
-            if (row < epi.rows) {
-#pragma unroll
-                for (int i = 0; i < 64; i += 4) {
-                    const int col = col0 + h * 64 + i;
-                    if (h * 64 + i >= bn || col >= epi.cols) break;
-                    const long idx = (long)row * epi.ld + col;
-                    float4 o1 = make_float4(sum1[i], sum1[i + 1], sum1[i + 2], sum1[i + 3]);
-                    float4 o2 = make_float4(sum2[i], sum2[i + 1], sum2[i + 2], sum2[i + 3]);
-                    if (OP == OP_FWD) {
-                        if (epi.aux1) {
-                            const float4 b1 = __ldg(reinterpret_cast<const float4 *>(epi.aux1 + col));
-                            const float4 b2 = __ldg(reinterpret_cast<const float4 *>(epi.aux2 + col));
-                            o1.x += b1.x, o1.y += b1.y, o1.z += b1.z, o1.w += b1.w;
-                            o2.x += b2.x, o2.y += b2.y, o2.z += b2.z, o2.w += b2.w;
-                        }
-                    } else {
-                        const float4 sc = __ldg(reinterpret_cast<const float4 *>(epi.aux1 + idx));
-                        o1.x *= sc.x, o1.y *= sc.y, o1.z *= sc.z, o1.w *= sc.w;
-                        o2.x = o2.x * sc.x * sc.x, o2.y = o2.y * sc.y * sc.y;
-                        o2.z = o2.z * sc.z * sc.z, o2.w = o2.w * sc.w * sc.w;
-                    }
-                    __stcs(reinterpret_cast<float4 *>(epi.out1 + idx), o1);
-                    __stcs(reinterpret_cast<float4 *>(epi.out2 + idx), o2);
-                }
-            }
+            TcEpilogue e = epi;
+            e.out1 += (long)blockIdx.z * epi.slice_elems;
+            e.out2 += (long)blockIdx.z * epi.slice_elems;
+            store_tile<OP>(e, row, col0 + h * 64, bn - h * 64, sum1, sum2);
         }
     }
     __syncwarp();
@@ -697,7 +717,9 @@ tagi_tc_linear_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __gri
     const int row0 = blockIdx.y * 256 + (int)cta * 128;          // this CTA's 128 rows of A and of the output
     const int col0 = (blockIdx.x >> 1) * bn;                      // the pair's columns
     const int brow0 = col0 + (int)cta * half;                     // this CTA's half of the B rows
-    const int nk = (kdim + BK - 1) / BK;
+    const int nk_all = (kdim + BK - 1) / BK;
+    const int kb = epi.slabs_per_slice > 0 ? (int)blockIdx.z * epi.slabs_per_slice : 0;  // first k-slab of this slice
+    const int nk = epi.slabs_per_slice > 0 ? min(nk_all - kb, epi.slabs_per_slice) : nk_all;
     const int chunk_len = CH > 0 ? CH : nk;
 
     if (threadIdx.x == 0) {
@@ -730,7 +752,7 @@ tagi_tc_linear_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __gri
                     break;
                 mbar_arrive_expect_tx(raw_full + r, RAW_SLOT);
                 const uint32_t st = raw_base + r * RAW_SLOT;
-                const int k0 = it * BK;
+                const int k0 = (kb + it) * BK;
                 load_tile<T::A_MN>(st, &tmA0, row0, k0, raw_full + r);
                 load_tile<T::A_MN>(st + TILE_BYTES, &tmA1, row0, k0, raw_full + r);
                 load_half_tile<T::B_MN>(st + 2 * TILE_BYTES, &tmB0, brow0, k0, raw_full + r);
@@ -885,31 +907,10 @@ tagi_tc_linear_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __gri
 
         if (ok) {
             const int row = row0 + q * 32 + lane;
-            if (row < epi.rows) {
-#pragma unroll
-                for (int i = 0; i < 64; i += 4) {
-                    const int col = col0 + h * 64 + i;
-                    if (h * 64 + i >= bn || col >= epi.cols) break;
-                    const long idx = (long)row * epi.ld + col;
-                    float4 o1 = make_float4(sum1[i], sum1[i + 1], sum1[i + 2], sum1[i + 3]);
-                    float4 o2 = make_float4(sum2[i], sum2[i + 1], sum2[i + 2], sum2[i + 3]);
-                    if (OP == OP_FWD) {
-                        if (epi.aux1) {
-                            const float4 b1 = __ldg(reinterpret_cast<const float4 *>(epi.aux1 + col));
-                            const float4 b2 = __ldg(reinterpret_cast<const float4 *>(epi.aux2 + col));
-                            o1.x += b1.x, o1.y += b1.y, o1.z += b1.z, o1.w += b1.w;
-                            o2.x += b2.x, o2.y += b2.y, o2.z += b2.z, o2.w += b2.w;
-                        }
-                    } else {
-                        const float4 sc = __ldg(reinterpret_cast<const float4 *>(epi.aux1 + idx));
-                        o1.x *= sc.x, o1.y *= sc.y, o1.z *= sc.z, o1.w *= sc.w;
-                        o2.x = o2.x * sc.x * sc.x, o2.y = o2.y * sc.y * sc.y;
-                        o2.z = o2.z * sc.z * sc.z, o2.w = o2.w * sc.w * sc.w;
-                    }
-                    __stcs(reinterpret_cast<float4 *>(epi.out1 + idx), o1);
-                    __stcs(reinterpret_cast<float4 *>(epi.out2 + idx), o2);
-                }
-            }
+            TcEpilogue e = epi;
+            e.out1 += (long)blockIdx.z * epi.slice_elems;
+            e.out2 += (long)blockIdx.z * epi.slice_elems;
+            store_tile<OP>(e, row, col0 + h * 64, bn - h * 64, sum1, sum2);
         }
     }
     __syncwarp();
@@ -996,7 +997,8 @@ int launch(const CUtensorMap &a0, const CUtensorMap &a1, const CUtensorMap &b0, 
         const long cost = ((tiles + 147) / 148) * (w + 16);  // + 16: per-tile work that does not shrink with the width
         if (best < 0 || cost < best) best = cost, bn = w;
     }
-    dim3 grid((epi.cols + bn - 1) / bn, (unsigned)row_tiles);
+    const unsigned slices = epi.slabs_per_slice > 0 ? (unsigned)(((kdim + BK - 1) / BK + epi.slabs_per_slice - 1) / epi.slabs_per_slice) : 1u;
+    dim3 grid((epi.cols + bn - 1) / bn, (unsigned)row_tiles, slices);
     cudaError_t e;
     if (g_variant == 1 || g_variant == 3) {
         // ring depths: the backward passes have room for four derived slots; the forward pass for three when the
@@ -1055,7 +1057,8 @@ int launch_pair(const CUtensorMap &a0, const CUtensorMap &a1, const CUtensorMap 
     }
     if (g_pair_bn) bn = g_pair_bn;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2 * (unsigned)((epi.cols + bn - 1) / bn), (unsigned)row_tiles);
+    const unsigned slices = epi.slabs_per_slice > 0 ? (unsigned)(((kdim + BK - 1) / BK + epi.slabs_per_slice - 1) / epi.slabs_per_slice) : 1u;
+    cfg.gridDim = dim3(2 * (unsigned)((epi.cols + bn - 1) / bn), (unsigned)row_tiles, slices);
     cfg.blockDim = dim3(NTHREADS2);
     cfg.stream = st;
     cudaLaunchAttribute attr;
@@ -1135,7 +1138,7 @@ int linear_tc_status(int *out, int reset) {
 }
 
 int linear_fwd_tc(const float *mu_w, const float *var_w, const float *mu_b, const float *var_b, const float *mu_a,
-                  const float *var_a, int B, int K, int N, float *mu_z, float *var_z, cudaStream_t st) {
+                  const float *var_a, int B, int K, int N, float *mu_z, float *var_z, cudaStream_t st, int npix) {
     CUtensorMap a0, a1, b0, b1;
     int rc;
     if ((rc = make_tmap(&a0, mu_a, K, B, false))) return rc;
@@ -1143,35 +1146,80 @@ int linear_fwd_tc(const float *mu_w, const float *var_w, const float *mu_b, cons
     const bool pair = use_pair(B);
     if ((rc = make_tmap(&b0, mu_w, K, N, false, pair ? 64 : 128))) return rc;
     if ((rc = make_tmap(&b1, var_w, K, N, false, pair ? 64 : 128))) return rc;
-    TcEpilogue epi{mu_z, var_z, mu_b, var_b, (long)N, B, N};
+    TcEpilogue epi{mu_z, var_z, mu_b, var_b, (long)N, B, N, npix, 0, 0};
     if (pair) return launch_pair<OP_FWD>(a0, a1, b0, b1, epi, K, st);
     return launch<OP_FWD>(a0, a1, b0, b1, epi, K, st);
 }
 
 int linear_bwd_state_tc(const float *mu_w, const float *jcb, const float *dmu_z, const float *dvar_z, int B, int K,
-                        int N, float *dmu_a, float *dvar_a, cudaStream_t st) {
+                        int N, float *dmu_a, float *dvar_a, cudaStream_t st, int npix) {
     // rows = batch, columns = input features, contraction over output features; mu_w [N][K] is MN-major here
     CUtensorMap a0, a1, b0;
     int rc;
     if ((rc = make_tmap(&a0, dmu_z, N, B, false))) return rc;
     if ((rc = make_tmap(&a1, dvar_z, N, B, false))) return rc;
     if ((rc = make_tmap(&b0, mu_w, K, N, true))) return rc;
-    TcEpilogue epi{dmu_a, dvar_a, jcb, nullptr, (long)K, B, K};
+    TcEpilogue epi{dmu_a, dvar_a, jcb, nullptr, (long)K, B, K, npix, 0, 0};
     if (use_pair(B)) return launch_pair<OP_BWD_STATE>(a0, a1, b0, b0, epi, N, st);
     return launch<OP_BWD_STATE>(a0, a1, b0, b0, epi, N, st);
 }
 
+// Sum of the contraction slices in slice order, then the scaling of the parameter pass (s and s*s)
+__global__ void __launch_bounds__(256) tc_reduce_slices_kernel(const float *__restrict__ part1, const float *__restrict__ part2,
+                                                               const float *__restrict__ scale, long n, int slices,
+                                                               float *__restrict__ out1, float *__restrict__ out2) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float a1 = 0.f, a2 = 0.f;
+    for (int z = 0; z < slices; z++) {
+        a1 += part1[(long)z * n + i];
+        a2 += part2[(long)z * n + i];
+    }
+    const float sc = __ldg(scale + i);
+    out1[i] = a1 * sc;
+    out2[i] = a2 * sc * sc;
+}
+
+// How many slices the contraction (B long) of a parameter pass with an N x K output should be cut into: none when the
+// output tiles already fill half the SMs, else about two waves of CTAs, keeping at least 64 k-slabs (1024 batch rows)
+// per slice. 1 = do not split.
+int linear_bwd_param_tc_slices(int B, int K, int N) {
+    const long tiles = (long)((N + 127) / 128) * ((K + 127) / 128);
+    const int nk = (B + BK - 1) / BK;
+    if (tiles > 74) return 1;
+    long s = (2 * 148 + tiles - 1) / tiles;
+    if (s > nk / 64) s = nk / 64;
+    return s < 2 ? 1 : (int)s;
+}
+
+// split_ws: optional scratch of at least 2 * slices * N * K floats (slices from linear_bwd_param_tc_slices); without it
+// the contraction is not split.
 int linear_bwd_param_tc(const float *var_w, const float *mu_a, const float *dmu_z, const float *dvar_z, int B, int K,
-                        int N, float *dmu_w, float *dvar_w, cudaStream_t st) {
+                        int N, float *dmu_w, float *dvar_w, cudaStream_t st, float *split_ws, int slices) {
     // rows = output features, columns = input features, contraction over the batch; both operands MN-major
     CUtensorMap a0, a1, b0;
     int rc;
     if ((rc = make_tmap(&a0, dmu_z, N, B, true))) return rc;
     if ((rc = make_tmap(&a1, dvar_z, N, B, true))) return rc;
     if ((rc = make_tmap(&b0, mu_a, K, B, true))) return rc;
-    TcEpilogue epi{dmu_w, dvar_w, var_w, nullptr, (long)K, N, K};
-    if (use_pair(N)) return launch_pair<OP_BWD_PARAM>(a0, a1, b0, b0, epi, B, st);
-    return launch<OP_BWD_PARAM>(a0, a1, b0, b0, epi, B, st);
+    if (!split_ws || slices < 2) {
+        TcEpilogue epi{dmu_w, dvar_w, var_w, nullptr, (long)K, N, K, 0, 0, 0};
+        if (use_pair(N)) return launch_pair<OP_BWD_PARAM>(a0, a1, b0, b0, epi, B, st);
+        return launch<OP_BWD_PARAM>(a0, a1, b0, b0, epi, B, st);
+    }
+    const long slice = (long)N * K;
+    const int nk = (B + BK - 1) / BK;
+    const int per = (nk + slices - 1) / slices;
+    const int used = (nk + per - 1) / per;
+    float *p1 = split_ws, *p2 = split_ws + (long)slices * slice;
+    TcEpilogue epi{p1, p2, nullptr, nullptr, (long)K, N, K, 0, per, slice};
+    rc = use_pair(N) ? launch_pair<OP_BWD_PARAM>(a0, a1, b0, b0, epi, B, st)
+                     : launch<OP_BWD_PARAM>(a0, a1, b0, b0, epi, B, st);
+    if (rc != TAGI_OK) return rc;
+    tc_reduce_slices_kernel<<<(unsigned)((slice + 255) / 256), 256, 0, st>>>(p1, p2, var_w, slice, used, dmu_w, dvar_w);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "tc_reduce_slices_kernel launch");
+    return TAGI_OK;
 }
 
 }  // namespace tagi

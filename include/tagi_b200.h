@@ -33,12 +33,13 @@ enum {
     TAGI_ERR_COMM = 4              /* NCCL / rendezvous failure */
 };
 
-/* Which arithmetic the three Linear entry points use.
+/* Which arithmetic the Linear and Conv2d entry points use.
  *   AUTO   : the measured-faster variant that supports the shape (default)
  *   FFMA   : FP32 fused multiply-add on the CUDA cores, any shape
  *   TF32X3 : tcgen05 tensor-core MMA, each FP32 product split into three TF32 products
  *            (hi*hi + hi*lo + lo*hi) accumulated in FP32 in tensor memory;
- *            shapes it cannot run return TAGI_ERR_UNSUPPORTED under this setting. */
+ *            shapes it cannot run return TAGI_ERR_UNSUPPORTED under this setting. Conv2d runs on the same kernels
+ *            after a gather pass that lays the receptive fields out as a matrix in library-owned scratch memory. */
 enum { TAGI_IMPL_AUTO = 0, TAGI_IMPL_FFMA = 1, TAGI_IMPL_TF32X3 = 2 };
 int tagi_set_impl(int impl);
 int tagi_get_impl(void);

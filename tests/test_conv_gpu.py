@@ -102,3 +102,65 @@ def test_geometry_errors(G):
     bad = CG(1, 1, 8, 8, 1, 5, 5, 3, 1, 0, 0, 0)   # ho / wo inconsistent (should be 6)
     with pytest.raises(TagiError):
         lib.tagi_conv2d_fwd(C.byref(bad), q, q, q, q, q, q, q, q, None)
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# Conv2d on the tensor-core kernels (gather pass + the Linear tcgen05 kernels), forced, and the FFMA path, forced
+# ------------------------------------------------------------------------------------------------------------------
+TC_GEOMS = [
+    dict(B=4, fi=32, hi=16, wi=16, fo=64, k=3, stride=1, pad=1, pad_type=1, has_bias=1),    # CNN conv2
+    dict(B=4, fi=64, hi=8, wi=8, fo=128, k=3, stride=1, pad=1, pad_type=1, has_bias=1),     # CNN conv3
+    dict(B=4, fi=64, hi=14, wi=14, fo=64, k=3, stride=1, pad=1, pad_type=1, has_bias=0),    # ResNet layer1 block conv
+    dict(B=4, fi=64, hi=14, wi=14, fo=128, k=3, stride=2, pad=1, pad_type=2, has_bias=0),   # down-sampling conv
+    dict(B=4, fi=64, hi=14, wi=14, fo=128, k=2, stride=2, pad=0, pad_type=0, has_bias=0),   # projection shortcut
+    dict(B=8, fi=128, hi=7, wi=7, fo=256, k=3, stride=1, pad=1, pad_type=1, has_bias=0),    # 7x7 images: 49 pixels
+    dict(B=4, fi=4, hi=10, wi=10, fo=8, k=5, stride=1, pad=2, pad_type=1, has_bias=1),      # tiny channels
+    dict(B=2, fi=16, hi=12, wi=12, fo=260, k=1, stride=1, pad=0, pad_type=0, has_bias=1),   # 1x1, ragged fo tile
+    dict(B=16, fi=32, hi=32, wi=32, fo=64, k=3, stride=1, pad=1, pad_type=1, has_bias=1),   # parameter pass in 16 slices
+    dict(B=6, fi=16, hi=30, wi=30, fo=32, k=3, stride=1, pad=1, pad_type=1, has_bias=0),    # ragged last slice
+    dict(B=4, fi=16, hi=15, wi=15, fo=32, k=3, stride=2, pad=1, pad_type=1, has_bias=1),    # stride 2, odd image
+    dict(B=4, fi=8, hi=19, wi=19, fo=16, k=5, stride=3, pad=2, pad_type=1, has_bias=0),     # stride 3, 5x5
+]
+
+
+@pytest.mark.parametrize("kw", TC_GEOMS, ids=lambda k: "fi{fi}_fo{fo}_h{hi}_k{k}_s{stride}_p{pad}t{pad_type}".format(**k))
+def test_conv_tensor_core_path(G, oracle, kw):
+    from cutagi_b200 import capi
+    from cutagi_b200.capi import lib
+    g = ConvGeom(**kw)
+    rng = np.random.default_rng(g.fi * 31 + g.fo)
+    lib.tagi_set_impl(capi.IMPL_TF32X3)
+    try:
+        capi.tc_status()
+        _run_all(G, oracle, g, G.conv_inputs(rng, g))
+        assert capi.tc_status() == 0
+    finally:
+        lib.tagi_set_impl(capi.IMPL_AUTO)
+
+
+def test_conv_ffma_path_forced(G, oracle):
+    from cutagi_b200 import capi
+    from cutagi_b200.capi import lib
+    g = ConvGeom(B=4, fi=32, hi=16, wi=16, fo=64, k=3, stride=1, pad=1, pad_type=1, has_bias=1)
+    lib.tagi_set_impl(capi.IMPL_FFMA)
+    try:
+        _run_all(G, oracle, g, G.conv_inputs(np.random.default_rng(2), g))
+    finally:
+        lib.tagi_set_impl(capi.IMPL_AUTO)
+
+
+def test_conv_tensor_core_rejects_odd_channels(G):
+    import torch
+    from cutagi_b200 import capi
+    from cutagi_b200.capi import ConvGeom as CG, TagiError, lib
+    q = torch.zeros(1 << 16, device="cuda").data_ptr()
+    g = CG(2, 3, 8, 8, 8, 8, 8, 3, 1, 1, 1, 0)   # fi = 3
+    lib.tagi_set_impl(capi.IMPL_TF32X3)
+    try:
+        with pytest.raises(TagiError) as e:
+            lib.tagi_conv2d_fwd(C.byref(g), q, q, q, q, q, q, q, q, None)
+        assert e.value.code == 3
+    finally:
+        lib.tagi_set_impl(capi.IMPL_AUTO)
+    lib.tagi_conv2d_fwd(C.byref(g), q, q, q, q, q, q, q, q, None)   # AUTO: FFMA kernels
+    torch.cuda.synchronize()
