@@ -39,6 +39,10 @@ using namespace ptx;
 constexpr int TM = 128, TN = 128, BK = 16;
 constexpr int TILE_BYTES = 128 * BK * 4;  // 8 KiB per operand tile
 constexpr int NCONV_WARPS = 8;
+// epilogue staging of the ts / pair kernels: per warp two 32 x 64 blocks with a row pitch of 68 floats
+constexpr uint32_t STAGE_PITCH = 68 * 4, STAGE_VALUE = 32 * STAGE_PITCH, STAGE_WARP = 2 * STAGE_VALUE;
+constexpr size_t STAGE_BYTES = (size_t)NCONV_WARPS * STAGE_WARP;
+__host__ __device__ constexpr size_t at_least_stage(size_t ring) { return ring > STAGE_BYTES ? ring : STAGE_BYTES; }
 constexpr int NTHREADS = 32 * (2 + NCONV_WARPS);       // all-shared-memory kernel: TMA, MMA, converters
 constexpr int NTHREADS2 = 32 * (3 + NCONV_WARPS);      // ts / pair kernels: TMA, two MMA issuers (warps 1, 10), converters
 constexpr int ISSUER2_WARP = 2 + NCONV_WARPS;
@@ -138,6 +142,60 @@ __device__ __forceinline__ void store_tile(const TcEpilogue &epi, int row, int c
         }
         __stcs(reinterpret_cast<float4 *>(epi.out1 + idx), o1);
         __stcs(reinterpret_cast<float4 *>(epi.out2 + idx), o2);
+    }
+}
+
+// The same through shared memory, for row-major outputs: in tensor memory a lane owns a row, so direct stores put the 32
+// lanes of an instruction on 32 different rows (32 half-used sectors per request). The warp writes its 32 x 64 block
+// of both sums to `stage` (row pitch 68 floats: conflict-free 16-byte accesses both ways), then every instruction
+// handles two rows with 16 lanes x 16 bytes each: scale loads and stores are contiguous 256-byte runs.
+template <int OP>
+__device__ __forceinline__ void store_tile_staged(const TcEpilogue &epi, uint32_t stage, int row_base, int lane, int c0,
+                                                  int valid, const float (&sum1)[64], const float (&sum2)[64]) {
+    const uint32_t mine = stage + lane * STAGE_PITCH;
+#pragma unroll
+    for (int i = 0; i < 64; i += 4) {
+        sts128(mine + i * 4, make_float4(sum1[i], sum1[i + 1], sum1[i + 2], sum1[i + 3]));
+        sts128(mine + STAGE_VALUE + i * 4, make_float4(sum2[i], sum2[i + 1], sum2[i + 2], sum2[i + 3]));
+    }
+    __syncwarp();
+    const int cl = (lane & 15) * 4, col = c0 + cl;
+    if (cl >= valid || col >= epi.cols) return;  // tile widths and cols are multiples of 4 on this path
+    const int r0 = lane >> 4;
+    const long idx0 = (long)(row_base + r0) * epi.ld + col;
+    const uint32_t src = stage + r0 * STAGE_PITCH + cl * 4;
+    // rows of this lane: row_base + r0 + 2 * it. The scale entries (or the bias) are fetched for all sixteen rows
+    // before the first store, so that the epilogue pays the memory latency once and not once per row.
+    float4 aux[16];
+    if (OP == OP_FWD) {
+        aux[0] = aux[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (epi.aux1) {
+            aux[0] = __ldg(reinterpret_cast<const float4 *>(epi.aux1 + col));
+            aux[1] = __ldg(reinterpret_cast<const float4 *>(epi.aux2 + col));
+        }
+    } else if (epi.aux1) {
+#pragma unroll
+        for (int it = 0; it < 16; it++)
+            if (row_base + r0 + 2 * it < epi.rows)
+                aux[it] = __ldg(reinterpret_cast<const float4 *>(epi.aux1 + idx0 + (long)(2 * it) * epi.ld));
+    }
+#pragma unroll
+    for (int it = 0; it < 16; it++) {
+        if (row_base + r0 + 2 * it < epi.rows) {
+            const long idx = idx0 + (long)(2 * it) * epi.ld;
+            float4 o1 = lds128(src + 2 * it * STAGE_PITCH), o2 = lds128(src + STAGE_VALUE + 2 * it * STAGE_PITCH);
+            if (OP == OP_FWD) {
+                o1.x += aux[0].x, o1.y += aux[0].y, o1.z += aux[0].z, o1.w += aux[0].w;
+                o2.x += aux[1].x, o2.y += aux[1].y, o2.z += aux[1].z, o2.w += aux[1].w;
+            } else if (epi.aux1) {  // no scale matrix: raw partial sums of a split contraction
+                const float4 sc = aux[it];
+                o1.x *= sc.x, o1.y *= sc.y, o1.z *= sc.z, o1.w *= sc.w;
+                o2.x = o2.x * sc.x * sc.x, o2.y = o2.y * sc.y * sc.y;
+                o2.z = o2.z * sc.z * sc.z, o2.w = o2.w * sc.w * sc.w;
+            }
+            __stcs(reinterpret_cast<float4 *>(epi.out1 + idx), o1);
+            __stcs(reinterpret_cast<float4 *>(epi.out2 + idx), o2);
+        }
     }
 }
 
@@ -399,7 +457,7 @@ template <> struct TsTraits<OP_BWD_PARAM> { static constexpr int NRAW = 3, NDER 
 // RS raw-ring slots, DS derived-ring slots (shared memory for B, tensor memory for A)
 template <int OP, int RS, int DS>
 constexpr size_t ts_smem_bytes() {
-    return (size_t)(RS * TsTraits<OP>::NRAW + DS * TsTraits<OP>::NDER) * TILE_BYTES + 1024 + 256;
+    return at_least_stage((size_t)(RS * TsTraits<OP>::NRAW + DS * TsTraits<OP>::NDER) * TILE_BYTES) + 1024 + 256;
 }
 
 __device__ __forceinline__ float hi_part(float x) { return __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
@@ -423,7 +481,8 @@ tagi_tc_linear_ts_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *aligned = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t raw_base = smem_base, der_base = smem_base + RS * NRAW * TILE_BYTES;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(aligned + (size_t)(RS * NRAW + DS * NDER) * TILE_BYTES);
+    // the epilogue stages its tile over the rings, so the barriers sit behind whichever is larger
+    uint64_t *bars = reinterpret_cast<uint64_t *>(aligned + at_least_stage((size_t)(RS * NRAW + DS * NDER) * TILE_BYTES));
     // stage_done[it % L] completes when the MMAs of k-slab `it` have finished: one commit per slab releases both the
     // raw slot (refilled RS slabs later) and the derived slot (overwritten DS slabs later)
     constexpr int L = RS > DS ? RS : DS;
@@ -632,7 +691,12 @@ tagi_tc_linear_ts_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_
             TcEpilogue e = epi;
             e.out1 += (long)blockIdx.z * epi.slice_elems;
             e.out2 += (long)blockIdx.z * epi.slice_elems;
-            store_tile<OP>(e, row, col0 + h * 64, bn - h * 64, sum1, sum2);
+            // all MMAs and TMA writes of this tile are complete (last acc_full phase): the operand rings are free
+            if (e.npix > 0)
+                store_tile<OP>(e, row, col0 + h * 64, bn - h * 64, sum1, sum2);
+            else
+                store_tile_staged<OP>(e, smem_base + (warp - 2) * STAGE_WARP, row - lane, lane, col0 + h * 64,
+                                      bn - h * 64, sum1, sum2);
         }
     }
     __syncwarp();
@@ -670,8 +734,8 @@ template <> struct PairTraits<OP_BWD_PARAM> { static constexpr int NRAW_B = 1, N
 
 template <int OP, int RS, int DS>
 constexpr size_t pair_smem_bytes() {
-    return (size_t)RS * (2 * TILE_BYTES + PairTraits<OP>::NRAW_B * HALF_BYTES) +
-           (size_t)DS * PairTraits<OP>::NDER * HALF_BYTES + 1024 + 256;
+    return at_least_stage((size_t)RS * (2 * TILE_BYTES + PairTraits<OP>::NRAW_B * HALF_BYTES) +
+                          (size_t)DS * PairTraits<OP>::NDER * HALF_BYTES) + 1024 + 256;
 }
 
 // B half tile: K-major one box of 64 rows; MN-major two boxes of 32 rows
@@ -704,7 +768,8 @@ tagi_tc_linear_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __gri
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *aligned = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t raw_base = smem_base, der_base = smem_base + RS * RAW_SLOT;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(aligned + (size_t)RS * RAW_SLOT + (size_t)DS * DER_SLOT);
+    // the epilogue stages its tile over the rings, so the barriers sit behind whichever is larger
+    uint64_t *bars = reinterpret_cast<uint64_t *>(aligned + at_least_stage((size_t)RS * RAW_SLOT + (size_t)DS * DER_SLOT));
     constexpr int L = RS > DS ? RS : DS;  // stage_done ring, as in the one-CTA kernel; completion is multicast to both CTAs
     uint64_t *raw_full = bars, *stage_done = bars + RS, *conv_done = bars + RS + L;
     uint64_t *acc_full = bars + RS + L + DS, *acc_empty = acc_full + 1;
@@ -725,7 +790,7 @@ tagi_tc_linear_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __gri
     if (threadIdx.x == 0) {
         for (int s = 0; s < RS; s++) mbar_init(raw_full + s, 1);
         for (int s = 0; s < L; s++) mbar_init(stage_done + s, 2);  // one commit from each MMA issuer
-        for (int s = 0; s < DS; s++) mbar_init(conv_done + s, 2 * NCONV_WARPS);  // used in CTA 0: both CTAs' warps arrive
+        for (int s = 0; s < DS; s++) mbar_init(conv_done + s, NCONV_WARPS);  // used in CTA 0: one warp group of each CTA arrives
         mbar_init(acc_full, 2);
         mbar_init(acc_empty, 2 * NCONV_WARPS);          // used in CTA 0 only
         *abort_flag = 0;
@@ -824,9 +889,22 @@ tagi_tc_linear_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __gri
             return true;
         };
 
+        // The converter warps work as two groups of four (h = 0 / 1) on alternate k-slabs, so that two slabs are being
+        // converted at any time: one slab's conversion is a chain of shared-memory loads, tcgen05.st, fences and a
+        // barrier arrive whose latency, not its instruction count, set the pace when all eight warps shared one slab.
         bool ok = true;
-        int pending = -1;
-        for (int it = 0; it < nk && ok; it++) {
+        int pending = -1;  // chunk whose MMAs may be issued and whose sums this warp has not collected yet
+        int scanned = 0;   // slabs below this index have been checked for chunk ends
+        auto note_chunk_ends = [&](int upto) {  // slabs scanned .. upto
+            for (int sl = scanned; sl <= upto && sl < nk && ok; sl++)
+                if (sl % chunk_len == chunk_len - 1 || sl == nk - 1) {
+                    if (pending >= 0) ok = drain(pending);
+                    pending = sl / chunk_len;
+                }
+            scanned = upto + 1;
+        };
+        const int gt = ct & 127;  // thread index inside the group
+        for (int it = h; it < nk && ok; it += 2) {
             const int r = it % RS, d = it % DS;
             ok = mbar_wait(raw_full + r, (it / RS) & 1, abort_flag, status, ST_TIMEOUT_RAW) &&
                  (it < DS || mbar_wait(stage_done + (it - DS) % L, ((it - DS) / L) & 1, abort_flag, status,
@@ -834,26 +912,27 @@ tagi_tc_linear_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __gri
             if (!ok) break;
             const uint32_t rs = raw_base + r * RAW_SLOT, rb = rs + 2 * TILE_BYTES, ds = der_base + d * DER_SLOT;
 
-            float a0[8], a1[8];
-            if (T::A_MN) {
-                const uint32_t g = rs + q * 2048;
 #pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    const int k = h * 8 + i;
-                    const uint32_t o = k * 128 + (((lane >> 3) ^ (k & 3)) << 5) + ((lane & 7) << 2);
-                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(a0[i]) : "r"(g + o));
-                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(a1[i]) : "r"(g + TILE_BYTES + o));
+            for (int kh = 0; kh < 2; kh++) {  // the two 8-wide k steps of the A tiles: this thread's row
+                float a0[8], a1[8];
+                if (T::A_MN) {
+                    const uint32_t g = rs + q * 2048;
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const int kk = kh * 8 + i;
+                        const uint32_t o = kk * 128 + (((lane >> 3) ^ (kk & 3)) << 5) + ((lane & 7) << 2);
+                        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(a0[i]) : "r"(g + o));
+                        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(a1[i]) : "r"(g + TILE_BYTES + o));
+                    }
+                } else {
+                    const uint32_t rowb = rs + arow * 64, sw = (arow >> 1) & 3;
+                    const float4 x0 = lds128(rowb + (((2 * kh) ^ sw) << 4)), x1 = lds128(rowb + (((2 * kh + 1) ^ sw) << 4));
+                    const float4 y0 = lds128(rowb + TILE_BYTES + (((2 * kh) ^ sw) << 4));
+                    const float4 y1 = lds128(rowb + TILE_BYTES + (((2 * kh + 1) ^ sw) << 4));
+                    a0[0] = x0.x, a0[1] = x0.y, a0[2] = x0.z, a0[3] = x0.w, a0[4] = x1.x, a0[5] = x1.y, a0[6] = x1.z, a0[7] = x1.w;
+                    a1[0] = y0.x, a1[1] = y0.y, a1[2] = y0.z, a1[3] = y0.w, a1[4] = y1.x, a1[5] = y1.y, a1[6] = y1.z, a1[7] = y1.w;
                 }
-            } else {
-                const uint32_t rowb = rs + arow * 64, sw = (arow >> 1) & 3;
-                const float4 x0 = lds128(rowb + (((2 * h) ^ sw) << 4)), x1 = lds128(rowb + (((2 * h + 1) ^ sw) << 4));
-                const float4 y0 = lds128(rowb + TILE_BYTES + (((2 * h) ^ sw) << 4));
-                const float4 y1 = lds128(rowb + TILE_BYTES + (((2 * h + 1) ^ sw) << 4));
-                a0[0] = x0.x, a0[1] = x0.y, a0[2] = x0.z, a0[3] = x0.w, a0[4] = x1.x, a0[5] = x1.y, a0[6] = x1.z, a0[7] = x1.w;
-                a1[0] = y0.x, a1[1] = y0.y, a1[2] = y0.z, a1[3] = y0.w, a1[4] = y1.x, a1[5] = y1.y, a1[6] = y1.z, a1[7] = y1.w;
-            }
-            {
-                const uint32_t at = lane_addr + A_COL0 + d * (NA * BK) + h * 8;
+                const uint32_t at = lane_addr + A_COL0 + d * (NA * BK) + kh * 8;
                 float t0[8], t1[8];
 #pragma unroll
                 for (int i = 0; i < 8; i++) t0[i] = hi_part(a0[i]), t1[i] = hi_part(a1[i]);
@@ -874,9 +953,10 @@ tagi_tc_linear_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __gri
                     tmem_st_32x8(at + 5 * BK, t1);
                 }
             }
-            // B halves: one 16-byte chunk per converter thread
-            {
-                const uint32_t o = ct * 16;
+            // B halves: two 16-byte chunks per thread of the group
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                const uint32_t o = gt * 16 + c * (HALF_BYTES / 2);
                 if (OP == OP_FWD) {
                     const float4 b0 = lds128(rb + o), b1 = lds128(rb + HALF_BYTES + o);
                     const float4 qq = make_float4(b0.x * b0.x, b0.y * b0.y, b0.z * b0.z, b0.w * b0.w);
@@ -901,8 +981,9 @@ tagi_tc_linear_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __gri
                 ok = drain(pending);
                 pending = -1;
             }
-            if (it % chunk_len == chunk_len - 1 || it == nk - 1) pending = it / chunk_len;
+            note_chunk_ends(it + 1);
         }
+        if (ok) note_chunk_ends(nk - 1);
         if (ok && pending >= 0) ok = drain(pending);
 
         if (ok) {
@@ -910,7 +991,12 @@ tagi_tc_linear_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __gri
             TcEpilogue e = epi;
             e.out1 += (long)blockIdx.z * epi.slice_elems;
             e.out2 += (long)blockIdx.z * epi.slice_elems;
-            store_tile<OP>(e, row, col0 + h * 64, bn - h * 64, sum1, sum2);
+            // all MMAs and TMA writes of this tile are complete (last acc_full phase): the operand rings are free
+            if (e.npix > 0)
+                store_tile<OP>(e, row, col0 + h * 64, bn - h * 64, sum1, sum2);
+            else
+                store_tile_staged<OP>(e, smem_base + (warp - 2) * STAGE_WARP, row - lane, lane, col0 + h * 64,
+                                      bn - h * 64, sum1, sum2);
         }
     }
     __syncwarp();
