@@ -3,8 +3,9 @@
 // This translation unit is compiled by oracle/Makefile against the reference's
 // headers and linked with object files built from the reference's own sources
 // (src/linear_layer.cpp, src/conv2d_layer.cpp, src/base_layer.cpp, ...), which
-// stay where they are. It drives `Linear` (include/linear_layer.h:99-141) and
-// `Conv2d` (include/conv2d_layer.h:20-81) exactly the way `Sequential` does
+// stay where they are. It drives `Linear` (include/linear_layer.h:99-141),
+// `Conv2d` (include/conv2d_layer.h:20-81), `BatchNorm2d`
+// (include/batchnorm_layer.h:8-64) and `AvgPool2d` (include/pooling_layer.h:13-70) exactly the way `Sequential` does
 // (src/sequential.cpp:323-331, 392-410): hidden/delta/temp state objects in,
 // `forward` / `backward` virtual calls, results read from the state objects and
 // from the layer's `delta_*` members. Nothing here restates any arithmetic.
@@ -21,6 +22,8 @@
 #include "conv2d_layer.h"
 #include "data_struct.h"
 #include "linear_layer.h"
+#include "batchnorm_layer.h"
+#include "pooling_layer.h"
 
 namespace {
 std::string g_err;
@@ -247,6 +250,111 @@ int tagi_ref_param_update(int batch_size, size_t nw, size_t nb, float *mu_w,
         out(mu_b, l.mu_b, nb);
         out(var_b, l.var_b, nb);
         if (neg_var) *neg_var = l.neg_var_w_counter;
+    });
+}
+
+// BatchNorm2d::forward in training mode (src/batchnorm_layer.cpp:849-985): batch statistics, running averages
+// (mu_ra / var_ra in, updated out; `first_batch` selects momentum 0 as the reference does), normalisation.
+int tagi_ref_bn2d_forward(int B, int C, int hi, int wi, int has_bias, int threads, int training, int first_batch,
+                          float eps, float momentum, const float *mu_w, const float *var_w, const float *mu_b,
+                          const float *var_b, const float *mu_a, const float *var_a, float *mu_ra, float *var_ra,
+                          float *mu_batch, float *var_batch, float *mu_z, float *var_z) {
+    return guarded([&] {
+        BatchNorm2d layer(C, eps, momentum, has_bias != 0);
+        set_params(layer, C, has_bias ? C : 0, mu_w, var_w, mu_b, var_b);
+        InitArgs args(wi, hi, C);
+        layer.compute_input_output_size(args);
+        layer.set_threads(threads);
+        layer.training = training != 0;
+        layer.first_batch = first_batch != 0;
+        layer.mu_ra = vec(mu_ra, C);
+        layer.var_ra = vec(var_ra, C);
+        size_t n = (size_t)C * hi * wi, cap = (size_t)B * n;
+        BaseHiddenStates in(cap, B), outs(cap, B);
+        BaseTempStates tmp(cap, B);
+        std::memcpy(in.mu_a.data(), mu_a, sizeof(float) * cap);
+        std::memcpy(in.var_a.data(), var_a, sizeof(float) * cap);
+        in.block_size = B;
+        in.actual_size = n;
+        layer.forward(in, outs, tmp);
+        out(mu_z, outs.mu_a, cap);
+        out(var_z, outs.var_a, cap);
+        out(mu_ra, layer.mu_ra, C);
+        out(var_ra, layer.var_ra, C);
+        out(mu_batch, layer.mu_norm_batch, C);
+        out(var_batch, layer.var_norm_batch, C);
+    });
+}
+
+// BatchNorm2d::backward (src/batchnorm_layer.cpp:987-1129); mu_a / jcb are the saved input states, mu_batch / var_batch
+// the batch statistics of the forward pass.
+int tagi_ref_bn2d_backward(int B, int C, int hi, int wi, int has_bias, int threads, float eps, const float *mu_w,
+                           const float *var_w, const float *var_b, const float *mu_a, const float *jcb,
+                           const float *mu_batch, const float *var_batch, const float *dmu_o, const float *dvar_o,
+                           float *dmu, float *dvar, float *dmu_w, float *dvar_w, float *dmu_b, float *dvar_b) {
+    return guarded([&] {
+        BatchNorm2d layer(C, eps, 0.9f, has_bias != 0);
+        set_params(layer, C, has_bias ? C : 0, mu_w, var_w, nullptr, var_b);
+        InitArgs args(wi, hi, C);
+        layer.compute_input_output_size(args);
+        layer.set_threads(threads);
+        layer.mu_norm_batch = vec(mu_batch, C);
+        layer.var_norm_batch = vec(var_batch, C);
+        size_t n = (size_t)C * hi * wi, cap = (size_t)B * n;
+        layer.input_size = layer.output_size = n;
+        layer.bwd_states->set_size(cap);
+        std::memcpy(layer.bwd_states->mu_a.data(), mu_a, sizeof(float) * cap);
+        std::memcpy(layer.bwd_states->jcb.data(), jcb, sizeof(float) * cap);
+        BaseDeltaStates din(cap, B), dout(cap, B);
+        BaseTempStates tmp(cap, B);
+        std::memcpy(din.delta_mu.data(), dmu_o, sizeof(float) * cap);
+        std::memcpy(din.delta_var.data(), dvar_o, sizeof(float) * cap);
+        din.block_size = B;
+        din.actual_size = n;
+        layer.backward(din, dout, tmp, true);
+        out(dmu, dout.delta_mu, cap);
+        out(dvar, dout.delta_var, cap);
+        out(dmu_w, layer.delta_mu_w, C);
+        out(dvar_w, layer.delta_var_w, C);
+        if (has_bias) {
+            out(dmu_b, layer.delta_mu_b, C);
+            out(dvar_b, layer.delta_var_b, C);
+        }
+    });
+}
+
+// AvgPool2d::forward / backward (src/pooling_layer.cpp:59-176); index tables built by the reference itself.
+int tagi_ref_avgpool2d(int B, int C, int hi, int wi, int k, int stride, int pad, int pad_type, int threads,
+                       const float *mu_a, const float *var_a, const float *jcb, const float *dmu_o,
+                       const float *dvar_o, int *wo, int *ho, float *mu_z, float *var_z, float *dmu, float *dvar) {
+    return guarded([&] {
+        AvgPool2d layer(k, stride, pad, pad_type);
+        InitArgs args(wi, hi, C);
+        layer.compute_input_output_size(args);
+        layer.set_threads(threads);
+        *wo = layer.out_width;
+        *ho = layer.out_height;
+        size_t n_in = (size_t)C * hi * wi, n_out = layer.output_size;
+        size_t cap = (size_t)B * (n_in > n_out ? n_in : n_out);
+        BaseHiddenStates in(cap, B), outs(cap, B);
+        BaseTempStates tmp(cap, B);
+        std::memcpy(in.mu_a.data(), mu_a, sizeof(float) * B * n_in);
+        std::memcpy(in.var_a.data(), var_a, sizeof(float) * B * n_in);
+        in.block_size = B;
+        in.actual_size = n_in;
+        layer.forward(in, outs, tmp);
+        out(mu_z, outs.mu_a, (size_t)B * n_out);
+        out(var_z, outs.var_a, (size_t)B * n_out);
+        if (!dmu_o) return;
+        std::memcpy(layer.bwd_states->jcb.data(), jcb, sizeof(float) * B * n_in);
+        BaseDeltaStates din(cap, B), dout(cap, B);
+        std::memcpy(din.delta_mu.data(), dmu_o, sizeof(float) * B * n_out);
+        std::memcpy(din.delta_var.data(), dvar_o, sizeof(float) * B * n_out);
+        din.block_size = B;
+        din.actual_size = n_out;
+        layer.backward(din, dout, tmp, true);
+        out(dmu, dout.delta_mu, (size_t)B * n_in);
+        out(dvar, dout.delta_var, (size_t)B * n_in);
     });
 }
 

@@ -64,6 +64,37 @@ void tagi_oracle_output_delta_selected(int B, int n_out, int n_enc, const float 
 /* Capped parameter update, src/base_layer.cpp:116-187; returns how many variances were reset to 1e-5. */
 int tagi_oracle_param_update(int batch_size, size_t n, float *mu, float *var, const float *dmu, const float *dvar);
 
+
+/* ---- layers around Conv2d in the CNN / ResNet configurations (fp32, activations [B][C][H*W]) ---- */
+/* BatchNorm2d batch statistics in training, src/batchnorm_layer.cpp:127-168: mean[c] = sum mu_a / n,
+ * var[c] = (sum (mu_a - mean)^2 + sum var_a) / (n - 1), n = B * wihi, sums over (b, pixel) in that order. */
+void tagi_oracle_bn2d_stats(int B, int C, int wihi, const float *mu_a, const float *var_a, float *mean, float *var);
+/* Running averages, src/batchnorm_layer.cpp:15-26: ra = ra * momentum + batch * (1 - momentum). */
+void tagi_oracle_bn2d_running(int C, float momentum, const float *mean, const float *var, float *mu_ra, float *var_ra);
+/* Normalisation with the given statistics, src/batchnorm_layer.cpp:170-206. */
+void tagi_oracle_bn2d_fwd(int B, int C, int wihi, int has_bias, float eps, const float *mu_w, const float *var_w,
+                          const float *mu_b, const float *var_b, const float *mu_a, const float *var_a,
+                          const float *mean, const float *var, float *mu_z, float *var_z);
+/* State deltas, src/batchnorm_layer.cpp:233-255. */
+void tagi_oracle_bn2d_bwd_state(int B, int C, int wihi, float eps, const float *mu_w, const float *jcb, const float *var,
+                                const float *dmu_o, const float *dvar_o, float *dmu, float *dvar);
+/* Parameter deltas, src/batchnorm_layer.cpp:307-357 followed by delta_param_sum (src/common.cpp:360-376). */
+void tagi_oracle_bn2d_bwd_param(int B, int C, int wihi, int has_bias, float eps, const float *var_w, const float *var_b,
+                                const float *mu_a, const float *mean, const float *var, const float *dmu_o,
+                                const float *dvar_o, float *dmu_w, float *dvar_w, float *dmu_b, float *dvar_b);
+/* AvgPool2d, src/pooling_layer.cpp:207-283 (forward) and :285-353 (state deltas), with the receptive field of
+ * src/indices.cpp (same rule as Conv2d: input pixel (oy*s - off + ky, ox*s - off + kx), off = pad for padding type 1,
+ * 0 with bottom/right padding for type 2); taps in the padding contribute nothing, the divisor stays k*k.
+ * g->fi = g->fo = channels, has_bias unused. */
+void tagi_oracle_avgpool2d_fwd(const tagi_oracle_conv_geom *g, const float *mu_a, const float *var_a, float *mu_z,
+                               float *var_z);
+void tagi_oracle_avgpool2d_bwd_state(const tagi_oracle_conv_geom *g, const float *jcb, const float *dmu_o,
+                                     const float *dvar_o, float *dmu, float *dvar);
+/* Residual connection, src/resnet_block.cpp:8-31: a += s (states, or deltas of a projection shortcut) and
+ * a += s * j, va += vs * j * j (identity shortcut, j = Jacobian of the block input). jcb may be NULL (= 1). */
+void tagi_oracle_add_shortcut(size_t n, const float *mu_s, const float *var_s, const float *jcb, float *mu_a,
+                              float *var_a);
+
 #ifdef __cplusplus
 }
 #endif

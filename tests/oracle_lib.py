@@ -181,6 +181,55 @@ class Oracle:
         """In place on mu, var; returns the number of variances that were reset."""
         return self.lib.tagi_oracle_param_update(batch_size, mu.size, _f(mu), _f(var), _f(dmu), _f(dvar))
 
+    # ---- BatchNorm2d / AvgPool2d / residual add (activations [B][C][H*W]) ---------------------------------
+    def bn2d_stats(self, mu_a, var_a):
+        B, C_, wihi = mu_a.shape
+        mean, var = np.empty(C_, np.float32), np.empty(C_, np.float32)
+        self.lib.tagi_oracle_bn2d_stats(B, C_, wihi, _f(mu_a), _f(var_a), _f(mean), _f(var))
+        return mean, var
+
+    def bn2d_running(self, momentum, mean, var, mu_ra, var_ra):
+        """In place on mu_ra, var_ra."""
+        self.lib.tagi_oracle_bn2d_running(mean.size, C.c_float(momentum), _f(mean), _f(var), _f(mu_ra), _f(var_ra))
+
+    def bn2d_fwd(self, eps, mu_w, var_w, mu_b, var_b, mu_a, var_a, mean, var):
+        B, C_, wihi = mu_a.shape
+        mz, vz = np.empty_like(mu_a), np.empty_like(mu_a)
+        self.lib.tagi_oracle_bn2d_fwd(B, C_, wihi, int(mu_b is not None), C.c_float(eps), _f(mu_w), _f(var_w), _f(mu_b),
+                                      _f(var_b), _f(mu_a), _f(var_a), _f(mean), _f(var), _f(mz), _f(vz))
+        return mz, vz
+
+    def bn2d_bwd_state(self, eps, mu_w, jcb, var, dmu_o, dvar_o):
+        B, C_, wihi = jcb.shape
+        dm, dv = np.empty_like(jcb), np.empty_like(jcb)
+        self.lib.tagi_oracle_bn2d_bwd_state(B, C_, wihi, C.c_float(eps), _f(mu_w), _f(jcb), _f(var), _f(dmu_o), _f(dvar_o),
+                                            _f(dm), _f(dv))
+        return dm, dv
+
+    def bn2d_bwd_param(self, eps, var_w, var_b, mu_a, mean, var, dmu_o, dvar_o):
+        B, C_, wihi = mu_a.shape
+        dmw, dvw, dmb, dvb = (np.zeros(C_, np.float32) for _ in range(4))
+        self.lib.tagi_oracle_bn2d_bwd_param(B, C_, wihi, int(var_b is not None), C.c_float(eps), _f(var_w), _f(var_b),
+                                            _f(mu_a), _f(mean), _f(var), _f(dmu_o), _f(dvar_o), _f(dmw), _f(dvw),
+                                            _f(dmb), _f(dvb))
+        return dmw, dvw, dmb, dvb
+
+    def avgpool2d_fwd(self, g, mu_a, var_a):
+        mz, vz = np.empty((g.B, g.n_out), np.float32), np.empty((g.B, g.n_out), np.float32)
+        gc = g.c()
+        self.lib.tagi_oracle_avgpool2d_fwd(C.byref(gc), _f(mu_a), _f(var_a), _f(mz), _f(vz))
+        return mz, vz
+
+    def avgpool2d_bwd_state(self, g, jcb, dmu_o, dvar_o):
+        dm, dv = np.empty((g.B, g.n_in), np.float32), np.empty((g.B, g.n_in), np.float32)
+        gc = g.c()
+        self.lib.tagi_oracle_avgpool2d_bwd_state(C.byref(gc), _f(jcb), _f(dmu_o), _f(dvar_o), _f(dm), _f(dv))
+        return dm, dv
+
+    def add_shortcut(self, mu_s, var_s, jcb, mu_a, var_a):
+        """In place on mu_a, var_a; jcb None for a plain sum."""
+        self.lib.tagi_oracle_add_shortcut(C.c_size_t(mu_a.size), _f(mu_s), _f(var_s), _f(jcb), _f(mu_a), _f(var_a))
+
 
 class RefLib:
     """The reference's CPU classes (Linear, Conv2d, BaseLayer update) through oracle/ref_shim.cpp."""
@@ -247,3 +296,34 @@ class RefLib:
             batch_size, C.c_size_t(mu_w.size), C.c_size_t(nb), _f(mu_w), _f(var_w), _f(mu_b), _f(var_b), _f(dmu_w),
             _f(dvar_w), _f(dmu_b), _f(dvar_b), C.byref(neg)))
         return neg.value
+
+    def bn2d_forward(self, eps, momentum, mu_w, var_w, mu_b, var_b, mu_a, var_a, mu_ra, var_ra, hi, wi, training=True,
+                     first_batch=True, threads=1):
+        """Returns mu_z, var_z, batch mean, batch variance; mu_ra / var_ra are updated in place."""
+        B, C_, wihi = mu_a.shape
+        mz, vz = np.empty_like(mu_a), np.empty_like(mu_a)
+        mb, vb = np.zeros(C_, np.float32), np.zeros(C_, np.float32)
+        self._chk(self.lib.tagi_ref_bn2d_forward(
+            B, C_, hi, wi, int(mu_b is not None), threads, int(training), int(first_batch), C.c_float(eps),
+            C.c_float(momentum), _f(mu_w), _f(var_w), _f(mu_b), _f(var_b), _f(mu_a), _f(var_a), _f(mu_ra), _f(var_ra),
+            _f(mb), _f(vb), _f(mz), _f(vz)))
+        return mz, vz, mb, vb
+
+    def bn2d_backward(self, eps, mu_w, var_w, var_b, mu_a, jcb, mean, var, dmu_o, dvar_o, hi, wi, threads=1):
+        B, C_, wihi = mu_a.shape
+        dm, dv = np.empty_like(mu_a), np.empty_like(mu_a)
+        dmw, dvw, dmb, dvb = (np.zeros(C_, np.float32) for _ in range(4))
+        self._chk(self.lib.tagi_ref_bn2d_backward(
+            B, C_, hi, wi, int(var_b is not None), threads, C.c_float(eps), _f(mu_w), _f(var_w), _f(var_b), _f(mu_a),
+            _f(jcb), _f(mean), _f(var), _f(dmu_o), _f(dvar_o), _f(dm), _f(dv), _f(dmw), _f(dvw), _f(dmb), _f(dvb)))
+        return dm, dv, dmw, dvw, dmb, dvb
+
+    def avgpool2d(self, g, mu_a, var_a, jcb=None, dmu_o=None, dvar_o=None, threads=1):
+        """Forward, and backward when deltas are given. g.fi channels; returns (mu_z, var_z, dmu, dvar, wo, ho)."""
+        wo, ho = C.c_int(0), C.c_int(0)
+        mz, vz = np.empty((g.B, g.n_out), np.float32), np.empty((g.B, g.n_out), np.float32)
+        dm, dv = np.zeros((g.B, g.n_in), np.float32), np.zeros((g.B, g.n_in), np.float32)
+        self._chk(self.lib.tagi_ref_avgpool2d(
+            g.B, g.fi, g.hi, g.wi, g.k, g.stride, g.pad, g.pad_type, threads, _f(mu_a), _f(var_a), _f(jcb), _f(dmu_o),
+            _f(dvar_o), C.byref(wo), C.byref(ho), _f(mz), _f(vz), _f(dm), _f(dv)))
+        return mz, vz, dm, dv, wo.value, ho.value
