@@ -174,6 +174,51 @@ int tagi_conv2d_bwd_param_noalloc(const tagi_conv2d_geom *g, const float *var_w,
                                   const float *mu_a, const float *dmu_z, const float *dvar_z, float *dmu_w,
                                   float *dvar_w, float *dmu_b, float *dvar_b, void *stream);
 
+/* ---- Layers between the Conv2d calls of the CNN / ResNet configurations: activations [B][C][H*W] ---- */
+
+/* BatchNorm2d forward. training != 0: per-channel batch statistics mean = sum mu_a / n, var = (sum (mu_a - mean)^2 +
+ * sum var_a) / (n - 1), n = B * wihi, written to mu_batch / var_batch; running averages updated in place as
+ * ra = ra * momentum + batch * (1 - momentum) (the caller passes momentum 0 for the first training batch, as the
+ * reference does); normalisation with the batch statistics. training == 0: normalisation with mu_ra / var_ra.
+ * inv = 1 / sqrt(var + eps); mu_z = inv * (mu_a - mean) * mu_w + mu_b;
+ * var_z = inv^2 * (var_a * (mu_w^2 + var_w) + var_w * (mu_a - mean)^2) + var_b.
+ * CPU definition BatchNorm2d::forward (src/batchnorm_layer.cpp:15-26,127-206,849-985); replaces
+ * batchnorm2d_stat_mean_var_cuda, batchnorm2d_sample_var_cuda, running_mean_var_cuda and batchnorm2d_fwd_mean_var_cuda
+ * (src/batchnorm_layer_cuda.cu:141-152,439-543). */
+int tagi_bn2d_fwd(int B, int C, int wihi, int has_bias, int training, float eps, float momentum, const float *mu_w,
+                  const float *var_w, const float *mu_b, const float *var_b, const float *mu_a, const float *var_a,
+                  float *mu_ra, float *var_ra, float *mu_batch, float *var_batch, float *mu_z, float *var_z,
+                  void *stream);
+
+/* BatchNorm2d backward in one pass. State deltas (state_update != 0): t = inv * mu_w * jcb; dmu = t * dmu_o;
+ * dvar = t^2 * dvar_o (jcb NULL = 1). Parameter deltas per channel: dmu_w = sum u * dmu_o, dvar_w = sum u^2 * dvar_o with
+ * u = inv * (mu_a - mean) * var_w; dmu_b = var_b * sum dmu_o, dvar_b = var_b^2 * sum dvar_o. mu_a / jcb are the layer's
+ * saved input, mu_batch / var_batch the statistics of its forward pass.
+ * CPU definition BatchNorm2d::backward (src/batchnorm_layer.cpp:233-255,307-357,987-1129, src/common.cpp:360-376);
+ * replaces batchnorm2d_bwd_delta_z_cuda, batchnorm2d_bwd_delta_w_cuda, batchnorm2d_bwd_delta_b_cuda and
+ * batchnorm2d_dual_sum_reduction (src/batchnorm_layer_cuda.cu:220-264,567-690). */
+int tagi_bn2d_bwd(int B, int C, int wihi, int has_bias, int state_update, float eps, const float *mu_w,
+                  const float *var_w, const float *var_b, const float *mu_a, const float *jcb, const float *mu_batch,
+                  const float *var_batch, const float *dmu_o, const float *dvar_o, float *dmu, float *dvar, float *dmu_w,
+                  float *dvar_w, float *dmu_b, float *dvar_b, void *stream);
+
+/* AvgPool2d. The geometry is a tagi_conv2d_geom with fi = fo = channels (has_bias unused) and the same receptive-field
+ * rule as Conv2d; taps in the padding contribute nothing while the divisors stay k*k (mean) and k^4 (variance).
+ * Global pooling (kernel = image width, which pytagi writes as stride -1) is passed with stride = k.
+ * Backward: dmu = jcb * (sum of dmu_o over the cells that contain the pixel) / k^2, dvar = jcb^2 * (...) / k^4.
+ * CPU definition src/pooling_layer.cpp:59-176,207-375; replaces avgpool2d_fwd_(overlapped_)mean_var_cuda and
+ * avgpool2d_bwd_(overlapped_)delta_z_cuda and their index tables (src/pooling_layer_cuda.cu:13-120). */
+int tagi_avgpool2d_fwd(const tagi_conv2d_geom *g, const float *mu_a, const float *var_a, float *mu_z, float *var_z,
+                       void *stream);
+int tagi_avgpool2d_bwd_state(const tagi_conv2d_geom *g, const float *jcb, const float *dmu_o, const float *dvar_o,
+                             float *dmu, float *dvar, void *stream);
+
+/* Residual connection, in place on mu_a / var_a: mu_a += mu_s * j, var_a += var_s * j^2 (jcb NULL: j = 1).
+ * CPU definition add_shortcut_mean_var / add_shortcut_delta (src/resnet_block.cpp:8-31); replaces
+ * add_shortcut_mean_var_cuda / add_shortcut_delta_cuda (src/resnet_block_cuda.cu:7-33). */
+int tagi_add_shortcut(const float *mu_s, const float *var_s, const float *jcb, size_t n, float *mu_a, float *var_a,
+                      void *stream);
+
 #ifdef __cplusplus
 }
 #endif
