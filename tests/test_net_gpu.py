@@ -1,0 +1,95 @@
+"""Whole networks on the device (cutagi_b200.nn: Conv2d, BatchNorm2d, AvgPool2d, LayerBlock, ResNetBlock, Linear, ReLU on
+the C ABI) against the oracle's network trainer, which reproduces the reference's own runs bit for bit
+(tests/test_net_cpu.py), and against those runs themselves (tests/golden/net_golden.npz)."""
+import os
+
+import numpy as np
+import pytest
+from oracle_net import OracleNet, net_golden_problems, resnet_spec
+
+pytestmark = pytest.mark.gpu
+GOLD = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "net_golden.npz"))
+
+
+def _rel(a, b):
+    b = np.asarray(b, np.float64)
+    return float(np.abs(np.asarray(a, np.float64).reshape(b.shape) - b).max() / max(np.abs(b).max(), 1e-300))
+
+
+def _device_net(spec, in_shape, cpu):
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from cutagi_b200 import nn
+    net = nn.build(spec, in_shape)
+    net.load_state_dict(cpu.state_dict())
+    return net, nn.OutputUpdater()
+
+
+@pytest.mark.parametrize("name", ["resnet", "cnn"])
+def test_small_networks_follow_the_reference_run(oracle, name):
+    spec, in_shape, batch, steps = net_golden_problems()[name]
+    cpu = OracleNet(oracle, spec, in_shape, seed=1)
+    net, upd = _device_net(spec, in_shape, cpu)
+    xs, var_y = GOLD[f"{name}_x"], np.full(batch * 4, 1.0, np.float32)
+    for s in range(steps):
+        mu, var = net(xs[s])
+        rmu, rvar = cpu.forward(xs[s])
+        assert np.array_equal(rmu, GOLD[f"{name}_mu"][s])          # the oracle is on the reference's own run
+        tol = (2e-5, 2e-4) if s == 0 else (1e-3, 1e-3)             # parameters drift apart slowly after updates
+        assert _rel(mu.cpu().numpy(), rmu) < tol[0] and _rel(var.cpu().numpy(), rvar) < tol[1], (s, _rel(mu.cpu().numpy(), rmu))
+        upd.update_using_indices(net, GOLD[f"{name}_obs"][s], var_y, GOLD[f"{name}_idx"][s])
+        cpu.update_using_indices(GOLD[f"{name}_obs"][s], var_y, GOLD[f"{name}_idx"][s], 4)
+        net.backward()
+        cpu.backward()
+        net.step()
+        cpu.step()
+    for k, (mw, vw, mb, vb) in net.state_dict().items():
+        assert _rel(mw, GOLD[f"{name}_final_{k}_mu_w"]) < 1e-3 and _rel(vw, GOLD[f"{name}_final_{k}_var_w"]) < 1e-3, k
+
+
+def test_resnet18_one_step_every_delta(oracle):
+    """The reference's ResNet-18 (64/128/256/512 channels, two blocks per width, projection shortcuts) on 16 x 16 inputs,
+    batch 4: one training step, predictions and every parameter-delta tensor against the oracle. The convolutions of
+    this network run on the tensor-core path."""
+    spec = resnet_spec(final_pool=2)
+    in_shape, batch = (3, 16, 16), 4
+    cpu = OracleNet(oracle, spec, in_shape, seed=5)
+    net, upd = _device_net(spec, in_shape, cpu)
+    rng = np.random.default_rng(2)
+    x = rng.standard_normal((batch, 3 * 16 * 16)).astype(np.float32)
+    mu, var = net(x)
+    rmu, rvar = cpu.forward(x)
+    assert _rel(mu.cpu().numpy(), rmu) < 1e-4 and _rel(var.cpu().numpy(), rvar) < 1e-3
+    obs = rng.standard_normal((batch, 11)).astype(np.float32)
+    var_obs = np.full((batch, 11), 0.5, np.float32)
+    upd.update(net, obs, var_obs)
+    cpu.update(obs, var_obs)
+    net.backward()
+    cpu.backward()
+    named, cnamed = net.named_layers(), cpu.named_layers()
+    assert set(named) == set(cnamed)
+    worst = 0.0
+    for k, layer in named.items():
+        d = cnamed[k].d
+        e1, e2 = _rel(layer.delta_mu_w.cpu().numpy(), d[0]), _rel(layer.delta_var_w.cpu().numpy(), d[1])
+        worst = max(worst, e1, e2)
+        assert e1 < 1e-3 and e2 < 1e-3, (k, e1, e2)
+    # inference mode uses the running averages
+    net.eval()
+    mu_e, var_e = net(x)
+    emu, evar = cpu.forward(x, train=False)
+    assert _rel(mu_e.cpu().numpy(), emu) < 1e-4 and _rel(var_e.cpu().numpy(), evar) < 1e-3
+
+
+def test_shape_errors_are_raised():
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from cutagi_b200 import nn
+    with pytest.raises(RuntimeError):
+        nn.build([("conv", 3, 4, 3, 1, 1, 1, True), ("relu",), ("bn", 5)], (3, 8, 8))
+    with pytest.raises(RuntimeError):
+        nn.build([("conv", 3, 4, 3, 2, 0, 0, True)], (3, 8, 8))   # (8 - 3) not divisible by the stride
+    with pytest.raises(RuntimeError):
+        nn.build([("res", [("conv", 3, 4, 3, 1, 1, 1, False)], None)], (3, 8, 8))   # identity shortcut, 3 != 4 channels
