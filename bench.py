@@ -422,6 +422,217 @@ def run_conv_layers(args):
               f"{tp:.3f} ms, {4 * pm / tp / 1e9:.1f} |")
 
 
+def resnet_flops(spec, shape):
+    """Algorithmic FLOP of one training step per sample: 14 P per Conv2d / Linear (6 forward + 4 state + 4 parameter),
+    10 P for the first layer (no state pass), P = output pixels * fo * fi * k * k."""
+    total, first = 0.0, True
+
+    def walk(spec, shape):
+        nonlocal total, first
+        for item in spec:
+            kind, a = item[0], item[1:]
+            if kind == "conv":
+                fi, fo, k, stride, pad, pad_type = a[:6]
+                num = shape[1] - k + (2 * pad if pad_type == 1 else pad if pad_type == 2 else 0)
+                ho = num // stride + 1
+                total += (10.0 if first else 14.0) * ho * ho * fo * fi * k * k
+                first = False
+                shape = (fo, ho, ho)
+            elif kind == "linear":
+                total += 14.0 * a[0] * a[1]
+                shape = (a[1],)
+            elif kind == "pool":
+                k, stride, pad, pad_type = a
+                stride = k if stride < 0 else stride
+                num = shape[1] - k + (2 * pad if pad_type == 1 else pad if pad_type == 2 else 0)
+                shape = (shape[0], num // stride + 1, num // stride + 1)
+            elif kind == "res":
+                out = walk(a[0], shape)
+                if a[1]:
+                    walk(a[1], shape)
+                shape = out
+        return shape
+    walk(spec, shape)
+    return total
+
+
+def run_resnet(args, rank, world, local_rank):
+    """Side workload (not the headline line): one TAGI training step of the reference's ResNet-18 (ReLU variant, 11
+    hierarchical-softmax outputs) on 64 x 3 x 224 x 224 synthetic N(0,1) images per GPU through the device-side mirror
+    of the pytagi API: forward, output update, backward with the parameter deltas averaged over the ranks (bucketed NCCL
+    exchange overlapped with the rest of the backward pass), capped update. Prints one JSON line: samples/s."""
+    import torch
+    import torch.distributed as dist
+    from cutagi_b200 import nn
+    from cutagi_b200.capi import lib, tc_status as capi_tc_status
+
+    torch.cuda.set_device(local_rank)
+    lib.tagi_set_impl({"auto": 0, "ffma": 1, "tf32x3": 2}[args.kernel_impl])
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    image, batch = args.image, args.batch
+    spec = nn.resnet18_spec(image)
+    net = nn.build(spec, (3, image, image), seed=1234)      # same parameters on every rank
+    upd, utils = nn.OutputUpdater(), nn.Utils()
+    rng = np.random.default_rng(100 + rank)
+    n_sets = 2
+    xs = [torch.from_numpy(rng.standard_normal((batch, 3 * image * image), dtype=np.float32)).pin_memory()
+          for _ in range(n_sets)]
+    obs_idx = [utils.label_to_obs(rng.integers(0, 10, batch), 10) for _ in range(n_sets)]
+    obs = [torch.from_numpy(o[0]).pin_memory() for o in obs_idx]
+    idx = [torch.from_numpy(o[1]).pin_memory() for o in obs_idx]
+    var_y = torch.full((batch * 4,), 1.0, device="cuda")
+    stream = torch.cuda.current_stream()
+    sp = stream.cuda_stream
+    deltas = net.delta_tensors()
+    xchg = None
+    if world > 1:
+        from cutagi_b200.comm import DeltaExchange
+        token = [f"/tmp/tagi_b200_rdv_{os.getpid()}_{time.time_ns()}"]
+        dist.broadcast_object_list(token, src=0)
+        xchg = DeltaExchange(deltas, rank, world, local_rank, token[0], bucket_bytes=args.bucket_mb << 20, average=True)
+        pos = {t.data_ptr(): i for i, t in enumerate(deltas)}
+
+        def hook(layer):
+            ids = [pos[t.data_ptr()] for t in layer.delta_tensors()]
+
+            def ready():
+                for i in ids:
+                    xchg.ready(i, sp)
+            return ready
+        for layer in net.named_layers().values():
+            layer.on_ready = hook(layer)
+    d_x = [torch.empty_like(xs[0], device="cuda") for _ in range(n_sets)]
+    d_obs = [torch.empty_like(obs[0], device="cuda") for _ in range(n_sets)]
+    d_idx = [torch.empty_like(idx[0], device="cuda") for _ in range(n_sets)]
+    for i in range(n_sets):
+        d_x[i].copy_(xs[i]), d_obs[i].copy_(obs[i]), d_idx[i].copy_(idx[i])
+    host_out = torch.empty(2, batch, 11).pin_memory()
+    it = [0]
+
+    def step(e2e=False):
+        i = it[0] % n_sets
+        it[0] += 1
+        if e2e:
+            d_x[i].copy_(xs[i], non_blocking=True)
+            d_obs[i].copy_(obs[i], non_blocking=True)
+            d_idx[i].copy_(idx[i], non_blocking=True)
+        mu, var = net(d_x[i])
+        upd.update_using_indices(net, d_obs[i], var_y, d_idx[i])
+        net.backward()
+        if xchg:
+            xchg.flush(sp)
+            xchg.wait(sp)
+        net.step()
+        if e2e:
+            host_out[0].copy_(mu, non_blocking=True)
+            host_out[1].copy_(var, non_blocking=True)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(fn, n):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sync_all()
+        e0.record(stream)
+        for _ in range(n):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        sync_all()
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    for _ in range(args.warmup):
+        step()
+    t0 = time.time()
+    ms = timed(step, args.steps) / args.steps
+    t1 = time.time()
+    ms_e2e = ms if args.profile else timed(lambda: step(True), args.steps) / args.steps
+    # phases on one rank's stream (no exchange wait inside): forward / output update + backward / update
+    phases = {}
+    if not args.profile:
+        def fwd():
+            net(d_x[0])
+
+        def bwd():
+            upd.update_using_indices(net, d_obs[0], var_y, d_idx[0])
+            net.backward()
+            if xchg:
+                xchg.flush(sp)
+                xchg.wait(sp)
+        fwd()
+        phases["forward_ms"] = timed(fwd, 3) / 3
+        phases["backward_ms"] = timed(bwd, 3) / 3
+        phases["update_ms"] = timed(net.step, 3) / 3
+    clocks = sampler.summary(t0, t1) if rank == 0 else None
+    if rank == 0:
+        sampler.stop()
+    status = capi_tc_status()
+    if xchg:
+        xchg.check()
+    if rank != 0:
+        if world > 1:
+            xchg.close()
+            dist.destroy_process_group()
+        return
+    flop = resnet_flops(spec, (3, image, image)) * batch
+    n_param = sum(t.numel() for t in deltas) // 2
+    peak = 0.0
+    try:
+        peak = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"] / 6.0
+    except Exception:
+        peak = 1590.0 / 6.0
+    cpu = None
+    if not args.no_cpu:
+        from oracle_lib import Oracle
+        from oracle_net import OracleNet
+        o = Oracle()
+        cnet = OracleNet(o, spec, (3, image, image), seed=1)
+        xb = rng.standard_normal((1, 3 * image * image)).astype(np.float32)
+        ob, ib, _ = utils.label_to_obs([3], 10)
+        tc0 = time.perf_counter()
+        cnet.forward(xb)
+        cnet.update_using_indices(ob, np.ones(4, np.float32), ib, 4)
+        cnet.backward()
+        cnet.step()
+        dt = time.perf_counter() - tc0
+        cpu = {"value": 1.0 / dt, "unit": "samples/s", "cores": os.cpu_count(), "kind": "port",
+               "sample": f"one training step at batch 1 ({dt:.1f} s), oracle port with OpenMP; linear in the batch"}
+    print(json.dumps({
+        "metric": "TAGI ResNet-18 training samples/s", "value": batch * world / (ms * 1e-3), "unit": "samples/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"resnet18_relu_3x{image}x{image}_batch{batch}_per_gpu (forward + output update + backward + "
+                               "capped update, 11 hierarchical-softmax outputs)",
+                   "parameters": n_param, "exchange": "none (1 GPU)" if world == 1 else
+                   f"bucketed NCCL allreduce (average) of {2 * n_param * 4 / 1e6:.0f} MB of parameter deltas, "
+                   f"{xchg.num_buckets} buckets of {args.bucket_mb} MiB, overlapped with the backward pass",
+                   "l2": "activations of a step exceed the 126 MB L2 many times over; no flush"},
+        "roofline": {"bound": "tensor", "achieved": flop / (ms * 1e-3) / 1e12, "peak": peak, "unit": "TFLOP/s",
+                     "frac": flop / (ms * 1e-3) / 1e12 / peak, "traffic": None,
+                     "note": "whole step: algorithmic FLOP of all Conv2d / Linear passes per GPU over the step time; the "
+                             "step also contains the HBM-bound ReLU / BatchNorm2d / AvgPool2d / residual passes", **phases},
+        "cpu_baseline": cpu,
+        "e2e": {"value": batch * world / (ms_e2e * 1e-3), "unit": "samples/s", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": int(xs[0].numel() * 4 + obs[0].numel() * 4 + idx[0].numel() * 4),
+                "d2h_bytes_per_step": int(host_out.numel() * 4)},
+        "gpu_launches": None, "tc_status": status, "clocks": clocks}))
+    if world > 1:
+        xchg.close()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -436,7 +647,20 @@ def main():
                     help="arithmetic of the kernels (tagi_set_impl)")
     ap.add_argument("--conv-layers", action="store_true",
                     help="print a per-layer timing table of the Conv2d entry points instead of the benchmark line")
+    ap.add_argument("--workload", default="linear", choices=["linear", "resnet18"],
+                    help="linear: the headline micro-benchmark; resnet18: one training step of the ResNet-18 configuration")
+    ap.add_argument("--image", type=int, default=224, help="resnet18: image extent (224 or a multiple of 8 such as 32)")
+    ap.add_argument("--batch", type=int, default=64, help="resnet18: samples per GPU")
+    ap.add_argument("--bucket-mb", type=int, default=32, help="resnet18: exchange bucket size in MiB")
     args = ap.parse_args()
+    if args.workload == "resnet18" and args.impl == "b200":
+        if args.steps == 200:
+            args.steps = 10
+        args.warmup = 1 if args.profile else max(args.warmup, 3)
+        args.no_cpu = args.no_cpu or args.profile
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        return run_resnet(args, int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")),
+                          int(os.environ.get("LOCAL_RANK", "0")))
     if args.conv_layers:
         args.steps = min(args.steps, 20)
         return run_conv_layers(args)

@@ -28,6 +28,10 @@ class Linear:
     """cutagi.Linear(ip_size, op_size, bias, gain_weight, gain_bias, method) (src/bindings/linear_layer_bindings.cpp:8-22).
     He initialisation as in src/param_init.cpp:5-22,158-187: mu ~ N(0, gain/sqrt(fan_in)), var = gain^2 / fan_in."""
 
+    # called right after the parameter deltas of this layer have been launched (the data-parallel exchange hooks in here,
+    # so that it overlaps the state pass and the backward of the earlier layers)
+    on_ready = None
+
     def __init__(self, input_size, output_size, bias=True, gain_weight=1.0, gain_bias=1.0, init_method="He", seed=None):
         self.input_size, self.output_size, self.bias = input_size, output_size, bias
         rng = np.random.default_rng(seed)
@@ -73,6 +77,8 @@ class Linear:
         lib.tagi_linear_bwd_param(_p(self.var_w), _p(self.var_b), _p(mu_a), _p(dmu), _p(dvar), B, self.input_size,
                                   self.output_size, int(self.bias), _p(self.delta_mu_w), _p(self.delta_var_w),
                                   _p(self.delta_mu_b), _p(self.delta_var_b), _stream())
+        if self.on_ready is not None:
+            self.on_ready()
         if not state_update:
             return None, None
         if jcb is None:
@@ -171,6 +177,8 @@ class Conv2d(Linear):
         lib.tagi_conv2d_bwd_param(ctypes.byref(g), _p(self.var_w), _p(self.var_b), _p(mu_a), _p(dmu), _p(dvar),
                                   _p(self.delta_mu_w), _p(self.delta_var_w), _p(self.delta_mu_b), _p(self.delta_var_b),
                                   _stream())
+        if self.on_ready is not None:
+            self.on_ready()
         if not state_update:
             return None, None
         if jcb is None:
@@ -229,6 +237,8 @@ class BatchNorm2d(Linear):
                           _p(self.mu_w), _p(self.var_w), _p(self.var_b), _p(mu_a), _p(jcb), _p(self.mu_batch),
                           _p(self.var_batch), _p(dmu), _p(dvar), _p(dmu_a), _p(dvar_a), _p(self.delta_mu_w),
                           _p(self.delta_var_w), _p(self.delta_mu_b), _p(self.delta_var_b), _stream())
+        if self.on_ready is not None:
+            self.on_ready()
         return dmu_a, dvar_a
 
 
@@ -503,3 +513,34 @@ def resnet18_spec(image=224, n_out=11):
         spec.append(("res", block(w, w), None))
         prev = w
     return spec + [("pool", final_pool, -1, 0, 0), ("linear", 512, n_out, True)]
+
+
+class Utils:
+    """pytagi.Utils.label_to_obs (pytagi/tagi_utils.py:24-48): class labels -> hierarchical-softmax observations."""
+
+    @staticmethod
+    def class_to_obs(num_classes):
+        """Per class: L = ceil(log2(num_classes)) observations (+1 for a 0 bit, -1 for a 1 bit, most significant bit
+        first) and the one-based output unit that carries each of them: the root for the first bit, then the node reached
+        by the bits read so far, nodes numbered level by level (src/cost.cpp:76-139)."""
+        L = max(1, math.ceil(math.log2(num_classes)))
+        level = [0] * (L + 1)
+        level[L] = num_classes
+        for i in range(L - 1, -1, -1):
+            level[i] = math.ceil(level[i + 1] / 2.0)
+        first = np.cumsum(level) + 1   # one-based index of the first node below each level
+        obs = np.empty((num_classes, L), np.float32)
+        idx = np.ones((num_classes, L), np.int32)
+        for r in range(num_classes):
+            bits = [(r >> (L - 1 - c)) & 1 for c in range(L)]
+            obs[r] = [(-1.0) ** b for b in bits]
+            for c in range(L - 1):
+                prefix = int("".join(str(b) for b in bits[: c + 1]), 2)
+                idx[r, c + 1] = prefix + first[c]
+        return obs, idx, L, int(idx.max())
+
+    def label_to_obs(self, labels, num_classes):
+        """Returns (obs, obs_idx, num_obs): flat float32 / int32 arrays of len(labels) * L entries."""
+        obs, idx, L, _ = self.class_to_obs(num_classes)
+        labels = np.asarray(labels, np.int64).reshape(-1)
+        return obs[labels].reshape(-1), idx[labels].reshape(-1), L

@@ -25,3 +25,25 @@ def test_oracle_training_reproduces_reference_bit_for_bit(oracle):
     for i, p in enumerate(net.p):
         for k in ("mu_w", "var_w", "mu_b", "var_b"):
             assert np.array_equal(p[k].reshape(-1), g[f"{k}{i}"]), (i, k)
+
+
+def test_label_to_obs_matches_the_reference():
+    """Hierarchical-softmax encoding of the device-side mirror (cutagi_b200.nn.Utils, host-only code) against the
+    observations and indices the reference derived from the same labels (tests/golden/train_cfg0_golden.npz)."""
+    import importlib.util
+    import os
+    import sys
+    import types
+    from oracle_train import cfg0_problem
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    g = np.load(os.path.join(root, "tests", "golden", "train_cfg0_golden.npz"))
+    _, _, labels = cfg0_problem(0)
+    # the package imports the CUDA library on import; the encoder itself is plain numpy, so load the class alone
+    src = open(os.path.join(root, "cutagi_b200", "nn.py")).read()
+    body = "import math\nimport numpy as np\n" + src[src.index("class Utils:"):]
+    mod = types.ModuleType("nn_utils_only")
+    exec(compile(body, "nn_utils_only", "exec"), mod.__dict__)
+    u = mod.Utils()
+    for s in range(labels.shape[0]):
+        obs, idx, n = u.label_to_obs(labels[s], 10)
+        assert n == 4 and np.array_equal(obs, g["obs"][s]) and np.array_equal(idx, g["idx"][s])
