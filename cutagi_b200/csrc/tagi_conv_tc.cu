@@ -79,6 +79,67 @@ __global__ void __launch_bounds__(256) delta_gather_kernel(const float *__restri
     }
 }
 
+// The same gathers for 2 x 2 and 3 x 3 kernels, tiled through shared memory so that both sides are coalesced and no
+// thread divides by a run-time number per element: a CTA stages the input patch of up to 32 output pixels
+// (tx x ty of one image) for 16 channels, read along image rows, and then writes the 16 * k * k columns of each pixel
+// as contiguous runs (one warp per pixel, lanes along the columns).
+//   FLIP = false: X[(b, oy, ox)][(c, ky, kx)] = src[b][c][oy*s - off + ky][ox*s - off + kx]      (im2col)
+//   FLIP = true : Z[(b, y, x)][(c, ky, kx)]   = src[b][c][y + off - ky][x + off - kx], stride 1  (the state pass's
+//                 gather of the deltas: the same patch with the taps read in reverse)
+// `g` describes the source tensor (C x H x W per image) and the pixel grid the rows run over (OH x OW).
+struct TileGeom {
+    int B, C, H, W, OH, OW, stride, off, tx, ty, tiles_x, tiles_y, Kc;
+};
+constexpr int GATHER_CT = 16;  // channels per CTA
+
+template <int NSRC, int KS, bool FLIP>
+__global__ void __launch_bounds__(256) gather_tiled_kernel(const float *__restrict__ s0, const float *__restrict__ s1,
+                                                           TileGeom g, float *__restrict__ d0, float *__restrict__ d1) {
+    extern __shared__ float patch[];
+    constexpr int K2 = KS * KS;
+    const int IH = (g.ty - 1) * g.stride + KS, IW = (g.tx - 1) * g.stride + KS, plane = IH * IW;
+    float *p0 = patch, *p1 = patch + GATHER_CT * plane;
+    int t = blockIdx.x;
+    const int tile_x = t % g.tiles_x;
+    t /= g.tiles_x;
+    const int tile_y = t % g.tiles_y, b = t / g.tiles_y;
+    const int c0 = blockIdx.y * GATHER_CT, nc = min(GATHER_CT, g.C - c0);
+    const int oy0 = tile_y * g.ty, ox0 = tile_x * g.tx;
+    // top-left source pixel of the patch
+    const int y0 = FLIP ? oy0 + g.off - (KS - 1) : oy0 * g.stride - g.off;
+    const int x0 = FLIP ? ox0 + g.off - (KS - 1) : ox0 * g.stride - g.off;
+    for (int i = threadIdx.x; i < nc * plane; i += 256) {
+        const int c = i / plane, r = i - c * plane, iy = r / IW, ix = r - iy * IW;
+        const int y = y0 + iy, x = x0 + ix;
+        float v0 = 0.f, v1 = 0.f;
+        if ((unsigned)y < (unsigned)g.H && (unsigned)x < (unsigned)g.W) {
+            const long a = ((long)b * g.C + c0 + c) * g.H * g.W + (long)y * g.W + x;
+            v0 = __ldg(s0 + a);
+            if (NSRC == 2) v1 = __ldg(s1 + a);
+        }
+        p0[i] = v0;
+        if (NSRC == 2) p1[i] = v1;
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, ncols = nc * K2;
+    for (int pix = warp; pix < g.tx * g.ty; pix += 8) {
+        const int py = pix / g.tx, px = pix - py * g.tx;
+        const int oy = oy0 + py, ox = ox0 + px;
+        if (oy >= g.OH || ox >= g.OW) continue;
+        const long row = ((long)b * g.OH + oy) * g.OW + ox;
+        float *o0 = d0 + row * g.Kc + (long)c0 * K2, *o1 = NSRC == 2 ? d1 + row * g.Kc + (long)c0 * K2 : nullptr;
+        const int base = py * g.stride * IW + px * g.stride;
+        for (int j = lane; j < ncols; j += 32) {
+            const int c = j / K2, tap = j - c * K2;
+            int ky = tap / KS, kx = tap - ky * KS;
+            if (FLIP) ky = KS - 1 - ky, kx = KS - 1 - kx;
+            const int a = c * plane + base + ky * IW + kx;
+            o0[j] = p0[a];
+            if (NSRC == 2) o1[j] = p1[a];
+        }
+    }
+}
+
 // W2[(co, tap)][ci] = w[co][ci][tap]: the weights with the input channel as the contiguous index
 __global__ void __launch_bounds__(256) weight_regroup_kernel(const float *__restrict__ w, G g, float *__restrict__ w2) {
     const long total = (long)g.fo * g.Kc;
@@ -153,6 +214,30 @@ inline unsigned grid_for(long total) {
 }
 inline int ok_or(cudaError_t e, const char *what) { return e == cudaSuccess ? TAGI_OK : cuda_fail(e, what); }
 
+// Launches the tiled gather when the kernel size has an instantiation; returns false when the caller should use the
+// general kernel. C, H, W: source tensor; OH, OW: pixel grid of the rows.
+template <int NSRC, bool FLIP>
+bool launch_gather_tiled(const float *s0, const float *s1, int B, int C, int H, int W, int OH, int OW, int k, int stride,
+                         int off, float *d0, float *d1, cudaStream_t st) {
+    if (k != 2 && k != 3) return false;
+    TileGeom g;
+    g.B = B, g.C = C, g.H = H, g.W = W, g.OH = OH, g.OW = OW, g.stride = FLIP ? 1 : stride, g.off = off;
+    g.tx = OW < 32 ? OW : 32;
+    g.ty = 32 / g.tx < OH ? 32 / g.tx : OH;
+    if (g.ty < 1) g.ty = 1;
+    g.tiles_x = (OW + g.tx - 1) / g.tx, g.tiles_y = (OH + g.ty - 1) / g.ty;
+    g.Kc = C * k * k;
+    const int IH = (g.ty - 1) * g.stride + k, IW = (g.tx - 1) * g.stride + k;
+    const size_t smem = (size_t)NSRC * GATHER_CT * IH * IW * sizeof(float);
+    if (smem > 48 * 1024) return false;
+    const dim3 grid((unsigned)((long)B * g.tiles_x * g.tiles_y), (unsigned)((C + GATHER_CT - 1) / GATHER_CT));
+    if (k == 3)
+        gather_tiled_kernel<NSRC, 3, FLIP><<<grid, 256, smem, st>>>(s0, s1, g, d0, d1);
+    else
+        gather_tiled_kernel<NSRC, 2, FLIP><<<grid, 256, smem, st>>>(s0, s1, g, d0, d1);
+    return true;
+}
+
 }  // namespace
 
 // Which Conv2d calls the tensor-core kernels take: 16-byte aligned tensors and every GEMM dimension a multiple of 4
@@ -179,8 +264,9 @@ int conv2d_fwd_tc(const tagi_conv2d_geom &cg, const float *mu_w, const float *va
     int rc = conv_scratch((size_t)2 * rows * g.Kc * sizeof(float), &ws);
     if (rc != TAGI_OK) return rc;
     float *x_mu = ws, *x_var = ws + rows * g.Kc;
-    im2col_kernel<2><<<grid_for(rows * g.Kc), 256, 0, st>>>(mu_a, var_a, g, x_mu, x_var);
-    if ((rc = ok_or(cudaGetLastError(), "im2col_kernel launch")) != TAGI_OK) return rc;
+    if (!launch_gather_tiled<2, false>(mu_a, var_a, g.B, g.fi, g.hi, g.wi, g.ho, g.wo, g.k, g.stride, g.off, x_mu, x_var, st))
+        im2col_kernel<2><<<grid_for(rows * g.Kc), 256, 0, st>>>(mu_a, var_a, g, x_mu, x_var);
+    if ((rc = ok_or(cudaGetLastError(), "im2col kernel launch")) != TAGI_OK) return rc;
     // rows = (image, output pixel), columns = output channels: exactly Linear's forward, written as [b][co][pixel]
     return linear_fwd_tc(mu_w, var_w, mu_b, var_b, x_mu, x_var, (int)rows, g.Kc, g.fo, mu_z, var_z, st, g.woho);
 }
@@ -210,8 +296,9 @@ int conv2d_bwd_state_tc(const tagi_conv2d_geom &cg, const float *mu_w, const flo
     rc = conv_scratch(((size_t)2 * rows * kd + (size_t)g.fo * g.Kc) * sizeof(float), &ws);
     if (rc != TAGI_OK) return rc;
     float *z_mu = ws, *z_var = ws + rows * kd, *w2 = ws + 2 * rows * kd;
-    delta_gather_kernel<<<grid_for(rows * kd), 256, 0, st>>>(dmu_z, dvar_z, g, z_mu, z_var);
-    if ((rc = ok_or(cudaGetLastError(), "delta_gather_kernel launch")) != TAGI_OK) return rc;
+    if (!launch_gather_tiled<2, true>(dmu_z, dvar_z, g.B, g.fo, g.ho, g.wo, g.hi, g.wi, g.k, 1, g.off, z_mu, z_var, st))
+        delta_gather_kernel<<<grid_for(rows * kd), 256, 0, st>>>(dmu_z, dvar_z, g, z_mu, z_var);
+    if ((rc = ok_or(cudaGetLastError(), "delta gather kernel launch")) != TAGI_OK) return rc;
     weight_regroup_kernel<<<grid_for((long)g.fo * g.Kc), 256, 0, st>>>(mu_w, g, w2);
     if ((rc = ok_or(cudaGetLastError(), "weight_regroup_kernel launch")) != TAGI_OK) return rc;
     // Linear's state pass with "output features" = (co, tap) and "input features" = ci; Jacobian and outputs in
@@ -230,8 +317,9 @@ int conv2d_bwd_param_tc(const tagi_conv2d_geom &cg, const float *var_w, const fl
     int rc = conv_scratch(((size_t)rows * g.Kc + (size_t)2 * rows * g.fo + part) * sizeof(float), &ws);
     if (rc != TAGI_OK) return rc;
     float *x_mu = ws, *d_mu = ws + rows * g.Kc, *d_var = d_mu + rows * g.fo, *split_ws = d_var + rows * g.fo;
-    im2col_kernel<1><<<grid_for(rows * g.Kc), 256, 0, st>>>(mu_a, nullptr, g, x_mu, nullptr);
-    if ((rc = ok_or(cudaGetLastError(), "im2col_kernel launch")) != TAGI_OK) return rc;
+    if (!launch_gather_tiled<1, false>(mu_a, nullptr, g.B, g.fi, g.hi, g.wi, g.ho, g.wo, g.k, g.stride, g.off, x_mu, nullptr, st))
+        im2col_kernel<1><<<grid_for(rows * g.Kc), 256, 0, st>>>(mu_a, nullptr, g, x_mu, nullptr);
+    if ((rc = ok_or(cudaGetLastError(), "im2col kernel launch")) != TAGI_OK) return rc;
     dim3 grid((g.woho + 31) / 32, (g.fo + 31) / 32, g.B);
     delta_regroup_kernel<<<grid, 256, 0, st>>>(dmu_z, dvar_z, g, d_mu, d_var);
     if ((rc = ok_or(cudaGetLastError(), "delta_regroup_kernel launch")) != TAGI_OK) return rc;
