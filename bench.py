@@ -159,6 +159,7 @@ def run_b200(args, rank, world, local_rank):
 
     torch.cuda.set_device(local_rank)
     lib.tagi_set_impl({"auto": 0, "ffma": 1, "tf32x3": 2}[args.kernel_impl])
+    lib.tagi_tc_set_sm_budget(args.sm_budget if args.sm_budget >= 0 else (0 if world == 1 else 132))
     devname = torch.cuda.get_device_name(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
@@ -647,6 +648,9 @@ def main():
                     help="arithmetic of the kernels (tagi_set_impl)")
     ap.add_argument("--conv-layers", action="store_true",
                     help="print a per-layer timing table of the Conv2d entry points instead of the benchmark line")
+    ap.add_argument("--sm-budget", type=int, default=-1,
+                    help="SMs the tensor-core kernels plan their tiles for (tagi_tc_set_sm_budget); default: all on one GPU, "
+                         "132 when the exchange's NCCL kernels run next to them (N > 1)")
     ap.add_argument("--workload", default="linear", choices=["linear", "resnet18"],
                     help="linear: the headline micro-benchmark; resnet18: one training step of the ResNet-18 configuration")
     ap.add_argument("--image", type=int, default=224, help="resnet18: image extent (224 or a multiple of 8 such as 32)")

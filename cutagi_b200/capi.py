@@ -29,6 +29,7 @@ _SIGNATURES = {
     "tagi_version": [],
     "tagi_tc_status": [C.POINTER(_i), _i],
     "tagi_tc_set_chunked": [_i],
+    "tagi_tc_set_sm_budget": [_i],
     "tagi_tc_set_variant": [_i],
     "tagi_linear_fwd": [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _p],
     "tagi_linear_bwd_state": [_p, _p, _p, _p, _i, _i, _i, _p, _p, _p],

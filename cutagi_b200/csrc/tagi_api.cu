@@ -55,6 +55,7 @@ int tagi_tc_status(int *status, int reset) {
     return linear_tc_status(status, reset);
 }
 int tagi_tc_set_chunked(int on) { return linear_tc_set_chunked(on); }
+int tagi_tc_set_sm_budget(int sms) { return linear_tc_set_sm_budget(sms); }
 int tagi_tc_set_variant(int v) { return linear_tc_set_variant(v); }
 
 // true -> run the tensor-core kernel; sets rc when the forced implementation cannot take the shape

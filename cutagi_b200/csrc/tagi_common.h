@@ -47,6 +47,7 @@ int linear_bias_delta(const float *var_b, const float *dmu_z, const float *dvar_
 bool linear_tc_supported(int B, int K, int N, std::initializer_list<const void *> ptrs);
 bool linear_tc_profitable(int B, int K, int N);
 int linear_tc_set_chunked(int on);
+int linear_tc_set_sm_budget(int sms);
 int linear_tc_set_variant(int v);
 int linear_tc_status(int *out, int reset);
 int linear_fwd_tc(const float *mu_w, const float *var_w, const float *mu_b, const float *var_b, const float *mu_a,

@@ -1064,6 +1064,7 @@ int g_deep = 0;     // deeper derived rings where tensor memory allows (diagnost
 int g_variant = 3;  // 3: CTA pairs (default; passes with < 256 output rows use 1); 1: one CTA, A-side tiles in tensor
                     // memory ("ts"); 0: every operand tile in shared memory ("ss")
 int g_pair_bn = 0;  // forces the pair kernel's tile width (diagnostic); 0 = chosen per launch
+int g_sms = 148;    // SMs the tile planning counts on (tagi_tc_set_sm_budget)
 int g_chunked = 1;  // 1: contraction accumulated in chunks of 256 (default); 0: one accumulation chain (diagnostic)
 
 template <int OP>
@@ -1080,7 +1081,7 @@ int launch(const CUtensorMap &a0, const CUtensorMap &a1, const CUtensorMap &b0, 
     long best = -1;
     for (int w = TN; w >= 64; w -= 16) {
         const long tiles = row_tiles * ((epi.cols + w - 1) / w);
-        const long cost = ((tiles + 147) / 148) * (w + 16);  // + 16: per-tile work that does not shrink with the width
+        const long cost = ((tiles + g_sms - 1) / g_sms) * (w + 16);  // + 16: per-tile work that does not shrink with the width
         if (best < 0 || cost < best) best = cost, bn = w;
     }
     const unsigned slices = epi.slabs_per_slice > 0 ? (unsigned)(((kdim + BK - 1) / BK + epi.slabs_per_slice - 1) / epi.slabs_per_slice) : 1u;
@@ -1138,7 +1139,7 @@ int launch_pair(const CUtensorMap &a0, const CUtensorMap &a1, const CUtensorMap 
     long best = -1;
     for (int w = TN; w >= 64; w -= 16) {  // 74 pairs run at a time
         const long tiles = row_tiles * ((epi.cols + w - 1) / w);
-        const long cost = ((tiles + 73) / 74) * (w + 16);
+        const long cost = ((tiles + g_sms / 2 - 1) / (g_sms / 2)) * (w + 16);
         if (best < 0 || cost < best) best = cost, bn = w;
     }
     if (g_pair_bn) bn = g_pair_bn;
@@ -1207,6 +1208,11 @@ int linear_tc_set_variant(int v) {
     g_deep = v == 2;
     if (v == 2) v = 1;
     g_variant = v;
+    return TAGI_OK;
+}
+int linear_tc_set_sm_budget(int sms) {
+    if (sms != 0 && (sms < 2 || sms > 148)) return fail(TAGI_ERR_INVALID_ARGUMENT, "SM budget must be 0 (all) or 2 .. 148");
+    g_sms = sms == 0 ? 148 : sms;
     return TAGI_OK;
 }
 int linear_tc_set_chunked(int on) {

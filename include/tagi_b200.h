@@ -59,6 +59,12 @@ int tagi_tc_set_chunked(int on);
  * operand tile in shared memory (the simplest kernel, bound by shared-memory bandwidth); 64, 80, 96, 112 or 128: as 3
  * with that tile width. Same results in all of them. */
 int tagi_tc_set_variant(int v);
+/* How many SMs the TF32X3 kernels plan their tile widths for: 0 (default) = all 148. A caller that runs another kernel
+ * next to them (the data-parallel exchange's NCCL kernels on their own stream hold some SMs for the length of a pass)
+ * passes the number that is left, so that a pass is cut into whole waves of the SMs it really gets: with 8 SMs taken,
+ * 148 tiles would need three waves of 70 pairs where 128 wider tiles need two. Results do not depend on it. No
+ * counterpart in the reference. */
+int tagi_tc_set_sm_budget(int sms);
 
 const char *tagi_last_error_string(void);
 /* Library version as major*10000 + minor*100 + patch. */

@@ -211,6 +211,23 @@ def test_tensor_core_one_cta_variants(G, oracle, force_impl, variant):
         lib.tagi_tc_set_variant(3)
 
 
+@pytest.mark.parametrize("sms", [132, 64])
+def test_tensor_core_sm_budget_only_changes_the_tiling(G, oracle, force_impl, sms):
+    """tagi_tc_set_sm_budget: tiles planned for fewer SMs (the exchange's kernels hold the rest); same results."""
+    from cutagi_b200 import capi
+    from cutagi_b200.capi import lib
+    force_impl(capi.IMPL_TF32X3)
+    lib.tagi_tc_set_sm_budget(sms)
+    try:
+        rng = np.random.default_rng(23)
+        _run_all(G, oracle, G.linear_inputs(rng, 512, 1024, 1536), tag=f"budget {sms} ")
+        assert capi.tc_status() == 0
+        with pytest.raises(capi.TagiError):
+            lib.tagi_tc_set_sm_budget(1)
+    finally:
+        lib.tagi_tc_set_sm_budget(0)
+
+
 def test_tensor_core_rejects_unaligned(G, force_impl):
     import torch
     from cutagi_b200 import capi
