@@ -634,6 +634,79 @@ def run_resnet(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def run_resnet_module(args):
+    """The same ResNet-18 step driven through cuTAGI's own extension module, the way pytagi drives it (host arrays in,
+    `Sequential.forward / backward / step`, `OutputUpdater.update_using_indices`): `--engine dropin` = cuTAGI with its
+    LinearCuda / Conv2dCuda on this library's C ABI (integration/_build), `--engine stock` = the unmodified cuTAGI CUDA
+    build for sm_100a (integration/_build/stock). Both are built where the cuTAGI sources are and travel as binaries.
+    Wall-clock per step, device synchronised by reading the outputs back; one GPU."""
+    import glob
+    sub = os.path.join(ROOT, "integration", "_build", "stock" if args.engine == "stock" else "")
+    if not glob.glob(os.path.join(sub, "cutagi*.so")):
+        print(json.dumps({"engine": args.engine, "unavailable": f"no cutagi module under {os.path.relpath(sub, ROOT)} "
+                          "(make -C integration [stock] needs the cuTAGI sources)"}))
+        return
+    sys.path.insert(0, sub)
+    import cutagi as m
+    image, batch = args.image, args.batch
+    keep = []
+
+    def conv(i, o, k, stride=1, pad=0, pad_type=1, w=0, h=0):
+        return m.Conv2d(i, o, k, False, stride, pad, pad_type, w, h)
+
+    def block(i, o, stride=1, pt=1):
+        layers = [conv(i, o, 3, stride, 1, pt), m.ReLU(), m.BatchNorm2d(o), conv(o, o, 3, 1, 1, 1), m.ReLU(), m.BatchNorm2d(o)]
+        keep.append(layers)
+        return m.LayerBlock(layers)
+    if image == 224:
+        layers = [conv(3, 64, 6, 2, 2, 1, 224, 224), m.ReLU(), m.BatchNorm2d(64), m.AvgPool2d(3, 2, 1, 2)]
+        final_pool = 7
+    else:
+        layers = [conv(3, 64, 3, 1, 1, 1, image, image), m.ReLU(), m.BatchNorm2d(64)]
+        final_pool = image // 8
+    prev = 64
+    for w in (64, 128, 256, 512):
+        if w == prev:
+            layers.append(m.ResNetBlock(block(prev, w)))
+        else:
+            sc = [conv(prev, w, 2, 2), m.ReLU(), m.BatchNorm2d(w)]
+            keep.append(sc)
+            layers.append(m.ResNetBlock(block(prev, w, 2, 2), m.LayerBlock(sc)))
+        layers.append(m.ResNetBlock(block(w, w)))
+        prev = w
+    layers += [m.AvgPool2d(final_pool), m.Linear(512, 11, True)]
+    keep.append(layers)
+    net = m.Sequential(layers)
+    net.to_device("cuda")
+    upd, hrc = m.OutputUpdater(net.device), m.Utils()
+    rng = np.random.default_rng(100)
+    x = rng.standard_normal(batch * 3 * image * image, dtype=np.float32)
+    obs, idx, _ = hrc.label_to_obs_wrapper(rng.integers(0, 10, batch).astype(np.int32), 10)
+    obs, idx, var_y = [float(v) for v in obs], [int(v) for v in idx], [1.0] * (batch * 4)
+
+    def step():
+        net.forward(x, None)
+        upd.update_using_indices(net.output_z_buffer, obs, var_y, idx, net.input_delta_z_buffer)
+        net.backward()
+        net.step()
+    for _ in range(max(1, min(args.warmup, 2))):
+        step()
+    net.get_outputs()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    mu, _ = net.get_outputs()
+    dt = (time.perf_counter() - t0) / args.steps
+    print(json.dumps({"metric": "TAGI ResNet-18 training samples/s", "engine":
+                      {"stock": "unmodified cuTAGI CUDA build (its own Linear / Conv2d kernels)",
+                       "dropin": "cuTAGI with LinearCuda / Conv2dCuda on libtagi_b200"}[args.engine],
+                      "value": batch / dt, "unit": "samples/s", "n_gpus": 1, "steps": args.steps, "ms_per_step": dt * 1e3,
+                      "timing": "wall clock around the module's own forward / backward / step calls (host input arrays, "
+                                "outputs read back at the end)",
+                      "config": {"workload": f"resnet18_relu_3x{image}x{image}_batch{batch}"},
+                      "finite_outputs": bool(np.all(np.isfinite(np.asarray(mu))))}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -653,13 +726,18 @@ def main():
                          "132 when the exchange's NCCL kernels run next to them (N > 1)")
     ap.add_argument("--workload", default="linear", choices=["linear", "resnet18"],
                     help="linear: the headline micro-benchmark; resnet18: one training step of the ResNet-18 configuration")
+    ap.add_argument("--engine", default="native", choices=["native", "dropin", "stock"],
+                    help="resnet18: native = this repository's device-side mirror; dropin / stock = cuTAGI's own module "
+                         "with / without this library's Linear and Conv2d kernels")
     ap.add_argument("--image", type=int, default=224, help="resnet18: image extent (224 or a multiple of 8 such as 32)")
     ap.add_argument("--batch", type=int, default=64, help="resnet18: samples per GPU")
     ap.add_argument("--bucket-mb", type=int, default=32, help="resnet18: exchange bucket size in MiB")
     args = ap.parse_args()
     if args.workload == "resnet18" and args.impl == "b200":
         if args.steps == 200:
-            args.steps = 10
+            args.steps = 10 if args.engine == "native" else 3
+        if args.engine != "native":
+            return run_resnet_module(args)
         args.warmup = 1 if args.profile else max(args.warmup, 3)
         args.no_cpu = args.no_cpu or args.profile
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
