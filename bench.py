@@ -707,6 +707,46 @@ def run_resnet_module(args):
                       "finite_outputs": bool(np.all(np.isfinite(np.asarray(mu))))}))
 
 
+def run_linear_module(args):
+    """The headline Linear layer (B = 1024, 4096 -> 4096) driven through cuTAGI's own extension module: one-layer
+    Sequential with input state update on, so that a step runs the forward, the parameter and the state pass.
+    `--engine stock` times cuTAGI's own CUDA kernels on this GPU, `--engine dropin` the same module on this library.
+    Wall clock per step including the module's host-to-device copy of the inputs (its public API takes host arrays)."""
+    import glob
+    sub = os.path.join(ROOT, "integration", "_build", "stock" if args.engine == "stock" else "")
+    if not glob.glob(os.path.join(sub, "cutagi*.so")):
+        print(json.dumps({"engine": args.engine, "unavailable": f"no cutagi module under {os.path.relpath(sub, ROOT)}"}))
+        return
+    sys.path.insert(0, sub)
+    import cutagi as m
+    layers = [m.Linear(K, N, True)]
+    net = m.Sequential(layers)
+    net.input_state_update = True
+    net.to_device("cuda")
+    x = make_inputs(100)
+    upd = m.OutputUpdater(net.device)
+    mu_x, var_x = x["mu_a"].reshape(-1), x["var_a"].reshape(-1)
+    obs, var_obs = np.zeros(B * N, np.float32), np.ones(B * N, np.float32)
+
+    def step(update):
+        net.forward(mu_x, var_x)
+        if update:
+            upd.update(net.output_z_buffer, obs, var_obs, net.input_delta_z_buffer)
+        net.backward()
+    step(True)
+    net.get_outputs()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step(False)     # the deltas of the first update stay in the buffer: same kernels, no host-side list conversion
+    net.get_outputs()
+    dt = (time.perf_counter() - t0) / args.steps
+    print(json.dumps({"metric": METRIC, "engine": {"stock": "unmodified cuTAGI CUDA build", "dropin":
+                      "cuTAGI with LinearCuda on libtagi_b200"}[args.engine], "value": FLOP_STEP / dt / 1e12, "unit": UNIT,
+                      "n_gpus": 1, "steps": args.steps, "ms_per_step": dt * 1e3, "config": {"workload": WORKLOAD},
+                      "timing": "wall clock around Sequential.forward(host arrays) + backward; includes the module's copy "
+                                "of 33.5 MB of inputs to the device per step"}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -743,6 +783,9 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         return run_resnet(args, int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")),
                           int(os.environ.get("LOCAL_RANK", "0")))
+    if args.workload == "linear" and args.engine != "native" and args.impl == "b200":
+        args.steps = min(args.steps, 20)
+        return run_linear_module(args)
     if args.conv_layers:
         args.steps = min(args.steps, 20)
         return run_conv_layers(args)
