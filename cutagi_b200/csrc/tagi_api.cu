@@ -167,18 +167,20 @@ int tagi_conv2d_out_size(int k, int stride, int wi, int hi, int pad, int pad_typ
 }
 
 // true -> run Conv2d on the tensor-core kernels; sets rc when the forced implementation cannot take the layer
-static bool pick_conv_tc(const char *who, const tagi_conv2d_geom &g, std::initializer_list<const void *> ptrs, int *rc) {
+static bool pick_conv_tc(const char *who, const tagi_conv2d_geom &g, int pass, std::initializer_list<const void *> ptrs,
+                         int *rc) {
     *rc = TAGI_OK;
     const int impl = current_impl();
     if (impl == TAGI_IMPL_FFMA) return false;
-    const bool ok = conv_tc_supported(g, ptrs);
+    const bool ok = conv_tc_supported(g, pass, ptrs);
     if (impl == TAGI_IMPL_TF32X3) {
         if (!ok)
-            *rc = fail(TAGI_ERR_UNSUPPORTED, std::string(who) + ": TF32X3 needs 16-byte aligned tensors and fi, fo, "
-                                                               "fi*k*k, B*ho*wo and B*hi*wi that are multiples of 4");
+            *rc = fail(TAGI_ERR_UNSUPPORTED, std::string(who) + ": TF32X3 needs 16-byte aligned tensors and fi*k*k (every "
+                                                               "pass), fo (backward passes) and fi (state pass at stride 1) "
+                                                               "that are multiples of 4");
         return ok;
     }
-    return ok && conv_tc_profitable(g);
+    return ok && conv_tc_profitable(g, pass);
 }
 
 static int check_geom(const tagi_conv2d_geom *g) {
@@ -213,7 +215,7 @@ int tagi_conv2d_fwd(const tagi_conv2d_geom *g, const float *mu_w, const float *v
         mu_b = var_b = nullptr;
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (pick_conv_tc(__func__, *g, {mu_w, var_w, mu_b, var_b, mu_a, var_a, mu_z, var_z}, &rc))
+    if (pick_conv_tc(__func__, *g, CONV_PASS_FWD, {mu_w, var_w, mu_b, var_b, mu_a, var_a, mu_z, var_z}, &rc))
         return conv2d_fwd_tc(*g, mu_w, var_w, mu_b, var_b, mu_a, var_a, mu_z, var_z, st);
     if (rc != TAGI_OK) return rc;
     return conv2d_fwd_ffma(*g, mu_w, var_w, mu_b, var_b, mu_a, var_a, mu_z, var_z, st);
@@ -230,7 +232,7 @@ int tagi_conv2d_bwd_state(const tagi_conv2d_geom *g, const float *mu_w, const fl
     TAGI_PTR(dmu_a);
     TAGI_PTR(dvar_a);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (pick_conv_tc(__func__, *g, {mu_w, jcb, dmu_z, dvar_z, dmu_a, dvar_a}, &rc))
+    if (pick_conv_tc(__func__, *g, CONV_PASS_STATE, {mu_w, jcb, dmu_z, dvar_z, dmu_a, dvar_a}, &rc))
         return conv2d_bwd_state_tc(*g, mu_w, jcb, dmu_z, dvar_z, dmu_a, dvar_a, st);
     if (rc != TAGI_OK) return rc;
     return conv2d_bwd_state_ffma(*g, mu_w, jcb, dmu_z, dvar_z, dmu_a, dvar_a, st);
@@ -253,7 +255,7 @@ int tagi_conv2d_bwd_param(const tagi_conv2d_geom *g, const float *var_w, const f
         TAGI_PTR(dvar_b);
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (pick_conv_tc(__func__, *g, {var_w, mu_a, dmu_z, dvar_z, dmu_w, dvar_w}, &rc)) {
+    if (pick_conv_tc(__func__, *g, CONV_PASS_PARAM, {var_w, mu_a, dmu_z, dvar_z, dmu_w, dvar_w}, &rc)) {
         rc = conv2d_bwd_param_tc(*g, var_w, mu_a, dmu_z, dvar_z, dmu_w, dvar_w, st);
         if (rc == TAGI_OK && g->has_bias) rc = conv_bias_delta(*g, var_b, dmu_z, dvar_z, dmu_b, dvar_b, st);
         return rc;

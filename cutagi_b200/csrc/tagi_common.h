@@ -72,8 +72,9 @@ int conv_scratch(size_t bytes, float **out);  // library-owned, grow-only, per d
 int conv_bias_delta(const tagi_conv2d_geom &g, const float *var_b, const float *dmu_z, const float *dvar_z,
                     float *dmu_b, float *dvar_b, cudaStream_t st);
 // Conv2d on the tensor-core Linear kernels (tagi_conv_tc.cu)
-bool conv_tc_supported(const tagi_conv2d_geom &g, std::initializer_list<const void *> ptrs);
-bool conv_tc_profitable(const tagi_conv2d_geom &g);
+enum { CONV_PASS_FWD = 0, CONV_PASS_STATE = 1, CONV_PASS_PARAM = 2 };
+bool conv_tc_supported(const tagi_conv2d_geom &g, int pass, std::initializer_list<const void *> ptrs);
+bool conv_tc_profitable(const tagi_conv2d_geom &g, int pass);
 int conv2d_fwd_tc(const tagi_conv2d_geom &g, const float *mu_w, const float *var_w, const float *mu_b,
                   const float *var_b, const float *mu_a, const float *var_a, float *mu_z, float *var_z,
                   cudaStream_t st);

@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(256) delta_gather_kernel(const float *__restri
     }
 }
 
-// The same gathers for 2 x 2 and 3 x 3 kernels, tiled through shared memory so that both sides are coalesced and no
+// The same gathers for 2 x 2, 3 x 3 and 6 x 6 kernels, tiled through shared memory so that both sides are coalesced and no
 // thread divides by a run-time number per element: a CTA stages the input patch of up to 32 output pixels
 // (tx x ty of one image) for 16 channels, read along image rows, and then writes the 16 * k * k columns of each pixel
 // as contiguous runs (one warp per pixel, lanes along the columns).
@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(256) delta_gather_kernel(const float *__restri
 //                 gather of the deltas: the same patch with the taps read in reverse)
 // `g` describes the source tensor (C x H x W per image) and the pixel grid the rows run over (OH x OW).
 struct TileGeom {
-    int B, C, H, W, OH, OW, stride, off, tx, ty, tiles_x, tiles_y, Kc;
+    int B, C, H, W, OH, OW, stride, off, tx, ty, tiles_x, tiles_y, Kc, ct;  // ct: channels staged per CTA (<= 16)
 };
 constexpr int GATHER_CT = 16;  // channels per CTA
 
@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(256) gather_tiled_kernel(const float *__restri
     extern __shared__ float patch[];
     constexpr int K2 = KS * KS;
     const int IH = (g.ty - 1) * g.stride + KS, IW = (g.tx - 1) * g.stride + KS, plane = IH * IW;
-    float *p0 = patch, *p1 = patch + GATHER_CT * plane;
+    float *p0 = patch, *p1 = patch + g.ct * plane;
     int t = blockIdx.x;
     const int tile_x = t % g.tiles_x;
     t /= g.tiles_x;
@@ -187,16 +187,13 @@ __global__ void __launch_bounds__(256) col2im_kernel(const float *__restrict__ c
         const long n = t / g.wihi;  // b * fi + ci
         const int y = q / g.wi, x = q - y * g.wi;
         float a0 = 0.f, a1 = 0.f;
-        for (int ky = 0; ky < g.k; ky++) {
-            const int ty = y + g.off - ky;
-            if (ty < 0) break;
-            const int oy = ty / g.stride;
-            if (oy * g.stride != ty || oy >= g.ho) continue;
-            for (int kx = 0; kx < g.k; kx++) {
-                const int tx = x + g.off - kx;
-                if (tx < 0) break;
-                const int ox = tx / g.stride;
-                if (ox * g.stride != tx || ox >= g.wo) continue;
+        // output rows / columns whose window contains the pixel: oy * s - off <= y <= oy * s - off + k - 1
+        const int oy_lo = max(0, (y + g.off - g.k + g.stride) / g.stride), oy_hi = min(g.ho - 1, (y + g.off) / g.stride);
+        const int ox_lo = max(0, (x + g.off - g.k + g.stride) / g.stride), ox_hi = min(g.wo - 1, (x + g.off) / g.stride);
+        for (int oy = oy_lo; oy <= oy_hi; oy++) {
+            const int ky = y + g.off - oy * g.stride;
+            for (int ox = ox_lo; ox <= ox_hi; ox++) {
+                const int kx = x + g.off - ox * g.stride;
                 const long i = (n * g.k2 + ky * g.k + kx) * g.woho + (long)oy * g.wo + ox;
                 a0 += __ldg(c0 + i);
                 a1 += __ldg(c1 + i);
@@ -219,7 +216,7 @@ inline int ok_or(cudaError_t e, const char *what) { return e == cudaSuccess ? TA
 template <int NSRC, bool FLIP>
 bool launch_gather_tiled(const float *s0, const float *s1, int B, int C, int H, int W, int OH, int OW, int k, int stride,
                          int off, float *d0, float *d1, cudaStream_t st) {
-    if (k != 2 && k != 3) return false;
+    if (k != 2 && k != 3 && k != 6) return false;
     TileGeom g;
     g.B = B, g.C = C, g.H = H, g.W = W, g.OH = OH, g.OW = OW, g.stride = FLIP ? 1 : stride, g.off = off;
     g.tx = OW < 32 ? OW : 32;
@@ -227,12 +224,15 @@ bool launch_gather_tiled(const float *s0, const float *s1, int B, int C, int H, 
     if (g.ty < 1) g.ty = 1;
     g.tiles_x = (OW + g.tx - 1) / g.tx, g.tiles_y = (OH + g.ty - 1) / g.ty;
     g.Kc = C * k * k;
+    g.ct = C < GATHER_CT ? C : GATHER_CT;
     const int IH = (g.ty - 1) * g.stride + k, IW = (g.tx - 1) * g.stride + k;
-    const size_t smem = (size_t)NSRC * GATHER_CT * IH * IW * sizeof(float);
+    const size_t smem = (size_t)NSRC * g.ct * IH * IW * sizeof(float);
     if (smem > 48 * 1024) return false;
     const dim3 grid((unsigned)((long)B * g.tiles_x * g.tiles_y), (unsigned)((C + GATHER_CT - 1) / GATHER_CT));
     if (k == 3)
         gather_tiled_kernel<NSRC, 3, FLIP><<<grid, 256, smem, st>>>(s0, s1, g, d0, d1);
+    else if (k == 6)
+        gather_tiled_kernel<NSRC, 6, FLIP><<<grid, 256, smem, st>>>(s0, s1, g, d0, d1);
     else
         gather_tiled_kernel<NSRC, 2, FLIP><<<grid, 256, smem, st>>>(s0, s1, g, d0, d1);
     return true;
@@ -242,17 +242,24 @@ bool launch_gather_tiled(const float *s0, const float *s1, int B, int C, int H, 
 
 // Which Conv2d calls the tensor-core kernels take: 16-byte aligned tensors and every GEMM dimension a multiple of 4
 // (TMA row pitches, vector stores), and enough work for 128-row tiles.
-bool conv_tc_supported(const tagi_conv2d_geom &cg, std::initializer_list<const void *> ptrs) {
+bool conv_tc_supported(const tagi_conv2d_geom &cg, int pass, std::initializer_list<const void *> ptrs) {
     const G g = geom_of(cg);
-    if (g.fo % 4 || g.fi % 4 || g.Kc % 4) return false;
-    if (((long)g.B * g.woho) % 4 || ((long)g.B * g.wihi) % 4) return false;
+    // row pitches of the matrices a pass hands to TMA (16-byte multiples) and its vector stores
+    bool ok = g.Kc % 4 == 0;                                                   // X and the weights [fo][Kc]
+    if (pass == CONV_PASS_PARAM) ok = ok && g.fo % 4 == 0;                      // D [rows][fo]
+    if (pass == CONV_PASS_STATE)
+        ok = ok && g.fo % 4 == 0 && (g.stride > 1 || g.fi % 4 == 0);           // D / Z, regrouped weights [..][fi]
+    if (!ok) return false;
     for (const void *p : ptrs)
         if (p && !aligned16(p)) return false;
     return true;
 }
-bool conv_tc_profitable(const tagi_conv2d_geom &cg) {
+// enough work for 128-row tiles with a contraction and a width that fill an MMA
+bool conv_tc_profitable(const tagi_conv2d_geom &cg, int pass) {
     const G g = geom_of(cg);
-    return g.fo >= 32 && g.fi >= 16 && (long)g.B * g.woho >= 256;
+    if ((long)g.B * g.woho < 256 || g.fo < 32) return false;
+    // the GEMM's width is fi for the stride-1 state pass and fi*k*k for every other pass
+    return pass == CONV_PASS_STATE && g.stride == 1 ? g.fi >= 16 : g.Kc >= 64;
 }
 
 int conv2d_fwd_tc(const tagi_conv2d_geom &cg, const float *mu_w, const float *var_w, const float *mu_b,

@@ -251,20 +251,14 @@ __global__ void __launch_bounds__(BLOCK) avgpool2d_bwd_kernel(const float *__res
             sv = __ldg(dv + oy * g.wo + ox);
         }
     } else {
-        for (int ky = g.k - 1; ky >= 0; ky--) {
-            const int ty = y + g.off - ky;
-            if (ty < 0 || ty % g.stride) continue;
-            const int oy = ty / g.stride;
-            if (oy >= g.ho) continue;
-            for (int kx = g.k - 1; kx >= 0; kx--) {
-                const int tx = x + g.off - kx;
-                if (tx < 0 || tx % g.stride) continue;
-                const int ox = tx / g.stride;
-                if (ox >= g.wo) continue;
+        // cells whose window contains the pixel, in ascending order (the order of the reference's index table)
+        const int oy_lo = max(0, (y + g.off - g.k + g.stride) / g.stride), oy_hi = min(g.ho - 1, (y + g.off) / g.stride);
+        const int ox_lo = max(0, (x + g.off - g.k + g.stride) / g.stride), ox_hi = min(g.wo - 1, (x + g.off) / g.stride);
+        for (int oy = oy_lo; oy <= oy_hi; oy++)
+            for (int ox = ox_lo; ox <= ox_hi; ox++) {
                 sm += __ldg(dm + oy * g.wo + ox);
                 sv += __ldg(dv + oy * g.wo + ox);
             }
-        }
     }
     const float j = jcb ? __ldg(jcb + t) : 1.f;
     const int k2 = g.k * g.k;

@@ -120,6 +120,7 @@ TC_GEOMS = [
     dict(B=6, fi=16, hi=30, wi=30, fo=32, k=3, stride=1, pad=1, pad_type=1, has_bias=0),    # ragged last slice
     dict(B=4, fi=16, hi=15, wi=15, fo=32, k=3, stride=2, pad=1, pad_type=1, has_bias=1),    # stride 2, odd image
     dict(B=4, fi=8, hi=19, wi=19, fo=16, k=5, stride=3, pad=2, pad_type=1, has_bias=0),     # stride 3, 5x5
+    dict(B=4, fi=3, hi=32, wi=32, fo=64, k=6, stride=2, pad=2, pad_type=1, has_bias=0),     # ResNet stem: 3 channels, 6x6
 ]
 
 
