@@ -457,11 +457,13 @@ def resnet_flops(spec, shape):
     return total
 
 
-def run_resnet(args, rank, world, local_rank):
-    """Side workload (not the headline line): one TAGI training step of the reference's ResNet-18 (ReLU variant, 11
-    hierarchical-softmax outputs) on 64 x 3 x 224 x 224 synthetic N(0,1) images per GPU through the device-side mirror
-    of the pytagi API: forward, output update, backward with the parameter deltas averaged over the ranks (bucketed NCCL
-    exchange overlapped with the rest of the backward pass), capped update. Prints one JSON line: samples/s."""
+def run_network(args, rank, world, local_rank):
+    """Side workloads (not the headline line): one TAGI training step of a whole network of the benchmark configurations
+    through the device-side mirror of the pytagi API: the reference's ResNet-18 (ReLU variant, 11 hierarchical-softmax
+    outputs, 64 x 3 x 224 x 224 N(0,1) images per GPU), the CIFAR-shaped CNN (batch 128) or the deep regression MLP
+    (1 -> 4096 -> 4096 -> 4096 -> 1, batch 2048). Step = forward, output update, backward with the parameter deltas
+    averaged over the ranks (bucketed NCCL exchange overlapped with the rest of the backward pass), capped update.
+    Prints one JSON line: samples/s."""
     import torch
     import torch.distributed as dist
     from cutagi_b200 import nn
@@ -471,18 +473,42 @@ def run_resnet(args, rank, world, local_rank):
     lib.tagi_set_impl({"auto": 0, "ffma": 1, "tf32x3": 2}[args.kernel_impl])
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    image, batch = args.image, args.batch
-    spec = nn.resnet18_spec(image)
-    net = nn.build(spec, (3, image, image), seed=1234)      # same parameters on every rank
-    upd, utils = nn.OutputUpdater(), nn.Utils()
+    image = args.image
     rng = np.random.default_rng(100 + rank)
     n_sets = 2
-    xs = [torch.from_numpy(rng.standard_normal((batch, 3 * image * image), dtype=np.float32)).pin_memory()
-          for _ in range(n_sets)]
-    obs_idx = [utils.label_to_obs(rng.integers(0, 10, batch), 10) for _ in range(n_sets)]
-    obs = [torch.from_numpy(o[0]).pin_memory() for o in obs_idx]
-    idx = [torch.from_numpy(o[1]).pin_memory() for o in obs_idx]
-    var_y = torch.full((batch * 4,), 1.0, device="cuda")
+    regression = args.workload == "mlp"
+    if args.workload == "resnet18":
+        batch = args.batch or 64
+        spec, in_shape = nn.resnet18_spec(image), (3, image, image)
+        name = f"resnet18_relu_3x{image}x{image}_batch{batch}_per_gpu"
+        draw = lambda: rng.standard_normal((batch, 3 * image * image), dtype=np.float32)
+    elif args.workload == "cnn":    # the CIFAR-shaped CNN: U[0,1] pixels, batch 128
+        batch = args.batch or 128
+        spec = [("conv", 3, 32, 3, 1, 1, 1, True), ("relu",), ("pool", 2, 2, 0, 0), ("conv", 32, 64, 3, 1, 1, 1, True),
+                ("relu",), ("pool", 2, 2, 0, 0), ("conv", 64, 128, 3, 1, 1, 1, True), ("relu",), ("pool", 2, 2, 0, 0),
+                ("linear", 2048, 256, True), ("relu",), ("linear", 256, 11, True)]
+        in_shape, name = (3, 32, 32), f"cifar_cnn_3x32x32_batch{batch}_per_gpu"
+        draw = lambda: rng.random((batch, 3 * 32 * 32), dtype=np.float32)
+    else:                           # the deep regression MLP 1 -> 4096 -> 4096 -> 4096 -> 1, batch 2048, x ~ U[-5, 5]
+        batch = args.batch or 2048
+        spec = [("linear", 1, 4096, True), ("relu",), ("linear", 4096, 4096, True), ("relu",), ("linear", 4096, 4096, True),
+                ("relu",), ("linear", 4096, 1, True)]
+        in_shape, name = (1,), f"regression_mlp_1-4096-4096-4096-1_batch{batch}_per_gpu"
+        draw = lambda: rng.uniform(-5, 5, (batch, 1)).astype(np.float32)
+    n_out = 1 if regression else 11
+    net = nn.build(spec, in_shape, seed=1234)      # same parameters on every rank
+    upd, utils = nn.OutputUpdater(), nn.Utils()
+    xs = [torch.from_numpy(draw()).pin_memory() for _ in range(n_sets)]
+    if regression:   # y = x^3 + eps, eps ~ N(0, 9), observation variance 9
+        obs = [torch.from_numpy((x.numpy() ** 3 + 3.0 * rng.standard_normal((batch, 1))).astype(np.float32)).pin_memory()
+               for x in xs]
+        idx = [torch.zeros(1, dtype=torch.int32).pin_memory() for _ in range(n_sets)]
+        var_y = torch.full((batch, 1), 9.0, device="cuda")
+    else:
+        obs_idx = [utils.label_to_obs(rng.integers(0, 10, batch), 10) for _ in range(n_sets)]
+        obs = [torch.from_numpy(o[0]).pin_memory() for o in obs_idx]
+        idx = [torch.from_numpy(o[1]).pin_memory() for o in obs_idx]
+        var_y = torch.full((batch * 4,), 1.0, device="cuda")
     stream = torch.cuda.current_stream()
     sp = stream.cuda_stream
     deltas = net.delta_tensors()
@@ -508,7 +534,13 @@ def run_resnet(args, rank, world, local_rank):
     d_idx = [torch.empty_like(idx[0], device="cuda") for _ in range(n_sets)]
     for i in range(n_sets):
         d_x[i].copy_(xs[i]), d_obs[i].copy_(obs[i]), d_idx[i].copy_(idx[i])
-    host_out = torch.empty(2, batch, 11).pin_memory()
+    host_out = torch.empty(2, batch, n_out).pin_memory()
+
+    def output_update(i):
+        if regression:
+            upd.update(net, d_obs[i], var_y)
+        else:
+            upd.update_using_indices(net, d_obs[i], var_y, d_idx[i])
     it = [0]
 
     def step(e2e=False):
@@ -519,7 +551,7 @@ def run_resnet(args, rank, world, local_rank):
             d_obs[i].copy_(obs[i], non_blocking=True)
             d_idx[i].copy_(idx[i], non_blocking=True)
         mu, var = net(d_x[i])
-        upd.update_using_indices(net, d_obs[i], var_y, d_idx[i])
+        output_update(i)
         net.backward()
         if xchg:
             xchg.flush(sp)
@@ -567,7 +599,7 @@ def run_resnet(args, rank, world, local_rank):
             net(d_x[0])
 
         def bwd():
-            upd.update_using_indices(net, d_obs[0], var_y, d_idx[0])
+            output_update(0)
             net.backward()
             if xchg:
                 xchg.flush(sp)
@@ -587,7 +619,7 @@ def run_resnet(args, rank, world, local_rank):
             xchg.close()
             dist.destroy_process_group()
         return
-    flop = resnet_flops(spec, (3, image, image)) * batch
+    flop = resnet_flops(spec, in_shape) * batch
     n_param = sum(t.numel() for t in deltas) // 2
     peak = 0.0
     try:
@@ -599,23 +631,28 @@ def run_resnet(args, rank, world, local_rank):
         from oracle_lib import Oracle
         from oracle_net import OracleNet
         o = Oracle()
-        cnet = OracleNet(o, spec, (3, image, image), seed=1)
-        xb = rng.standard_normal((1, 3 * image * image)).astype(np.float32)
-        ob, ib, _ = utils.label_to_obs([3], 10)
+        cnet = OracleNet(o, spec, in_shape, seed=1)
+        nb = {"resnet18": 1, "cnn": 16, "mlp": 16}[args.workload]   # batch of the CPU sample
+        xb = draw()[:nb]
         tc0 = time.perf_counter()
         cnet.forward(xb)
-        cnet.update_using_indices(ob, np.ones(4, np.float32), ib, 4)
+        if regression:
+            cnet.update(xb ** 3, np.full((nb, 1), 9.0, np.float32))
+        else:
+            ob, ib, _ = utils.label_to_obs(rng.integers(0, 10, nb), 10)
+            cnet.update_using_indices(ob, np.ones(4 * nb, np.float32), ib, 4)
         cnet.backward()
         cnet.step()
         dt = time.perf_counter() - tc0
-        cpu = {"value": 1.0 / dt, "unit": "samples/s", "cores": os.cpu_count(), "kind": "port",
-               "sample": f"one training step at batch 1 ({dt:.1f} s), oracle port with OpenMP; linear in the batch"}
+        cpu = {"value": nb / dt, "unit": "samples/s", "cores": os.cpu_count(), "kind": "port",
+               "sample": f"one training step at batch {nb} ({dt:.1f} s), oracle port with OpenMP; linear in the batch"}
     print(json.dumps({
-        "metric": "TAGI ResNet-18 training samples/s", "value": batch * world / (ms * 1e-3), "unit": "samples/s",
+        "metric": {"resnet18": "TAGI ResNet-18 training samples/s", "cnn": "TAGI CNN training samples/s",
+                   "mlp": "TAGI regression MLP training samples/s"}[args.workload],
+        "value": batch * world / (ms * 1e-3), "unit": "samples/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"resnet18_relu_3x{image}x{image}_batch{batch}_per_gpu (forward + output update + backward + "
-                               "capped update, 11 hierarchical-softmax outputs)",
+        "config": {"workload": f"{name} (forward + output update + backward + capped update)",
                    "parameters": n_param, "exchange": "none (1 GPU)" if world == 1 else
                    f"bucketed NCCL allreduce (average) of {2 * n_param * 4 / 1e6:.0f} MB of parameter deltas, "
                    f"{xchg.num_buckets} buckets of {args.bucket_mb} MiB, overlapped with the backward pass",
@@ -764,24 +801,28 @@ def main():
     ap.add_argument("--sm-budget", type=int, default=-1,
                     help="SMs the tensor-core kernels plan their tiles for (tagi_tc_set_sm_budget); default: all on one GPU, "
                          "132 when the exchange's NCCL kernels run next to them (N > 1)")
-    ap.add_argument("--workload", default="linear", choices=["linear", "resnet18"],
-                    help="linear: the headline micro-benchmark; resnet18: one training step of the ResNet-18 configuration")
+    ap.add_argument("--workload", default="linear", choices=["linear", "resnet18", "cnn", "mlp"],
+                    help="linear: the headline micro-benchmark; resnet18 / cnn / mlp: one training step of the ResNet-18, "
+                         "CIFAR-shaped CNN or deep regression MLP configuration through the device-side mirror")
     ap.add_argument("--engine", default="native", choices=["native", "dropin", "stock"],
                     help="resnet18: native = this repository's device-side mirror; dropin / stock = cuTAGI's own module "
                          "with / without this library's Linear and Conv2d kernels")
     ap.add_argument("--image", type=int, default=224, help="resnet18: image extent (224 or a multiple of 8 such as 32)")
-    ap.add_argument("--batch", type=int, default=64, help="resnet18: samples per GPU")
+    ap.add_argument("--batch", type=int, default=0, help="network workloads: samples per GPU (default: the configuration's)")
     ap.add_argument("--bucket-mb", type=int, default=32, help="resnet18: exchange bucket size in MiB")
     args = ap.parse_args()
-    if args.workload == "resnet18" and args.impl == "b200":
+    if args.workload != "linear" and args.impl == "b200":
         if args.steps == 200:
             args.steps = 10 if args.engine == "native" else 3
         if args.engine != "native":
+            if args.workload != "resnet18":
+                ap.error("--engine dropin / stock is available for the linear and resnet18 workloads")
+            args.batch = args.batch or 64
             return run_resnet_module(args)
         args.warmup = 1 if args.profile else max(args.warmup, 3)
         args.no_cpu = args.no_cpu or args.profile
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        return run_resnet(args, int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")),
+        return run_network(args, int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")),
                           int(os.environ.get("LOCAL_RANK", "0")))
     if args.workload == "linear" and args.engine != "native" and args.impl == "b200":
         args.steps = min(args.steps, 20)
