@@ -326,7 +326,7 @@ def run_b200(args, rank, world, local_rank):
     # DRAM traffic of one launch of each kernel, from the ncu capture summarised in
     # profiles/tagi_tc_linear_pair_kernel_b1024_4096.md (dram__bytes_read.sum + dram__bytes_write.sum); the FFMA kernels
     # have not been captured
-    ncu_traffic = {"tagi_linear_fwd": 327.9e6, "tagi_linear_bwd_state": 202.6e6, "tagi_linear_bwd_param": 219.9e6}
+    ncu_traffic = {"tagi_linear_fwd": 322.1e6, "tagi_linear_bwd_state": 203.3e6, "tagi_linear_bwd_param": 218.5e6}
     roofline = {"bound": bound, "kernel": dom, "achieved": achieved, "peak": peak, "unit": UNIT,
                 "frac": achieved / peak, "traffic": ncu_traffic[dom] if impl == IMPL_TF32X3 else None,
                 "traffic_unit": "bytes per launch (ncu, dram read + write)", "peak_note": peak_note,
