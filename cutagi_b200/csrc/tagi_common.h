@@ -50,10 +50,26 @@ int linear_tc_set_chunked(int on);
 int linear_tc_set_sm_budget(int sms);
 int linear_tc_set_variant(int v);
 int linear_tc_status(int *out, int reset);
+// Implicit Conv2d operand for the pair kernel's A side (forward: receptive fields of the activations; state pass at
+// stride 1: the deltas each input pixel receives). Row R of A is pixel (b, py, px) of a pixel grid OHW / OW per image,
+// column kc = (c, ky, kx); its value is src[b][c][y0 + sign * ky][x0 + sign * kx] with
+//   sign = +1: y0 = py * stride - off,  x0 = px * stride - off      (im2col)
+//   sign = -1: y0 = py + off,           x0 = px + off               (delta gather)
+// and zero outside the source image. on == 0: A tiles come by TMA from a matrix in memory.
+struct ConvGather {
+    int on;
+    const float *s0, *s1;
+    int C, H, W, OW, OHW, k, stride, off, sign;
+    long rows;
+};
+
 int linear_fwd_tc(const float *mu_w, const float *var_w, const float *mu_b, const float *var_b, const float *mu_a,
-                  const float *var_a, int B, int K, int N, float *mu_z, float *var_z, cudaStream_t st, int npix = 0);
+                  const float *var_a, int B, int K, int N, float *mu_z, float *var_z, cudaStream_t st, int npix = 0,
+                  const ConvGather *cg = nullptr);
+bool linear_tc_pair_for(int rows);  // true when a pass with this many output rows runs on the CTA-pair kernel
 int linear_bwd_state_tc(const float *mu_w, const float *jcb, const float *dmu_z, const float *dvar_z, int B, int K,
-                        int N, float *dmu_a, float *dvar_a, cudaStream_t st, int npix = 0);
+                        int N, float *dmu_a, float *dvar_a, cudaStream_t st, int npix = 0,
+                        const ConvGather *cg = nullptr);
 // npix > 0: the rows are (image, pixel) pairs and outputs / the Jacobian are laid out [image][channel][pixel] (Conv2d)
 int linear_bwd_param_tc(const float *var_w, const float *mu_a, const float *dmu_z, const float *dvar_z, int B, int K,
                         int N, float *dmu_w, float *dvar_w, cudaStream_t st, float *split_ws = nullptr, int slices = 1);

@@ -211,6 +211,19 @@ inline unsigned grid_for(long total) {
 }
 inline int ok_or(cudaError_t e, const char *what) { return e == cudaSuccess ? TAGI_OK : cuda_fail(e, what); }
 
+// The CTA-pair kernel can gather a Conv2d operand itself (tap masks are 32-bit words). Every column tile of a row block
+// gathers the block's operand again, so this pays while the output is at most one tile (128 columns) wide: measured on
+// the ResNet-18 shapes, 64 and 128 channels gain 15-35 %, 256 and 512 channels lose 25-45 % against the gather pass
+// through scratch memory. TAGI_B200_CONV_GATHER=explicit / implicit forces one of the two, for comparison.
+inline bool implicit_ok(const G &g, long rows, int cols) {
+    static const int mode = [] {
+        const char *e = getenv("TAGI_B200_CONV_GATHER");
+        return !e ? 0 : std::string(e) == "explicit" ? 1 : std::string(e) == "implicit" ? 2 : 0;
+    }();
+    if (mode == 1 || g.k > 16 || rows >= (1L << 31) || !linear_tc_pair_for((int)rows)) return false;
+    return mode == 2 || cols <= 128;
+}
+
 // Launches the tiled gather when the kernel size has an instantiation; returns false when the caller should use the
 // general kernel. C, H, W: source tensor; OH, OW: pixel grid of the rows.
 template <int NSRC, bool FLIP>
@@ -267,6 +280,11 @@ int conv2d_fwd_tc(const tagi_conv2d_geom &cg, const float *mu_w, const float *va
                   cudaStream_t st) {
     const G g = geom_of(cg);
     const long rows = (long)g.B * g.woho;
+    if (implicit_ok(g, rows, g.fo)) {
+        // implicit GEMM: the kernel gathers the receptive fields itself while it stages its A tiles
+        ConvGather ig{1, mu_a, var_a, g.fi, g.hi, g.wi, g.wo, g.woho, g.k, g.stride, g.off, +1, rows};
+        return linear_fwd_tc(mu_w, var_w, mu_b, var_b, nullptr, nullptr, (int)rows, g.Kc, g.fo, mu_z, var_z, st, g.woho, &ig);
+    }
     float *ws = nullptr;
     int rc = conv_scratch((size_t)2 * rows * g.Kc * sizeof(float), &ws);
     if (rc != TAGI_OK) return rc;
@@ -300,6 +318,15 @@ int conv2d_bwd_state_tc(const tagi_conv2d_geom &cg, const float *mu_w, const flo
     }
     const long rows = (long)g.B * g.wihi;
     const int kd = g.fo * g.k2;
+    if (implicit_ok(g, rows, g.fi)) {
+        float *w2i = nullptr;
+        if ((rc = conv_scratch((size_t)g.fo * g.Kc * sizeof(float), &w2i)) != TAGI_OK) return rc;
+        weight_regroup_kernel<<<grid_for((long)g.fo * g.Kc), 256, 0, st>>>(mu_w, g, w2i);
+        if ((rc = ok_or(cudaGetLastError(), "weight_regroup_kernel launch")) != TAGI_OK) return rc;
+        // implicit GEMM: row = input pixel, column (co, ky, kx) = delta at output pixel (y + off - ky, x + off - kx)
+        ConvGather ig{1, dmu_z, dvar_z, g.fo, g.ho, g.wo, g.wi, g.wihi, g.k, 1, g.off, -1, rows};
+        return linear_bwd_state_tc(w2i, jcb, nullptr, nullptr, (int)rows, g.fi, kd, dmu_a, dvar_a, st, g.wihi, &ig);
+    }
     rc = conv_scratch(((size_t)2 * rows * kd + (size_t)g.fo * g.Kc) * sizeof(float), &ws);
     if (rc != TAGI_OK) return rc;
     float *z_mu = ws, *z_var = ws + rows * kd, *w2 = ws + 2 * rows * kd;

@@ -44,7 +44,9 @@ constexpr uint32_t STAGE_PITCH = 68 * 4, STAGE_VALUE = 32 * STAGE_PITCH, STAGE_W
 constexpr size_t STAGE_BYTES = (size_t)NCONV_WARPS * STAGE_WARP;
 __host__ __device__ constexpr size_t at_least_stage(size_t ring) { return ring > STAGE_BYTES ? ring : STAGE_BYTES; }
 constexpr int NTHREADS = 32 * (2 + NCONV_WARPS);       // all-shared-memory kernel: TMA, MMA, converters
-constexpr int NTHREADS2 = 32 * (3 + NCONV_WARPS);      // ts / pair kernels: TMA, two MMA issuers (warps 1, 10), converters
+constexpr int NTHREADS2 = 32 * (4 + NCONV_WARPS);      // ts / pair kernels: TMA, two MMA issuers (warps 1, 10), converters,
+                                                       // and warp 11, which gathers Conv2d operands (pair kernel only)
+constexpr int GATHER_WARP = 3 + NCONV_WARPS;
 constexpr int ISSUER2_WARP = 2 + NCONV_WARPS;
 constexpr int CHUNKS = TILE_BYTES / 16;  // 16-byte chunks per tile
 
@@ -74,6 +76,7 @@ struct TcEpilogue {
     int slabs_per_slice;
     long slice_elems;
 };
+
 
 __device__ __forceinline__ float lo_part(float x) { return x - __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
 __device__ __forceinline__ float4 lo_part(float4 v) {
@@ -571,7 +574,7 @@ tagi_tc_linear_ts_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_
                 if (it % chunk_len == chunk_len - 1 || it == nk - 1) mma_commit(acc_full);
             }
         }
-    } else {
+    } else if (warp >= 2 && warp < 2 + NCONV_WARPS) {  // warp 11 has no role in this kernel
         // ------------------------------------------------------------------ converters + accumulation + epilogue
         const int ct = threadIdx.x - 64;
         const int q = warp & 3;         // tensor-memory lane quadrant of this warp
@@ -753,7 +756,7 @@ template <int OP, int CH, int RS, int DS>
 __global__ void __launch_bounds__(NTHREADS2, 1)
 tagi_tc_linear_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
                            const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
-                           const TcEpilogue epi, const int kdim, const int bn, int *status) {
+                           const TcEpilogue epi, const ConvGather cg, const int kdim, const int bn, int *status) {
     using T = OpTraits<OP>;
     using S = PairTraits<OP>;
     constexpr int NRAW_B = S::NRAW_B, NDER = S::NDER, NA = S::NA;
@@ -788,15 +791,18 @@ tagi_tc_linear_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __gri
     const int chunk_len = CH > 0 ? CH : nk;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < RS; s++) mbar_init(raw_full + s, 1);
+        // one arrival from the TMA thread; with gathered A tiles one more from each of the 64 gathering threads
+        for (int s = 0; s < RS; s++) mbar_init(raw_full + s, OP != OP_BWD_PARAM && cg.on ? 65 : 1);
         for (int s = 0; s < L; s++) mbar_init(stage_done + s, 2);  // one commit from each MMA issuer
         for (int s = 0; s < DS; s++) mbar_init(conv_done + s, NCONV_WARPS);  // used in CTA 0: one warp group of each CTA arrives
         mbar_init(acc_full, 2);
         mbar_init(acc_empty, 2 * NCONV_WARPS);          // used in CTA 0 only
         *abort_flag = 0;
         mbar_init_fence();
-        prefetch_tmap(&tmA0);
-        prefetch_tmap(&tmA1);
+        if (OP == OP_BWD_PARAM || !cg.on) {
+            prefetch_tmap(&tmA0);
+            prefetch_tmap(&tmA1);
+        }
         prefetch_tmap(&tmB0);
         if (OP == OP_FWD) prefetch_tmap(&tmB1);
     }
@@ -807,7 +813,72 @@ tagi_tc_linear_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __gri
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == 0) {
+    if (OP != OP_BWD_PARAM && cg.on && (warp == 0 || warp == GATHER_WARP)) {
+        // ------------------------------------------------------------------ Conv2d: A tiles gathered with cp.async
+        // Warps 0 and 11: each lane owns two of the CTA's 128 rows (pixels). The k index (channel, tap) is the same
+        // for all lanes of an instruction, so consecutive lanes read consecutive pixels of one image row: coalesced.
+        // Lane 0 of warp 0 also issues the TMA loads of the B tiles. Elements land in the 64-byte swizzle the
+        // converter warps read (chunk c of row r at chunk c ^ ((r >> 1) & 3)).
+        const int gw = warp == 0 ? 0 : 1;
+        const int k2 = cg.k * cg.k;
+        long base[2];
+        uint32_t ymask[2], xmask[2], dst_row[2], swz[2];
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const int r = gw * 64 + j * 32 + lane;
+            const long R = (long)row0 + r;
+            dst_row[j] = r * 64;
+            swz[j] = (r >> 1) & 3;
+            ymask[j] = xmask[j] = 0;
+            base[j] = 0;
+            if (R < cg.rows) {
+                const long bimg = R / cg.OHW;
+                const int pp = (int)(R - bimg * cg.OHW), py = pp / cg.OW, px = pp - py * cg.OW;
+                const int y0 = cg.sign > 0 ? py * cg.stride - cg.off : py + cg.off;
+                const int x0 = cg.sign > 0 ? px * cg.stride - cg.off : px + cg.off;
+                base[j] = (bimg * cg.C * cg.H + y0) * cg.W + x0;
+                for (int t = 0; t < cg.k; t++) {
+                    if ((unsigned)(y0 + cg.sign * t) < (unsigned)cg.H) ymask[j] |= 1u << t;
+                    if ((unsigned)(x0 + cg.sign * t) < (unsigned)cg.W) xmask[j] |= 1u << t;
+                }
+            }
+        }
+        // (channel, ky, kx) of the next k index, advanced incrementally
+        int kc = kb * BK, ci = kc / k2, ky = (kc - ci * k2) / cg.k, kx = kc - ci * k2 - ky * cg.k;
+        const long plane = (long)cg.H * cg.W;
+        for (int it = 0; it < nk; it++) {
+            const int r = it % RS;
+            if (it >= RS && !mbar_wait(stage_done + (it - RS) % L, ((it - RS) / L) & 1, abort_flag, status, ST_TIMEOUT_EMPTY))
+                break;
+            const uint32_t st = raw_base + r * RAW_SLOT;
+            if (warp == 0 && lane == 0) {
+                mbar_arrive_expect_tx(raw_full + r, RAW_SLOT - 2 * TILE_BYTES);
+                const int k0 = (kb + it) * BK;
+                load_half_tile<T::B_MN>(st + 2 * TILE_BYTES, &tmB0, brow0, k0, raw_full + r);
+                if (OP == OP_FWD) load_half_tile<T::B_MN>(st + 2 * TILE_BYTES + HALF_BYTES, &tmB1, brow0, k0, raw_full + r);
+            }
+#pragma unroll 4
+            for (int j16 = 0; j16 < BK; j16++) {
+                const long off = ci * plane + cg.sign * (ky * cg.W + kx);
+                const bool kok = kc < kdim;
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    const bool v = kok && ((ymask[j] >> ky) & 1u) && ((xmask[j] >> kx) & 1u);
+                    const long a = v ? base[j] + off : 0;
+                    const uint32_t d = st + dst_row[j] + ((((uint32_t)j16 >> 2) ^ swz[j]) << 4) + ((j16 & 3) << 2);
+                    cp_async_f32(d, cg.s0 + a, v);
+                    cp_async_f32(d + TILE_BYTES, cg.s1 + a, v);
+                }
+                kc++;
+                if (++kx == cg.k) {
+                    kx = 0;
+                    if (++ky == cg.k) ky = 0, ci++;
+                }
+            }
+            cp_async_arrive(raw_full + r);
+        }
+        cp_async_wait_all();
+    } else if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (each CTA for itself)
         if (lane == 0) {
             for (int it = 0; it < nk; it++) {
@@ -859,7 +930,7 @@ tagi_tc_linear_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __gri
                 if (it % chunk_len == chunk_len - 1 || it == nk - 1) mma_commit_pair(acc_full);
             }
         }
-    } else {
+    } else if (warp >= 2 && warp < 2 + NCONV_WARPS) {
         // ------------------------------------------------------------------ converters + accumulation + epilogue
         const int ct = threadIdx.x - 64;
         const int q = warp & 3;
@@ -1131,7 +1202,7 @@ int launch(const CUtensorMap &a0, const CUtensorMap &a1, const CUtensorMap &b0, 
 // CTA-pair variant: grid.x = 2 x column tiles (cluster of two along x), grid.y = 256-row tiles.
 template <int OP>
 int launch_pair(const CUtensorMap &a0, const CUtensorMap &a1, const CUtensorMap &b0, const CUtensorMap &b1,
-                const TcEpilogue &epi, int kdim, cudaStream_t st) {
+                const TcEpilogue &epi, int kdim, cudaStream_t st, const ConvGather &cg = ConvGather{}) {
     int *status = status_word();
     if (!status) return fail(TAGI_ERR_CUDA, "cannot allocate the tensor-core status word");
     const long row_tiles = (epi.rows + 255) / 256;
@@ -1163,7 +1234,7 @@ int launch_pair(const CUtensorMap &a0, const CUtensorMap &a1, const CUtensorMap 
         cfg.dynamicSmemBytes = sm;                                                               \
         e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);       \
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");                       \
-        e = cudaLaunchKernelEx(&cfg, k, a0, a1, b0, b1, epi, kdim, bn, status);                  \
+        e = cudaLaunchKernelEx(&cfg, k, a0, a1, b0, b1, epi, cg, kdim, bn, status);              \
     } while (0)
     // ring depths: hand-offs cross two SMs here, so the derived ring is as deep as tensor memory allows (backward:
     // four slots; forward: three when the accumulators fit 2 x 112 columns, else two)
@@ -1230,28 +1301,38 @@ int linear_tc_status(int *out, int reset) {
 }
 
 int linear_fwd_tc(const float *mu_w, const float *var_w, const float *mu_b, const float *var_b, const float *mu_a,
-                  const float *var_a, int B, int K, int N, float *mu_z, float *var_z, cudaStream_t st, int npix) {
+                  const float *var_a, int B, int K, int N, float *mu_z, float *var_z, cudaStream_t st, int npix,
+                  const ConvGather *cg) {
     CUtensorMap a0, a1, b0, b1;
     int rc;
-    if ((rc = make_tmap(&a0, mu_a, K, B, false))) return rc;
-    if ((rc = make_tmap(&a1, var_a, K, B, false))) return rc;
     const bool pair = use_pair(B);
     if ((rc = make_tmap(&b0, mu_w, K, N, false, pair ? 64 : 128))) return rc;
     if ((rc = make_tmap(&b1, var_w, K, N, false, pair ? 64 : 128))) return rc;
     TcEpilogue epi{mu_z, var_z, mu_b, var_b, (long)N, B, N, npix, 0, 0};
+    if (cg) {  // A = the receptive fields of (mu_a, var_a), gathered inside the kernel
+        if (!pair) return fail(TAGI_ERR_UNSUPPORTED, "implicit Conv2d operands need the CTA-pair kernel");
+        return launch_pair<OP_FWD>(b0, b0, b0, b1, epi, K, st, *cg);
+    }
+    if ((rc = make_tmap(&a0, mu_a, K, B, false))) return rc;
+    if ((rc = make_tmap(&a1, var_a, K, B, false))) return rc;
     if (pair) return launch_pair<OP_FWD>(a0, a1, b0, b1, epi, K, st);
     return launch<OP_FWD>(a0, a1, b0, b1, epi, K, st);
 }
+bool linear_tc_pair_for(int rows) { return use_pair(rows); }
 
 int linear_bwd_state_tc(const float *mu_w, const float *jcb, const float *dmu_z, const float *dvar_z, int B, int K,
-                        int N, float *dmu_a, float *dvar_a, cudaStream_t st, int npix) {
+                        int N, float *dmu_a, float *dvar_a, cudaStream_t st, int npix, const ConvGather *cg) {
     // rows = batch, columns = input features, contraction over output features; mu_w [N][K] is MN-major here
     CUtensorMap a0, a1, b0;
     int rc;
-    if ((rc = make_tmap(&a0, dmu_z, N, B, false))) return rc;
-    if ((rc = make_tmap(&a1, dvar_z, N, B, false))) return rc;
     if ((rc = make_tmap(&b0, mu_w, K, N, true))) return rc;
     TcEpilogue epi{dmu_a, dvar_a, jcb, nullptr, (long)K, B, K, npix, 0, 0};
+    if (cg) {  // A = the deltas each input pixel receives, gathered inside the kernel
+        if (!use_pair(B)) return fail(TAGI_ERR_UNSUPPORTED, "implicit Conv2d operands need the CTA-pair kernel");
+        return launch_pair<OP_BWD_STATE>(b0, b0, b0, b0, epi, N, st, *cg);
+    }
+    if ((rc = make_tmap(&a0, dmu_z, N, B, false))) return rc;
+    if ((rc = make_tmap(&a1, dvar_z, N, B, false))) return rc;
     if (use_pair(B)) return launch_pair<OP_BWD_STATE>(a0, a1, b0, b0, epi, N, st);
     return launch<OP_BWD_STATE>(a0, a1, b0, b0, epi, N, st);
 }

@@ -99,6 +99,17 @@ __device__ __forceinline__ bool mbar_spin(uint64_t *bar, uint32_t parity, volati
     }
 }
 
+// ----------------------------------------------------------------------------- cp.async (4-byte gathers)
+// Copies 4 bytes global -> shared asynchronously; `valid` false writes zero and reads nothing.
+__device__ __forceinline__ void cp_async_f32(uint32_t smem_dst, const float *src, bool valid) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_dst), "l"(src), "r"(valid ? 4 : 0) : "memory");
+}
+// The barrier receives one arrival (already counted in its init count) when all cp.async of this thread so far are done
+__device__ __forceinline__ void cp_async_arrive(uint64_t *bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 // ----------------------------------------------------------------------------- proxies / fences
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }

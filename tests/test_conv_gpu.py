@@ -121,6 +121,10 @@ TC_GEOMS = [
     dict(B=4, fi=16, hi=15, wi=15, fo=32, k=3, stride=2, pad=1, pad_type=1, has_bias=1),    # stride 2, odd image
     dict(B=4, fi=8, hi=19, wi=19, fo=16, k=5, stride=3, pad=2, pad_type=1, has_bias=0),     # stride 3, 5x5
     dict(B=4, fi=3, hi=32, wi=32, fo=64, k=6, stride=2, pad=2, pad_type=1, has_bias=0),     # ResNet stem: 3 channels, 6x6
+    # outputs wider than one tile take the gather pass through scratch, narrower ones gather inside the kernel:
+    dict(B=4, fi=192, hi=10, wi=10, fo=32, k=3, stride=1, pad=1, pad_type=1, has_bias=1),   # state pass explicit, forward implicit
+    dict(B=4, fi=32, hi=10, wi=10, fo=192, k=3, stride=1, pad=1, pad_type=1, has_bias=1),   # forward explicit, state pass implicit
+    dict(B=5, fi=16, hi=13, wi=11, fo=32, k=3, stride=1, pad=1, pad_type=1, has_bias=0),    # 715 rows: ragged last row tile
 ]
 
 
