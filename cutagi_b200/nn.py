@@ -469,15 +469,21 @@ class OutputUpdater:
 def build(spec, in_shape, seed=None):
     """Sequential from a spec (list of tuples): ("conv", fi, fo, k, stride, pad, pad_type, bias), ("linear", K, N, bias),
     ("relu",), ("bn", C), ("pool", k, stride, pad, pad_type), ("res", [main spec], [shortcut spec] or None)."""
+    count = [0]
+
+    def next_seed():   # one seed per parameterised layer, so that equally shaped layers do not start identical
+        count[0] += 1
+        return None if seed is None else seed + count[0]
+
     def layers(spec):
         out = []
         for item in spec:
             kind, a = item[0], item[1:]
             if kind == "conv":
                 fi, fo, k, stride, pad, pad_type, bias = a
-                out.append(Conv2d(fi, fo, k, bias=bias, stride=stride, padding=pad, padding_type=pad_type, seed=seed))
+                out.append(Conv2d(fi, fo, k, bias=bias, stride=stride, padding=pad, padding_type=pad_type, seed=next_seed()))
             elif kind == "linear":
-                out.append(Linear(a[0], a[1], bias=a[2], seed=seed))
+                out.append(Linear(a[0], a[1], bias=a[2], seed=next_seed()))
             elif kind == "relu":
                 out.append(ReLU())
             elif kind == "bn":
