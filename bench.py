@@ -588,6 +588,36 @@ def run_network(args, rank, world, local_rank):
         sampler.start()
     for _ in range(args.warmup):
         step()
+    eager_step = step
+    if args.graph and world == 1:
+        # The whole step (about 70 launches for the CNN, 1000 for ResNet-18) replayed as one CUDA graph per input buffer:
+        # for the small configurations the step is bound by launch overhead, not by the kernels. Scratch buffers have
+        # reached their final size during the warm-up steps, so nothing allocates while the stream is being captured.
+        torch.cuda.synchronize()
+        graphs, outs = [], []
+        for i in range(n_sets):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                mu, var = net(d_x[i])
+                output_update(i)
+                net.backward()
+                net.step()
+            graphs.append(g)
+            outs.append((mu, var))
+
+        def step(e2e=False):
+            i = it[0] % n_sets
+            it[0] += 1
+            if e2e:
+                d_x[i].copy_(xs[i], non_blocking=True)
+                d_obs[i].copy_(obs[i], non_blocking=True)
+                d_idx[i].copy_(idx[i], non_blocking=True)
+            graphs[i].replay()
+            if e2e:
+                host_out[0].copy_(outs[i][0], non_blocking=True)
+                host_out[1].copy_(outs[i][1], non_blocking=True)
+        for _ in range(2):
+            step()
     t0 = time.time()
     ms = timed(step, args.steps) / args.steps
     t1 = time.time()
@@ -653,6 +683,7 @@ def run_network(args, rank, world, local_rank):
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"{name} (forward + output update + backward + capped update)",
+                   "launch": "one CUDA graph per step" if (args.graph and world == 1) else "one launch per kernel",
                    "parameters": n_param, "exchange": "none (1 GPU)" if world == 1 else
                    f"bucketed NCCL allreduce (average) of {2 * n_param * 4 / 1e6:.0f} MB of parameter deltas, "
                    f"{xchg.num_buckets} buckets of {args.bucket_mb} MiB, overlapped with the backward pass",
@@ -804,6 +835,8 @@ def main():
     ap.add_argument("--workload", default="linear", choices=["linear", "resnet18", "cnn", "mlp"],
                     help="linear: the headline micro-benchmark; resnet18 / cnn / mlp: one training step of the ResNet-18, "
                          "CIFAR-shaped CNN or deep regression MLP configuration through the device-side mirror")
+    ap.add_argument("--graph", action="store_true",
+                    help="network workloads on one GPU: replay the training step as a CUDA graph")
     ap.add_argument("--engine", default="native", choices=["native", "dropin", "stock"],
                     help="resnet18: native = this repository's device-side mirror; dropin / stock = cuTAGI's own module "
                          "with / without this library's Linear and Conv2d kernels")
