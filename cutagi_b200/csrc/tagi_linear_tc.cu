@@ -819,33 +819,36 @@ tagi_tc_linear_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __gri
         // for all lanes of an instruction, so consecutive lanes read consecutive pixels of one image row: coalesced.
         // Lane 0 of warp 0 also issues the TMA loads of the B tiles. Elements land in the 64-byte swizzle the
         // converter warps read (chunk c of row r at chunk c ^ ((r >> 1) & 3)).
+        // The gather loop of these two warps paces the whole pipeline when tiles are narrow, so its per-element work is
+        // kept minimal: the (channel, tap) of each of a slab's 16 k indices is worked out by one lane each and
+        // broadcast, validity is one bit of a per-row tap mask, destination offsets are per-row constants.
         const int gw = warp == 0 ? 0 : 1;
         const int k2 = cg.k * cg.k;
-        long base[2];
-        uint32_t ymask[2], xmask[2], dst_row[2], swz[2];
+        const long plane = (long)cg.H * cg.W;
+        const float *base[2];
+        unsigned long long tapmask[2];  // bit (ky * k + kx): that tap of the row's pixel lies inside the source image
+        uint32_t relc[2][4];            // byte offset of 16-byte chunk c of the row inside an A tile (64-byte swizzle)
 #pragma unroll
         for (int j = 0; j < 2; j++) {
             const int r = gw * 64 + j * 32 + lane;
             const long R = (long)row0 + r;
-            dst_row[j] = r * 64;
-            swz[j] = (r >> 1) & 3;
-            ymask[j] = xmask[j] = 0;
-            base[j] = 0;
+#pragma unroll
+            for (int c = 0; c < 4; c++) relc[j][c] = r * 64 + ((c ^ ((r >> 1) & 3)) << 4);
+            tapmask[j] = 0;
+            base[j] = cg.s0;
             if (R < cg.rows) {
                 const long bimg = R / cg.OHW;
                 const int pp = (int)(R - bimg * cg.OHW), py = pp / cg.OW, px = pp - py * cg.OW;
                 const int y0 = cg.sign > 0 ? py * cg.stride - cg.off : py + cg.off;
                 const int x0 = cg.sign > 0 ? px * cg.stride - cg.off : px + cg.off;
-                base[j] = (bimg * cg.C * cg.H + y0) * cg.W + x0;
-                for (int t = 0; t < cg.k; t++) {
-                    if ((unsigned)(y0 + cg.sign * t) < (unsigned)cg.H) ymask[j] |= 1u << t;
-                    if ((unsigned)(x0 + cg.sign * t) < (unsigned)cg.W) xmask[j] |= 1u << t;
-                }
+                base[j] = cg.s0 + (bimg * cg.C * cg.H + y0) * cg.W + x0;
+                for (int ty = 0; ty < cg.k; ty++)
+                    for (int tx = 0; tx < cg.k; tx++)
+                        if ((unsigned)(y0 + cg.sign * ty) < (unsigned)cg.H && (unsigned)(x0 + cg.sign * tx) < (unsigned)cg.W)
+                            tapmask[j] |= 1ull << (ty * cg.k + tx);
             }
         }
-        // (channel, ky, kx) of the next k index, advanced incrementally
-        int kc = kb * BK, ci = kc / k2, ky = (kc - ci * k2) / cg.k, kx = kc - ci * k2 - ky * cg.k;
-        const long plane = (long)cg.H * cg.W;
+        const long s1_off = cg.s1 - cg.s0;  // the second source has the same layout
         for (int it = 0; it < nk; it++) {
             const int r = it % RS;
             if (it >= RS && !mbar_wait(stage_done + (it - RS) % L, ((it - RS) / L) & 1, abort_flag, status, ST_TIMEOUT_EMPTY))
@@ -857,22 +860,26 @@ tagi_tc_linear_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __gri
                 load_half_tile<T::B_MN>(st + 2 * TILE_BYTES, &tmB0, brow0, k0, raw_full + r);
                 if (OP == OP_FWD) load_half_tile<T::B_MN>(st + 2 * TILE_BYTES + HALF_BYTES, &tmB1, brow0, k0, raw_full + r);
             }
-#pragma unroll 4
+            // lane j < 16 decodes k index j of this slab: element offset of (channel, tap) and the tap's mask bit
+            int my_off = 0, my_tap = 63;  // bit 63 is never set: k indices past the contraction read zeros
+            {
+                const int kc = (kb + it) * BK + (lane & 15);
+                if (kc < kdim) {
+                    const int ci = kc / k2, t = kc - ci * k2, ky = t / cg.k, kx = t - ky * cg.k;
+                    my_off = (int)(ci * plane) + cg.sign * (ky * cg.W + kx);
+                    my_tap = t;
+                }
+            }
+#pragma unroll
             for (int j16 = 0; j16 < BK; j16++) {
-                const long off = ci * plane + cg.sign * (ky * cg.W + kx);
-                const bool kok = kc < kdim;
+                const int off = __shfl_sync(0xffffffffu, my_off, j16), tap = __shfl_sync(0xffffffffu, my_tap, j16);
 #pragma unroll
                 for (int j = 0; j < 2; j++) {
-                    const bool v = kok && ((ymask[j] >> ky) & 1u) && ((xmask[j] >> kx) & 1u);
-                    const long a = v ? base[j] + off : 0;
-                    const uint32_t d = st + dst_row[j] + ((((uint32_t)j16 >> 2) ^ swz[j]) << 4) + ((j16 & 3) << 2);
-                    cp_async_f32(d, cg.s0 + a, v);
-                    cp_async_f32(d + TILE_BYTES, cg.s1 + a, v);
-                }
-                kc++;
-                if (++kx == cg.k) {
-                    kx = 0;
-                    if (++ky == cg.k) ky = 0, ci++;
+                    const bool v = (tapmask[j] >> tap) & 1ull;
+                    const float *src = v ? base[j] + off : cg.s0;
+                    const uint32_t d = st + relc[j][j16 >> 2] + ((j16 & 3) << 2);
+                    cp_async_f32(d, src, v);
+                    cp_async_f32(d + TILE_BYTES, src + s1_off, v);
                 }
             }
             cp_async_arrive(raw_full + r);
