@@ -479,8 +479,8 @@ def run_network(args, rank, world, local_rank):
     regression = args.workload == "mlp"
     if args.workload == "resnet18":
         batch = args.batch or 64
-        spec, in_shape = nn.resnet18_spec(image), (3, image, image)
-        name = f"resnet18_relu_3x{image}x{image}_batch{batch}_per_gpu"
+        spec, in_shape = nn.resnet18_spec(image, act=args.act), (3, image, image)
+        name = f"resnet18_{args.act}_3x{image}x{image}_batch{batch}_per_gpu"
         draw = lambda: rng.standard_normal((batch, 3 * image * image), dtype=np.float32)
     elif args.workload == "cnn":    # the CIFAR-shaped CNN: U[0,1] pixels, batch 128
         batch = args.batch or 128
@@ -840,6 +840,8 @@ def main():
     ap.add_argument("--engine", default="native", choices=["native", "dropin", "stock"],
                     help="resnet18: native = this repository's device-side mirror; dropin / stock = cuTAGI's own module "
                          "with / without this library's Linear and Conv2d kernels")
+    ap.add_argument("--act", default="relu", choices=["relu", "mrelu"],
+                    help="resnet18 (native engine): ReLU as in the reference's C++ test or MixtureReLU as in its Python example")
     ap.add_argument("--image", type=int, default=224, help="resnet18: image extent (224 or a multiple of 8 such as 32)")
     ap.add_argument("--batch", type=int, default=0, help="network workloads: samples per GPU (default: the configuration's)")
     ap.add_argument("--bucket-mb", type=int, default=32, help="resnet18: exchange bucket size in MiB")

@@ -39,6 +39,7 @@ _SIGNATURES = {
     "tagi_conv2d_bwd_state": [C.POINTER(ConvGeom), _p, _p, _p, _p, _p, _p, _p],
     "tagi_conv2d_bwd_param": [C.POINTER(ConvGeom), _p, _p, _p, _p, _p, _p, _p, _p, _p, _p],
     "tagi_relu_fwd": [_p, _p, C.c_size_t, _p, _p, _p, _p],
+    "tagi_mixture_relu_fwd": [_p, _p, C.c_size_t, _p, _p, _p, _p],
     "tagi_output_delta": [_p, _p, _p, _p, _p, C.c_size_t, _p, _p, _p],
     "tagi_output_delta_selected": [_p, _p, _p, _p, _p, _p, _i, _i, _i, _p, _p, _p],
     "tagi_param_update": [_i, C.c_size_t, _p, _p, _p, _p, _p, _p],

@@ -25,6 +25,22 @@ __global__ void relu_kernel(const float *__restrict__ mu_z, const float *__restr
     }
 }
 
+// src/activation.cpp:152-178 (rectified-Gaussian moments; Phi by erfc as in src/common.cpp:315-319)
+__global__ void mixture_relu_kernel(const float *__restrict__ mu_z, const float *__restrict__ var_z, size_t n,
+                                    float *__restrict__ mu_a, float *__restrict__ var_a, float *__restrict__ jcb) {
+    const size_t i = (size_t)blockIdx.x * BLOCK + threadIdx.x;
+    if (i >= n) return;
+    constexpr float SQRT_2PI = 2.5066282746310002f;
+    const float m = mu_z[i], v = var_z[i];
+    const float sd = sqrtf(v), alpha = m / sd;
+    const float pdf = (1.0f / SQRT_2PI) * expf(-0.5f * alpha * alpha);
+    const float cdf = 0.5f * erfcf(-alpha * 0.7071067811865475f);
+    const float t = m * cdf + sd * pdf;
+    mu_a[i] = fmaxf(0.000001f, t);
+    var_a[i] = fmaxf(0.000001f, -t * t + 2 * t * m - m * sd * pdf + (v - m * m) * cdf);
+    jcb[i] = cdf;
+}
+
 // src/base_output_updater.cpp:8-29
 __global__ void output_delta_kernel(const float *__restrict__ mu_a, const float *__restrict__ var_a,
                                     const float *__restrict__ jcb, const float *__restrict__ obs,
@@ -103,6 +119,18 @@ int tagi_relu_fwd(const float *mu_z, const float *var_z, size_t n, float *mu_a, 
     TAGI_PTR(jcb);
     relu_kernel<<<blocks_for(n), BLOCK, 0, static_cast<cudaStream_t>(stream)>>>(mu_z, var_z, n, mu_a, var_a, jcb);
     return launched("relu_kernel launch");
+}
+
+int tagi_mixture_relu_fwd(const float *mu_z, const float *var_z, size_t n, float *mu_a, float *var_a, float *jcb,
+                          void *stream) {
+    TAGI_REQUIRE(n > 0, "n must be positive");
+    TAGI_PTR(mu_z);
+    TAGI_PTR(var_z);
+    TAGI_PTR(mu_a);
+    TAGI_PTR(var_a);
+    TAGI_PTR(jcb);
+    mixture_relu_kernel<<<blocks_for(n), BLOCK, 0, static_cast<cudaStream_t>(stream)>>>(mu_z, var_z, n, mu_a, var_a, jcb);
+    return launched("mixture_relu_kernel launch");
 }
 
 int tagi_output_delta(const float *mu_a, const float *var_a, const float *jcb, const float *obs, const float *var_obs,

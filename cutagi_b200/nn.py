@@ -124,6 +124,15 @@ class ReLU(_NoParams):
         return dmu, dvar
 
 
+class MixtureReLU(ReLU):
+    """cutagi.MixtureReLU(): rectified-Gaussian moments instead of the ReLU's linearisation (src/activation.cpp:152-178)."""
+
+    def forward(self, mu_z, var_z, jcb, train=True):
+        mu_a, var_a, j = torch.empty_like(mu_z), torch.empty_like(mu_z), torch.empty_like(mu_z)
+        lib.tagi_mixture_relu_fwd(_p(mu_z), _p(var_z), mu_z.numel(), _p(mu_a), _p(var_a), _p(j), _stream())
+        return mu_a, var_a, j
+
+
 def _geom(B, fi, hi, wi, fo, k, stride, pad, pad_type, has_bias):
     wo, ho = capi.conv_out_size(k, stride, wi, hi, pad, pad_type)
     return capi.ConvGeom(B, fi, hi, wi, fo, ho, wo, k, stride, pad, pad_type, int(has_bias))
@@ -486,6 +495,8 @@ def build(spec, in_shape, seed=None):
                 out.append(Linear(a[0], a[1], bias=a[2], seed=next_seed()))
             elif kind == "relu":
                 out.append(ReLU())
+            elif kind == "mrelu":
+                out.append(MixtureReLU())
             elif kind == "bn":
                 out.append(BatchNorm2d(a[0]))
             elif kind == "pool":
@@ -498,24 +509,25 @@ def build(spec, in_shape, seed=None):
     return Sequential(*layers(spec), in_shape=in_shape)
 
 
-def resnet18_spec(image=224, n_out=11):
-    """The reference's ResNet-18 (examples/tagi_resnet_model.py:146-268 for 224 x 224 inputs, :56-143 / 
-    test/cpp_unit/test_resnet.cpp:84-110,228-263 for 32 x 32), with ReLU as in the C++ test."""
+def resnet18_spec(image=224, n_out=11, act="relu"):
+    """The reference's ResNet-18 (examples/tagi_resnet_model.py:146-268 for 224 x 224 inputs, :56-143 /
+    test/cpp_unit/test_resnet.cpp:84-110,228-263 for 32 x 32); act = "relu" as in the C++ test or "mrelu" (MixtureReLU) as in
+    the Python example."""
     def block(i, o, stride=1, pt=1):
-        return [("conv", i, o, 3, stride, 1, pt, False), ("relu",), ("bn", o), ("conv", o, o, 3, 1, 1, 1, False), ("relu",),
+        return [("conv", i, o, 3, stride, 1, pt, False), (act,), ("bn", o), ("conv", o, o, 3, 1, 1, 1, False), (act,),
                 ("bn", o)]
     if image == 224:
-        spec = [("conv", 3, 64, 6, 2, 2, 1, False), ("relu",), ("bn", 64), ("pool", 3, 2, 1, 2)]
+        spec = [("conv", 3, 64, 6, 2, 2, 1, False), (act,), ("bn", 64), ("pool", 3, 2, 1, 2)]
         final_pool = 7
     else:
-        spec = [("conv", 3, 64, 3, 1, 1, 1, False), ("relu",), ("bn", 64)]
+        spec = [("conv", 3, 64, 3, 1, 1, 1, False), (act,), ("bn", 64)]
         final_pool = image // 8
     prev = 64
     for w in (64, 128, 256, 512):
         if w == prev:
             spec.append(("res", block(prev, w), None))
         else:
-            spec.append(("res", block(prev, w, 2, 2), [("conv", prev, w, 2, 2, 0, 1, False), ("relu",), ("bn", w)]))
+            spec.append(("res", block(prev, w, 2, 2), [("conv", prev, w, 2, 2, 0, 1, False), (act,), ("bn", w)]))
         spec.append(("res", block(w, w), None))
         prev = w
     return spec + [("pool", final_pool, -1, 0, 0), ("linear", 512, n_out, True)]

@@ -141,6 +141,14 @@ int tagi_conv2d_bwd_param(const tagi_conv2d_geom *g, const float *var_w, const f
  * CPU definition relu_mean_var (src/activation.cpp:7-29); replaces relu_mean_var_cuda (src/activation_cuda.cu:8-24). */
 int tagi_relu_fwd(const float *mu_z, const float *var_z, size_t n, float *mu_a, float *var_a, float *jcb, void *stream);
 
+/* MixtureReLU moments (rectified Gaussian): alpha = mu_z / sqrt(var_z); mu_a = max(1e-6, mu_z * Phi(alpha) +
+ * sqrt(var_z) * phi(alpha)); var_a = max(1e-6, -mu_a'^2 + 2 * mu_a' * mu_z - mu_z * sqrt(var_z) * phi(alpha) +
+ * (var_z - mu_z^2) * Phi(alpha)) with mu_a' the unfloored mean; jcb = Phi(alpha).
+ * CPU definition mixture_relu_mean_var (src/activation.cpp:152-178); replaces mixture_relu_mean_var_cuda
+ * (src/activation_cuda.cu:130-157). */
+int tagi_mixture_relu_fwd(const float *mu_z, const float *var_z, size_t n, float *mu_a, float *var_a, float *jcb,
+                          void *stream);
+
 /* Output-layer innovation, n entries: t = jcb / (var_a + var_obs); dmu = t * (obs - mu_a); dvar = -t * jcb; zero where t
  * is not finite or obs is NaN. CPU definition compute_delta_z_output (src/base_output_updater.cpp:8-29); replaces
  * update_delta_z_cuda (src/output_updater_cuda.cu:3-27). */

@@ -22,6 +22,7 @@
 #include "conv2d_layer.h"
 #include "data_struct.h"
 #include "linear_layer.h"
+#include "activation.h"
 #include "batchnorm_layer.h"
 #include "pooling_layer.h"
 
@@ -355,6 +356,17 @@ int tagi_ref_avgpool2d(int B, int C, int hi, int wi, int k, int stride, int pad,
         layer.backward(din, dout, tmp, true);
         out(dmu, dout.delta_mu, (size_t)B * n_in);
         out(dvar, dout.delta_var, (size_t)B * n_in);
+    });
+}
+
+// mixture_relu_mean_var (src/activation.cpp:152-178), the CPU kernel behind MixtureReLU::forward (:724-744)
+int tagi_ref_mixture_relu(size_t n, const float *mu_z, const float *var_z, float *mu_a, float *var_a, float *jcb) {
+    return guarded([&] {
+        std::vector<float> mz = vec(mu_z, n), vz = vec(var_z, n), ma(n), va(n), j(n);
+        mixture_relu_mean_var(mz, vz, 0, (int)n, ma, j, va);
+        out(mu_a, ma, n);
+        out(var_a, va, n);
+        out(jcb, j, n);
     });
 }
 

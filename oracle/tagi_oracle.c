@@ -52,6 +52,21 @@ void tagi_oracle_relu(size_t n, const float *mu_z, const float *var_z, float *mu
     }
 }
 
+void tagi_oracle_mixture_relu(size_t n, const float *mu_z, const float *var_z, float *mu_a, float *var_a, float *jcb) {
+    const float SQRT_2PI = 2.5066282746310002f;
+    for (size_t i = 0; i < n; i++) {
+        float m = mu_z[i];
+        float sd = powf(var_z[i], 0.5f);
+        float alpha = m / sd;
+        float pdf = (1.0f / SQRT_2PI) * expf(-0.5f * alpha * alpha);
+        float cdf = 0.5f * erfcf(-alpha * 0.7071067811865475f);
+        float t = m * cdf + sd * pdf;
+        mu_a[i] = fmaxf(0.000001f, t);
+        var_a[i] = fmaxf(0.000001f, -t * t + 2 * t * m - m * sd * pdf + (var_z[i] - m * m) * cdf);
+        jcb[i] = cdf;
+    }
+}
+
 void tagi_oracle_output_delta(size_t n, const float *mu_a, const float *var_a, const float *jcb, const float *obs,
                               const float *var_obs, float *dmu, float *dvar) {
     for (size_t i = 0; i < n; i++) {

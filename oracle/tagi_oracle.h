@@ -52,6 +52,9 @@ TAGI_ORACLE_DECL(double, _f64)
 /* Neighbours of the path, fp32 elementwise, needed to run whole training steps. */
 /* ReLU moments, src/activation.cpp:7-29. */
 void tagi_oracle_relu(size_t n, const float *mu_z, const float *var_z, float *mu_a, float *var_a, float *jcb);
+/* MixtureReLU moments (rectified Gaussian), src/activation.cpp:152-178: alpha = mu_z / sqrt(var_z),
+ * mu_a = max(1e-6, mu_z * Phi(alpha) + sqrt(var_z) * phi(alpha)), var_a likewise floored, jcb = Phi(alpha). */
+void tagi_oracle_mixture_relu(size_t n, const float *mu_z, const float *var_z, float *mu_a, float *var_a, float *jcb);
 /* Output innovation, src/base_output_updater.cpp:8-29: all n entries. */
 void tagi_oracle_output_delta(size_t n, const float *mu_a, const float *var_a, const float *jcb, const float *obs,
                               const float *var_obs, float *dmu, float *dvar);

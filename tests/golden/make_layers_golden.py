@@ -1,4 +1,5 @@
-"""Generates tests/golden/layers_golden.npz from the reference's own CPU classes `BatchNorm2d` and `AvgPool2d`.
+"""Generates tests/golden/layers_golden.npz from the reference's own CPU classes `BatchNorm2d` and `AvgPool2d` and its
+MixtureReLU kernel.
 
 Run in the build container, where the reference sources exist:
     make -C oracle ref && python tests/golden/make_layers_golden.py
@@ -64,6 +65,12 @@ def main():
         out.update({p + "geom": np.array([g.B, g.fi, g.hi, g.wi, g.k, g.stride, g.pad, g.pad_type, g.ho, g.wo]),
                     p + "mu_a": ma, p + "var_a": va, p + "jcb": j, p + "dmu_o": dmo, p + "dvar_o": dvo, p + "mu_z": mz,
                     p + "var_z": vz, p + "dmu": dm, p + "dvar": dv})
+    # MixtureReLU moments (src/activation.cpp:152-178): means on both sides of zero, small and large variances
+    rng = np.random.default_rng(6000)
+    mz = np.concatenate([rng.standard_normal(4000) * 2, np.linspace(-12, 12, 97)]).astype(f)
+    vz = np.concatenate([rng.uniform(1e-4, 3, 4000), np.full(97, 0.5)]).astype(f)
+    ma, va, j = ref.mixture_relu(mz, vz)
+    out.update({"mrelu_mu_z": mz, "mrelu_var_z": vz, "mrelu_mu_a": ma, "mrelu_var_a": va, "mrelu_jcb": j})
     out["n_bn"], out["n_pool"] = np.array(len(BN_CASES)), np.array(len(POOL_CASES))
     out["eps_momentum"] = np.array([EPS, MOMENTUM], np.float32)
     path = os.path.join(HERE, "layers_golden.npz")

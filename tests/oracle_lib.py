@@ -162,6 +162,11 @@ class Oracle:
         self.lib.tagi_oracle_relu(C.c_size_t(mu_z.size), _f(mu_z), _f(var_z), _f(ma), _f(va), _f(j))
         return ma, va, j
 
+    def mixture_relu(self, mu_z, var_z):
+        ma, va, j = np.empty_like(mu_z), np.empty_like(mu_z), np.empty_like(mu_z)
+        self.lib.tagi_oracle_mixture_relu(C.c_size_t(mu_z.size), _f(mu_z), _f(var_z), _f(ma), _f(va), _f(j))
+        return ma, va, j
+
     def output_delta(self, mu_a, var_a, jcb, obs, var_obs):
         dm, dv = np.empty_like(mu_a), np.empty_like(mu_a)
         self.lib.tagi_oracle_output_delta(C.c_size_t(mu_a.size), _f(mu_a), _f(var_a), _f(jcb), _f(obs), _f(var_obs),
@@ -327,3 +332,8 @@ class RefLib:
             g.B, g.fi, g.hi, g.wi, g.k, g.stride, g.pad, g.pad_type, threads, _f(mu_a), _f(var_a), _f(jcb), _f(dmu_o),
             _f(dvar_o), C.byref(wo), C.byref(ho), _f(mz), _f(vz), _f(dm), _f(dv)))
         return mz, vz, dm, dv, wo.value, ho.value
+
+    def mixture_relu(self, mu_z, var_z):
+        ma, va, j = np.empty_like(mu_z), np.empty_like(mu_z), np.empty_like(mu_z)
+        self._chk(self.lib.tagi_ref_mixture_relu(C.c_size_t(mu_z.size), _f(mu_z), _f(var_z), _f(ma), _f(va), _f(j)))
+        return ma, va, j

@@ -4,7 +4,7 @@ ReLU, BatchNorm2d, AvgPool2d, LayerBlock and ResNetBlock composed the way the re
 
 A network is described by a spec, a list of tuples, from which both this CPU trainer and the device-side mirror
 (cutagi_b200.nn.build) are constructed:
-    ("conv", fi, fo, k, stride, pad, pad_type, bias)   ("linear", K, N, bias)   ("relu",)
+    ("conv", fi, fo, k, stride, pad, pad_type, bias)   ("linear", K, N, bias)   ("relu",)   ("mrelu",)
     ("bn", C)   ("pool", k, stride, pad, pad_type)   ("res", [main spec], [shortcut spec] or None)
 Parameter names follow the reference's state_dict ("Conv2d.0", "BatchNorm2d.main.3.2", "Linear.6", ...).
 """
@@ -106,6 +106,11 @@ class OReLU:
 
     def named(self, prefix, idx):
         return {}
+
+
+class OMixtureReLU(OReLU):
+    def forward(self, mu, var, jcb, train=True):
+        return self.o.mixture_relu(mu, var)
 
 
 class OBatchNorm2d:
@@ -275,6 +280,8 @@ def build_layers(o, spec):
             out.append(OLinear(o, *a))
         elif kind == "relu":
             out.append(OReLU(o))
+        elif kind == "mrelu":
+            out.append(OMixtureReLU(o))
         elif kind == "bn":
             out.append(OBatchNorm2d(o, *a))
         elif kind == "pool":

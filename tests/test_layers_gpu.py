@@ -195,3 +195,19 @@ def test_add_shortcut(G, oracle):
         lib.tagi_add_shortcut(G.p(ds), G.p(dvs), G.p(dj), n, G.p(da), G.p(dva), None)
         G.check("mu", da.cpu().numpy(), ra, G.RTOL_MU)
         G.check("var", dva.cpu().numpy(), rva, G.RTOL_VAR)
+
+
+def test_mixture_relu(G, oracle):
+    """tagi_mixture_relu_fwd against the reference's outputs (golden) and, on a larger tensor, against the oracle."""
+    from cutagi_b200.capi import lib
+    rng = np.random.default_rng(12)
+    big_m, big_v = (rng.standard_normal(300001) * 3).astype(f32), rng.uniform(1e-4, 4, 300001).astype(f32)
+    for mz, vz, ref in ((np.ascontiguousarray(GOLD["mrelu_mu_z"]), np.ascontiguousarray(GOLD["mrelu_var_z"]),
+                         (GOLD["mrelu_mu_a"], GOLD["mrelu_var_a"], GOLD["mrelu_jcb"])),
+                        (big_m, big_v, oracle.mixture_relu(big_m, big_v))):
+        dm, dv = G.dev(mz), G.dev(vz)
+        o = [G.Out(mz.size) for _ in range(3)]
+        lib.tagi_mixture_relu_fwd(G.p(dm), G.p(dv), mz.size, o[0].ptr(), o[1].ptr(), o[2].ptr(), None)
+        G.check("mu_a", o[0].get(), ref[0], G.RTOL_MU)
+        G.check("var_a", o[1].get(), ref[1], G.RTOL_VAR)
+        G.check("jcb", o[2].get(), ref[2], G.RTOL_MU)

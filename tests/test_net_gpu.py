@@ -82,6 +82,30 @@ def test_resnet18_one_step_every_delta(oracle):
     assert _rel(mu_e.cpu().numpy(), emu) < 1e-4 and _rel(var_e.cpu().numpy(), evar) < 1e-3
 
 
+def test_mixture_relu_resnet_one_step(oracle):
+    """The MixtureReLU variant of the small ResNet (examples/tagi_resnet_model.py uses MixtureReLU): one step against the
+    oracle."""
+    spec, in_shape, batch, _ = net_golden_problems()["resnet"]
+    spec = [tuple(("mrelu",) if it == ("relu",) else it) if it[0] != "res" else
+            ("res", [("mrelu",) if x == ("relu",) else x for x in it[1]],
+             None if it[2] is None else [("mrelu",) if x == ("relu",) else x for x in it[2]]) for it in spec]
+    cpu = OracleNet(oracle, spec, in_shape, seed=3)
+    net, upd = _device_net(spec, in_shape, cpu)
+    rng = np.random.default_rng(4)
+    x = rng.standard_normal((batch, int(np.prod(in_shape)))).astype(np.float32)
+    mu, var = net(x)
+    rmu, rvar = cpu.forward(x)
+    assert _rel(mu.cpu().numpy(), rmu) < 1e-4 and _rel(var.cpu().numpy(), rvar) < 1e-3
+    obs = rng.standard_normal((batch, 11)).astype(np.float32)
+    upd.update(net, obs, np.full((batch, 11), 0.5, np.float32))
+    cpu.update(obs, np.full((batch, 11), 0.5, np.float32))
+    net.backward()
+    cpu.backward()
+    for k, layer in net.named_layers().items():
+        d = cpu.named_layers()[k].d
+        assert _rel(layer.delta_mu_w.cpu().numpy(), d[0]) < 1e-3 and _rel(layer.delta_var_w.cpu().numpy(), d[1]) < 1e-3, k
+
+
 def test_shape_errors_are_raised():
     import torch
     if not torch.cuda.is_available():

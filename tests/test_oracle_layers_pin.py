@@ -48,6 +48,12 @@ def test_avgpool2d_matches_golden(oracle, i):
     assert np.array_equal(dm, g["dmu"]) and np.array_equal(dv, g["dvar"])
 
 
+def test_mixture_relu_matches_golden(oracle):
+    ma, va, j = oracle.mixture_relu(np.ascontiguousarray(GOLD["mrelu_mu_z"]), np.ascontiguousarray(GOLD["mrelu_var_z"]))
+    assert np.array_equal(ma, GOLD["mrelu_mu_a"]) and np.array_equal(va, GOLD["mrelu_var_a"])
+    assert np.array_equal(j, GOLD["mrelu_jcb"])
+
+
 def test_add_shortcut(oracle):
     """src/resnet_block.cpp:8-31."""
     rng = np.random.default_rng(3)
