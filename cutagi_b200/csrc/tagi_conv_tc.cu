@@ -211,10 +211,10 @@ inline unsigned grid_for(long total) {
 }
 inline int ok_or(cudaError_t e, const char *what) { return e == cudaSuccess ? TAGI_OK : cuda_fail(e, what); }
 
-// The CTA-pair kernel can gather a Conv2d operand itself. Every column tile of a row block
-// gathers the block's operand again, so this pays while the output is at most one tile (128 columns) wide: measured on
-// the ResNet-18 shapes, 64 and 128 channels gain 15-35 %, 256 and 512 channels lose 25-45 % against the gather pass
-// through scratch memory. TAGI_B200_CONV_GATHER=explicit / implicit forces one of the two, for comparison.
+// The CTA-pair kernel can gather a Conv2d operand itself. Every column tile of a row block gathers the block's operand
+// again, so this pays while the output is at most two tiles (256 columns) wide: measured on the ResNet-18 shapes,
+// 64 / 128 channels gain 30 % against the gather pass through scratch memory, 256 channels are level, 512 channels lose
+// 10-20 %. TAGI_B200_CONV_GATHER=explicit / implicit forces one of the two, for comparison.
 inline bool implicit_ok(const G &g, long rows, int cols) {
     static const int mode = [] {
         const char *e = getenv("TAGI_B200_CONV_GATHER");
@@ -222,7 +222,7 @@ inline bool implicit_ok(const G &g, long rows, int cols) {
     }();
     // (the kernel keeps one validity bit per tap in a 64-bit word, bit 63 reserved: kernels up to 7 x 7)
     if (mode == 1 || g.k > 7 || rows >= (1L << 31) || !linear_tc_pair_for((int)rows)) return false;
-    return mode == 2 || cols <= 128;
+    return mode == 2 || cols <= 256;
 }
 
 // Launches the tiled gather when the kernel size has an instantiation; returns false when the caller should use the
