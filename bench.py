@@ -189,19 +189,31 @@ def run_b200(args, rank, world, local_rank):
     # own stream right after the parameter pass so that it overlaps the state pass (the order cuTAGI's Conv2d uses:
     # parameters first, then states).
     xchg = None
+    pieces = max(1, args.param_pieces)
+    cuts = [N * i // pieces for i in range(pieces + 1)]
     if world > 1:
         from cutagi_b200.comm import DeltaExchange
         token = [f"/tmp/tagi_b200_rdv_{os.getpid()}_{time.time_ns()}"]
         dist.broadcast_object_list(token, src=0)
-        xchg = DeltaExchange([o[k] for k in ("dmu_w", "dvar_w", "dmu_b", "dvar_b")], rank, world, local_rank, token[0],
-                             bucket_bytes=64 << 20, average=True)
+        # The parameter pass runs range by range over the output features (tagi_linear_bwd_param_rows) and every range's
+        # deltas are handed to the exchange as soon as they are launched, so that the allreduce of one range overlaps the
+        # computation of the next and the state pass.
+        views = []
+        for n0, n1 in zip(cuts[:-1], cuts[1:]):
+            views += [o["dmu_w"][n0:n1], o["dvar_w"][n0:n1], o["dmu_b"][n0:n1], o["dvar_b"][n0:n1]]
+        xchg = DeltaExchange(views, rank, world, local_rank, token[0], bucket_bytes=(N // pieces) * K * 8 + (1 << 20),
+                             average=True)
 
     def step(p=p):
         k_fwd(p)
-        k_param(p)
         if xchg:
-            for i in range(4):
-                xchg.ready(i, sp)
+            for j, (n0, n1) in enumerate(zip(cuts[:-1], cuts[1:])):
+                lib.tagi_linear_bwd_param_rows(p["var_w"], p["var_b"], p["mu_a"], p["dmu_z"], p["dvar_z"], B, K, N, n0, n1,
+                                               1, p["dmu_w"], p["dvar_w"], p["dmu_b"], p["dvar_b"], sp)
+                for i in range(4):
+                    xchg.ready(4 * j + i, sp)
+        else:
+            k_param(p)
         k_state(p)
         if xchg:
             xchg.wait(sp)
@@ -350,12 +362,14 @@ def run_b200(args, rank, world, local_rank):
         "config": {"workload": WORKLOAD, "impl": {1: "ffma (FP32 CUDA cores)", 2: "tf32x3 (tcgen05, 3 TF32 products per "
                                                   "FP32 product, FP32 accumulation)"}.get(impl, str(impl)),
                    "device": devname, "l2": "inputs (604 MB per step) exceed the 126 MB L2; no flush",
-                   "exchange": ("allreduce(avg) of parameter deltas: %d NCCL buckets on a side stream, overlapped with the "
-                                "state pass" % xchg.num_buckets) if world > 1 else "none (1 GPU)"},
+                   "exchange": ("allreduce(avg) of parameter deltas: parameter pass and exchange in %d ranges of output "
+                                "features, %d NCCL buckets on a side stream, each range's exchange overlapped with the "
+                                "next range's parameter pass and the state pass" % (pieces, xchg.num_buckets))
+                   if world > 1 else "none (1 GPU)"},
         "roofline": roofline, "cpu_baseline": cpu_baseline,
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h},
-        "gpu_launches": 4 * args.steps, "tc_status": tc_status, "clocks": clocks}))
+        "gpu_launches": (4 if world == 1 else 2 + 2 * pieces) * args.steps, "tc_status": tc_status, "clocks": clocks}))
     if world > 1:
         xchg.close()
         dist.destroy_process_group()
@@ -832,6 +846,8 @@ def main():
     ap.add_argument("--sm-budget", type=int, default=-1,
                     help="SMs the tensor-core kernels plan their tiles for (tagi_tc_set_sm_budget); default: all on one GPU, "
                          "132 when the exchange's NCCL kernels run next to them (N > 1)")
+    ap.add_argument("--param-pieces", type=int, default=4,
+                    help="linear, N > 1: ranges of output features the parameter pass and the exchange are cut into")
     ap.add_argument("--workload", default="linear", choices=["linear", "resnet18", "cnn", "mlp"],
                     help="linear: the headline micro-benchmark; resnet18 / cnn / mlp: one training step of the ResNet-18, "
                          "CIFAR-shaped CNN or deep regression MLP configuration through the device-side mirror")

@@ -34,6 +34,7 @@ _SIGNATURES = {
     "tagi_linear_fwd": [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _p],
     "tagi_linear_bwd_state": [_p, _p, _p, _p, _i, _i, _i, _p, _p, _p],
     "tagi_linear_bwd_param": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _p, _p, _p],
+    "tagi_linear_bwd_param_rows": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p],
     "tagi_conv2d_out_size": [_i, _i, _i, _i, _i, _i, C.POINTER(_i), C.POINTER(_i)],
     "tagi_conv2d_fwd": [C.POINTER(ConvGeom), _p, _p, _p, _p, _p, _p, _p, _p, _p],
     "tagi_conv2d_bwd_state": [C.POINTER(ConvGeom), _p, _p, _p, _p, _p, _p, _p],

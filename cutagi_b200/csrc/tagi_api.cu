@@ -145,6 +145,36 @@ int tagi_linear_bwd_param(const float *var_w, const float *var_b, const float *m
     return rc;
 }
 
+int tagi_linear_bwd_param_rows(const float *var_w, const float *var_b, const float *mu_a, const float *dmu_z,
+                               const float *dvar_z, int B, int K, int N, int n0, int n1, int has_bias, float *dmu_w,
+                               float *dvar_w, float *dmu_b, float *dvar_b, void *stream) {
+    TAGI_DIMS();
+    TAGI_REQUIRE(0 <= n0 && n0 < n1 && n1 <= N, "0 <= n0 < n1 <= N required");
+    TAGI_PTR(var_w);
+    TAGI_PTR(mu_a);
+    TAGI_PTR(dmu_z);
+    TAGI_PTR(dvar_z);
+    TAGI_PTR(dmu_w);
+    TAGI_PTR(dvar_w);
+    if (has_bias) {
+        TAGI_PTR(var_b);
+        TAGI_PTR(dmu_b);
+        TAGI_PTR(dvar_b);
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int Nr = n1 - n0;
+    const long w0 = (long)n0 * K;
+    var_w += w0, dmu_w += w0, dvar_w += w0, dmu_z += n0, dvar_z += n0;
+    int rc = TAGI_OK;
+    if (N % 4 == 0 && pick_tc(__func__, B, K, Nr, {var_w, mu_a, dmu_z, dvar_z, dmu_w, dvar_w}, &rc))
+        rc = linear_bwd_param_tc(var_w, mu_a, dmu_z, dvar_z, B, K, Nr, dmu_w, dvar_w, st, nullptr, 1, N);
+    else if (rc == TAGI_OK || N % 4 != 0)
+        rc = linear_bwd_param_ffma(var_w, mu_a, dmu_z, dvar_z, B, K, Nr, dmu_w, dvar_w, st, N);
+    if (rc != TAGI_OK) return rc;
+    if (has_bias) rc = linear_bias_delta(var_b + n0, dmu_z, dvar_z, B, Nr, dmu_b + n0, dvar_b + n0, st, N);
+    return rc;
+}
+
 /* ------------------------------------------------------------------ Conv2d */
 
 int tagi_conv2d_out_size(int k, int stride, int wi, int hi, int pad, int pad_type, int *wo, int *ho) {

@@ -38,10 +38,10 @@ int linear_fwd_ffma(const float *mu_w, const float *var_w, const float *mu_b, co
 int linear_bwd_state_ffma(const float *mu_w, const float *jcb, const float *dmu_z, const float *dvar_z, int B, int K,
                           int N, float *dmu_a, float *dvar_a, cudaStream_t st);
 int linear_bwd_param_ffma(const float *var_w, const float *mu_a, const float *dmu_z, const float *dvar_z, int B,
-                          int K, int N, float *dmu_w, float *dvar_w, cudaStream_t st);
+                          int K, int N, float *dmu_w, float *dvar_w, cudaStream_t st, long ldz = 0);
 // column sums of the [B][N] deltas scaled by var_b, var_b^2
 int linear_bias_delta(const float *var_b, const float *dmu_z, const float *dvar_z, int B, int N, float *dmu_b,
-                      float *dvar_b, cudaStream_t st);
+                      float *dvar_b, cudaStream_t st, long ldz = 0);
 
 // tcgen05 / 3xTF32 implementations (tagi_linear_tc.cu)
 bool linear_tc_supported(int B, int K, int N, std::initializer_list<const void *> ptrs);
@@ -72,7 +72,8 @@ int linear_bwd_state_tc(const float *mu_w, const float *jcb, const float *dmu_z,
                         const ConvGather *cg = nullptr);
 // npix > 0: the rows are (image, pixel) pairs and outputs / the Jacobian are laid out [image][channel][pixel] (Conv2d)
 int linear_bwd_param_tc(const float *var_w, const float *mu_a, const float *dmu_z, const float *dvar_z, int B, int K,
-                        int N, float *dmu_w, float *dvar_w, cudaStream_t st, float *split_ws = nullptr, int slices = 1);
+                        int N, float *dmu_w, float *dvar_w, cudaStream_t st, float *split_ws = nullptr, int slices = 1,
+                        long ldz = 0);
 int linear_bwd_param_tc_slices(int B, int K, int N);
 
 // Conv2d on the FFMA engine (tagi_conv_ffma.cu)

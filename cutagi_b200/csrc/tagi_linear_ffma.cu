@@ -14,7 +14,7 @@ inline int done(cudaError_t e) { return e == cudaSuccess ? TAGI_OK : cuda_fail(e
 // result does not depend on scheduling.
 __global__ void __launch_bounds__(256) bias_delta_kernel(const float *__restrict__ var_b,
                                                          const float *__restrict__ dmu_z,
-                                                         const float *__restrict__ dvar_z, int B, int N,
+                                                         const float *__restrict__ dvar_z, int B, int N, long ld,
                                                          float *__restrict__ dmu_b, float *__restrict__ dvar_b) {
     __shared__ float s1[8][33], s2[8][33];
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
@@ -22,8 +22,8 @@ __global__ void __launch_bounds__(256) bias_delta_kernel(const float *__restrict
     float a1 = 0.f, a2 = 0.f;
     if (n < N)
         for (int b = ty; b < B; b += 8) {
-            a1 += __ldg(dmu_z + (long)b * N + n);
-            a2 += __ldg(dvar_z + (long)b * N + n);
+            a1 += __ldg(dmu_z + (long)b * ld + n);
+            a2 += __ldg(dvar_z + (long)b * ld + n);
         }
     s1[ty][tx] = a1;
     s2[ty][tx] = a2;
@@ -66,9 +66,11 @@ int linear_bwd_state_ffma(const float *mu_w, const float *jcb, const float *dmu_
 }
 
 int linear_bwd_param_ffma(const float *var_w, const float *mu_a, const float *dmu_z, const float *dvar_z, int B,
-                          int K, int N, float *dmu_w, float *dvar_w, cudaStream_t st) {
-    // rows = output features, columns = input features, contraction over the batch
-    StridedOperand<DER_PAIR> A{dmu_z, dvar_z, 1, (long)N, N, B};
+                          int K, int N, float *dmu_w, float *dvar_w, cudaStream_t st, long ldz) {
+    // rows = output features, columns = input features, contraction over the batch; ldz: row pitch of the delta
+    // matrices (more than N when only a range of the output features is computed)
+    if (ldz == 0) ldz = N;
+    StridedOperand<DER_PAIR> A{dmu_z, dvar_z, 1, ldz, N, B};
     StridedOperand<DER_SQUARE> X{mu_a, nullptr, 1, (long)K, K, B};
     EpiRowScale epi{dmu_w, dvar_w, var_w, (long)K,
                     K % 4 == 0 && aligned16(dmu_w) && aligned16(dvar_w) && aligned16(var_w)};
@@ -77,8 +79,8 @@ int linear_bwd_param_ffma(const float *var_w, const float *mu_a, const float *dm
 }
 
 int linear_bias_delta(const float *var_b, const float *dmu_z, const float *dvar_z, int B, int N, float *dmu_b,
-                      float *dvar_b, cudaStream_t st) {
-    bias_delta_kernel<<<(N + 31) / 32, 256, 0, st>>>(var_b, dmu_z, dvar_z, B, N, dmu_b, dvar_b);
+                      float *dvar_b, cudaStream_t st, long ldz) {
+    bias_delta_kernel<<<(N + 31) / 32, 256, 0, st>>>(var_b, dmu_z, dvar_z, B, N, ldz ? ldz : N, dmu_b, dvar_b);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "bias_delta_kernel launch");
     return TAGI_OK;

@@ -1110,11 +1110,12 @@ EncodeTiledFn encode_fn() {
 
 // Tensor map over a row-major FP32 matrix [outer][inner]. K-major operand tiles: box 16 x 128, 64-byte
 // swizzle; MN-major: box 32 x 16, 128-byte swizzle with 32-byte atoms.
-int make_tmap(CUtensorMap *tm, const float *ptr, uint64_t inner, uint64_t outer, bool mn_major, unsigned kmajor_rows = 128) {
+int make_tmap(CUtensorMap *tm, const float *ptr, uint64_t inner, uint64_t outer, bool mn_major, unsigned kmajor_rows = 128,
+              uint64_t pitch = 0) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail(TAGI_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[2] = {inner, outer};
-    cuuint64_t strides[1] = {inner * sizeof(float)};
+    cuuint64_t strides[1] = {(pitch ? pitch : inner) * sizeof(float)};
     cuuint32_t box[2] = {mn_major ? 32u : (cuuint32_t)BK, mn_major ? (cuuint32_t)BK : (cuuint32_t)kmajor_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(ptr), dims, strides, box, estr,
@@ -1375,12 +1376,13 @@ int linear_bwd_param_tc_slices(int B, int K, int N) {
 // split_ws: optional scratch of at least 2 * slices * N * K floats (slices from linear_bwd_param_tc_slices); without it
 // the contraction is not split.
 int linear_bwd_param_tc(const float *var_w, const float *mu_a, const float *dmu_z, const float *dvar_z, int B, int K,
-                        int N, float *dmu_w, float *dvar_w, cudaStream_t st, float *split_ws, int slices) {
-    // rows = output features, columns = input features, contraction over the batch; both operands MN-major
+                        int N, float *dmu_w, float *dvar_w, cudaStream_t st, float *split_ws, int slices, long ldz) {
+    // rows = output features, columns = input features, contraction over the batch; both operands MN-major.
+    // ldz: row pitch of the delta matrices (0 = N; larger when only a range of the output features is computed)
     CUtensorMap a0, a1, b0;
     int rc;
-    if ((rc = make_tmap(&a0, dmu_z, N, B, true))) return rc;
-    if ((rc = make_tmap(&a1, dvar_z, N, B, true))) return rc;
+    if ((rc = make_tmap(&a0, dmu_z, N, B, true, 128, ldz))) return rc;
+    if ((rc = make_tmap(&a1, dvar_z, N, B, true, 128, ldz))) return rc;
     if ((rc = make_tmap(&b0, mu_a, K, B, true))) return rc;
     if (!split_ws || slices < 2) {
         TcEpilogue epi{dmu_w, dvar_w, var_w, nullptr, (long)K, N, K, 0, 0, 0};

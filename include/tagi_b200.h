@@ -97,6 +97,15 @@ int tagi_linear_bwd_param(const float *var_w, const float *var_b, const float *m
                           const float *dvar_z, int B, int K, int N, int has_bias, float *dmu_w, float *dvar_w,
                           float *dmu_b, float *dvar_b, void *stream);
 
+/* The same pass for the output features n0 .. n1-1 only: rows n0 .. n1-1 of dmu_w / dvar_w and entries n0 .. n1-1 of
+ * dmu_b / dvar_b are written, everything else is left alone. All pointers are those of the whole tensors. A caller that
+ * exchanges the deltas between data-parallel ranks in pieces (src/ddp.cpp:113-146 exchanges whole tensors after the
+ * whole backward pass) runs the pass range by range and starts the exchange of a range while the next one is computed;
+ * the ranges together give exactly the result of tagi_linear_bwd_param. */
+int tagi_linear_bwd_param_rows(const float *var_w, const float *var_b, const float *mu_a, const float *dmu_z,
+                               const float *dvar_z, int B, int K, int N, int n0, int n1, int has_bias, float *dmu_w,
+                               float *dvar_w, float *dmu_b, float *dvar_b, void *stream);
+
 /* ------------------------------------------------------------------ Conv2d */
 
 /* Geometry of one Conv2d call. The receptive field of output pixel (oy, ox), tap (ky, kx) is input pixel

@@ -228,6 +228,35 @@ def test_tensor_core_sm_budget_only_changes_the_tiling(G, oracle, force_impl, sm
         lib.tagi_tc_set_sm_budget(0)
 
 
+@pytest.mark.parametrize("B,K,N,cuts", [(256, 512, 768, (0, 256, 512, 768)), (64, 100, 37, (0, 5, 36, 37)),
+                                         (128, 256, 384, (0, 128, 384))])
+def test_parameter_pass_by_row_ranges(G, oracle, B, K, N, cuts):
+    """tagi_linear_bwd_param_rows over a partition of the output features gives the whole pass (tensor-core ranges where
+    aligned, FFMA otherwise); rows outside a range are left alone."""
+    import torch
+    from cutagi_b200.capi import lib
+    x = G.linear_inputs(np.random.default_rng(B + N), B, K, N)
+    ref = oracle.linear_bwd_param(x["var_w"], x["var_b"], x["mu_a"], x["dmu_z"], x["dvar_z"])
+    d = {k: G.dev(x[k]) for k in ("var_w", "var_b", "mu_a", "dmu_z", "dvar_z")}
+    ow, ov, obm, obv = G.Out(N * K), G.Out(N * K), G.Out(N), G.Out(N)
+    for n0, n1 in zip(cuts[:-1], cuts[1:]):
+        lib.tagi_linear_bwd_param_rows(G.p(d["var_w"]), G.p(d["var_b"]), G.p(d["mu_a"]), G.p(d["dmu_z"]), G.p(d["dvar_z"]),
+                                       B, K, N, n0, n1, 1, ow.ptr(), ov.ptr(), obm.ptr(), obv.ptr(), None)
+    G.check("dmu_w", ow.get((N, K)), ref[0], G.RTOL_MU)
+    G.check("dvar_w", ov.get((N, K)), ref[1], G.RTOL_VAR)
+    G.check("dmu_b", obm.get(), ref[2], G.RTOL_MU)
+    G.check("dvar_b", obv.get(), ref[3], G.RTOL_VAR)
+    # a single range leaves the other rows untouched
+    keep = torch.full((N * K,), 7.0, device="cuda")
+    keep2, kb, kb2 = keep.clone(), torch.full((N,), 7.0, device="cuda"), torch.full((N,), 7.0, device="cuda")
+    lib.tagi_linear_bwd_param_rows(G.p(d["var_w"]), G.p(d["var_b"]), G.p(d["mu_a"]), G.p(d["dmu_z"]), G.p(d["dvar_z"]), B, K,
+                                   N, cuts[1], cuts[2], 1, G.p(keep), G.p(keep2), G.p(kb), G.p(kb2), None)
+    h = keep.cpu().numpy().reshape(N, K)
+    assert np.all(h[: cuts[1]] == 7.0) and np.all(h[cuts[2]:] == 7.0) and not np.any(h[cuts[1]:cuts[2]] == 7.0)
+    hb = kb.cpu().numpy()
+    assert np.all(hb[: cuts[1]] == 7.0) and np.all(hb[cuts[2]:] == 7.0)
+
+
 def test_tensor_core_rejects_unaligned(G, force_impl):
     import torch
     from cutagi_b200 import capi
