@@ -846,7 +846,7 @@ def main():
     ap.add_argument("--sm-budget", type=int, default=-1,
                     help="SMs the tensor-core kernels plan their tiles for (tagi_tc_set_sm_budget); default: all on one GPU, "
                          "132 when the exchange's NCCL kernels run next to them (N > 1)")
-    ap.add_argument("--param-pieces", type=int, default=4,
+    ap.add_argument("--param-pieces", type=int, default=2,
                     help="linear, N > 1: ranges of output features the parameter pass and the exchange are cut into")
     ap.add_argument("--workload", default="linear", choices=["linear", "resnet18", "cnn", "mlp"],
                     help="linear: the headline micro-benchmark; resnet18 / cnn / mlp: one training step of the ResNet-18, "
