@@ -102,24 +102,37 @@ __device__ __forceinline__ void store_tile(const TcEpilogue &epi, int row, int c
         // [image][channel][pixel]: consecutive lanes hold consecutive pixels, so each channel's store is coalesced
         const int img = row / epi.npix, pix = row - img * epi.npix;
         const long base = (long)img * epi.cols * epi.npix + pix;
+        // eight columns at a time: their scale entries are loaded together, so that the epilogue waits for memory once
+        // per group and not once per column
 #pragma unroll
-        for (int i = 0; i < 64; i++) {
-            const int col = c0 + i;
-            if (i >= valid || col >= epi.cols) break;
-            const long idx = base + (long)col * epi.npix;
-            float o1 = sum1[i], o2 = sum2[i];
-            if (OP == OP_FWD) {
-                if (epi.aux1) {
-                    o1 += __ldg(epi.aux1 + col);
-                    o2 += __ldg(epi.aux2 + col);
-                }
-            } else if (epi.aux1) {
-                const float sc = __ldg(epi.aux1 + idx);
-                o1 *= sc;
-                o2 = o2 * sc * sc;
+        for (int i0 = 0; i0 < 64; i0 += 8) {
+            float sc[8];
+            bool ok[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const int col = c0 + i0 + u;
+                ok[u] = i0 + u < valid && col < epi.cols;
+                sc[u] = 1.f;
+                if (OP != OP_FWD && epi.aux1 && ok[u]) sc[u] = __ldg(epi.aux1 + base + (long)col * epi.npix);
             }
-            __stcs(epi.out1 + idx, o1);
-            __stcs(epi.out2 + idx, o2);
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                if (!ok[u]) continue;
+                const int col = c0 + i0 + u;
+                const long idx = base + (long)col * epi.npix;
+                float o1 = sum1[i0 + u], o2 = sum2[i0 + u];
+                if (OP == OP_FWD) {
+                    if (epi.aux1) {
+                        o1 += __ldg(epi.aux1 + col);
+                        o2 += __ldg(epi.aux2 + col);
+                    }
+                } else {
+                    o1 *= sc[u];
+                    o2 = o2 * sc[u] * sc[u];
+                }
+                __stcs(epi.out1 + idx, o1);
+                __stcs(epi.out2 + idx, o2);
+            }
         }
         return;
     }
