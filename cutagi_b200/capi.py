@@ -44,6 +44,7 @@ _SIGNATURES = {
     "tagi_output_delta": [_p, _p, _p, _p, _p, C.c_size_t, _p, _p, _p],
     "tagi_output_delta_selected": [_p, _p, _p, _p, _p, _p, _i, _i, _i, _p, _p, _p],
     "tagi_param_update": [_i, C.c_size_t, _p, _p, _p, _p, _p, _p],
+    "tagi_param_update_multi": [_i, _i, _p, _p, _p],
     "tagi_conv2d_bwd_param_noalloc": [C.POINTER(ConvGeom), _p, _p, _p, _p, _p, _p, _p, _p, _p, _p],
     "tagi_bn2d_fwd": [_i, _i, _i, _i, _i, C.c_float, C.c_float] + [_p] * 13,
     "tagi_bn2d_bwd": [_i, _i, _i, _i, _i, C.c_float] + [_p] * 16,

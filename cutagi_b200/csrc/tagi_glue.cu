@@ -100,6 +100,24 @@ inline int launched(const char *what) {
     return e == cudaSuccess ? TAGI_OK : cuda_fail(e, what);
 }
 
+// The same update for a table of tensors (device array), one launch: blockIdx.y selects the tensor
+__global__ void param_update_multi_kernel(const tagi_param_tensor *__restrict__ t, float cap, int *__restrict__ neg) {
+    const tagi_param_tensor x = t[blockIdx.y];
+    for (size_t i = (size_t)blockIdx.x * BLOCK + threadIdx.x; i < x.n; i += (size_t)gridDim.x * BLOCK) {
+        const float dm = x.dmu[i], dv = x.dvar[i];
+        const float sm = (float)((dm > 0.f) - (dm < 0.f)), sv = (float)((dv > 0.f) - (dv < 0.f));
+        float v = x.var[i];
+        const float bar = sqrtf(v) / cap;
+        x.mu[i] += sm * fminf(fabsf(dm), bar);
+        v += sv * fminf(fabsf(dv), bar);
+        if (v <= 0.f) {
+            v = 1e-5f;
+            if (neg) atomicAdd(neg, 1);
+        }
+        x.var[i] = v;
+    }
+}
+
 }  // namespace
 }  // namespace tagi
 
@@ -168,6 +186,17 @@ int tagi_output_delta_selected(const float *mu_a, const float *var_a, const floa
     output_delta_selected_kernel<<<blocks_for(n_sel), BLOCK, 0, st>>>(mu_a, var_a, jcb, obs, var_obs, selected_idx,
                                                                       n_sel, n_out, n_enc, dmu, dvar);
     return launched("output_delta_selected_kernel launch");
+}
+
+int tagi_param_update_multi(int batch_size, int n_tensors, const tagi_param_tensor *tensors, int *neg_var_count,
+                            void *stream) {
+    TAGI_REQUIRE(batch_size > 0 && n_tensors > 0, "batch_size and n_tensors must be positive");
+    TAGI_REQUIRE(tensors != nullptr, "tensors is null");
+    const float cap = batch_size == 1 ? 0.1f : (batch_size < 256 ? 2.0f : 3.0f);
+    // one CTA column per tensor, 148 * 4 CTAs along each tensor (grid-stride): one launch for the whole network
+    param_update_multi_kernel<<<dim3(148 * 4, n_tensors), BLOCK, 0, static_cast<cudaStream_t>(stream)>>>(tensors, cap,
+                                                                                                       neg_var_count);
+    return launched("param_update_multi_kernel launch");
 }
 
 int tagi_param_update(int batch_size, size_t n, float *mu, float *var, const float *dmu, const float *dvar,

@@ -418,6 +418,7 @@ class Sequential:
             named[k].load(dict(mu_w=np.asarray(v[0], np.float32), var_w=np.asarray(v[1], np.float32),
                                mu_b=None if v[2] is None else np.asarray(v[2], np.float32),
                                var_b=None if v[3] is None else np.asarray(v[3], np.float32)))
+        self._ptable = None   # the tensors were replaced: the update table is rebuilt on the next step
 
     def delta_tensors(self):
         """All parameter-delta tensors in the order the backward pass produces them."""
@@ -446,8 +447,18 @@ class Sequential:
         self.input_delta = (dmu, dvar)
 
     def step(self):
-        for layer in self.layers:
-            layer.step(self.batch)
+        """Capped update of every parameter tensor of the network in one launch (tagi_param_update_multi)."""
+        if getattr(self, "_ptable", None) is None:
+            rows = []
+            for layer in self.named_layers().values():
+                rows.append((layer.mu_w, layer.var_w, layer.delta_mu_w, layer.delta_var_w))
+                if layer.mu_b is not None:
+                    rows.append((layer.mu_b, layer.var_b, layer.delta_mu_b, layer.delta_var_b))
+            table = [[t[0].data_ptr(), t[1].data_ptr(), t[2].data_ptr(), t[3].data_ptr(), t[0].numel()] for t in rows]
+            self._ptable = torch.tensor(table, dtype=torch.int64, device="cuda")   # five 8-byte fields per descriptor
+            self._ptable_rows = rows                                                # keeps the tensors alive
+            self.neg_var = torch.zeros(1, dtype=torch.int32, device="cuda")
+        lib.tagi_param_update_multi(self.batch, self._ptable.shape[0], _p(self._ptable), _p(self.neg_var), _stream())
 
 
 class OutputUpdater:

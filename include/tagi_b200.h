@@ -179,6 +179,18 @@ int tagi_output_delta_selected(const float *mu_a, const float *var_a, const floa
 int tagi_param_update(int batch_size, size_t n, float *mu, float *var, const float *dmu, const float *dvar,
                       int *neg_var_count, void *stream);
 
+/* The same capped update for every parameter tensor of a network in one launch. `tensors` is a DEVICE array of n_tensors
+ * descriptors (the caller builds it once; weights and biases of every layer are separate entries). The reference updates
+ * layer by layer (Sequential::step -> update_weights / update_biases per layer, src/sequential.cpp:440-448) with a blocking
+ * copy of the negative-variance counter after each; here the counter stays on the device. */
+typedef struct {
+    float *mu, *var;
+    const float *dmu, *dvar;
+    size_t n;
+} tagi_param_tensor;
+int tagi_param_update_multi(int batch_size, int n_tensors, const tagi_param_tensor *tensors, int *neg_var_count,
+                            void *stream);
+
 /* Same result as tagi_conv2d_bwd_param, for callers that must not allocate device memory while they run: a trainer
  * that gave the whole GPU to its own memory pool at start-up, a service with a fixed memory budget on a shared GPU, or
  * code running while another thread of the process captures a stream in the global capture mode (cudaMalloc is not

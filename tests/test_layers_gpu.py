@@ -211,3 +211,33 @@ def test_mixture_relu(G, oracle):
         G.check("mu_a", o[0].get(), ref[0], G.RTOL_MU)
         G.check("var_a", o[1].get(), ref[1], G.RTOL_VAR)
         G.check("jcb", o[2].get(), ref[2], G.RTOL_MU)
+
+
+@pytest.mark.parametrize("i", range(4))
+def test_param_update_single_and_multi(G, golden, i):
+    """tagi_param_update and tagi_param_update_multi against the reference's BaseLayer::update_weights / update_biases
+    (tests/golden/ops_golden.npz: batch sizes on both sides of the cap-factor thresholds, deltas that hit the cap and that
+    drive variances negative). The weight variance reset counter is the reference's neg_var_w_counter."""
+    import torch
+    from cutagi_b200.capi import lib
+    g = {k[len(f"upd{i}_"):]: np.ascontiguousarray(golden[k]) for k in golden.files if k.startswith(f"upd{i}_")}
+    bs = int(g["batch"][0])
+    for multi in (False, True):
+        t = {k: G.dev(g[k]) for k in ("mu_w0", "var_w0", "mu_b0", "var_b0", "dmu_w", "dvar_w", "dmu_b", "dvar_b")}
+        neg = torch.zeros(1, dtype=torch.int32, device="cuda")
+        if multi:
+            table = torch.tensor([[t["mu_w0"].data_ptr(), t["var_w0"].data_ptr(), t["dmu_w"].data_ptr(),
+                                   t["dvar_w"].data_ptr(), t["mu_w0"].numel()]], dtype=torch.int64, device="cuda")
+            lib.tagi_param_update_multi(bs, 1, table.data_ptr(), neg.data_ptr(), None)
+            table_b = torch.tensor([[t["mu_b0"].data_ptr(), t["var_b0"].data_ptr(), t["dmu_b"].data_ptr(),
+                                     t["dvar_b"].data_ptr(), t["mu_b0"].numel()]], dtype=torch.int64, device="cuda")
+            lib.tagi_param_update_multi(bs, 1, table_b.data_ptr(), None, None)
+        else:
+            lib.tagi_param_update(bs, t["mu_w0"].numel(), G.p(t["mu_w0"]), G.p(t["var_w0"]), G.p(t["dmu_w"]), G.p(t["dvar_w"]),
+                                  neg.data_ptr(), None)
+            lib.tagi_param_update(bs, t["mu_b0"].numel(), G.p(t["mu_b0"]), G.p(t["var_b0"]), G.p(t["dmu_b"]), G.p(t["dvar_b"]),
+                                  None, None)
+        torch.cuda.synchronize()
+        for a, b in (("mu_w0", "mu_w1"), ("var_w0", "var_w1"), ("mu_b0", "mu_b1"), ("var_b0", "var_b1")):
+            G.check(b, t[a].cpu().numpy(), g[b], 1e-6)
+        assert int(neg.item()) == int(g["neg"][0])
