@@ -35,8 +35,8 @@ __device__ __forceinline__ float block_sum(float v, float *red) {
 
 // Address of element i (0 <= i < B * wihi, (image, pixel) order) of channel c
 __device__ __forceinline__ long chan_elem(long i, int c, int C, int wihi) {
-    const long b = i / wihi;
-    return (b * C + c) * wihi + (i - b * wihi);
+    const unsigned b = (unsigned)i / (unsigned)wihi;  // i < B * wihi < 2^31 (checked at the entry points): 32-bit division
+    return ((long)b * C + c) * wihi + ((unsigned)i - b * (unsigned)wihi);
 }
 
 // src/batchnorm_layer.cpp:127-168. Partial of slice s of channel c: (count, mean, M2, sum of var_a).
@@ -277,6 +277,21 @@ __global__ void __launch_bounds__(BLOCK) add_shortcut_kernel(const float *__rest
     var_a[i] += __ldg(var_s + i) * j * j;
 }
 
+// four elements per thread with 16-byte accesses (n a multiple of 4, 16-byte aligned tensors)
+__global__ void __launch_bounds__(BLOCK) add_shortcut_vec4_kernel(const float4 *__restrict__ mu_s, const float4 *__restrict__ var_s,
+                                                                  const float4 *__restrict__ jcb, size_t n4,
+                                                                  float4 *__restrict__ mu_a, float4 *__restrict__ var_a) {
+    const size_t i = (size_t)blockIdx.x * BLOCK + threadIdx.x;
+    if (i >= n4) return;
+    const float4 j = jcb ? __ldg(jcb + i) : make_float4(1.f, 1.f, 1.f, 1.f);
+    const float4 s = __ldg(mu_s + i), vs = __ldg(var_s + i);
+    float4 a = mu_a[i], va = var_a[i];
+    a.x += s.x * j.x, a.y += s.y * j.y, a.z += s.z * j.z, a.w += s.w * j.w;
+    va.x += vs.x * j.x * j.x, va.y += vs.y * j.y * j.y, va.z += vs.z * j.z * j.z, va.w += vs.w * j.w * j.w;
+    mu_a[i] = a;
+    var_a[i] = va;
+}
+
 inline int launched(const char *what) {
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? TAGI_OK : cuda_fail(e, what);
@@ -354,7 +369,12 @@ int avgpool2d_bwd(const tagi_conv2d_geom &g, const float *jcb, const float *dmu_
 int add_shortcut(size_t n, const float *mu_s, const float *var_s, const float *jcb, float *mu_a, float *var_a,
                  cudaStream_t st) {
     if (n == 0) return TAGI_OK;
-    add_shortcut_kernel<<<(unsigned)((n + BLOCK - 1) / BLOCK), BLOCK, 0, st>>>(mu_s, var_s, jcb, n, mu_a, var_a);
+    if (n % 4 == 0 && aligned16(mu_s) && aligned16(var_s) && aligned16(mu_a) && aligned16(var_a) && (!jcb || aligned16(jcb)))
+        add_shortcut_vec4_kernel<<<(unsigned)((n / 4 + BLOCK - 1) / BLOCK), BLOCK, 0, st>>>(
+            reinterpret_cast<const float4 *>(mu_s), reinterpret_cast<const float4 *>(var_s),
+            reinterpret_cast<const float4 *>(jcb), n / 4, reinterpret_cast<float4 *>(mu_a), reinterpret_cast<float4 *>(var_a));
+    else
+        add_shortcut_kernel<<<(unsigned)((n + BLOCK - 1) / BLOCK), BLOCK, 0, st>>>(mu_s, var_s, jcb, n, mu_a, var_a);
     return launched("add_shortcut_kernel launch");
 }
 
