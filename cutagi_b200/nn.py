@@ -4,7 +4,7 @@ TAGI training steps run through the C ABI.
 
 Every arithmetic step is a call into libtagi_b200.so; torch is used for device memory only. The mirror exists for
 parity tests and measurements. Inside cuTAGI the same entry points are reached through the reference's own classes
-(see INTEGRATION.md); this module is not meant to replace them.
+(the shims under integration/); this module is not meant to replace them.
 """
 import ctypes
 import math
