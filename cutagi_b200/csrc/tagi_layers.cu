@@ -148,6 +148,9 @@ __global__ void __launch_bounds__(BLOCK) bn2d_apply_kernel(const float *__restri
 // State deltas (src/batchnorm_layer.cpp:233-255) and the per-slice sums of the parameter deltas (:307-357) in one
 // pass over the saved input, the Jacobian and the incoming deltas.
 // Partial of slice s of channel c: (sum t * dmu_o, sum t * t * dvar_o, sum dmu_o, sum dvar_o), t = inv * (mu_a - mean) * var_w.
+// VEC = 4: H*W is a multiple of 4 and the tensors are 16-byte aligned, so every group of four consecutive elements of a
+// channel lies in one image plane and moves as one 16-byte access.
+template <int VEC>
 __global__ void __launch_bounds__(BLOCK) bn2d_bwd_kernel(const float *__restrict__ mu_w, const float *__restrict__ var_w,
                                                          const float *__restrict__ mu_a, const float *__restrict__ jcb,
                                                          const float *__restrict__ mean, const float *__restrict__ var,
@@ -161,21 +164,42 @@ __global__ void __launch_bounds__(BLOCK) bn2d_bwd_kernel(const float *__restrict
     const int cnt = (int)min((long)SLICE, n - i0);
     const float inv = 1.0f / sqrtf(__ldg(var + c) + eps), m = __ldg(mean + c), w = __ldg(mu_w + c), vw = __ldg(var_w + c);
     float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    auto one = [&](float a_, float j_, float dm, float dv, float &o1, float &o2) {
+        const float t = inv * (a_ - m) * vw;
+        s0 += t * dm;
+        s1 += t * dv * t;
+        s2 += dm;
+        s3 += dv;
+        const float u = inv * w * j_;
+        o1 = u * dm;
+        o2 = u * dv * u;
+    };
 #pragma unroll 4
-    for (int e = 0; e < PER_THREAD; e++) {
-        const int j = threadIdx.x + e * BLOCK;
+    for (int e = 0; e < PER_THREAD / VEC; e++) {
+        const int j = (threadIdx.x + e * BLOCK) * VEC;
         if (j < cnt) {
             const long a = chan_elem(i0 + j, c, C, wihi);
-            const float dm = __ldg(dmu_o + a), dv = __ldg(dvar_o + a);
-            const float t = inv * (__ldg(mu_a + a) - m) * vw;
-            s0 += t * dm;
-            s1 += t * dv * t;
-            s2 += dm;
-            s3 += dv;
-            if (state_update) {
-                const float u = inv * w * (jcb ? __ldg(jcb + a) : 1.f);
-                dmu[a] = u * dm;
-                dvar[a] = u * dv * u;
+            if (VEC == 4) {
+                const float4 dm = __ldg(reinterpret_cast<const float4 *>(dmu_o + a));
+                const float4 dv = __ldg(reinterpret_cast<const float4 *>(dvar_o + a));
+                const float4 x = __ldg(reinterpret_cast<const float4 *>(mu_a + a));
+                const float4 jj = jcb ? __ldg(reinterpret_cast<const float4 *>(jcb + a)) : make_float4(1.f, 1.f, 1.f, 1.f);
+                float4 o1, o2;
+                one(x.x, jj.x, dm.x, dv.x, o1.x, o2.x);
+                one(x.y, jj.y, dm.y, dv.y, o1.y, o2.y);
+                one(x.z, jj.z, dm.z, dv.z, o1.z, o2.z);
+                one(x.w, jj.w, dm.w, dv.w, o1.w, o2.w);
+                if (state_update) {
+                    *reinterpret_cast<float4 *>(dmu + a) = o1;
+                    *reinterpret_cast<float4 *>(dvar + a) = o2;
+                }
+            } else {
+                float o1, o2;
+                one(__ldg(mu_a + a), jcb ? __ldg(jcb + a) : 1.f, __ldg(dmu_o + a), __ldg(dvar_o + a), o1, o2);
+                if (state_update) {
+                    dmu[a] = o1;
+                    dvar[a] = o2;
+                }
             }
         }
     }
@@ -335,8 +359,14 @@ int bn2d_bwd(int B, int C, int wihi, int state_update, float eps, const float *m
     int rc;
     if ((rc = conv_scratch((size_t)C * slices * sizeof(float4), &ws)) != TAGI_OK) return rc;
     float4 *part = reinterpret_cast<float4 *>(ws);
-    bn2d_bwd_kernel<<<dim3(slices, C), BLOCK, 0, st>>>(mu_w, var_w, mu_a, jcb, mu_batch, var_batch, dmu_o, dvar_o, eps, C,
-                                                       wihi, n, state_update, dmu, dvar, part);
+    const bool vec = wihi % 4 == 0 && aligned16(mu_a) && aligned16(dmu_o) && aligned16(dvar_o) && (!jcb || aligned16(jcb)) &&
+                     (!state_update || (aligned16(dmu) && aligned16(dvar)));
+    if (vec)
+        bn2d_bwd_kernel<4><<<dim3(slices, C), BLOCK, 0, st>>>(mu_w, var_w, mu_a, jcb, mu_batch, var_batch, dmu_o, dvar_o, eps,
+                                                              C, wihi, n, state_update, dmu, dvar, part);
+    else
+        bn2d_bwd_kernel<1><<<dim3(slices, C), BLOCK, 0, st>>>(mu_w, var_w, mu_a, jcb, mu_batch, var_batch, dmu_o, dvar_o, eps,
+                                                              C, wihi, n, state_update, dmu, dvar, part);
     if ((rc = launched("bn2d_bwd_kernel launch")) != TAGI_OK) return rc;
     bn2d_bwd_final_kernel<<<(C + 127) / 128, 128, 0, st>>>(part, slices, var_b, C, dmu_w, dvar_w, dmu_b, dvar_b);
     return launched("bn2d_bwd_final_kernel launch");
