@@ -765,7 +765,9 @@ __device__ __forceinline__ void load_half_tile(uint32_t dst, const CUtensorMap *
     }
 }
 
-template <int OP, int CH, int RS, int DS>
+// GATHER: the A tiles of the forward / state pass are gathered inside the kernel (Conv2d, launched with 384 threads);
+// without it the kernel is launched with 352 threads and contains none of that code.
+template <int OP, int CH, int RS, int DS, bool GATHER>
 __global__ void __launch_bounds__(NTHREADS2, 1)
 tagi_tc_linear_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
                            const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
@@ -805,14 +807,14 @@ tagi_tc_linear_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __gri
 
     if (threadIdx.x == 0) {
         // one arrival from the TMA thread; with gathered A tiles one more from each of the 64 gathering threads
-        for (int s = 0; s < RS; s++) mbar_init(raw_full + s, OP != OP_BWD_PARAM && cg.on ? 65 : 1);
+        for (int s = 0; s < RS; s++) mbar_init(raw_full + s, GATHER && cg.on ? 65 : 1);
         for (int s = 0; s < L; s++) mbar_init(stage_done + s, 2);  // one commit from each MMA issuer
         for (int s = 0; s < DS; s++) mbar_init(conv_done + s, NCONV_WARPS);  // used in CTA 0: one warp group of each CTA arrives
         mbar_init(acc_full, 2);
         mbar_init(acc_empty, 2 * NCONV_WARPS);          // used in CTA 0 only
         *abort_flag = 0;
         mbar_init_fence();
-        if (OP == OP_BWD_PARAM || !cg.on) {
+        if (!GATHER || !cg.on) {
             prefetch_tmap(&tmA0);
             prefetch_tmap(&tmA1);
         }
@@ -826,7 +828,7 @@ tagi_tc_linear_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __gri
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
 
-    if (OP != OP_BWD_PARAM && cg.on && (warp == 0 || warp == GATHER_WARP)) {
+    if (GATHER && cg.on && (warp == 0 || warp == GATHER_WARP)) {
         // ------------------------------------------------------------------ Conv2d: A tiles gathered with cp.async
         // Warps 0 and 11: each lane owns two of the CTA's 128 rows (pixels). The k index (channel, tap) is the same
         // for all lanes of an instruction, so consecutive lanes read consecutive pixels of one image row: coalesced.
@@ -1248,14 +1250,20 @@ int launch_pair(const CUtensorMap &a0, const CUtensorMap &a1, const CUtensorMap 
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     cudaError_t e;
-#define TAGI_PAIR_LAUNCH(CHV, RSV, DSV)                                                        \
+#define TAGI_PAIR_LAUNCH_G(CHV, RSV, DSV, GV)                                                  \
     do {                                                                                         \
-        auto k = tagi_tc_linear_pair_kernel<OP, CHV, RSV, DSV>;                                  \
+        auto k = tagi_tc_linear_pair_kernel<OP, CHV, RSV, DSV, GV>;                              \
         constexpr size_t sm = pair_smem_bytes<OP, RSV, DSV>();                                   \
         cfg.dynamicSmemBytes = sm;                                                               \
+        cfg.blockDim = dim3(GV ? NTHREADS2 : NTHREADS2 - 32);                                    \
         e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);       \
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");                       \
         e = cudaLaunchKernelEx(&cfg, k, a0, a1, b0, b1, epi, cg, kdim, bn, status);              \
+    } while (0)
+#define TAGI_PAIR_LAUNCH(CHV, RSV, DSV)                                      \
+    do {                                                                       \
+        if (OP != OP_BWD_PARAM && cg.on) TAGI_PAIR_LAUNCH_G(CHV, RSV, DSV, OP != OP_BWD_PARAM); \
+        else TAGI_PAIR_LAUNCH_G(CHV, RSV, DSV, false);                         \
     } while (0)
     // ring depths: hand-offs cross two SMs here, so the derived ring is as deep as tensor memory allows (backward:
     // four slots; forward: three when the accumulators fit 2 x 112 columns, else two)
@@ -1269,6 +1277,7 @@ int launch_pair(const CUtensorMap &a0, const CUtensorMap &a1, const CUtensorMap 
         if (g_chunked) TAGI_PAIR_LAUNCH(CHUNK_STAGES, 6, 4); else TAGI_PAIR_LAUNCH(0, 6, 4);
     }
 #undef TAGI_PAIR_LAUNCH
+#undef TAGI_PAIR_LAUNCH_G
     if (e != cudaSuccess) return cuda_fail(e, "tensor-core Linear pair kernel launch");
     return TAGI_OK;
 }
