@@ -40,6 +40,8 @@ _SIGNATURES = {
     "tagi_conv2d_bwd_state": [C.POINTER(ConvGeom), _p, _p, _p, _p, _p, _p, _p],
     "tagi_conv2d_bwd_param": [C.POINTER(ConvGeom), _p, _p, _p, _p, _p, _p, _p, _p, _p, _p],
     "tagi_relu_fwd": [_p, _p, C.c_size_t, _p, _p, _p, _p],
+    "tagi_linear_fwd_relu": [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _p, _p],
+    "tagi_conv2d_fwd_relu": [C.POINTER(ConvGeom), _p, _p, _p, _p, _p, _p, _p, _p, _p, _p],
     "tagi_mixture_relu_fwd": [_p, _p, C.c_size_t, _p, _p, _p, _p],
     "tagi_output_delta": [_p, _p, _p, _p, _p, C.c_size_t, _p, _p, _p],
     "tagi_output_delta_selected": [_p, _p, _p, _p, _p, _p, _i, _i, _i, _p, _p, _p],

@@ -102,6 +102,35 @@ int tagi_linear_fwd(const float *mu_w, const float *var_w, const float *mu_b, co
     return linear_fwd_ffma(mu_w, var_w, mu_b, var_b, mu_a, var_a, B, K, N, mu_z, var_z, st);
 }
 
+int tagi_linear_fwd_relu(const float *mu_w, const float *var_w, const float *mu_b, const float *var_b, const float *mu_a,
+                         const float *var_a, int B, int K, int N, int has_bias, float *mu_a_out, float *var_a_out,
+                         float *jcb_out, void *stream) {
+    TAGI_DIMS();
+    TAGI_PTR(mu_w);
+    TAGI_PTR(var_w);
+    TAGI_PTR(mu_a);
+    TAGI_PTR(var_a);
+    TAGI_PTR(mu_a_out);
+    TAGI_PTR(var_a_out);
+    TAGI_PTR(jcb_out);
+    if (has_bias) {
+        TAGI_PTR(mu_b);
+        TAGI_PTR(var_b);
+    } else {
+        mu_b = var_b = nullptr;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int rc;
+    // one kernel where the forward runs on CTA pairs; otherwise the forward followed by the ReLU in place
+    if (pick_tc(__func__, B, K, N, {mu_w, var_w, mu_b, var_b, mu_a, var_a, mu_a_out, var_a_out, jcb_out}, &rc) &&
+        linear_tc_pair_for(B))
+        return linear_fwd_tc(mu_w, var_w, mu_b, var_b, mu_a, var_a, B, K, N, mu_a_out, var_a_out, st, 0, nullptr, jcb_out);
+    if (rc != TAGI_OK) return rc;
+    rc = tagi_linear_fwd(mu_w, var_w, mu_b, var_b, mu_a, var_a, B, K, N, has_bias, mu_a_out, var_a_out, stream);
+    if (rc != TAGI_OK) return rc;
+    return tagi_relu_fwd(mu_a_out, var_a_out, (size_t)B * N, mu_a_out, var_a_out, jcb_out, stream);
+}
+
 int tagi_linear_bwd_state(const float *mu_w, const float *jcb, const float *dmu_z, const float *dvar_z, int B, int K,
                           int N, float *dmu_a, float *dvar_a, void *stream) {
     TAGI_DIMS();
@@ -249,6 +278,35 @@ int tagi_conv2d_fwd(const tagi_conv2d_geom *g, const float *mu_w, const float *v
         return conv2d_fwd_tc(*g, mu_w, var_w, mu_b, var_b, mu_a, var_a, mu_z, var_z, st);
     if (rc != TAGI_OK) return rc;
     return conv2d_fwd_ffma(*g, mu_w, var_w, mu_b, var_b, mu_a, var_a, mu_z, var_z, st);
+}
+
+int tagi_conv2d_fwd_relu(const tagi_conv2d_geom *g, const float *mu_w, const float *var_w, const float *mu_b,
+                         const float *var_b, const float *mu_a, const float *var_a, float *mu_a_out, float *var_a_out,
+                         float *jcb_out, void *stream) {
+    int rc = check_geom(g);
+    if (rc != TAGI_OK) return rc;
+    TAGI_PTR(mu_w);
+    TAGI_PTR(var_w);
+    TAGI_PTR(mu_a);
+    TAGI_PTR(var_a);
+    TAGI_PTR(mu_a_out);
+    TAGI_PTR(var_a_out);
+    TAGI_PTR(jcb_out);
+    if (g->has_bias) {
+        TAGI_PTR(mu_b);
+        TAGI_PTR(var_b);
+    } else {
+        mu_b = var_b = nullptr;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (pick_conv_tc(__func__, *g, CONV_PASS_FWD, {mu_w, var_w, mu_b, var_b, mu_a, var_a, mu_a_out, var_a_out, jcb_out},
+                     &rc) &&
+        conv2d_fwd_tc_fuses_relu(*g))
+        return conv2d_fwd_tc(*g, mu_w, var_w, mu_b, var_b, mu_a, var_a, mu_a_out, var_a_out, st, jcb_out);
+    if (rc != TAGI_OK) return rc;
+    rc = tagi_conv2d_fwd(g, mu_w, var_w, mu_b, var_b, mu_a, var_a, mu_a_out, var_a_out, stream);
+    if (rc != TAGI_OK) return rc;
+    return tagi_relu_fwd(mu_a_out, var_a_out, (size_t)g->B * g->fo * g->ho * g->wo, mu_a_out, var_a_out, jcb_out, stream);
 }
 
 int tagi_conv2d_bwd_state(const tagi_conv2d_geom *g, const float *mu_w, const float *jcb, const float *dmu_z,

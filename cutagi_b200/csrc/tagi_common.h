@@ -65,7 +65,9 @@ struct ConvGather {
 
 int linear_fwd_tc(const float *mu_w, const float *var_w, const float *mu_b, const float *var_b, const float *mu_a,
                   const float *var_a, int B, int K, int N, float *mu_z, float *var_z, cudaStream_t st, int npix = 0,
-                  const ConvGather *cg = nullptr);
+                  const ConvGather *cg = nullptr, float *relu_jcb = nullptr);
+// relu_jcb (only when linear_tc_pair_for(B)): the ReLU is folded into the epilogue; mu_z / var_z receive the moments
+// after the ReLU and relu_jcb its Jacobian
 bool linear_tc_pair_for(int rows);  // true when a pass with this many output rows runs on the CTA-pair kernel
 int linear_bwd_state_tc(const float *mu_w, const float *jcb, const float *dmu_z, const float *dvar_z, int B, int K,
                         int N, float *dmu_a, float *dvar_a, cudaStream_t st, int npix = 0,
@@ -94,7 +96,8 @@ bool conv_tc_supported(const tagi_conv2d_geom &g, int pass, std::initializer_lis
 bool conv_tc_profitable(const tagi_conv2d_geom &g, int pass);
 int conv2d_fwd_tc(const tagi_conv2d_geom &g, const float *mu_w, const float *var_w, const float *mu_b,
                   const float *var_b, const float *mu_a, const float *var_a, float *mu_z, float *var_z,
-                  cudaStream_t st);
+                  cudaStream_t st, float *relu_jcb = nullptr);
+bool conv2d_fwd_tc_fuses_relu(const tagi_conv2d_geom &g);  // the forward of this geometry runs on the CTA-pair kernel
 int conv2d_bwd_state_tc(const tagi_conv2d_geom &g, const float *mu_w, const float *jcb, const float *dmu_z,
                         const float *dvar_z, float *dmu_a, float *dvar_a, cudaStream_t st);
 int conv2d_bwd_param_tc(const tagi_conv2d_geom &g, const float *var_w, const float *mu_a, const float *dmu_z,

@@ -92,19 +92,36 @@ struct TileGeom {
 };
 constexpr int GATHER_CT = 16;  // channels per CTA
 
-template <int NSRC, int KS, bool FLIP>
+constexpr int GATHER_PIX = 128;  // output pixels per CTA at most
+
+// VEC = 4: 16-byte stores (the CTA's column count, its first column and Kc are multiples of 4); VEC = 1 otherwise.
+template <int NSRC, int KS, bool FLIP, int VEC>
 __global__ void __launch_bounds__(256) gather_tiled_kernel(const float *__restrict__ s0, const float *__restrict__ s1,
                                                            TileGeom g, float *__restrict__ d0, float *__restrict__ d1) {
     extern __shared__ float patch[];
     constexpr int K2 = KS * KS;
+    __shared__ __align__(16) int tapoff[GATHER_CT * K2];  // column (c, ky, kx) -> offset inside the staged patch
+    __shared__ int pixbase[GATHER_PIX];                    // pixel of the tile -> its window's first patch element
+    __shared__ int pixrow[GATHER_PIX];                     // pixel of the tile -> row of the output matrix, -1 outside
     const int IH = (g.ty - 1) * g.stride + KS, IW = (g.tx - 1) * g.stride + KS, plane = IH * IW;
     float *p0 = patch, *p1 = patch + g.ct * plane;
     int t = blockIdx.x;
     const int tile_x = t % g.tiles_x;
     t /= g.tiles_x;
     const int tile_y = t % g.tiles_y, b = t / g.tiles_y;
-    const int c0 = blockIdx.y * GATHER_CT, nc = min(GATHER_CT, g.C - c0);
+    const int c0 = blockIdx.y * GATHER_CT, nc = min(GATHER_CT, g.C - c0), ncols = nc * K2, npix = g.tx * g.ty;
     const int oy0 = tile_y * g.ty, ox0 = tile_x * g.tx;
+    for (int j = threadIdx.x; j < ncols; j += 256) {
+        const int c = j / K2, tap = j - c * K2;
+        int ky = tap / KS, kx = tap - ky * KS;
+        if (FLIP) ky = KS - 1 - ky, kx = KS - 1 - kx;
+        tapoff[j] = c * plane + ky * IW + kx;
+    }
+    for (int pix = threadIdx.x; pix < npix; pix += 256) {
+        const int py = pix / g.tx, px = pix - py * g.tx, oy = oy0 + py, ox = ox0 + px;
+        pixbase[pix] = (py * IW + px) * g.stride;
+        pixrow[pix] = oy < g.OH && ox < g.OW ? (b * g.OH + oy) * g.OW + ox : -1;
+    }
     // top-left source pixel of the patch
     const int y0 = FLIP ? oy0 + g.off - (KS - 1) : oy0 * g.stride - g.off;
     const int x0 = FLIP ? ox0 + g.off - (KS - 1) : ox0 * g.stride - g.off;
@@ -121,21 +138,22 @@ __global__ void __launch_bounds__(256) gather_tiled_kernel(const float *__restri
         if (NSRC == 2) p1[i] = v1;
     }
     __syncthreads();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, ncols = nc * K2;
-    for (int pix = warp; pix < g.tx * g.ty; pix += 8) {
-        const int py = pix / g.tx, px = pix - py * g.tx;
-        const int oy = oy0 + py, ox = ox0 + px;
-        if (oy >= g.OH || ox >= g.OW) continue;
-        const long row = ((long)b * g.OH + oy) * g.OW + ox;
-        float *o0 = d0 + row * g.Kc + (long)c0 * K2, *o1 = NSRC == 2 ? d1 + row * g.Kc + (long)c0 * K2 : nullptr;
-        const int base = py * g.stride * IW + px * g.stride;
-        for (int j = lane; j < ncols; j += 32) {
-            const int c = j / K2, tap = j - c * K2;
-            int ky = tap / KS, kx = tap - ky * KS;
-            if (FLIP) ky = KS - 1 - ky, kx = KS - 1 - kx;
-            const int a = c * plane + base + ky * IW + kx;
-            o0[j] = p0[a];
-            if (NSRC == 2) o1[j] = p1[a];
+    // one item = VEC consecutive columns of one pixel's row; items run column-fastest over the threads
+    const int q = ncols / VEC;
+    for (int i = threadIdx.x; i < npix * q; i += 256) {
+        const int pix = i / q, jv = i - pix * q, row = pixrow[pix];
+        if (row < 0) continue;
+        const int pb = pixbase[pix];
+        const long o = (long)row * g.Kc + (long)c0 * K2 + jv * VEC;
+        if (VEC == 4) {
+            const int4 a = *reinterpret_cast<const int4 *>(tapoff + 4 * jv);
+            *reinterpret_cast<float4 *>(d0 + o) = make_float4(p0[pb + a.x], p0[pb + a.y], p0[pb + a.z], p0[pb + a.w]);
+            if (NSRC == 2)
+                *reinterpret_cast<float4 *>(d1 + o) = make_float4(p1[pb + a.x], p1[pb + a.y], p1[pb + a.z], p1[pb + a.w]);
+        } else {
+            const int a = tapoff[jv];
+            d0[o] = p0[pb + a];
+            if (NSRC == 2) d1[o] = p1[pb + a];
         }
     }
 }
@@ -183,8 +201,9 @@ __global__ void __launch_bounds__(256) col2im_kernel(const float *__restrict__ c
                                                      float *__restrict__ o1) {
     const long total = (long)g.B * g.fi * g.wihi;
     for (long t = (long)blockIdx.x * 256 + threadIdx.x; t < total; t += (long)gridDim.x * 256) {
-        const int q = (int)(t % g.wihi);
-        const long n = t / g.wihi;  // b * fi + ci
+        // t < 2^31 (checked at the entry points): 32-bit divisions
+        const unsigned n = (unsigned)t / (unsigned)g.wihi;  // b * fi + ci
+        const int q = (int)((unsigned)t - n * (unsigned)g.wihi);
         const int y = q / g.wi, x = q - y * g.wi;
         float a0 = 0.f, a1 = 0.f;
         // output rows / columns whose window contains the pixel: oy * s - off <= y <= oy * s - off + k - 1
@@ -194,7 +213,7 @@ __global__ void __launch_bounds__(256) col2im_kernel(const float *__restrict__ c
             const int ky = y + g.off - oy * g.stride;
             for (int ox = ox_lo; ox <= ox_hi; ox++) {
                 const int kx = x + g.off - ox * g.stride;
-                const long i = (n * g.k2 + ky * g.k + kx) * g.woho + (long)oy * g.wo + ox;
+                const long i = ((long)n * g.k2 + ky * g.k + kx) * g.woho + oy * g.wo + ox;
                 a0 += __ldg(c0 + i);
                 a1 += __ldg(c1 + i);
             }
@@ -233,22 +252,36 @@ bool launch_gather_tiled(const float *s0, const float *s1, int B, int C, int H, 
     if (k != 2 && k != 3 && k != 6) return false;
     TileGeom g;
     g.B = B, g.C = C, g.H = H, g.W = W, g.OH = OH, g.OW = OW, g.stride = FLIP ? 1 : stride, g.off = off;
-    g.tx = OW < 32 ? OW : 32;
-    g.ty = 32 / g.tx < OH ? 32 / g.tx : OH;
-    if (g.ty < 1) g.ty = 1;
-    g.tiles_x = (OW + g.tx - 1) / g.tx, g.tiles_y = (OH + g.ty - 1) / g.ty;
+    // tiles of up to 128 pixels: the row cut into equal pieces of at most 32 pixels, as many rows as fit
+    const int nx = (OW + 31) / 32;
+    g.tx = (OW + nx - 1) / nx;
+    g.ty = GATHER_PIX / g.tx < OH ? GATHER_PIX / g.tx : OH;
     g.Kc = C * k * k;
     g.ct = C < GATHER_CT ? C : GATHER_CT;
-    const int IH = (g.ty - 1) * g.stride + k, IW = (g.tx - 1) * g.stride + k;
-    const size_t smem = (size_t)NSRC * g.ct * IH * IW * sizeof(float);
-    if (smem > 48 * 1024) return false;
+    auto smem_of = [&](int ty) {
+        const int IH = (ty - 1) * g.stride + k, IW = (g.tx - 1) * g.stride + k;
+        return (size_t)NSRC * g.ct * IH * IW * sizeof(float);
+    };
+    while (g.ty > 1 && smem_of(g.ty) > 40 * 1024) g.ty--;
+    const size_t smem = smem_of(g.ty);
+    if (smem > 40 * 1024 || (long)B * OH * OW >= (1L << 31)) return false;
+    g.tiles_x = (OW + g.tx - 1) / g.tx, g.tiles_y = (OH + g.ty - 1) / g.ty;
     const dim3 grid((unsigned)((long)B * g.tiles_x * g.tiles_y), (unsigned)((C + GATHER_CT - 1) / GATHER_CT));
+    // 16-byte stores when every CTA's column block starts and ends on a multiple of 4 columns
+    const int k2 = k * k, last = C % GATHER_CT;
+    const bool vec = g.Kc % 4 == 0 && (g.ct * k2) % 4 == 0 && (last * k2) % 4 == 0 && aligned16(d0) && (NSRC == 1 || aligned16(d1));
+#define TAGI_GATHER_LAUNCH(KSV)                                                                       \
+    do {                                                                                              \
+        if (vec) gather_tiled_kernel<NSRC, KSV, FLIP, 4><<<grid, 256, smem, st>>>(s0, s1, g, d0, d1); \
+        else gather_tiled_kernel<NSRC, KSV, FLIP, 1><<<grid, 256, smem, st>>>(s0, s1, g, d0, d1);     \
+    } while (0)
     if (k == 3)
-        gather_tiled_kernel<NSRC, 3, FLIP><<<grid, 256, smem, st>>>(s0, s1, g, d0, d1);
+        TAGI_GATHER_LAUNCH(3);
     else if (k == 6)
-        gather_tiled_kernel<NSRC, 6, FLIP><<<grid, 256, smem, st>>>(s0, s1, g, d0, d1);
+        TAGI_GATHER_LAUNCH(6);
     else
-        gather_tiled_kernel<NSRC, 2, FLIP><<<grid, 256, smem, st>>>(s0, s1, g, d0, d1);
+        TAGI_GATHER_LAUNCH(2);
+#undef TAGI_GATHER_LAUNCH
     return true;
 }
 
@@ -278,13 +311,14 @@ bool conv_tc_profitable(const tagi_conv2d_geom &cg, int pass) {
 
 int conv2d_fwd_tc(const tagi_conv2d_geom &cg, const float *mu_w, const float *var_w, const float *mu_b,
                   const float *var_b, const float *mu_a, const float *var_a, float *mu_z, float *var_z,
-                  cudaStream_t st) {
+                  cudaStream_t st, float *relu_jcb) {
     const G g = geom_of(cg);
     const long rows = (long)g.B * g.woho;
     if (implicit_ok(g, rows, g.fo)) {
         // implicit GEMM: the kernel gathers the receptive fields itself while it stages its A tiles
         ConvGather ig{1, mu_a, var_a, g.fi, g.hi, g.wi, g.wo, g.woho, g.k, g.stride, g.off, +1, rows};
-        return linear_fwd_tc(mu_w, var_w, mu_b, var_b, nullptr, nullptr, (int)rows, g.Kc, g.fo, mu_z, var_z, st, g.woho, &ig);
+        return linear_fwd_tc(mu_w, var_w, mu_b, var_b, nullptr, nullptr, (int)rows, g.Kc, g.fo, mu_z, var_z, st, g.woho, &ig,
+                             relu_jcb);
     }
     float *ws = nullptr;
     int rc = conv_scratch((size_t)2 * rows * g.Kc * sizeof(float), &ws);
@@ -294,7 +328,13 @@ int conv2d_fwd_tc(const tagi_conv2d_geom &cg, const float *mu_w, const float *va
         im2col_kernel<2><<<grid_for(rows * g.Kc), 256, 0, st>>>(mu_a, var_a, g, x_mu, x_var);
     if ((rc = ok_or(cudaGetLastError(), "im2col kernel launch")) != TAGI_OK) return rc;
     // rows = (image, output pixel), columns = output channels: exactly Linear's forward, written as [b][co][pixel]
-    return linear_fwd_tc(mu_w, var_w, mu_b, var_b, x_mu, x_var, (int)rows, g.Kc, g.fo, mu_z, var_z, st, g.woho);
+    return linear_fwd_tc(mu_w, var_w, mu_b, var_b, x_mu, x_var, (int)rows, g.Kc, g.fo, mu_z, var_z, st, g.woho, nullptr,
+                         relu_jcb);
+}
+bool conv2d_fwd_tc_fuses_relu(const tagi_conv2d_geom &cg) {
+    const G g = geom_of(cg);
+    const long rows = (long)g.B * g.woho;
+    return rows < (1L << 31) && linear_tc_pair_for((int)rows);
 }
 
 int conv2d_bwd_state_tc(const tagi_conv2d_geom &cg, const float *mu_w, const float *jcb, const float *dmu_z,

@@ -40,6 +40,8 @@ __device__ __forceinline__ long chan_elem(long i, int c, int C, int wihi) {
 }
 
 // src/batchnorm_layer.cpp:127-168. Partial of slice s of channel c: (count, mean, M2, sum of var_a).
+// VEC = 4: H*W is a multiple of 4 and the tensors are 16-byte aligned (16-byte loads, see bn2d_bwd_kernel).
+template <int VEC>
 __global__ void __launch_bounds__(BLOCK) bn2d_stats_partial_kernel(const float *__restrict__ mu_a,
                                                                    const float *__restrict__ var_a, int C, int wihi,
                                                                    long n, float4 *__restrict__ part) {
@@ -50,14 +52,23 @@ __global__ void __launch_bounds__(BLOCK) bn2d_stats_partial_kernel(const float *
     float x[PER_THREAD];
     float sm = 0.f, sv = 0.f;
 #pragma unroll
-    for (int e = 0; e < PER_THREAD; e++) {
-        const int j = threadIdx.x + e * BLOCK;
-        x[e] = 0.f;
-        if (j < cnt) {
+    for (int e = 0; e < PER_THREAD / VEC; e++) {
+        const int j = (threadIdx.x + e * BLOCK) * VEC;
+#pragma unroll
+        for (int v = 0; v < VEC; v++) x[e * VEC + v] = 0.f;
+        if (j < cnt) {  // cnt is a multiple of VEC: a group of VEC elements is inside the slice or outside it
             const long a = chan_elem(i0 + j, c, C, wihi);
-            x[e] = __ldg(mu_a + a);
-            sm += x[e];
-            sv += __ldg(var_a + a);
+            if (VEC == 4) {
+                const float4 m = __ldg(reinterpret_cast<const float4 *>(mu_a + a));
+                const float4 v = __ldg(reinterpret_cast<const float4 *>(var_a + a));
+                x[e * 4] = m.x, x[e * 4 + 1] = m.y, x[e * 4 + 2] = m.z, x[e * 4 + 3] = m.w;
+                sm += (m.x + m.y) + (m.z + m.w);
+                sv += (v.x + v.y) + (v.z + v.w);
+            } else {
+                x[e] = __ldg(mu_a + a);
+                sm += x[e];
+                sv += __ldg(var_a + a);
+            }
         }
     }
     sm = block_sum(sm, red);
@@ -65,8 +76,11 @@ __global__ void __launch_bounds__(BLOCK) bn2d_stats_partial_kernel(const float *
     const float mean = sm / cnt;
     float m2 = 0.f;
 #pragma unroll
-    for (int e = 0; e < PER_THREAD; e++)
-        if (threadIdx.x + e * BLOCK < cnt) m2 += (x[e] - mean) * (x[e] - mean);
+    for (int e = 0; e < PER_THREAD / VEC; e++)
+        if ((threadIdx.x + e * BLOCK) * VEC < cnt) {
+#pragma unroll
+            for (int v = 0; v < VEC; v++) m2 += (x[e * VEC + v] - mean) * (x[e * VEC + v] - mean);
+        }
     m2 = block_sum(m2, red);
     if (threadIdx.x == 0) part[(long)c * gridDim.x + blockIdx.x] = make_float4((float)cnt, mean, m2, sv);
 }
@@ -257,37 +271,55 @@ __global__ void __launch_bounds__(BLOCK) avgpool2d_fwd_kernel(const float *__res
     var_z[t] = sv / (k2 * k2);
 }
 
-// src/pooling_layer.cpp:285-375: each input pixel collects the deltas of the cells that contain it; one thread per input
+// src/pooling_layer.cpp:285-375: each input pixel collects the deltas of the cells that contain it; one thread per VEC
+// consecutive pixels of a row (VEC = 4: wi a multiple of 4 and 16-byte aligned tensors)
+template <int VEC>
 __global__ void __launch_bounds__(BLOCK) avgpool2d_bwd_kernel(const float *__restrict__ jcb, const float *__restrict__ dmu_o,
-                                                              const float *__restrict__ dvar_o, PoolGeom g, long total,
+                                                              const float *__restrict__ dvar_o, PoolGeom g, unsigned items,
                                                               float *__restrict__ dmu, float *__restrict__ dvar) {
-    const long t = (long)blockIdx.x * BLOCK + threadIdx.x;
-    if (t >= total) return;
-    const int wihi = g.wi * g.hi, q = (int)(t % wihi);
-    const long plane = t / wihi;
-    const int y = q / g.wi, x = q - y * g.wi;
-    const float *dm = dmu_o + plane * g.ho * g.wo, *dv = dvar_o + plane * g.ho * g.wo;
-    float sm = 0.f, sv = 0.f;
+    const unsigned it = blockIdx.x * BLOCK + threadIdx.x;
+    if (it >= items) return;
+    const unsigned t = it * VEC, wihi = g.wi * g.hi, plane = t / wihi, q = t - plane * wihi;
+    const int y = q / g.wi, x0 = q - y * g.wi;
+    const float *dm = dmu_o + (size_t)plane * g.ho * g.wo, *dv = dvar_o + (size_t)plane * g.ho * g.wo;
+    float sm[VEC], sv[VEC];
     if (!g.overlap) {  // k == stride: the cell of the pixel; k == image width (global pooling): the only cell
-        const int oy = g.k == g.stride ? y / g.k : 0, ox = g.k == g.stride ? x / g.k : 0;
-        if (oy < g.ho && ox < g.wo) {
-            sm = __ldg(dm + oy * g.wo + ox);
-            sv = __ldg(dv + oy * g.wo + ox);
+        const int oy = g.k == g.stride ? y / g.k : 0;
+#pragma unroll
+        for (int v = 0; v < VEC; v++) {
+            const int ox = g.k == g.stride ? (x0 + v) / g.k : 0;
+            const bool in = oy < g.ho && ox < g.wo;
+            sm[v] = in ? __ldg(dm + oy * g.wo + ox) : 0.f;
+            sv[v] = in ? __ldg(dv + oy * g.wo + ox) : 0.f;
         }
     } else {
         // cells whose window contains the pixel, in ascending order (the order of the reference's index table)
         const int oy_lo = max(0, (y + g.off - g.k + g.stride) / g.stride), oy_hi = min(g.ho - 1, (y + g.off) / g.stride);
-        const int ox_lo = max(0, (x + g.off - g.k + g.stride) / g.stride), ox_hi = min(g.wo - 1, (x + g.off) / g.stride);
-        for (int oy = oy_lo; oy <= oy_hi; oy++)
-            for (int ox = ox_lo; ox <= ox_hi; ox++) {
-                sm += __ldg(dm + oy * g.wo + ox);
-                sv += __ldg(dv + oy * g.wo + ox);
-            }
+#pragma unroll
+        for (int v = 0; v < VEC; v++) {
+            const int x = x0 + v;
+            const int ox_lo = max(0, (x + g.off - g.k + g.stride) / g.stride), ox_hi = min(g.wo - 1, (x + g.off) / g.stride);
+            float a = 0.f, c = 0.f;
+            for (int oy = oy_lo; oy <= oy_hi; oy++)
+                for (int ox = ox_lo; ox <= ox_hi; ox++) {
+                    a += __ldg(dm + oy * g.wo + ox);
+                    c += __ldg(dv + oy * g.wo + ox);
+                }
+            sm[v] = a, sv[v] = c;
+        }
     }
-    const float j = jcb ? __ldg(jcb + t) : 1.f;
     const int k2 = g.k * g.k;
-    dmu[t] = sm * j / k2;
-    dvar[t] = sv * j * j / (k2 * k2);
+    if (VEC == 4) {
+        const float4 j = jcb ? __ldg(reinterpret_cast<const float4 *>(jcb + t)) : make_float4(1.f, 1.f, 1.f, 1.f);
+        *reinterpret_cast<float4 *>(dmu + t) = make_float4(sm[0] * j.x / k2, sm[1] * j.y / k2, sm[2] * j.z / k2, sm[3] * j.w / k2);
+        const int k4 = k2 * k2;
+        *reinterpret_cast<float4 *>(dvar + t) =
+            make_float4(sv[0] * j.x * j.x / k4, sv[1] * j.y * j.y / k4, sv[2] * j.z * j.z / k4, sv[3] * j.w * j.w / k4);
+    } else {
+        const float j = jcb ? __ldg(jcb + t) : 1.f;
+        dmu[t] = sm[0] * j / k2;
+        dvar[t] = sv[0] * j * j / (k2 * k2);
+    }
 }
 
 // src/resnet_block.cpp:8-31
@@ -333,7 +365,10 @@ int bn2d_fwd(int B, int C, int wihi, int training, float eps, float momentum, co
         float *ws = nullptr;
         if ((rc = conv_scratch((size_t)C * slices * sizeof(float4), &ws)) != TAGI_OK) return rc;
         float4 *part = reinterpret_cast<float4 *>(ws);
-        bn2d_stats_partial_kernel<<<dim3(slices, C), BLOCK, 0, st>>>(mu_a, var_a, C, wihi, n, part);
+        if (wihi % 4 == 0 && aligned16(mu_a) && aligned16(var_a))
+            bn2d_stats_partial_kernel<4><<<dim3(slices, C), BLOCK, 0, st>>>(mu_a, var_a, C, wihi, n, part);
+        else
+            bn2d_stats_partial_kernel<1><<<dim3(slices, C), BLOCK, 0, st>>>(mu_a, var_a, C, wihi, n, part);
         if ((rc = launched("bn2d_stats_partial_kernel launch")) != TAGI_OK) return rc;
         bn2d_stats_final_kernel<<<(C + 127) / 128, 128, 0, st>>>(part, slices, n, momentum, mu_batch, var_batch, mu_ra,
                                                                  var_ra, C);
@@ -391,8 +426,12 @@ int avgpool2d_fwd(const tagi_conv2d_geom &g, const float *mu_a, const float *var
 int avgpool2d_bwd(const tagi_conv2d_geom &g, const float *jcb, const float *dmu_o, const float *dvar_o, float *dmu,
                   float *dvar, cudaStream_t st) {
     const long total = (long)g.B * g.fi * g.hi * g.wi;
-    avgpool2d_bwd_kernel<<<(unsigned)((total + BLOCK - 1) / BLOCK), BLOCK, 0, st>>>(jcb, dmu_o, dvar_o, pool_geom(g), total,
-                                                                                     dmu, dvar);
+    if (g.wi % 4 == 0 && aligned16(dmu) && aligned16(dvar) && (!jcb || aligned16(jcb)))
+        avgpool2d_bwd_kernel<4><<<(unsigned)((total / 4 + BLOCK - 1) / BLOCK), BLOCK, 0, st>>>(
+            jcb, dmu_o, dvar_o, pool_geom(g), (unsigned)(total / 4), dmu, dvar);
+    else
+        avgpool2d_bwd_kernel<1><<<(unsigned)((total + BLOCK - 1) / BLOCK), BLOCK, 0, st>>>(jcb, dmu_o, dvar_o, pool_geom(g),
+                                                                                            (unsigned)total, dmu, dvar);
     return launched("avgpool2d_bwd_kernel launch");
 }
 

@@ -75,7 +75,18 @@ struct TcEpilogue {
     // out + z * slice_elems (0 slabs_per_slice: the whole contraction in one slice)
     int slabs_per_slice;
     long slice_elems;
+    // Forward with the ReLU folded in (kernels instantiated with RELU only): out1 / out2 receive the moments after the
+    // ReLU and out3 its Jacobian (src/activation.cpp:7-29); the pre-activation moments are not written.
+    float *out3;
 };
+
+// ReLU moments of one output: mu_a = max(mu_z, 0); where that is 0 the variance and the Jacobian are 0 too
+__device__ __forceinline__ float relu_moments(float &m, float &v) {
+    m = fmaxf(m, 0.f);
+    const bool off = m == 0.f;
+    v = off ? 0.f : v;
+    return off ? 0.f : 1.f;
+}
 
 
 __device__ __forceinline__ float lo_part(float x) { return x - __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
@@ -94,7 +105,7 @@ __device__ __forceinline__ void sts128(uint32_t addr, float4 v) {
 
 // One thread's 64 columns (starting at column c0, `valid` of them inside the tile) of output row `row`:
 // forward adds the bias of the column, the backward passes scale by the matrix entry (s and s*s).
-template <int OP>
+template <int OP, bool RELU = false>
 __device__ __forceinline__ void store_tile(const TcEpilogue &epi, int row, int c0, int valid, const float (&sum1)[64],
                                            const float (&sum2)[64]) {
     if (row >= epi.rows) return;
@@ -130,6 +141,7 @@ __device__ __forceinline__ void store_tile(const TcEpilogue &epi, int row, int c
                     o1 *= sc[u];
                     o2 = o2 * sc[u] * sc[u];
                 }
+                if (RELU) __stcs(epi.out3 + idx, relu_moments(o1, o2));
                 __stcs(epi.out1 + idx, o1);
                 __stcs(epi.out2 + idx, o2);
             }
@@ -156,6 +168,12 @@ __device__ __forceinline__ void store_tile(const TcEpilogue &epi, int row, int c
             o2.x = o2.x * sc.x * sc.x, o2.y = o2.y * sc.y * sc.y;
             o2.z = o2.z * sc.z * sc.z, o2.w = o2.w * sc.w * sc.w;
         }
+        if (RELU) {
+            float4 j;
+            j.x = relu_moments(o1.x, o2.x), j.y = relu_moments(o1.y, o2.y);
+            j.z = relu_moments(o1.z, o2.z), j.w = relu_moments(o1.w, o2.w);
+            __stcs(reinterpret_cast<float4 *>(epi.out3 + idx), j);
+        }
         __stcs(reinterpret_cast<float4 *>(epi.out1 + idx), o1);
         __stcs(reinterpret_cast<float4 *>(epi.out2 + idx), o2);
     }
@@ -165,7 +183,7 @@ __device__ __forceinline__ void store_tile(const TcEpilogue &epi, int row, int c
 // lanes of an instruction on 32 different rows (32 half-used sectors per request). The warp writes its 32 x 64 block
 // of both sums to `stage` (row pitch 68 floats: conflict-free 16-byte accesses both ways), then every instruction
 // handles two rows with 16 lanes x 16 bytes each: scale loads and stores are contiguous 256-byte runs.
-template <int OP>
+template <int OP, bool RELU = false>
 __device__ __forceinline__ void store_tile_staged(const TcEpilogue &epi, uint32_t stage, int row_base, int lane, int c0,
                                                   int valid, const float (&sum1)[64], const float (&sum2)[64]) {
     const uint32_t mine = stage + lane * STAGE_PITCH;
@@ -208,6 +226,12 @@ __device__ __forceinline__ void store_tile_staged(const TcEpilogue &epi, uint32_
                 o1.x *= sc.x, o1.y *= sc.y, o1.z *= sc.z, o1.w *= sc.w;
                 o2.x = o2.x * sc.x * sc.x, o2.y = o2.y * sc.y * sc.y;
                 o2.z = o2.z * sc.z * sc.z, o2.w = o2.w * sc.w * sc.w;
+            }
+            if (RELU) {
+                float4 j;
+                j.x = relu_moments(o1.x, o2.x), j.y = relu_moments(o1.y, o2.y);
+                j.z = relu_moments(o1.z, o2.z), j.w = relu_moments(o1.w, o2.w);
+                __stcs(reinterpret_cast<float4 *>(epi.out3 + idx), j);
             }
             __stcs(reinterpret_cast<float4 *>(epi.out1 + idx), o1);
             __stcs(reinterpret_cast<float4 *>(epi.out2 + idx), o2);
@@ -765,13 +789,15 @@ __device__ __forceinline__ void load_half_tile(uint32_t dst, const CUtensorMap *
     }
 }
 
-// GATHER: the A tiles of the forward / state pass are gathered inside the kernel (Conv2d, launched with 384 threads);
-// without it the kernel is launched with 352 threads and contains none of that code.
-template <int OP, int CH, int RS, int DS, bool GATHER>
+// FL bit 0 (GATHER): the A tiles of the forward / state pass are gathered inside the kernel (Conv2d, launched with 384
+// threads); without it the kernel is launched with 352 threads and contains none of that code.
+// FL bit 1 (RELU, forward only): the epilogue applies the ReLU and writes its Jacobian (TcEpilogue::out3).
+template <int OP, int CH, int RS, int DS, int FL>
 __global__ void __launch_bounds__(NTHREADS2, 1)
 tagi_tc_linear_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
                            const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
                            const TcEpilogue epi, const ConvGather cg, const int kdim, const int bn, int *status) {
+    constexpr bool GATHER = (FL & 1) != 0, RELU = (FL & 2) != 0 && OP == OP_FWD;
     using T = OpTraits<OP>;
     using S = PairTraits<OP>;
     constexpr int NRAW_B = S::NRAW_B, NDER = S::NDER, NA = S::NA;
@@ -1086,10 +1112,10 @@ tagi_tc_linear_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __gri
             e.out2 += (long)blockIdx.z * epi.slice_elems;
             // all MMAs and TMA writes of this tile are complete (last acc_full phase): the operand rings are free
             if (e.npix > 0)
-                store_tile<OP>(e, row, col0 + h * 64, bn - h * 64, sum1, sum2);
+                store_tile<OP, RELU>(e, row, col0 + h * 64, bn - h * 64, sum1, sum2);
             else
-                store_tile_staged<OP>(e, smem_base + (warp - 2) * STAGE_WARP, row - lane, lane, col0 + h * 64,
-                                      bn - h * 64, sum1, sum2);
+                store_tile_staged<OP, RELU>(e, smem_base + (warp - 2) * STAGE_WARP, row - lane, lane, col0 + h * 64,
+                                            bn - h * 64, sum1, sum2);
         }
     }
     __syncwarp();
@@ -1255,15 +1281,19 @@ int launch_pair(const CUtensorMap &a0, const CUtensorMap &a1, const CUtensorMap 
         auto k = tagi_tc_linear_pair_kernel<OP, CHV, RSV, DSV, GV>;                              \
         constexpr size_t sm = pair_smem_bytes<OP, RSV, DSV>();                                   \
         cfg.dynamicSmemBytes = sm;                                                               \
-        cfg.blockDim = dim3(GV ? NTHREADS2 : NTHREADS2 - 32);                                    \
+        cfg.blockDim = dim3(((GV) & 1) ? NTHREADS2 : NTHREADS2 - 32);                            \
         e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);       \
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");                       \
         e = cudaLaunchKernelEx(&cfg, k, a0, a1, b0, b1, epi, cg, kdim, bn, status);              \
     } while (0)
-#define TAGI_PAIR_LAUNCH(CHV, RSV, DSV)                                      \
-    do {                                                                       \
-        if (OP != OP_BWD_PARAM && cg.on) TAGI_PAIR_LAUNCH_G(CHV, RSV, DSV, OP != OP_BWD_PARAM); \
-        else TAGI_PAIR_LAUNCH_G(CHV, RSV, DSV, false);                         \
+#define TAGI_PAIR_LAUNCH(CHV, RSV, DSV)                                                                  \
+    do {                                                                                                   \
+        constexpr int G = OP != OP_BWD_PARAM ? 1 : 0, R = OP == OP_FWD ? 2 : 0;                            \
+        const bool gather = OP != OP_BWD_PARAM && cg.on, relu = OP == OP_FWD && epi.out3 != nullptr;       \
+        if (gather && relu) TAGI_PAIR_LAUNCH_G(CHV, RSV, DSV, G | R);                                      \
+        else if (gather) TAGI_PAIR_LAUNCH_G(CHV, RSV, DSV, G);                                             \
+        else if (relu) TAGI_PAIR_LAUNCH_G(CHV, RSV, DSV, R);                                               \
+        else TAGI_PAIR_LAUNCH_G(CHV, RSV, DSV, 0);                                                         \
     } while (0)
     // ring depths: hand-offs cross two SMs here, so the derived ring is as deep as tensor memory allows (backward:
     // four slots; forward: three when the accumulators fit 2 x 112 columns, else two)
@@ -1332,13 +1362,15 @@ int linear_tc_status(int *out, int reset) {
 
 int linear_fwd_tc(const float *mu_w, const float *var_w, const float *mu_b, const float *var_b, const float *mu_a,
                   const float *var_a, int B, int K, int N, float *mu_z, float *var_z, cudaStream_t st, int npix,
-                  const ConvGather *cg) {
+                  const ConvGather *cg, float *relu_jcb) {
     CUtensorMap a0, a1, b0, b1;
     int rc;
     const bool pair = use_pair(B);
     if ((rc = make_tmap(&b0, mu_w, K, N, false, pair ? 64 : 128))) return rc;
     if ((rc = make_tmap(&b1, var_w, K, N, false, pair ? 64 : 128))) return rc;
-    TcEpilogue epi{mu_z, var_z, mu_b, var_b, (long)N, B, N, npix, 0, 0};
+    // relu_jcb: the ReLU is applied in the epilogue (CTA-pair kernel only): mu_z / var_z receive the moments after it
+    if (relu_jcb && !pair) return fail(TAGI_ERR_UNSUPPORTED, "the fused ReLU needs the CTA-pair kernel");
+    TcEpilogue epi{mu_z, var_z, mu_b, var_b, (long)N, B, N, npix, 0, 0, relu_jcb};
     if (cg) {  // A = the receptive fields of (mu_a, var_a), gathered inside the kernel
         if (!pair) return fail(TAGI_ERR_UNSUPPORTED, "implicit Conv2d operands need the CTA-pair kernel");
         return launch_pair<OP_FWD>(b0, b0, b0, b1, epi, K, st, *cg);

@@ -60,13 +60,21 @@ class Linear:
         self.delta_var_b = torch.zeros_like(self.var_b) if self.bias else None
         self.neg_var = torch.zeros(1, dtype=torch.int32, device=dev)
 
-    def forward(self, mu_a, var_a, jcb, train=True):
+    def forward(self, mu_a, var_a, jcb, train=True, relu=False):
+        """relu=True: the ReLU layer that follows is folded into the call (tagi_linear_fwd_relu) and the moments after it
+        and its Jacobian are returned."""
         B = mu_a.shape[0]
         if mu_a.shape[1] != self.input_size:
             raise RuntimeError(f"Input size mismatch: {self.input_size} vs {mu_a.shape[1]}")
         self.saved = (mu_a, jcb)   # what the reference copies into bwd_states (src/base_layer.cpp:212-228)
         mu_z = torch.empty(B, self.output_size, device=mu_a.device)
         var_z = torch.empty_like(mu_z)
+        if relu:
+            j = torch.empty_like(mu_z)
+            lib.tagi_linear_fwd_relu(_p(self.mu_w), _p(self.var_w), _p(self.mu_b), _p(self.var_b), _p(mu_a), _p(var_a), B,
+                                     self.input_size, self.output_size, int(self.bias), _p(mu_z), _p(var_z), _p(j),
+                                     _stream())
+            return mu_z, var_z, j
         lib.tagi_linear_fwd(_p(self.mu_w), _p(self.var_w), _p(self.mu_b), _p(self.var_b), _p(mu_a), _p(var_a), B,
                             self.input_size, self.output_size, int(self.bias), _p(mu_z), _p(var_z), _stream())
         return mu_z, var_z, None   # Jacobian of a Linear output is one
@@ -168,7 +176,7 @@ class Conv2d(Linear):
     def _g(self, B):
         return _geom(B, self.fi, self.hi, self.wi, self.fo, self.k, self.stride, self.pad, self.pad_type, self.bias)
 
-    def forward(self, mu_a, var_a, jcb, train=True):
+    def forward(self, mu_a, var_a, jcb, train=True, relu=False):
         B = mu_a.shape[0]
         if mu_a.shape[1] != self.input_size:
             raise RuntimeError(f"Input size mismatch: {self.input_size} vs {mu_a.shape[1]}")
@@ -176,6 +184,11 @@ class Conv2d(Linear):
         mu_z = torch.empty(B, self.fo * self.ho * self.wo, device=mu_a.device)
         var_z = torch.empty_like(mu_z)
         g = self._g(B)
+        if relu:
+            j = torch.empty_like(mu_z)
+            lib.tagi_conv2d_fwd_relu(ctypes.byref(g), _p(self.mu_w), _p(self.var_w), _p(self.mu_b), _p(self.var_b),
+                                     _p(mu_a), _p(var_a), _p(mu_z), _p(var_z), _p(j), _stream())
+            return mu_z, var_z, j
         lib.tagi_conv2d_fwd(ctypes.byref(g), _p(self.mu_w), _p(self.var_w), _p(self.mu_b), _p(self.var_b), _p(mu_a),
                             _p(var_a), _p(mu_z), _p(var_z), _stream())
         return mu_z, var_z, None
@@ -290,6 +303,24 @@ class AvgPool2d(_NoParams):
         return dmu_a, dvar_a
 
 
+fuse_relu = True   # run a Linear / Conv2d layer and the ReLU layer directly behind it as one call
+
+
+def _forward_layers(layers, mu, var, jcb, train):
+    """The layers in order. A Linear / Conv2d layer directly followed by a ReLU layer runs as one fused call
+    (tagi_linear_fwd_relu / tagi_conv2d_fwd_relu): same results, the moments before the ReLU are never stored."""
+    i = 0
+    while i < len(layers):
+        layer = layers[i]
+        if fuse_relu and type(layer) in (Linear, Conv2d) and i + 1 < len(layers) and type(layers[i + 1]) is ReLU:
+            mu, var, jcb = layer.forward(mu, var, jcb, train, relu=True)
+            i += 2
+        else:
+            mu, var, jcb = layer.forward(mu, var, jcb, train)
+            i += 1
+    return mu, var, jcb
+
+
 class LayerBlock:
     """cutagi.LayerBlock(*layers) (src/layer_block.cpp:151-220): the layers in order; in the backward pass the block's
     first layer runs only when the block is asked for state deltas."""
@@ -303,9 +334,7 @@ class LayerBlock:
         return shape
 
     def forward(self, mu, var, jcb, train=True):
-        for layer in self.layers:
-            mu, var, jcb = layer.forward(mu, var, jcb, train)
-        return mu, var, jcb
+        return _forward_layers(self.layers, mu, var, jcb, train)
 
     def backward(self, dmu, dvar, state_update=True):
         for layer in reversed(self.layers[1:]):
@@ -434,8 +463,7 @@ class Sequential:
                                                                          device="cuda").reshape(mu.shape).contiguous()
         jcb = None
         self.batch = mu.shape[0]
-        for layer in self.layers:
-            mu, var, jcb = layer.forward(mu, var, jcb, self.training)
+        mu, var, jcb = _forward_layers(self.layers, mu, var, jcb, self.training)
         self.output = (mu, var, jcb)
         self.delta = (torch.zeros_like(mu), torch.zeros_like(mu))   # input_delta_z_buffer
         return mu, var

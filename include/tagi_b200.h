@@ -150,6 +150,20 @@ int tagi_conv2d_bwd_param(const tagi_conv2d_geom *g, const float *var_w, const f
  * CPU definition relu_mean_var (src/activation.cpp:7-29); replaces relu_mean_var_cuda (src/activation_cuda.cu:8-24). */
 int tagi_relu_fwd(const float *mu_z, const float *var_z, size_t n, float *mu_a, float *var_a, float *jcb, void *stream);
 
+/* tagi_linear_fwd / tagi_conv2d_fwd followed by tagi_relu_fwd on their outputs, as one call: mu_a_out, var_a_out and
+ * jcb_out are what the ReLU layer behind the Linear / Conv2d layer would hold; the moments before the ReLU are not
+ * written. Where the forward pass runs on CTA pairs (256 or more output rows) the ReLU is applied in the kernel's
+ * epilogue, which saves the ReLU pass's reads and the write of the pre-activation moments; otherwise the two steps run
+ * one after the other. Results are those of the two separate calls, bit for bit. Replaces LinearCuda::forward /
+ * Conv2dCuda::forward followed by ReLUCuda::forward -> relu_mean_var_cuda (src/activation_cuda.cu:8-24, 510-544) when a
+ * ReLU layer follows the layer directly; nothing else reads the layer's own output. */
+int tagi_linear_fwd_relu(const float *mu_w, const float *var_w, const float *mu_b, const float *var_b, const float *mu_a,
+                         const float *var_a, int B, int K, int N, int has_bias, float *mu_a_out, float *var_a_out,
+                         float *jcb_out, void *stream);
+int tagi_conv2d_fwd_relu(const tagi_conv2d_geom *g, const float *mu_w, const float *var_w, const float *mu_b,
+                         const float *var_b, const float *mu_a, const float *var_a, float *mu_a_out, float *var_a_out,
+                         float *jcb_out, void *stream);
+
 /* MixtureReLU moments (rectified Gaussian): alpha = mu_z / sqrt(var_z); mu_a = max(1e-6, mu_z * Phi(alpha) +
  * sqrt(var_z) * phi(alpha)); var_a = max(1e-6, -mu_a'^2 + 2 * mu_a' * mu_z - mu_z * sqrt(var_z) * phi(alpha) +
  * (var_z - mu_z^2) * Phi(alpha)) with mu_a' the unfloored mean; jcb = Phi(alpha).

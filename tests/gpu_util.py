@@ -75,6 +75,23 @@ def linear_fwd(mw, vw, mb, vb, ma, va, misalign=0):
     return mz.get((B, N)), vz.get((B, N))
 
 
+def linear_fwd_relu(mw, vw, mb, vb, ma, va, misalign=0):
+    B, K = ma.shape
+    N = mw.shape[0]
+    d = [dev(x, misalign) for x in (mw, vw, mb, vb, ma, va)]
+    o = [Out(B * N, misalign) for _ in range(3)]
+    lib.tagi_linear_fwd_relu(p(d[0]), p(d[1]), p(d[2]), p(d[3]), p(d[4]), p(d[5]), B, K, N, int(mb is not None),
+                             o[0].ptr(), o[1].ptr(), o[2].ptr(), None)
+    return tuple(x.get((B, N)) for x in o)
+
+
+def relu_of(mz, vz):
+    """The ReLU moments (src/activation.cpp:7-29) of forward outputs, on the host."""
+    ma = np.maximum(mz, np.float32(0))
+    off = ma == 0
+    return ma, np.where(off, np.float32(0), vz), np.where(off, np.float32(0), np.float32(1))
+
+
 def linear_bwd_state(mw, jcb, dm, dv, misalign=0):
     B, K = jcb.shape
     N = mw.shape[0]
@@ -107,6 +124,15 @@ def conv_fwd(g, mw, vw, mb, vb, ma, va):
     cg = cgeom(g)
     lib.tagi_conv2d_fwd(C.byref(cg), p(d[0]), p(d[1]), p(d[2]), p(d[3]), p(d[4]), p(d[5]), mz.ptr(), vz.ptr(), None)
     return mz.get((g.B, g.n_out)), vz.get((g.B, g.n_out))
+
+
+def conv_fwd_relu(g, mw, vw, mb, vb, ma, va):
+    d = [dev(x) for x in (mw, vw, mb, vb, ma, va)]
+    o = [Out(g.B * g.n_out) for _ in range(3)]
+    cg = cgeom(g)
+    lib.tagi_conv2d_fwd_relu(C.byref(cg), p(d[0]), p(d[1]), p(d[2]), p(d[3]), p(d[4]), p(d[5]), o[0].ptr(), o[1].ptr(),
+                             o[2].ptr(), None)
+    return tuple(x.get((g.B, g.n_out)) for x in o)
 
 
 def conv_bwd_state(g, mw, jcb, dm, dv):

@@ -169,3 +169,26 @@ def test_conv_tensor_core_rejects_odd_channels(G):
         lib.tagi_set_impl(capi.IMPL_AUTO)
     lib.tagi_conv2d_fwd(C.byref(g), q, q, q, q, q, q, q, q, None)   # AUTO: FFMA kernels
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("kw", TC_GEOMS[:6] + TC_GEOMS[12:], ids=lambda k: "fi{fi}_fo{fo}_h{hi}_k{k}_s{stride}".format(**k))
+@pytest.mark.parametrize("impl", ["auto", "ffma"])
+def test_conv_forward_with_fused_relu(G, kw, impl):
+    """tagi_conv2d_fwd_relu = tagi_conv2d_fwd followed by the ReLU moments, bit for bit: in the epilogue of the CTA-pair
+    kernel (256 or more output rows, implicit and explicit gathers) and as two steps elsewhere."""
+    from cutagi_b200 import capi
+    from cutagi_b200.capi import lib
+    g = ConvGeom(**kw)
+    x = G.conv_inputs(np.random.default_rng(g.fi * 7 + g.fo), g)
+    lib.tagi_set_impl(capi.IMPL_FFMA if impl == "ffma" else capi.IMPL_AUTO)
+    try:
+        capi.tc_status()
+        args = (g, x["mu_w"], x["var_w"], x["mu_b"], x["var_b"], x["mu_a"], x["var_a"])
+        mz, vz = G.conv_fwd(*args)
+        got = G.conv_fwd_relu(*args)
+        assert capi.tc_status() == 0
+    finally:
+        lib.tagi_set_impl(capi.IMPL_AUTO)
+    assert (mz < 0).any() and (mz > 0).any()
+    for name, a, b in zip(("mu_a", "var_a", "jcb"), got, G.relu_of(mz, vz)):
+        np.testing.assert_array_equal(a, b, err_msg=name)

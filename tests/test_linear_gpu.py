@@ -301,3 +301,29 @@ def test_benchmark_shape_is_tensor_core_and_in_tolerance_vs_f64(G, oracle, force
     G.check("mu_z vs f64", mz[rows], m64, G.RTOL_MU)
     G.check("var_z vs f64", vz[rows], v64, G.RTOL_VAR)
     assert capi.tc_status() == 0
+
+
+@pytest.mark.parametrize("B,K,N", [(256, 1024, 1024), (1024, 512, 1536), (300, 260, 132), (130, 256, 132), (32, 784, 128),
+                                   (3, 5, 11)])
+@pytest.mark.parametrize("bias", [True, False])
+def test_forward_with_fused_relu(G, B, K, N, bias):
+    """tagi_linear_fwd_relu = tagi_linear_fwd followed by the ReLU moments, bit for bit: in the epilogue of the CTA-pair
+    kernel (256 or more rows) and as two steps on the other kernels."""
+    from cutagi_b200 import capi
+    x = G.linear_inputs(np.random.default_rng(B + K + N), B, K, N, bias)
+    capi.tc_status()
+    args = (x["mu_w"], x["var_w"], x["mu_b"], x["var_b"], x["mu_a"], x["var_a"])
+    mz, vz = G.linear_fwd(*args)
+    got = G.linear_fwd_relu(*args)
+    assert capi.tc_status() == 0
+    assert (mz < 0).any() and (mz > 0).any()
+    for name, a, b in zip(("mu_a", "var_a", "jcb"), got, G.relu_of(mz, vz)):
+        np.testing.assert_array_equal(a, b, err_msg=name)
+
+
+def test_fused_relu_rejects_null_jacobian(G):
+    import torch
+    from cutagi_b200.capi import TagiError, lib
+    q = torch.zeros(1 << 12, device="cuda").data_ptr()
+    with pytest.raises(TagiError):
+        lib.tagi_linear_fwd_relu(q, q, q, q, q, q, 4, 8, 8, 1, q, q, None, None)
