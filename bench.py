@@ -369,7 +369,7 @@ def run_b200(args, rank, world, local_rank):
         "roofline": roofline, "cpu_baseline": cpu_baseline,
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h},
-        "gpu_launches": (4 if world == 1 else 2 + 2 * pieces) * args.steps, "tc_status": tc_status, "clocks": clocks}))
+        "gpu_launches": (3 if world == 1 else 2 + pieces) * args.steps, "tc_status": tc_status, "clocks": clocks}))
     if world > 1:
         xchg.close()
         dist.destroy_process_group()

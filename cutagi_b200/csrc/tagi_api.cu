@@ -165,9 +165,12 @@ int tagi_linear_bwd_param(const float *var_w, const float *var_b, const float *m
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     int rc;
-    if (pick_tc(__func__, B, K, N, {var_w, mu_a, dmu_z, dvar_z, dmu_w, dvar_w}, &rc))
+    if (pick_tc(__func__, B, K, N, {var_w, mu_a, dmu_z, dvar_z, dmu_w, dvar_w}, &rc)) {
+        if (has_bias && linear_bwd_param_tc_fuses_bias(N))  // weight and bias deltas from one kernel
+            return linear_bwd_param_tc(var_w, mu_a, dmu_z, dvar_z, B, K, N, dmu_w, dvar_w, st, nullptr, 1, 0, var_b, dmu_b,
+                                       dvar_b);
         rc = linear_bwd_param_tc(var_w, mu_a, dmu_z, dvar_z, B, K, N, dmu_w, dvar_w, st);
-    else if (rc == TAGI_OK)
+    } else if (rc == TAGI_OK)
         rc = linear_bwd_param_ffma(var_w, mu_a, dmu_z, dvar_z, B, K, N, dmu_w, dvar_w, st);
     if (rc != TAGI_OK) return rc;
     if (has_bias) rc = linear_bias_delta(var_b, dmu_z, dvar_z, B, N, dmu_b, dvar_b, st);
@@ -195,9 +198,12 @@ int tagi_linear_bwd_param_rows(const float *var_w, const float *var_b, const flo
     const long w0 = (long)n0 * K;
     var_w += w0, dmu_w += w0, dvar_w += w0, dmu_z += n0, dvar_z += n0;
     int rc = TAGI_OK;
-    if (N % 4 == 0 && pick_tc(__func__, B, K, Nr, {var_w, mu_a, dmu_z, dvar_z, dmu_w, dvar_w}, &rc))
+    if (N % 4 == 0 && pick_tc(__func__, B, K, Nr, {var_w, mu_a, dmu_z, dvar_z, dmu_w, dvar_w}, &rc)) {
+        if (has_bias && linear_bwd_param_tc_fuses_bias(Nr))
+            return linear_bwd_param_tc(var_w, mu_a, dmu_z, dvar_z, B, K, Nr, dmu_w, dvar_w, st, nullptr, 1, N, var_b + n0,
+                                       dmu_b + n0, dvar_b + n0);
         rc = linear_bwd_param_tc(var_w, mu_a, dmu_z, dvar_z, B, K, Nr, dmu_w, dvar_w, st, nullptr, 1, N);
-    else if (rc == TAGI_OK || N % 4 != 0)
+    } else if (rc == TAGI_OK || N % 4 != 0)
         rc = linear_bwd_param_ffma(var_w, mu_a, dmu_z, dvar_z, B, K, Nr, dmu_w, dvar_w, st, N);
     if (rc != TAGI_OK) return rc;
     if (has_bias) rc = linear_bias_delta(var_b + n0, dmu_z, dvar_z, B, Nr, dmu_b + n0, dvar_b + n0, st, N);

@@ -75,7 +75,10 @@ int linear_bwd_state_tc(const float *mu_w, const float *jcb, const float *dmu_z,
 // npix > 0: the rows are (image, pixel) pairs and outputs / the Jacobian are laid out [image][channel][pixel] (Conv2d)
 int linear_bwd_param_tc(const float *var_w, const float *mu_a, const float *dmu_z, const float *dvar_z, int B, int K,
                         int N, float *dmu_w, float *dvar_w, cudaStream_t st, float *split_ws = nullptr, int slices = 1,
-                        long ldz = 0);
+                        long ldz = 0, const float *var_b = nullptr, float *dmu_b = nullptr, float *dvar_b = nullptr);
+// true: the parameter pass of N output features (without a split contraction) can produce the bias deltas itself when it
+// is given var_b / dmu_b / dvar_b, so that linear_bias_delta's pass over the deltas is not needed
+bool linear_bwd_param_tc_fuses_bias(int N);
 int linear_bwd_param_tc_slices(int B, int K, int N);
 
 // Conv2d on the FFMA engine (tagi_conv_ffma.cu)

@@ -78,6 +78,9 @@ struct TcEpilogue {
     // Forward with the ReLU folded in (kernels instantiated with RELU only): out1 / out2 receive the moments after the
     // ReLU and out3 its Jacobian (src/activation.cpp:7-29); the pre-activation moments are not written.
     float *out3;
+    // Parameter pass with the bias deltas folded in (kernels instantiated with BIAS only): bias1 / bias2 receive the
+    // row sums of the two A operands (the deltas) times aux2[row] and its square
+    float *bias1, *bias2;
 };
 
 // ReLU moments of one output: mu_a = max(mu_z, 0); where that is 0 the variance and the Jacobian are 0 too
@@ -792,12 +795,15 @@ __device__ __forceinline__ void load_half_tile(uint32_t dst, const CUtensorMap *
 // FL bit 0 (GATHER): the A tiles of the forward / state pass are gathered inside the kernel (Conv2d, launched with 384
 // threads); without it the kernel is launched with 352 threads and contains none of that code.
 // FL bit 1 (RELU, forward only): the epilogue applies the ReLU and writes its Jacobian (TcEpilogue::out3).
+// FL bit 2 (BIAS, parameter pass without a split contraction): the converter threads, which read every delta of their
+// output feature anyway, also add them up; the pairs of the first column tile write the bias deltas.
 template <int OP, int CH, int RS, int DS, int FL>
 __global__ void __launch_bounds__(NTHREADS2, 1)
 tagi_tc_linear_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
                            const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
                            const TcEpilogue epi, const ConvGather cg, const int kdim, const int bn, int *status) {
     constexpr bool GATHER = (FL & 1) != 0, RELU = (FL & 2) != 0 && OP == OP_FWD;
+    constexpr bool BIAS = (FL & 4) != 0 && OP == OP_BWD_PARAM;
     using T = OpTraits<OP>;
     using S = PairTraits<OP>;
     constexpr int NRAW_B = S::NRAW_B, NDER = S::NDER, NA = S::NA;
@@ -988,6 +994,7 @@ tagi_tc_linear_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __gri
         float sum1[64], sum2[64];
 #pragma unroll
         for (int i = 0; i < 64; i++) sum1[i] = sum2[i] = 0.f;
+        float bsum0 = 0.f, bsum1 = 0.f;  // BIAS: sums of this thread's row of the two A operands over its k-slabs
 
         auto drain = [&](int c) -> bool {
             if (!mbar_wait(acc_full, c & 1, abort_flag, status, ST_TIMEOUT_ACC)) return false;
@@ -1051,6 +1058,10 @@ tagi_tc_linear_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __gri
                     a0[0] = x0.x, a0[1] = x0.y, a0[2] = x0.z, a0[3] = x0.w, a0[4] = x1.x, a0[5] = x1.y, a0[6] = x1.z, a0[7] = x1.w;
                     a1[0] = y0.x, a1[1] = y0.y, a1[2] = y0.z, a1[3] = y0.w, a1[4] = y1.x, a1[5] = y1.y, a1[6] = y1.z, a1[7] = y1.w;
                 }
+                if (BIAS) {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) bsum0 += a0[i], bsum1 += a1[i];
+                }
                 const uint32_t at = lane_addr + A_COL0 + d * (NA * BK) + kh * 8;
                 float t0[8], t1[8];
 #pragma unroll
@@ -1105,6 +1116,23 @@ tagi_tc_linear_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __gri
         if (ok) note_chunk_ends(nk - 1);
         if (ok && pending >= 0) ok = drain(pending);
 
+        if (BIAS) {
+            // the two converter groups took alternate k-slabs: group 1 hands its sums over through shared memory behind
+            // the epilogue's staging area (inside the operand rings, which are idle by now)
+            static_assert(!BIAS || (size_t)RS * RAW_SLOT + (size_t)DS * DER_SLOT >= STAGE_BYTES + 128 * 8,
+                          "no room for the bias hand-over behind the staging area");
+            const uint32_t slot = smem_base + (uint32_t)STAGE_BYTES + arow * 8;
+            if (h == 1 && ok) asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(slot), "f"(bsum0), "f"(bsum1) : "memory");
+            asm volatile("bar.sync 1, %0;" ::"n"(NCONV_WARPS * 32) : "memory");
+            const int row = row0 + arow;
+            if (h == 0 && ok && col0 == 0 && row < epi.rows) {
+                float p0, p1;
+                asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(p0), "=f"(p1) : "r"(slot));
+                const float vb = __ldg(epi.aux2 + row);
+                epi.bias1[row] = (bsum0 + p0) * vb;
+                epi.bias2[row] = (bsum1 + p1) * vb * vb;
+            }
+        }
         if (ok) {
             const int row = row0 + q * 32 + lane;
             TcEpilogue e = epi;
@@ -1290,14 +1318,15 @@ int launch_pair(const CUtensorMap &a0, const CUtensorMap &a1, const CUtensorMap 
     do {                                                                                                   \
         constexpr int G = OP != OP_BWD_PARAM ? 1 : 0, R = OP == OP_FWD ? 2 : 0;                            \
         const bool gather = OP != OP_BWD_PARAM && cg.on, relu = OP == OP_FWD && epi.out3 != nullptr;       \
-        if (gather && relu) TAGI_PAIR_LAUNCH_G(CHV, RSV, DSV, G | R);                                      \
+        if (OP == OP_BWD_PARAM && epi.bias1 != nullptr) TAGI_PAIR_LAUNCH_G(CHV, RSV, DSV, 4 - G * 4);      \
+        else if (gather && relu) TAGI_PAIR_LAUNCH_G(CHV, RSV, DSV, G | R);                                 \
         else if (gather) TAGI_PAIR_LAUNCH_G(CHV, RSV, DSV, G);                                             \
         else if (relu) TAGI_PAIR_LAUNCH_G(CHV, RSV, DSV, R);                                               \
         else TAGI_PAIR_LAUNCH_G(CHV, RSV, DSV, 0);                                                         \
     } while (0)
     // ring depths: hand-offs cross two SMs here, so the derived ring is as deep as tensor memory allows (backward:
     // four slots; forward: three when the accumulators fit 2 x 112 columns, else two)
-    if (OP == OP_FWD) {
+    if constexpr (OP == OP_FWD) {
         if (bn <= 112) {
             if (g_chunked) TAGI_PAIR_LAUNCH(CHUNK_STAGES, 5, 3); else TAGI_PAIR_LAUNCH(0, 5, 3);
         } else {
@@ -1381,6 +1410,7 @@ int linear_fwd_tc(const float *mu_w, const float *var_w, const float *mu_b, cons
     return launch<OP_FWD>(a0, a1, b0, b1, epi, K, st);
 }
 bool linear_tc_pair_for(int rows) { return use_pair(rows); }
+bool linear_bwd_param_tc_fuses_bias(int N) { return use_pair(N); }
 
 int linear_bwd_state_tc(const float *mu_w, const float *jcb, const float *dmu_z, const float *dvar_z, int B, int K,
                         int N, float *dmu_a, float *dvar_a, cudaStream_t st, int npix, const ConvGather *cg) {
@@ -1430,7 +1460,8 @@ int linear_bwd_param_tc_slices(int B, int K, int N) {
 // split_ws: optional scratch of at least 2 * slices * N * K floats (slices from linear_bwd_param_tc_slices); without it
 // the contraction is not split.
 int linear_bwd_param_tc(const float *var_w, const float *mu_a, const float *dmu_z, const float *dvar_z, int B, int K,
-                        int N, float *dmu_w, float *dvar_w, cudaStream_t st, float *split_ws, int slices, long ldz) {
+                        int N, float *dmu_w, float *dvar_w, cudaStream_t st, float *split_ws, int slices, long ldz,
+                        const float *var_b, float *dmu_b, float *dvar_b) {
     // rows = output features, columns = input features, contraction over the batch; both operands MN-major.
     // ldz: row pitch of the delta matrices (0 = N; larger when only a range of the output features is computed)
     CUtensorMap a0, a1, b0;
@@ -1440,7 +1471,12 @@ int linear_bwd_param_tc(const float *var_w, const float *mu_a, const float *dmu_
     if ((rc = make_tmap(&b0, mu_a, K, B, true))) return rc;
     if (!split_ws || slices < 2) {
         TcEpilogue epi{dmu_w, dvar_w, var_w, nullptr, (long)K, N, K, 0, 0, 0};
-        if (use_pair(N)) return launch_pair<OP_BWD_PARAM>(a0, a1, b0, b0, epi, B, st);
+        if (use_pair(N)) {
+            // var_b: the bias deltas come out of the same kernel (see linear_bwd_param_tc_fuses_bias)
+            if (var_b) epi.aux2 = var_b, epi.bias1 = dmu_b, epi.bias2 = dvar_b;
+            return launch_pair<OP_BWD_PARAM>(a0, a1, b0, b0, epi, B, st);
+        }
+        if (var_b) return fail(TAGI_ERR_UNSUPPORTED, "bias deltas are folded into the CTA-pair kernel only");
         return launch<OP_BWD_PARAM>(a0, a1, b0, b0, epi, B, st);
     }
     const long slice = (long)N * K;
