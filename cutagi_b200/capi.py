@@ -7,6 +7,7 @@ LIB_PATH = os.path.join(HERE, "libtagi_b200.so")
 
 TAGI_OK = 0
 IMPL_AUTO, IMPL_FFMA, IMPL_TF32X3 = 0, 1, 2
+ACT_RELU, ACT_MIXTURE_RELU = 1, 2   # tagi_linear_fwd_act / tagi_conv2d_fwd_act
 
 
 class TagiError(RuntimeError):
@@ -42,6 +43,8 @@ _SIGNATURES = {
     "tagi_relu_fwd": [_p, _p, C.c_size_t, _p, _p, _p, _p],
     "tagi_linear_fwd_relu": [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _p, _p],
     "tagi_conv2d_fwd_relu": [C.POINTER(ConvGeom), _p, _p, _p, _p, _p, _p, _p, _p, _p, _p],
+    "tagi_linear_fwd_act": [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _p, _p, _p],
+    "tagi_conv2d_fwd_act": [C.POINTER(ConvGeom), _p, _p, _p, _p, _p, _p, _i, _p, _p, _p, _p],
     "tagi_mixture_relu_fwd": [_p, _p, C.c_size_t, _p, _p, _p, _p],
     "tagi_output_delta": [_p, _p, _p, _p, _p, C.c_size_t, _p, _p, _p],
     "tagi_output_delta_selected": [_p, _p, _p, _p, _p, _p, _i, _i, _i, _p, _p, _p],

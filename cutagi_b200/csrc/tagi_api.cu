@@ -102,10 +102,16 @@ int tagi_linear_fwd(const float *mu_w, const float *var_w, const float *mu_b, co
     return linear_fwd_ffma(mu_w, var_w, mu_b, var_b, mu_a, var_a, B, K, N, mu_z, var_z, st);
 }
 
-int tagi_linear_fwd_relu(const float *mu_w, const float *var_w, const float *mu_b, const float *var_b, const float *mu_a,
-                         const float *var_a, int B, int K, int N, int has_bias, float *mu_a_out, float *var_a_out,
-                         float *jcb_out, void *stream) {
+static int act_after(int act, float *mu, float *var, size_t n, float *jcb, void *stream) {
+    return act == TAGI_ACT_RELU ? tagi_relu_fwd(mu, var, n, mu, var, jcb, stream)
+                                : tagi_mixture_relu_fwd(mu, var, n, mu, var, jcb, stream);
+}
+
+int tagi_linear_fwd_act(const float *mu_w, const float *var_w, const float *mu_b, const float *var_b, const float *mu_a,
+                        const float *var_a, int B, int K, int N, int has_bias, int act, float *mu_a_out, float *var_a_out,
+                        float *jcb_out, void *stream) {
     TAGI_DIMS();
+    TAGI_REQUIRE(act == TAGI_ACT_RELU || act == TAGI_ACT_MIXTURE_RELU, "unknown activation id");
     TAGI_PTR(mu_w);
     TAGI_PTR(var_w);
     TAGI_PTR(mu_a);
@@ -121,21 +127,30 @@ int tagi_linear_fwd_relu(const float *mu_w, const float *var_w, const float *mu_
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     int rc;
-    // one kernel where the forward runs on CTA pairs; otherwise the forward followed by the ReLU in place
+    // ReLU: one kernel where the forward runs on CTA pairs. Otherwise, and for the MixtureReLU (whose erf / exp arithmetic
+    // in the epilogue, 64 columns per thread, was measured slower than a pass of its own), the forward followed by the
+    // activation in place.
     if (pick_tc(__func__, B, K, N, {mu_w, var_w, mu_b, var_b, mu_a, var_a, mu_a_out, var_a_out, jcb_out}, &rc) &&
-        linear_tc_pair_for(B))
+        linear_tc_pair_for(B) && act == TAGI_ACT_RELU)
         return linear_fwd_tc(mu_w, var_w, mu_b, var_b, mu_a, var_a, B, K, N, mu_a_out, var_a_out, st, 0, nullptr, jcb_out);
     if (rc != TAGI_OK) return rc;
     rc = tagi_linear_fwd(mu_w, var_w, mu_b, var_b, mu_a, var_a, B, K, N, has_bias, mu_a_out, var_a_out, stream);
     if (rc != TAGI_OK) return rc;
-    return tagi_relu_fwd(mu_a_out, var_a_out, (size_t)B * N, mu_a_out, var_a_out, jcb_out, stream);
+    return act_after(act, mu_a_out, var_a_out, (size_t)B * N, jcb_out, stream);
+}
+
+int tagi_linear_fwd_relu(const float *mu_w, const float *var_w, const float *mu_b, const float *var_b, const float *mu_a,
+                         const float *var_a, int B, int K, int N, int has_bias, float *mu_a_out, float *var_a_out,
+                         float *jcb_out, void *stream) {
+    return tagi_linear_fwd_act(mu_w, var_w, mu_b, var_b, mu_a, var_a, B, K, N, has_bias, TAGI_ACT_RELU, mu_a_out, var_a_out,
+                               jcb_out, stream);
 }
 
 int tagi_linear_bwd_state(const float *mu_w, const float *jcb, const float *dmu_z, const float *dvar_z, int B, int K,
                           int N, float *dmu_a, float *dvar_a, void *stream) {
     TAGI_DIMS();
     TAGI_PTR(mu_w);
-    TAGI_PTR(jcb);
+    if (jcb) TAGI_PTR(jcb);
     TAGI_PTR(dmu_z);
     TAGI_PTR(dvar_z);
     TAGI_PTR(dmu_a);
@@ -286,11 +301,12 @@ int tagi_conv2d_fwd(const tagi_conv2d_geom *g, const float *mu_w, const float *v
     return conv2d_fwd_ffma(*g, mu_w, var_w, mu_b, var_b, mu_a, var_a, mu_z, var_z, st);
 }
 
-int tagi_conv2d_fwd_relu(const tagi_conv2d_geom *g, const float *mu_w, const float *var_w, const float *mu_b,
-                         const float *var_b, const float *mu_a, const float *var_a, float *mu_a_out, float *var_a_out,
-                         float *jcb_out, void *stream) {
+int tagi_conv2d_fwd_act(const tagi_conv2d_geom *g, const float *mu_w, const float *var_w, const float *mu_b,
+                        const float *var_b, const float *mu_a, const float *var_a, int act, float *mu_a_out,
+                        float *var_a_out, float *jcb_out, void *stream) {
     int rc = check_geom(g);
     if (rc != TAGI_OK) return rc;
+    TAGI_REQUIRE(act == TAGI_ACT_RELU || act == TAGI_ACT_MIXTURE_RELU, "unknown activation id");
     TAGI_PTR(mu_w);
     TAGI_PTR(var_w);
     TAGI_PTR(mu_a);
@@ -307,12 +323,18 @@ int tagi_conv2d_fwd_relu(const tagi_conv2d_geom *g, const float *mu_w, const flo
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (pick_conv_tc(__func__, *g, CONV_PASS_FWD, {mu_w, var_w, mu_b, var_b, mu_a, var_a, mu_a_out, var_a_out, jcb_out},
                      &rc) &&
-        conv2d_fwd_tc_fuses_relu(*g))
+        conv2d_fwd_tc_fuses_relu(*g) && act == TAGI_ACT_RELU)
         return conv2d_fwd_tc(*g, mu_w, var_w, mu_b, var_b, mu_a, var_a, mu_a_out, var_a_out, st, jcb_out);
     if (rc != TAGI_OK) return rc;
     rc = tagi_conv2d_fwd(g, mu_w, var_w, mu_b, var_b, mu_a, var_a, mu_a_out, var_a_out, stream);
     if (rc != TAGI_OK) return rc;
-    return tagi_relu_fwd(mu_a_out, var_a_out, (size_t)g->B * g->fo * g->ho * g->wo, mu_a_out, var_a_out, jcb_out, stream);
+    return act_after(act, mu_a_out, var_a_out, (size_t)g->B * g->fo * g->ho * g->wo, jcb_out, stream);
+}
+
+int tagi_conv2d_fwd_relu(const tagi_conv2d_geom *g, const float *mu_w, const float *var_w, const float *mu_b,
+                         const float *var_b, const float *mu_a, const float *var_a, float *mu_a_out, float *var_a_out,
+                         float *jcb_out, void *stream) {
+    return tagi_conv2d_fwd_act(g, mu_w, var_w, mu_b, var_b, mu_a, var_a, TAGI_ACT_RELU, mu_a_out, var_a_out, jcb_out, stream);
 }
 
 int tagi_conv2d_bwd_state(const tagi_conv2d_geom *g, const float *mu_w, const float *jcb, const float *dmu_z,
@@ -320,7 +342,7 @@ int tagi_conv2d_bwd_state(const tagi_conv2d_geom *g, const float *mu_w, const fl
     int rc = check_geom(g);
     if (rc != TAGI_OK) return rc;
     TAGI_PTR(mu_w);
-    TAGI_PTR(jcb);
+    if (jcb) TAGI_PTR(jcb);
     TAGI_PTR(dmu_z);
     TAGI_PTR(dvar_z);
     TAGI_PTR(dmu_a);

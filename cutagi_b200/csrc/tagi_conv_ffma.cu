@@ -296,7 +296,7 @@ int conv2d_bwd_state_ffma(const tagi_conv2d_geom &cg, const float *mu_w, const f
     WeightForInputChannel<DER_SQUARE> W{mu_w, nullptr, g, g.fi, Kd};
     DeltaForInputPixel<DER_PAIR> D{dmu_z, dvar_z, g, N, Kd};
     EpiChanPix epi{dmu_a, dvar_a, nullptr, nullptr, jcb, g.fi, g.wihi,
-                   g.wihi % 4 == 0 && aligned16(dmu_a) && aligned16(dvar_a) && aligned16(jcb)};
+                   g.wihi % 4 == 0 && aligned16(dmu_a) && aligned16(dvar_a) && (!jcb || aligned16(jcb))};
     return done(dispatch_ffma<decltype(W), decltype(D), EpiChanPix, LOAD_K_SCALAR, LOAD_K_SCALAR, LOAD_R_SCALAR,
                               LOAD_R_SCALAR>(W, D, epi, M, N, Kd, false, false, st),
                 "conv2d state backward launch");

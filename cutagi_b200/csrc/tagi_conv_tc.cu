@@ -218,7 +218,7 @@ __global__ void __launch_bounds__(256) col2im_kernel(const float *__restrict__ c
                 a1 += __ldg(c1 + i);
             }
         }
-        const float j = __ldg(jcb + t);
+        const float j = jcb ? __ldg(jcb + t) : 1.f;
         o0[t] = a0 * j;
         o1[t] = a1 * j * j;
     }

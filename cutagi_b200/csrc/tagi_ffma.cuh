@@ -350,18 +350,18 @@ struct EpiRowBias {
 // parameter pass; same association as the reference: (sum * s) * s)
 struct EpiRowScale {
     float *out1, *out2;
-    const float *scale;
+    const float *scale;  // null: every entry is one
     long ld;
     bool vec_ok;
     __device__ __forceinline__ void store(int m, int n, int, float c1, float c2) const {
         const long i = (long)m * ld + n;
-        const float s = __ldg(scale + i);
+        const float s = scale ? __ldg(scale + i) : 1.f;
         out1[i] = c1 * s;
         out2[i] = c2 * s * s;
     }
     __device__ __forceinline__ void store4(int m, int n, int, float4 c1, float4 c2) const {
         const long i = (long)m * ld + n;
-        const float4 s = __ldg(reinterpret_cast<const float4 *>(scale + i));
+        const float4 s = scale ? __ldg(reinterpret_cast<const float4 *>(scale + i)) : make_float4(1.f, 1.f, 1.f, 1.f);
         c1.x *= s.x, c1.y *= s.y, c1.z *= s.z, c1.w *= s.w;
         c2.x = c2.x * s.x * s.x, c2.y = c2.y * s.y * s.y, c2.z = c2.z * s.z * s.z, c2.w = c2.w * s.w * s.w;
         __stcs(reinterpret_cast<float4 *>(out1 + i), c1);

@@ -251,10 +251,10 @@ __global__ void __launch_bounds__(BLOCK) avgpool2d_fwd_kernel(const float *__res
                                                               float *__restrict__ var_z) {
     const long t = (long)blockIdx.x * BLOCK + threadIdx.x;
     if (t >= total) return;
-    const int woho = g.wo * g.ho, p = (int)(t % woho);
-    const long plane = t / woho;
-    const int oy = p / g.wo, ox = p - oy * g.wo;
-    const float *a = mu_a + plane * g.hi * g.wi, *v = var_a + plane * g.hi * g.wi;
+    // total < 2^31 (checked at the entry points): 32-bit divisions
+    const unsigned woho = g.wo * g.ho, plane = (unsigned)t / woho;
+    const int p = (int)((unsigned)t - plane * woho), oy = p / g.wo, ox = p - oy * g.wo;
+    const float *a = mu_a + (size_t)plane * g.hi * g.wi, *v = var_a + (size_t)plane * g.hi * g.wi;
     float sm = 0.f, sv = 0.f;
     for (int ky = 0; ky < g.k; ky++) {
         const int y = oy * g.stride - g.off + ky;
@@ -295,17 +295,38 @@ __global__ void __launch_bounds__(BLOCK) avgpool2d_bwd_kernel(const float *__res
     } else {
         // cells whose window contains the pixel, in ascending order (the order of the reference's index table)
         const int oy_lo = max(0, (y + g.off - g.k + g.stride) / g.stride), oy_hi = min(g.ho - 1, (y + g.off) / g.stride);
+        int lo[VEC], hi[VEC];
 #pragma unroll
         for (int v = 0; v < VEC; v++) {
             const int x = x0 + v;
-            const int ox_lo = max(0, (x + g.off - g.k + g.stride) / g.stride), ox_hi = min(g.wo - 1, (x + g.off) / g.stride);
-            float a = 0.f, c = 0.f;
-            for (int oy = oy_lo; oy <= oy_hi; oy++)
-                for (int ox = ox_lo; ox <= ox_hi; ox++) {
-                    a += __ldg(dm + oy * g.wo + ox);
-                    c += __ldg(dv + oy * g.wo + ox);
+            lo[v] = max(0, (x + g.off - g.k + g.stride) / g.stride), hi[v] = min(g.wo - 1, (x + g.off) / g.stride);
+            sm[v] = sv[v] = 0.f;
+        }
+        constexpr int MAXC = 8;  // cells of a row that the VEC pixels share (3 for 3 x 3 windows at stride 2)
+        if (VEC > 1 && hi[VEC - 1] - lo[0] < MAXC) {
+            // every cell is loaded once for the VEC pixels; each pixel adds its own cells in the same ascending order
+            for (int oy = oy_lo; oy <= oy_hi; oy++) {
+                float cm[MAXC], cv[MAXC];
+#pragma unroll
+                for (int c = 0; c < MAXC; c++) {
+                    const bool in = lo[0] + c <= hi[VEC - 1];
+                    cm[c] = in ? __ldg(dm + oy * g.wo + lo[0] + c) : 0.f;
+                    cv[c] = in ? __ldg(dv + oy * g.wo + lo[0] + c) : 0.f;
                 }
-            sm[v] = a, sv[v] = c;
+#pragma unroll
+                for (int v = 0; v < VEC; v++)
+#pragma unroll
+                    for (int c = 0; c < MAXC; c++)
+                        if (lo[0] + c >= lo[v] && lo[0] + c <= hi[v]) sm[v] += cm[c], sv[v] += cv[c];
+            }
+        } else {
+#pragma unroll
+            for (int v = 0; v < VEC; v++)
+                for (int oy = oy_lo; oy <= oy_hi; oy++)
+                    for (int ox = lo[v]; ox <= hi[v]; ox++) {
+                        sm[v] += __ldg(dm + oy * g.wo + ox);
+                        sv[v] += __ldg(dv + oy * g.wo + ox);
+                    }
         }
     }
     const int k2 = g.k * g.k;

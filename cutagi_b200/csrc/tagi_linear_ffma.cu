@@ -60,7 +60,7 @@ int linear_bwd_state_ffma(const float *mu_w, const float *jcb, const float *dmu_
     StridedOperand<DER_PAIR> A{dmu_z, dvar_z, (long)N, 1, B, N};
     StridedOperand<DER_SQUARE> W{mu_w, nullptr, 1, (long)K, K, N};
     EpiRowScale epi{dmu_a, dvar_a, jcb, (long)K,
-                    K % 4 == 0 && aligned16(dmu_a) && aligned16(dvar_a) && aligned16(jcb)};
+                    K % 4 == 0 && aligned16(dmu_a) && aligned16(dvar_a) && (!jcb || aligned16(jcb))};
     return done(dispatch_ffma<decltype(A), decltype(W), EpiRowScale, LOAD_K_VEC4, LOAD_K_SCALAR, LOAD_R_VEC4, LOAD_R_SCALAR>(
         A, W, epi, B, K, N, N % 4 == 0 && aligned16(dmu_z) && aligned16(dvar_z), K % 4 == 0 && aligned16(mu_w), st));
 }

@@ -60,20 +60,20 @@ class Linear:
         self.delta_var_b = torch.zeros_like(self.var_b) if self.bias else None
         self.neg_var = torch.zeros(1, dtype=torch.int32, device=dev)
 
-    def forward(self, mu_a, var_a, jcb, train=True, relu=False):
-        """relu=True: the ReLU layer that follows is folded into the call (tagi_linear_fwd_relu) and the moments after it
-        and its Jacobian are returned."""
+    def forward(self, mu_a, var_a, jcb, train=True, act=0):
+        """act = capi.ACT_RELU / ACT_MIXTURE_RELU: the activation layer that follows is folded into the call
+        (tagi_linear_fwd_act) and the moments after it and its Jacobian are returned."""
         B = mu_a.shape[0]
         if mu_a.shape[1] != self.input_size:
             raise RuntimeError(f"Input size mismatch: {self.input_size} vs {mu_a.shape[1]}")
         self.saved = (mu_a, jcb)   # what the reference copies into bwd_states (src/base_layer.cpp:212-228)
         mu_z = torch.empty(B, self.output_size, device=mu_a.device)
         var_z = torch.empty_like(mu_z)
-        if relu:
+        if act:
             j = torch.empty_like(mu_z)
-            lib.tagi_linear_fwd_relu(_p(self.mu_w), _p(self.var_w), _p(self.mu_b), _p(self.var_b), _p(mu_a), _p(var_a), B,
-                                     self.input_size, self.output_size, int(self.bias), _p(mu_z), _p(var_z), _p(j),
-                                     _stream())
+            lib.tagi_linear_fwd_act(_p(self.mu_w), _p(self.var_w), _p(self.mu_b), _p(self.var_b), _p(mu_a), _p(var_a), B,
+                                    self.input_size, self.output_size, int(self.bias), act, _p(mu_z), _p(var_z), _p(j),
+                                    _stream())
             return mu_z, var_z, j
         lib.tagi_linear_fwd(_p(self.mu_w), _p(self.var_w), _p(self.mu_b), _p(self.var_b), _p(mu_a), _p(var_a), B,
                             self.input_size, self.output_size, int(self.bias), _p(mu_z), _p(var_z), _stream())
@@ -89,8 +89,6 @@ class Linear:
             self.on_ready()
         if not state_update:
             return None, None
-        if jcb is None:
-            jcb = torch.ones_like(mu_a)
         dmu_a, dvar_a = torch.empty_like(mu_a), torch.empty_like(mu_a)
         lib.tagi_linear_bwd_state(_p(self.mu_w), _p(jcb), _p(dmu), _p(dvar), B, self.input_size, self.output_size,
                                   _p(dmu_a), _p(dvar_a), _stream())
@@ -176,7 +174,7 @@ class Conv2d(Linear):
     def _g(self, B):
         return _geom(B, self.fi, self.hi, self.wi, self.fo, self.k, self.stride, self.pad, self.pad_type, self.bias)
 
-    def forward(self, mu_a, var_a, jcb, train=True, relu=False):
+    def forward(self, mu_a, var_a, jcb, train=True, act=0):
         B = mu_a.shape[0]
         if mu_a.shape[1] != self.input_size:
             raise RuntimeError(f"Input size mismatch: {self.input_size} vs {mu_a.shape[1]}")
@@ -184,10 +182,10 @@ class Conv2d(Linear):
         mu_z = torch.empty(B, self.fo * self.ho * self.wo, device=mu_a.device)
         var_z = torch.empty_like(mu_z)
         g = self._g(B)
-        if relu:
+        if act:
             j = torch.empty_like(mu_z)
-            lib.tagi_conv2d_fwd_relu(ctypes.byref(g), _p(self.mu_w), _p(self.var_w), _p(self.mu_b), _p(self.var_b),
-                                     _p(mu_a), _p(var_a), _p(mu_z), _p(var_z), _p(j), _stream())
+            lib.tagi_conv2d_fwd_act(ctypes.byref(g), _p(self.mu_w), _p(self.var_w), _p(self.mu_b), _p(self.var_b),
+                                    _p(mu_a), _p(var_a), act, _p(mu_z), _p(var_z), _p(j), _stream())
             return mu_z, var_z, j
         lib.tagi_conv2d_fwd(ctypes.byref(g), _p(self.mu_w), _p(self.var_w), _p(self.mu_b), _p(self.var_b), _p(mu_a),
                             _p(var_a), _p(mu_z), _p(var_z), _stream())
@@ -203,8 +201,6 @@ class Conv2d(Linear):
             self.on_ready()
         if not state_update:
             return None, None
-        if jcb is None:
-            jcb = torch.ones_like(mu_a)
         dmu_a, dvar_a = torch.empty_like(mu_a), torch.empty_like(mu_a)
         lib.tagi_conv2d_bwd_state(ctypes.byref(g), _p(self.mu_w), _p(jcb), _p(dmu), _p(dvar), _p(dmu_a), _p(dvar_a),
                                   _stream())
@@ -308,12 +304,14 @@ fuse_relu = True   # run a Linear / Conv2d layer and the ReLU layer directly beh
 
 def _forward_layers(layers, mu, var, jcb, train):
     """The layers in order. A Linear / Conv2d layer directly followed by a ReLU layer runs as one fused call
-    (tagi_linear_fwd_relu / tagi_conv2d_fwd_relu): same results, the moments before the ReLU are never stored."""
+    (tagi_linear_fwd_act / tagi_conv2d_fwd_act): same results, the moments before the activation are never stored.
+    (A MixtureReLU stays a pass of its own: inside the forward kernel it was measured slower.)"""
+    fusable = {ReLU: capi.ACT_RELU}
     i = 0
     while i < len(layers):
         layer = layers[i]
-        if fuse_relu and type(layer) in (Linear, Conv2d) and i + 1 < len(layers) and type(layers[i + 1]) is ReLU:
-            mu, var, jcb = layer.forward(mu, var, jcb, train, relu=True)
+        if fuse_relu and type(layer) in (Linear, Conv2d) and i + 1 < len(layers) and type(layers[i + 1]) in fusable:
+            mu, var, jcb = layer.forward(mu, var, jcb, train, act=fusable[type(layers[i + 1])])
             i += 2
         else:
             mu, var, jcb = layer.forward(mu, var, jcb, train)

@@ -41,6 +41,8 @@ enum {
  *            shapes it cannot run return TAGI_ERR_UNSUPPORTED under this setting. Conv2d runs on the same kernels
  *            after a gather pass that lays the receptive fields out as a matrix in library-owned scratch memory. */
 enum { TAGI_IMPL_AUTO = 0, TAGI_IMPL_FFMA = 1, TAGI_IMPL_TF32X3 = 2 };
+/* activations that tagi_linear_fwd_act / tagi_conv2d_fwd_act can fold into the forward pass */
+enum { TAGI_ACT_RELU = 1, TAGI_ACT_MIXTURE_RELU = 2 };
 int tagi_set_impl(int impl);
 int tagi_get_impl(void);
 
@@ -83,7 +85,9 @@ int tagi_linear_fwd(const float *mu_w, const float *var_w, const float *mu_b, co
 /* dmu_a = jcb * (dmu_z.mu_w) ; dvar_a = jcb^2 * (dvar_z.mu_w^2).
  * Replaces linear_state_backward_cuda (src/linear_layer_cuda.cu:75-121), kernels linear_bwd_delta_z_v4/v3
  * (include/linear_cuda_kernel.cuh:894,776); CPU definition linear_bwd_fc_delta_z (src/linear_layer.cpp:245-272).
- * jcb is the Jacobian saved by the forward pass (bwd_states->jcb), [B][K]. */
+ * jcb is the Jacobian saved by the forward pass (bwd_states->jcb), [B][K]; NULL stands for a Jacobian of ones (the
+ * input of the layer was not an activation's output: cuTAGI fills bwd_states->jcb with ones then,
+ * src/base_layer_cuda.cu:464-486), which saves reading it. */
 int tagi_linear_bwd_state(const float *mu_w, const float *jcb, const float *dmu_z, const float *dvar_z,
                           int B, int K, int N, float *dmu_a, float *dvar_a, void *stream);
 
@@ -130,7 +134,8 @@ int tagi_conv2d_fwd(const tagi_conv2d_geom *g, const float *mu_w, const float *v
 
 /* Replaces conv2d_state_backward_cuda (src/conv2d_layer_cuda.cu:90-147), kernels conv2d_bwd_delta_z_cuda_v2/v1
  * (include/conv2d_cuda_kernel.cuh:948,864) and the Jacobian permute launch (src/conv2d_layer_cuda.cu:504-511);
- * CPU definition conv2d_bwd_delta_z (src/conv2d_layer.cpp:363-403). jcb is in the natural [B][fi][hi*wi] layout. */
+ * CPU definition conv2d_bwd_delta_z (src/conv2d_layer.cpp:363-403). jcb is in the natural [B][fi][hi*wi] layout; NULL
+ * stands for a Jacobian of ones, as for tagi_linear_bwd_state. */
 int tagi_conv2d_bwd_state(const tagi_conv2d_geom *g, const float *mu_w, const float *jcb, const float *dmu_z,
                           const float *dvar_z, float *dmu_a, float *dvar_a, void *stream);
 
@@ -160,6 +165,16 @@ int tagi_relu_fwd(const float *mu_z, const float *var_z, size_t n, float *mu_a, 
 int tagi_linear_fwd_relu(const float *mu_w, const float *var_w, const float *mu_b, const float *var_b, const float *mu_a,
                          const float *var_a, int B, int K, int N, int has_bias, float *mu_a_out, float *var_a_out,
                          float *jcb_out, void *stream);
+/* The same with the activation named by `act`: TAGI_ACT_RELU, or TAGI_ACT_MIXTURE_RELU for tagi_mixture_relu_fwd's
+ * moments (MixtureReLUCuda::forward -> mixture_relu_mean_var_cuda, src/activation_cuda.cu:130-157, 726-759). Only the ReLU
+ * runs inside the forward kernel; the MixtureReLU always runs as a second step in place on the outputs (its erf / exp
+ * arithmetic in the epilogue was measured slower than a pass of its own). */
+int tagi_linear_fwd_act(const float *mu_w, const float *var_w, const float *mu_b, const float *var_b, const float *mu_a,
+                        const float *var_a, int B, int K, int N, int has_bias, int act, float *mu_a_out, float *var_a_out,
+                        float *jcb_out, void *stream);
+int tagi_conv2d_fwd_act(const tagi_conv2d_geom *g, const float *mu_w, const float *var_w, const float *mu_b,
+                        const float *var_b, const float *mu_a, const float *var_a, int act, float *mu_a_out,
+                        float *var_a_out, float *jcb_out, void *stream);
 int tagi_conv2d_fwd_relu(const tagi_conv2d_geom *g, const float *mu_w, const float *var_w, const float *mu_b,
                          const float *var_b, const float *mu_a, const float *var_a, float *mu_a_out, float *var_a_out,
                          float *jcb_out, void *stream);

@@ -75,14 +75,27 @@ def linear_fwd(mw, vw, mb, vb, ma, va, misalign=0):
     return mz.get((B, N)), vz.get((B, N))
 
 
-def linear_fwd_relu(mw, vw, mb, vb, ma, va, misalign=0):
+def linear_fwd_relu(mw, vw, mb, vb, ma, va, misalign=0, act=None):
+    """act None: tagi_linear_fwd_relu; else tagi_linear_fwd_act with that activation id."""
     B, K = ma.shape
     N = mw.shape[0]
     d = [dev(x, misalign) for x in (mw, vw, mb, vb, ma, va)]
     o = [Out(B * N, misalign) for _ in range(3)]
-    lib.tagi_linear_fwd_relu(p(d[0]), p(d[1]), p(d[2]), p(d[3]), p(d[4]), p(d[5]), B, K, N, int(mb is not None),
-                             o[0].ptr(), o[1].ptr(), o[2].ptr(), None)
+    if act is None:
+        lib.tagi_linear_fwd_relu(p(d[0]), p(d[1]), p(d[2]), p(d[3]), p(d[4]), p(d[5]), B, K, N, int(mb is not None),
+                                 o[0].ptr(), o[1].ptr(), o[2].ptr(), None)
+    else:
+        lib.tagi_linear_fwd_act(p(d[0]), p(d[1]), p(d[2]), p(d[3]), p(d[4]), p(d[5]), B, K, N, int(mb is not None), act,
+                                o[0].ptr(), o[1].ptr(), o[2].ptr(), None)
     return tuple(x.get((B, N)) for x in o)
+
+
+def mixture_relu(mz, vz):
+    """tagi_mixture_relu_fwd on forward outputs."""
+    d = [dev(x) for x in (mz, vz)]
+    o = [Out(mz.size) for _ in range(3)]
+    lib.tagi_mixture_relu_fwd(p(d[0]), p(d[1]), mz.size, o[0].ptr(), o[1].ptr(), o[2].ptr(), None)
+    return tuple(x.get(mz.shape) for x in o)
 
 
 def relu_of(mz, vz):
@@ -93,8 +106,9 @@ def relu_of(mz, vz):
 
 
 def linear_bwd_state(mw, jcb, dm, dv, misalign=0):
-    B, K = jcb.shape
-    N = mw.shape[0]
+    """jcb None: the NULL Jacobian (ones)."""
+    B = dm.shape[0]
+    N, K = mw.shape
     d = [dev(x, misalign) for x in (mw, jcb, dm, dv)]
     oa, ob = Out(B * K, misalign), Out(B * K, misalign)
     lib.tagi_linear_bwd_state(p(d[0]), p(d[1]), p(d[2]), p(d[3]), B, K, N, oa.ptr(), ob.ptr(), None)
@@ -126,12 +140,16 @@ def conv_fwd(g, mw, vw, mb, vb, ma, va):
     return mz.get((g.B, g.n_out)), vz.get((g.B, g.n_out))
 
 
-def conv_fwd_relu(g, mw, vw, mb, vb, ma, va):
+def conv_fwd_relu(g, mw, vw, mb, vb, ma, va, act=None):
     d = [dev(x) for x in (mw, vw, mb, vb, ma, va)]
     o = [Out(g.B * g.n_out) for _ in range(3)]
     cg = cgeom(g)
-    lib.tagi_conv2d_fwd_relu(C.byref(cg), p(d[0]), p(d[1]), p(d[2]), p(d[3]), p(d[4]), p(d[5]), o[0].ptr(), o[1].ptr(),
-                             o[2].ptr(), None)
+    if act is None:
+        lib.tagi_conv2d_fwd_relu(C.byref(cg), p(d[0]), p(d[1]), p(d[2]), p(d[3]), p(d[4]), p(d[5]), o[0].ptr(), o[1].ptr(),
+                                 o[2].ptr(), None)
+    else:
+        lib.tagi_conv2d_fwd_act(C.byref(cg), p(d[0]), p(d[1]), p(d[2]), p(d[3]), p(d[4]), p(d[5]), act, o[0].ptr(),
+                                o[1].ptr(), o[2].ptr(), None)
     return tuple(x.get((g.B, g.n_out)) for x in o)
 
 

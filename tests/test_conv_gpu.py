@@ -192,3 +192,39 @@ def test_conv_forward_with_fused_relu(G, kw, impl):
     assert (mz < 0).any() and (mz > 0).any()
     for name, a, b in zip(("mu_a", "var_a", "jcb"), got, G.relu_of(mz, vz)):
         np.testing.assert_array_equal(a, b, err_msg=name)
+
+
+@pytest.mark.parametrize("kw", [TC_GEOMS[0], TC_GEOMS[3], TC_GEOMS[5], TC_GEOMS[6], TC_GEOMS[13]],
+                         ids=lambda k: "fi{fi}_fo{fo}_h{hi}_k{k}_s{stride}".format(**k))
+@pytest.mark.parametrize("impl", ["auto", "ffma"])
+def test_conv_state_pass_with_null_jacobian(G, kw, impl):
+    """jcb = NULL stands for a Jacobian of ones: same bits as the pass given a tensor of ones (implicit and explicit
+    gathers, the col2im pass of strided layers, the FFMA kernels)."""
+    from cutagi_b200 import capi
+    from cutagi_b200.capi import lib
+    g = ConvGeom(**kw)
+    x = G.conv_inputs(np.random.default_rng(g.fi * 3 + g.fo), g)
+    ones = np.ones_like(x["jcb"])
+    lib.tagi_set_impl(capi.IMPL_FFMA if impl == "ffma" else capi.IMPL_AUTO)
+    try:
+        ref = G.conv_bwd_state(g, x["mu_w"], ones, x["dmu_z"], x["dvar_z"])
+        got = G.conv_bwd_state(g, x["mu_w"], None, x["dmu_z"], x["dvar_z"])
+    finally:
+        lib.tagi_set_impl(capi.IMPL_AUTO)
+    for name, a, b in zip(("dmu_a", "dvar_a"), got, ref):
+        np.testing.assert_array_equal(a, b, err_msg=name)
+
+
+@pytest.mark.parametrize("kw", [TC_GEOMS[0], TC_GEOMS[3], TC_GEOMS[14], TC_GEOMS[6]],
+                         ids=lambda k: "fi{fi}_fo{fo}_h{hi}_k{k}_s{stride}".format(**k))
+def test_conv_forward_with_fused_mixture_relu(G, kw):
+    """tagi_conv2d_fwd_act(TAGI_ACT_MIXTURE_RELU) against tagi_conv2d_fwd followed by tagi_mixture_relu_fwd."""
+    from cutagi_b200 import capi
+    g = ConvGeom(**kw)
+    x = G.conv_inputs(np.random.default_rng(g.fi * 11 + g.fo), g)
+    args = (g, x["mu_w"], x["var_w"], x["mu_b"], x["var_b"], x["mu_a"], x["var_a"])
+    ref = G.mixture_relu(*G.conv_fwd(*args))
+    got = G.conv_fwd_relu(*args, act=capi.ACT_MIXTURE_RELU)
+    assert capi.tc_status() == 0
+    for name, a, b, tol in zip(("mu_a", "var_a", "jcb"), got, ref, (G.RTOL_MU, G.RTOL_VAR, G.RTOL_MU)):
+        G.check(name, a, b, tol)

@@ -327,3 +327,35 @@ def test_fused_relu_rejects_null_jacobian(G):
     q = torch.zeros(1 << 12, device="cuda").data_ptr()
     with pytest.raises(TagiError):
         lib.tagi_linear_fwd_relu(q, q, q, q, q, q, 4, 8, 8, 1, q, q, None, None)
+
+
+@pytest.mark.parametrize("B,K,N,impl", [(256, 1024, 512, "auto"), (300, 260, 132, "tc"), (130, 256, 132, "auto"),
+                                        (33, 65, 17, "auto"), (512, 256, 384, "ffma")])
+def test_state_pass_with_null_jacobian(G, force_impl, B, K, N, impl):
+    """jcb = NULL stands for a Jacobian of ones: same bits as the pass given a tensor of ones, on every kernel."""
+    from cutagi_b200 import capi
+    if impl != "auto":
+        force_impl(capi.IMPL_TF32X3 if impl == "tc" else capi.IMPL_FFMA)
+    x = G.linear_inputs(np.random.default_rng(B + N), B, K, N)
+    ones = np.ones((B, K), np.float32)
+    ref = G.linear_bwd_state(x["mu_w"], ones, x["dmu_z"], x["dvar_z"])
+    got = G.linear_bwd_state(x["mu_w"], None, x["dmu_z"], x["dvar_z"])
+    for name, a, b in zip(("dmu_a", "dvar_a"), got, ref):
+        np.testing.assert_array_equal(a, b, err_msg=name)
+
+
+@pytest.mark.parametrize("B,K,N", [(256, 1024, 1024), (300, 260, 132), (130, 256, 132), (3, 5, 11)])
+def test_forward_with_fused_mixture_relu(G, B, K, N):
+    """tagi_linear_fwd_act(TAGI_ACT_MIXTURE_RELU) against tagi_linear_fwd followed by tagi_mixture_relu_fwd, and with
+    TAGI_ACT_RELU bit for bit against tagi_linear_fwd_relu; unknown activation ids are refused."""
+    from cutagi_b200 import capi
+    x = G.linear_inputs(np.random.default_rng(B + K + N + 1), B, K, N, True)
+    args = (x["mu_w"], x["var_w"], x["mu_b"], x["var_b"], x["mu_a"], x["var_a"])
+    ref = G.mixture_relu(*G.linear_fwd(*args))
+    got = G.linear_fwd_relu(*args, act=capi.ACT_MIXTURE_RELU)
+    for name, a, b, tol in zip(("mu_a", "var_a", "jcb"), got, ref, (G.RTOL_MU, G.RTOL_VAR, G.RTOL_MU)):
+        G.check(name, a, b, tol)
+    for a, b in zip(G.linear_fwd_relu(*args, act=capi.ACT_RELU), G.linear_fwd_relu(*args)):
+        np.testing.assert_array_equal(a, b)
+    with pytest.raises(capi.TagiError):
+        G.linear_fwd_relu(*args, act=7)
