@@ -29,6 +29,8 @@ _SIGNATURES = {
     "tagi_get_impl": [],
     "tagi_version": [],
     "tagi_tc_status": [C.POINTER(_i), _i],
+    "tagi_reserve_scratch": [C.c_size_t],
+    "tagi_release_scratch": [],
     "tagi_tc_set_chunked": [_i],
     "tagi_tc_set_sm_budget": [_i],
     "tagi_tc_set_variant": [_i],
@@ -71,6 +73,8 @@ def load():
                 "cutagi_b200 has no CPU or PyTorch fallback")
         _lib = C.CDLL(LIB_PATH)
         _lib.tagi_last_error_string.restype = C.c_char_p
+        _lib.tagi_conv2d_workspace_bytes.restype = C.c_size_t
+        _lib.tagi_conv2d_workspace_bytes.argtypes = [C.POINTER(ConvGeom)]
         for name, args in _SIGNATURES.items():
             fn = getattr(_lib, name)
             fn.argtypes = args
@@ -83,7 +87,7 @@ class _Lib:
 
     def __getattr__(self, name):
         fn = getattr(load(), name)
-        if name in ("tagi_get_impl", "tagi_version", "tagi_last_error_string"):
+        if name in ("tagi_get_impl", "tagi_version", "tagi_last_error_string", "tagi_conv2d_workspace_bytes"):
             return fn
 
         def checked(*args):

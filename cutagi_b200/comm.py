@@ -13,6 +13,8 @@ _p, _i, _z = C.c_void_p, C.c_int, C.c_size_t
 _SIG = {
     "tagi_rendezvous_publish": [C.c_char_p, _p, _z],
     "tagi_rendezvous_fetch": [C.c_char_p, _p, _z, _i],
+    "tagi_rendezvous_publish_id": [C.c_char_p, _p, _i],
+    "tagi_rendezvous_fetch_id": [C.c_char_p, _p, _i, _i],
     "tagi_comm_plan_buckets": [C.POINTER(_z), _i, _z, C.POINTER(_i)],
     "tagi_comm_create_id": [_p],
     "tagi_comm_init": [_p, _i, _i, _i],
@@ -30,6 +32,8 @@ _SIG = {
     "tagi_comm_broadcast": [_p, _z, _i, _p],
     "tagi_comm_check": [],
     "tagi_comm_barrier": [],
+    "tagi_comm_sync_stream": [],
+    "tagi_comm_set_max_ctas": [_i],
     "tagi_comm_destroy": [],
 }
 _RAW = {"tagi_comm_rank", "tagi_comm_world_size", "tagi_comm_num_buckets", "tagi_comm_bucket_of",
@@ -86,6 +90,17 @@ def rendezvous_fetch(path, nbytes, timeout_ms):
     return buf.raw
 
 
+def rendezvous_publish_id(path, ident: bytes, world_size):
+    assert len(ident) == ID_BYTES
+    _call("tagi_rendezvous_publish_id", path.encode(), ident, world_size)
+
+
+def rendezvous_fetch_id(path, world_size, timeout_ms):
+    buf = C.create_string_buffer(ID_BYTES)
+    _call("tagi_rendezvous_fetch_id", path.encode(), buf, world_size, timeout_ms)
+    return buf.raw
+
+
 def plan_buckets(counts, bucket_bytes):
     """Bucket index of every tensor (greedy packing in registration order) and the number of buckets."""
     n = len(counts)
@@ -102,8 +117,10 @@ class DeltaExchange:
     """
 
     def __init__(self, tensors, rank, world_size, device, rendezvous_path, bucket_bytes=32 << 20, average=True,
-                 timeout_ms=60000):
+                 timeout_ms=60000, max_ctas=0):
         self.average = int(average)
+        if max_ctas:
+            _call("tagi_comm_set_max_ctas", max_ctas)
         _call("tagi_comm_init_file", rendezvous_path.encode(), rank, world_size, device, timeout_ms)
         self.index = [_call("tagi_comm_register", t.data_ptr(), t.numel()) for t in tensors]
         _call("tagi_comm_finalize_buckets", bucket_bytes)
@@ -123,6 +140,13 @@ class DeltaExchange:
 
     def check(self):
         _call("tagi_comm_check")
+
+    def barrier(self):
+        _call("tagi_comm_barrier")
+
+    def allreduce(self, t, stream_ptr, average=None):
+        _call("tagi_comm_allreduce", t.data_ptr(), t.numel(), self.average if average is None else int(average),
+              stream_ptr)
 
     def close(self):
         _call("tagi_comm_destroy")

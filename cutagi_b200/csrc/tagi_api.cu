@@ -54,6 +54,8 @@ int tagi_tc_status(int *status, int reset) {
     TAGI_REQUIRE(status != nullptr, "null status pointer");
     return linear_tc_status(status, reset);
 }
+int tagi_reserve_scratch(size_t bytes) { return reserve_scratch(bytes); }
+int tagi_release_scratch(void) { return release_scratch(); }
 int tagi_tc_set_chunked(int on) { return linear_tc_set_chunked(on); }
 int tagi_tc_set_sm_budget(int sms) { return linear_tc_set_sm_budget(sms); }
 int tagi_tc_set_variant(int v) { return linear_tc_set_variant(v); }
@@ -213,6 +215,9 @@ int tagi_linear_bwd_param_rows(const float *var_w, const float *var_b, const flo
     const long w0 = (long)n0 * K;
     var_w += w0, dmu_w += w0, dvar_w += w0, dmu_z += n0, dvar_z += n0;
     int rc = TAGI_OK;
+    if (N % 4 != 0 && current_impl() == TAGI_IMPL_TF32X3)
+        return fail(TAGI_ERR_UNSUPPORTED, std::string(__func__) + ": TF32X3 needs N (the row pitch of the deltas) to be a "
+                                                                  "multiple of 4");
     if (N % 4 == 0 && pick_tc(__func__, B, K, Nr, {var_w, mu_a, dmu_z, dvar_z, dmu_w, dvar_w}, &rc)) {
         if (has_bias && linear_bwd_param_tc_fuses_bias(Nr))
             return linear_bwd_param_tc(var_w, mu_a, dmu_z, dvar_z, B, K, Nr, dmu_w, dvar_w, st, nullptr, 1, N, var_b + n0,
@@ -275,6 +280,15 @@ static int check_geom(const tagi_conv2d_geom *g) {
                      (long)g->fo * g->fi * g->k * g->k < lim,
                  "tensor extent exceeds 2^31 elements");
     return TAGI_OK;
+}
+
+size_t tagi_conv2d_workspace_bytes(const tagi_conv2d_geom *g) {
+    if (check_geom(g) != TAGI_OK) return 0;
+    const size_t a = conv_tc_workspace_bytes(*g), b = conv_ffma_workspace_bytes(*g);
+    // BatchNorm statistics of the layer's output share the block: 16 bytes per channel and 4096-element slice
+    const size_t bn = (size_t)g->fo * (((size_t)g->B * g->ho * g->wo + 4095) / 4096) * 16;
+    const size_t m = a > b ? a : b;
+    return m > bn ? m : bn;
 }
 
 int tagi_conv2d_fwd(const tagi_conv2d_geom *g, const float *mu_w, const float *var_w, const float *mu_b,

@@ -90,7 +90,13 @@ int conv2d_bwd_state_ffma(const tagi_conv2d_geom &g, const float *mu_w, const fl
 int conv2d_bwd_param_ffma(const tagi_conv2d_geom &g, const float *var_w, const float *var_b, const float *mu_a,
                           const float *dmu_z, const float *dvar_z, float *dmu_w, float *dvar_w, float *dmu_b,
                           float *dvar_b, cudaStream_t st);
-int conv_scratch(size_t bytes, float **out);  // library-owned, grow-only, per device
+// Library-owned scratch of the current device, grow-only; st = the stream the caller launches on (growth is refused
+// while that stream is being captured). Blocks that were handed out are retired, not freed, when a larger one is needed.
+int conv_scratch(size_t bytes, float **out, cudaStream_t st);
+int reserve_scratch(size_t bytes);
+size_t conv_tc_workspace_bytes(const tagi_conv2d_geom &g);
+size_t conv_ffma_workspace_bytes(const tagi_conv2d_geom &g);
+int release_scratch();
 int conv_bias_delta(const tagi_conv2d_geom &g, const float *var_b, const float *dmu_z, const float *dvar_z,
                     float *dmu_b, float *dvar_b, cudaStream_t st);
 // Conv2d on the tensor-core Linear kernels (tagi_conv_tc.cu)

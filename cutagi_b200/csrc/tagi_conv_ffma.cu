@@ -10,6 +10,7 @@
 //   parameter bwd    fo x (fi*k*k)  x (B*ho*wo)     A = output deltas,    B = gathered activations
 // The columns are the memory-contiguous index of each output tensor.
 #include <mutex>
+#include <vector>
 
 #include "tagi_common.h"
 #include "tagi_ffma.cuh"
@@ -302,13 +303,17 @@ int conv2d_bwd_state_ffma(const tagi_conv2d_geom &cg, const float *mu_w, const f
                 "conv2d state backward launch");
 }
 
-// Scratch of the Conv2d implementations (split-contraction partial sums here, gathered matrices in the tensor-core
-// path): one grow-only buffer per device, owned by the library. Calls that use it are ordered by the stream they
-// run on; calls on different streams of one device that both need scratch must not overlap.
+// Scratch of the Conv2d implementations (split-contraction partial sums here, regrouped weights and gathered matrices
+// in the tensor-core path): one grow-only block per device, owned by the library. Calls that use it are ordered by the
+// stream they run on; calls on different streams of one device that both need scratch must not overlap.
+// A block that has been handed out is never freed while the library may still be used: when a larger one is needed the
+// old block is retired (kept until tagi_release_scratch), because kernels already launched and CUDA graphs already
+// captured may still hold its address.
 namespace {
 struct Scratch {
     float *ptr = nullptr;
     size_t bytes = 0;
+    std::vector<float *> retired;
 };
 Scratch g_scratch[64];
 std::mutex g_scratch_mu;
@@ -321,7 +326,7 @@ int conv_bias_delta(const tagi_conv2d_geom &cg, const float *var_b, const float 
     return done(cudaGetLastError(), "conv_bias_delta_kernel launch");
 }
 
-int conv_scratch(size_t bytes, float **out) {
+int conv_scratch(size_t bytes, float **out, cudaStream_t st) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
@@ -329,20 +334,69 @@ int conv_scratch(size_t bytes, float **out) {
     std::lock_guard<std::mutex> lk(g_scratch_mu);
     Scratch &s = g_scratch[dev];
     if (s.bytes < bytes) {
-        if (s.ptr) {
-            e = cudaDeviceSynchronize();  // earlier calls may still be using the old buffer
-            if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceSynchronize");
-            cudaFree(s.ptr);
-            s.ptr = nullptr;
-            s.bytes = 0;
-        }
+        // no allocation while the caller's stream is being captured: it would break the capture
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(st, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone)
+            return fail(TAGI_ERR_UNSUPPORTED,
+                        "Conv2d scratch of " + std::to_string(bytes) + " bytes is needed while the stream is being captured (" +
+                            std::to_string(s.bytes) + " reserved): call tagi_reserve_scratch before the capture");
         const size_t want = bytes + bytes / 2;
-        e = cudaMalloc(&s.ptr, want);
-        if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(split-K scratch)");
+        float *fresh = nullptr;
+        e = cudaMalloc(&fresh, want);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(Conv2d scratch)");
+        if (s.ptr) s.retired.push_back(s.ptr);
+        s.ptr = fresh;
         s.bytes = want;
     }
     *out = s.ptr;
     return TAGI_OK;
+}
+
+int reserve_scratch(size_t bytes) {
+    float *p = nullptr;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (dev < 0 || dev >= 64) return fail(TAGI_ERR_UNSUPPORTED, "device index out of range");
+    std::lock_guard<std::mutex> lk(g_scratch_mu);
+    Scratch &s = g_scratch[dev];
+    if (s.bytes >= bytes) return TAGI_OK;
+    e = cudaMalloc(&p, bytes);   // exactly what was asked for: the caller has sized it
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(Conv2d scratch)");
+    if (s.ptr) s.retired.push_back(s.ptr);
+    s.ptr = p;
+    s.bytes = bytes;
+    return TAGI_OK;
+}
+
+int release_scratch() {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (dev < 0 || dev >= 64) return fail(TAGI_ERR_UNSUPPORTED, "device index out of range");
+    e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceSynchronize");
+    std::lock_guard<std::mutex> lk(g_scratch_mu);
+    Scratch &s = g_scratch[dev];
+    for (float *p : s.retired) cudaFree(p);
+    s.retired.clear();
+    if (s.ptr) cudaFree(s.ptr);
+    s.ptr = nullptr;
+    s.bytes = 0;
+    return TAGI_OK;
+}
+
+// Scratch of the FFMA parameter pass (partial sums of the split contraction), same slicing rule as below
+size_t conv_ffma_workspace_bytes(const tagi_conv2d_geom &cg) {
+    const Geom g = make_geom(cg);
+    const int M = g.fo, N = g.Kc, Kd = g.B * g.woho;
+    const int tm = M >= 128 && N >= 128 ? 128 : 64;
+    const long tiles = (long)((M + tm - 1) / tm) * ((N + tm - 1) / tm);
+    long splits = (2 * 148 + tiles - 1) / tiles;
+    const long max_splits = (Kd + 255) / 256;
+    if (splits > max_splits) splits = max_splits;
+    if (splits < 1) splits = 1;
+    return (size_t)2 * splits * M * N * sizeof(float);
 }
 
 int conv2d_bwd_param_ffma(const tagi_conv2d_geom &cg, const float *var_w, const float *var_b, const float *mu_a,
@@ -373,7 +427,7 @@ int conv2d_bwd_param_ffma(const tagi_conv2d_geom &cg, const float *var_w, const 
     } else {
         const long slice = (long)M * N;
         float *ws = nullptr;
-        rc = conv_scratch((size_t)2 * splits * slice * sizeof(float), &ws);
+        rc = conv_scratch((size_t)2 * splits * slice * sizeof(float), &ws, st);
         if (rc != TAGI_OK) return rc;
         EpiPartial epi{ws, ws + (long)splits * slice, (long)N, slice, N % 4 == 0};
         // the kernel may use fewer slices than asked for (slice length is rounded up); it reports through the grid,

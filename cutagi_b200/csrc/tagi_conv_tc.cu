@@ -309,6 +309,19 @@ bool conv_tc_profitable(const tagi_conv2d_geom &cg, int pass) {
     return pass == CONV_PASS_STATE && g.stride == 1 ? g.fi >= 16 : g.Kc >= 64;
 }
 
+// Upper bound of the scratch any of the three passes of this geometry asks for on the tensor-core path
+size_t conv_tc_workspace_bytes(const tagi_conv2d_geom &cg) {
+    const G g = geom_of(cg);
+    const size_t rows = (size_t)g.B * g.woho, rows_in = (size_t)g.B * g.wihi, w = (size_t)g.fo * g.Kc;
+    const size_t fwd = 2 * rows * g.Kc + 2 * w;
+    const size_t state = g.stride > 1 ? 2 * rows * g.fo + 2 * rows * g.Kc : 2 * rows_in * g.fo * g.k2 + w;
+    const int slices = linear_bwd_param_tc_slices((int)rows, g.Kc, g.fo);
+    const size_t param = rows * g.Kc + 2 * rows * g.fo + (size_t)2 * (slices > 1 ? slices : 1) * w;
+    size_t m = fwd > state ? fwd : state;
+    m = m > param ? m : param;
+    return m * sizeof(float);
+}
+
 int conv2d_fwd_tc(const tagi_conv2d_geom &cg, const float *mu_w, const float *var_w, const float *mu_b,
                   const float *var_b, const float *mu_a, const float *var_a, float *mu_z, float *var_z,
                   cudaStream_t st, float *relu_jcb) {
@@ -321,7 +334,7 @@ int conv2d_fwd_tc(const tagi_conv2d_geom &cg, const float *mu_w, const float *va
                              relu_jcb);
     }
     float *ws = nullptr;
-    int rc = conv_scratch((size_t)2 * rows * g.Kc * sizeof(float), &ws);
+    int rc = conv_scratch((size_t)2 * rows * g.Kc * sizeof(float), &ws, st);
     if (rc != TAGI_OK) return rc;
     float *x_mu = ws, *x_var = ws + rows * g.Kc;
     if (!launch_gather_tiled<2, false>(mu_a, var_a, g.B, g.fi, g.hi, g.wi, g.ho, g.wo, g.k, g.stride, g.off, x_mu, x_var, st))
@@ -344,7 +357,7 @@ int conv2d_bwd_state_tc(const tagi_conv2d_geom &cg, const float *mu_w, const flo
     int rc;
     if (g.stride > 1) {
         const long rows = (long)g.B * g.woho;
-        if ((rc = conv_scratch(((size_t)2 * rows * g.fo + (size_t)2 * rows * g.Kc) * sizeof(float), &ws)) != TAGI_OK)
+        if ((rc = conv_scratch(((size_t)2 * rows * g.fo + (size_t)2 * rows * g.Kc) * sizeof(float), &ws, st)) != TAGI_OK)
             return rc;
         float *d_mu = ws, *d_var = d_mu + rows * g.fo, *c_mu = d_var + rows * g.fo, *c_var = c_mu + rows * g.Kc;
         dim3 grid((g.woho + 31) / 32, (g.fo + 31) / 32, g.B);
@@ -361,14 +374,14 @@ int conv2d_bwd_state_tc(const tagi_conv2d_geom &cg, const float *mu_w, const flo
     const int kd = g.fo * g.k2;
     if (implicit_ok(g, rows, g.fi)) {
         float *w2i = nullptr;
-        if ((rc = conv_scratch((size_t)g.fo * g.Kc * sizeof(float), &w2i)) != TAGI_OK) return rc;
+        if ((rc = conv_scratch((size_t)g.fo * g.Kc * sizeof(float), &w2i, st)) != TAGI_OK) return rc;
         weight_regroup_kernel<<<grid_for((long)g.fo * g.Kc), 256, 0, st>>>(mu_w, g, w2i);
         if ((rc = ok_or(cudaGetLastError(), "weight_regroup_kernel launch")) != TAGI_OK) return rc;
         // implicit GEMM: row = input pixel, column (co, ky, kx) = delta at output pixel (y + off - ky, x + off - kx)
         ConvGather ig{1, dmu_z, dvar_z, g.fo, g.ho, g.wo, g.wi, g.wihi, g.k, 1, g.off, -1, rows};
         return linear_bwd_state_tc(w2i, jcb, nullptr, nullptr, (int)rows, g.fi, kd, dmu_a, dvar_a, st, g.wihi, &ig);
     }
-    rc = conv_scratch(((size_t)2 * rows * kd + (size_t)g.fo * g.Kc) * sizeof(float), &ws);
+    rc = conv_scratch(((size_t)2 * rows * kd + (size_t)g.fo * g.Kc) * sizeof(float), &ws, st);
     if (rc != TAGI_OK) return rc;
     float *z_mu = ws, *z_var = ws + rows * kd, *w2 = ws + 2 * rows * kd;
     if (!launch_gather_tiled<2, true>(dmu_z, dvar_z, g.B, g.fo, g.ho, g.wo, g.hi, g.wi, g.k, 1, g.off, z_mu, z_var, st))
@@ -389,7 +402,7 @@ int conv2d_bwd_param_tc(const tagi_conv2d_geom &cg, const float *var_w, const fl
     const int slices = linear_bwd_param_tc_slices((int)rows, g.Kc, g.fo);
     const size_t part = slices > 1 ? (size_t)2 * slices * g.fo * g.Kc : 0;
     float *ws = nullptr;
-    int rc = conv_scratch(((size_t)rows * g.Kc + (size_t)2 * rows * g.fo + part) * sizeof(float), &ws);
+    int rc = conv_scratch(((size_t)rows * g.Kc + (size_t)2 * rows * g.fo + part) * sizeof(float), &ws, st);
     if (rc != TAGI_OK) return rc;
     float *x_mu = ws, *d_mu = ws + rows * g.Kc, *d_var = d_mu + rows * g.fo, *split_ws = d_var + rows * g.fo;
     if (!launch_gather_tiled<1, false>(mu_a, nullptr, g.B, g.fi, g.hi, g.wi, g.ho, g.wo, g.k, g.stride, g.off, x_mu, nullptr, st))

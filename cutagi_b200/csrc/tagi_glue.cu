@@ -20,18 +20,19 @@ __device__ __forceinline__ void relu_one(float mz, float vz, float &ma, float &v
         va = vz;
     }
 }
-__global__ void relu_kernel(const float *__restrict__ mu_z, const float *__restrict__ var_z, size_t n,
-                            float *__restrict__ mu_a, float *__restrict__ var_a, float *__restrict__ jcb) {
+// The activation kernels may run in place (mu_a == mu_z, var_a == var_z): no __restrict__, no read-only loads; every
+// thread reads its own elements before it writes them.
+__global__ void relu_kernel(const float *mu_z, const float *var_z, size_t n, float *mu_a, float *var_a, float *jcb) {
     const size_t i = (size_t)blockIdx.x * BLOCK + threadIdx.x;
     if (i >= n) return;
     relu_one(mu_z[i], var_z[i], mu_a[i], var_a[i], jcb[i]);
 }
 // four elements per thread with 16-byte accesses (n a multiple of 4, 16-byte aligned tensors)
-__global__ void relu_vec4_kernel(const float4 *__restrict__ mu_z, const float4 *__restrict__ var_z, size_t n4,
-                                 float4 *__restrict__ mu_a, float4 *__restrict__ var_a, float4 *__restrict__ jcb) {
+__global__ void relu_vec4_kernel(const float4 *mu_z, const float4 *var_z, size_t n4, float4 *mu_a, float4 *var_a,
+                                 float4 *jcb) {
     const size_t i = (size_t)blockIdx.x * BLOCK + threadIdx.x;
     if (i >= n4) return;
-    const float4 m = __ldg(mu_z + i), v = __ldg(var_z + i);
+    const float4 m = mu_z[i], v = var_z[i];
     float4 a, va, j;
     relu_one(m.x, v.x, a.x, va.x, j.x);
     relu_one(m.y, v.y, a.y, va.y, j.y);
@@ -53,8 +54,8 @@ __device__ __forceinline__ void mixture_relu_one(float m, float v, float &ma, fl
     va = fmaxf(0.000001f, -t * t + 2 * t * m - m * sd * pdf + (v - m * m) * cdf);
     j = cdf;
 }
-__global__ void mixture_relu_kernel(const float *__restrict__ mu_z, const float *__restrict__ var_z, size_t n,
-                                    float *__restrict__ mu_a, float *__restrict__ var_a, float *__restrict__ jcb) {
+__global__ void mixture_relu_kernel(const float *mu_z, const float *var_z, size_t n, float *mu_a, float *var_a,
+                                    float *jcb) {
     const size_t i = (size_t)blockIdx.x * BLOCK + threadIdx.x;
     if (i >= n) return;
     float ma, va, j;
@@ -64,8 +65,8 @@ __global__ void mixture_relu_kernel(const float *__restrict__ mu_z, const float 
     jcb[i] = j;
 }
 // four elements per thread with 16-byte accesses (n a multiple of 4, 16-byte aligned tensors)
-__global__ void mixture_relu_vec4_kernel(const float4 *__restrict__ mu_z, const float4 *__restrict__ var_z, size_t n4,
-                                         float4 *__restrict__ mu_a, float4 *__restrict__ var_a, float4 *__restrict__ jcb) {
+__global__ void mixture_relu_vec4_kernel(const float4 *mu_z, const float4 *var_z, size_t n4, float4 *mu_a, float4 *var_a,
+                                         float4 *jcb) {
     const size_t i = (size_t)blockIdx.x * BLOCK + threadIdx.x;
     if (i >= n4) return;
     const float4 m = mu_z[i], v = var_z[i];

@@ -384,7 +384,7 @@ int bn2d_fwd(int B, int C, int wihi, int training, float eps, float momentum, co
     if (training) {
         const int slices = (int)((n + SLICE - 1) / SLICE);
         float *ws = nullptr;
-        if ((rc = conv_scratch((size_t)C * slices * sizeof(float4), &ws)) != TAGI_OK) return rc;
+        if ((rc = conv_scratch((size_t)C * slices * sizeof(float4), &ws, st)) != TAGI_OK) return rc;
         float4 *part = reinterpret_cast<float4 *>(ws);
         if (wihi % 4 == 0 && aligned16(mu_a) && aligned16(var_a))
             bn2d_stats_partial_kernel<4><<<dim3(slices, C), BLOCK, 0, st>>>(mu_a, var_a, C, wihi, n, part);
@@ -413,7 +413,7 @@ int bn2d_bwd(int B, int C, int wihi, int state_update, float eps, const float *m
     const int slices = (int)((n + SLICE - 1) / SLICE);
     float *ws = nullptr;
     int rc;
-    if ((rc = conv_scratch((size_t)C * slices * sizeof(float4), &ws)) != TAGI_OK) return rc;
+    if ((rc = conv_scratch((size_t)C * slices * sizeof(float4), &ws, st)) != TAGI_OK) return rc;
     float4 *part = reinterpret_cast<float4 *>(ws);
     const bool vec = wihi % 4 == 0 && aligned16(mu_a) && aligned16(dmu_o) && aligned16(dvar_o) && (!jcb || aligned16(jcb)) &&
                      (!state_update || (aligned16(dmu) && aligned16(dvar)));

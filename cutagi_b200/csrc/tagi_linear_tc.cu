@@ -5,15 +5,17 @@
 //                                                 lo(x) = x - hi(x)  (exact in FP32)
 // by three kind::tf32 MMAs that accumulate in FP32 in tensor memory. The tensor core reads the
 // upper 19 bits of each 32-bit operand, so the raw FP32 tile that TMA lands in shared memory
-// already is the hi operand; only the lo tiles and the derived tiles (mu^2 + var, mu^2, and their
-// lo parts) are produced, by a group of converter warps, elementwise at the same swizzled
-// shared-memory offsets as the raw tiles. Nothing derived is ever written to HBM.
+// already is the hi operand of the B side; the lo tiles and the derived tiles (mu^2 + var, mu^2, and their
+// lo parts) are produced by a group of converter warps: B-side tiles elementwise at the same swizzled
+// shared-memory offsets as the raw tiles, A-side tiles straight into tensor memory. Nothing derived is ever
+// written to HBM.
 //
-// One CTA computes a 128 x 128 tile of both outputs (mean-like D1, variance-like D2):
-//   warp 0      TMA producer: raw operand tiles, K-slab of 16, multi-stage ring
-//   warp 1      MMA issuer (one thread): 6 or 9 tf32 products per 8-wide k step; owns tensor memory
-//   warps 2-9   converters; they also add finished chunks (tcgen05.ld) to register sums and run the epilogue
-//               (bias / scale -> HBM)
+// Two kernels: one CTA per 128 x bn tile of both outputs ("ts", passes with fewer than 256 output rows) and CTA
+// pairs on 256 x bn tiles ("pair", everything else). Roles of a CTA's warps:
+//   warp 0        TMA producer: raw operand tiles, K-slab of 16, multi-stage ring
+//   warps 1, 10   MMA issuers (one thread each): D1 and D2; warp 1 owns tensor memory
+//   warps 2-9     converters; they also add finished chunks (tcgen05.ld) to register sums and run the epilogue
+//                 (bias / scale -> HBM)
 // Operands whose contraction index is contiguous in memory are staged K-major (64-byte swizzle);
 // the others (mu_w in the state pass, both operands of the parameter pass) are staged MN-major
 // (128-byte swizzle), which kind::tf32 accepts, so no transpose pass exists anywhere.
@@ -21,9 +23,8 @@
 // The tensor core's FP32 accumulation loses a little on every MMA (its error grows with the number of
 // MMAs chained into one accumulator and with the accumulator's magnitude), which over thousands of k
 // steps would exceed the 1e-5 / 1e-4 tolerance. The contraction is therefore cut into chunks of 256:
-// each chunk accumulates from zero in one of two tensor-memory accumulator sets, and while the next
-// chunk runs in the other set the converter warps add the finished chunk to running sums that they
-// keep in registers (plain FP32 adds, one per chunk).
+// each chunk accumulates from zero in tensor memory and the converter warps add the finished chunk to
+// running sums that they keep in registers (plain FP32 adds, one per chunk).
 #include <cuda.h>
 
 #include <mutex>
@@ -43,7 +44,6 @@ constexpr int NCONV_WARPS = 8;
 constexpr uint32_t STAGE_PITCH = 68 * 4, STAGE_VALUE = 32 * STAGE_PITCH, STAGE_WARP = 2 * STAGE_VALUE;
 constexpr size_t STAGE_BYTES = (size_t)NCONV_WARPS * STAGE_WARP;
 __host__ __device__ constexpr size_t at_least_stage(size_t ring) { return ring > STAGE_BYTES ? ring : STAGE_BYTES; }
-constexpr int NTHREADS = 32 * (2 + NCONV_WARPS);       // all-shared-memory kernel: TMA, MMA, converters
 constexpr int NTHREADS2 = 32 * (4 + NCONV_WARPS);      // ts / pair kernels: TMA, two MMA issuers (warps 1, 10), converters,
                                                        // and warp 11, which gathers Conv2d operands (pair kernel only)
 constexpr int GATHER_WARP = 3 + NCONV_WARPS;
@@ -53,15 +53,10 @@ constexpr int CHUNKS = TILE_BYTES / 16;  // 16-byte chunks per tile
 enum { OP_FWD = 0, OP_BWD_STATE = 1, OP_BWD_PARAM = 2 };
 
 template <int OP> struct OpTraits;
-// tiles per stage: forward A0 A1 A0l A1l S Sl | B0 B1 B0l B1l Q Ql ; backward A0 A1 A0l A1l | W Wl Q Ql
-template <> struct OpTraits<OP_FWD> { static constexpr int NTILES = 12, STAGES = 2, A_MN = 0, B_MN = 0, B_BASE = 6, NRAW = 4; };
-template <> struct OpTraits<OP_BWD_STATE> { static constexpr int NTILES = 8, STAGES = 3, A_MN = 0, B_MN = 1, B_BASE = 4, NRAW = 3; };
-template <> struct OpTraits<OP_BWD_PARAM> { static constexpr int NTILES = 8, STAGES = 3, A_MN = 1, B_MN = 1, B_BASE = 4, NRAW = 3; };
-
-template <int OP>
-constexpr size_t tc_smem_bytes() {
-    return (size_t)OpTraits<OP>::STAGES * OpTraits<OP>::NTILES * TILE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
-}
+// which operands of a pass are staged MN-major
+template <> struct OpTraits<OP_FWD> { static constexpr int A_MN = 0, B_MN = 0; };
+template <> struct OpTraits<OP_BWD_STATE> { static constexpr int A_MN = 0, B_MN = 1; };
+template <> struct OpTraits<OP_BWD_PARAM> { static constexpr int A_MN = 1, B_MN = 1; };
 
 struct TcEpilogue {
     float *out1, *out2;
@@ -254,238 +249,16 @@ __device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap *tm, i
         tma_load_2d(dst, tm, k0, row0, bar);
     }
 }
-// descriptor of the 8-wide k step j (0 or 1) of a tile
-template <int MN>
-__device__ __forceinline__ uint64_t tile_desc(uint32_t addr, int j) {
-    return MN ? make_smem_desc(addr + j * 1024, 2048, 512, SWZ_128B_BASE32B)
-              : make_smem_desc(addr + j * 32, 16, 512, SWZ_64B);
-}
-
 // Contraction chunk: CHUNK_STAGES k-slabs (256 k) accumulate in one tensor-memory set before they are
 // added to the register sums. CHUNK_STAGES == 0 (template) means a single chunk: everything stays in set 0.
 constexpr int CHUNK_STAGES = 16;
 
-template <int OP, int CH>
-__global__ void __launch_bounds__(NTHREADS, 1)
-tagi_tc_linear_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
-                      const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
-                      const TcEpilogue epi, const int kdim, const int bn, int *status) {
-    using T = OpTraits<OP>;
-    constexpr int STAGES = T::STAGES, NTILES = T::NTILES;
-    constexpr uint32_t NCOLS = 512;  // two accumulator sets of (D1, D2), 128 columns each
-    // bn = columns per tile (a multiple of 16, at most 128): the MMA's N. Operand tiles are always staged 128 wide.
-    const uint32_t IDESC = make_idesc_tf32(TM, bn, T::A_MN, T::B_MN);
-
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
-    uint8_t *aligned = smem_raw + (smem_base - smem_u32(smem_raw));
-    uint64_t *bars = reinterpret_cast<uint64_t *>(aligned + (size_t)STAGES * NTILES * TILE_BYTES);
-    uint64_t *raw_full = bars, *conv_done = bars + STAGES, *empty = bars + 2 * STAGES;
-    uint64_t *acc_full = bars + 3 * STAGES, *acc_empty = bars + 3 * STAGES + 2;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * STAGES + 4);
-    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row0 = blockIdx.y * TM, col0 = blockIdx.x * bn;
-    const int nk = (kdim + BK - 1) / BK;
-    const int chunk_len = CH > 0 ? CH : nk;  // stages per chunk
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; s++) {
-            mbar_init(raw_full + s, 1);
-            mbar_init(conv_done + s, NCONV_WARPS);
-            mbar_init(empty + s, 1);
-        }
-        for (int s = 0; s < 2; s++) {
-            mbar_init(acc_full + s, 1);
-            mbar_init(acc_empty + s, NCONV_WARPS);
-        }
-        *abort_flag = 0;
-        mbar_init_fence();
-        prefetch_tmap(&tmA0);
-        prefetch_tmap(&tmA1);
-        prefetch_tmap(&tmB0);
-        if (OP == OP_FWD) prefetch_tmap(&tmB1);
-    }
-    if (warp == 1) tmem_alloc(tmem_slot, NCOLS);
-    tc_fence_before_sync();
-    __syncthreads();
-    tc_fence_after_sync();
-    const uint32_t tmem = *tmem_slot;
-
-    if (warp == 0) {
-        // ------------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            for (int it = 0; it < nk; it++) {
-                const int s = it % STAGES;
-                if (!mbar_wait(empty + s, ((it / STAGES) & 1) ^ 1, abort_flag, status, ST_TIMEOUT_EMPTY)) break;
-                mbar_arrive_expect_tx(raw_full + s, T::NRAW * TILE_BYTES);
-                const uint32_t st = smem_base + s * NTILES * TILE_BYTES;
-                const int k0 = it * BK;
-                load_tile<T::A_MN>(st + 0 * TILE_BYTES, &tmA0, row0, k0, raw_full + s);
-                load_tile<T::A_MN>(st + 1 * TILE_BYTES, &tmA1, row0, k0, raw_full + s);
-                load_tile<T::B_MN>(st + T::B_BASE * TILE_BYTES, &tmB0, col0, k0, raw_full + s);
-                if (OP == OP_FWD) load_tile<T::B_MN>(st + (T::B_BASE + 1) * TILE_BYTES, &tmB1, col0, k0, raw_full + s);
-            }
-        }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            uint32_t f1 = 0, f2 = 0;  // accumulate flags of the current chunk's D1, D2
-            uint32_t d1 = tmem, d2 = tmem + 128;
-            bool ok = true;
-            for (int it = 0; it < nk && ok; it++) {
-                const int s = it % STAGES;
-                if (it % chunk_len == 0) {
-                    // a new chunk starts from zero in the other accumulator set, once the converters have drained it
-                    const int c = it / chunk_len, set = c & 1;
-                    ok = mbar_wait(acc_empty + set, ((c >> 1) & 1) ^ 1, abort_flag, status, ST_TIMEOUT_ACC);
-                    if (!ok) break;
-                    d1 = tmem + set * 256, d2 = d1 + 128;
-                    f1 = f2 = 0;
-                }
-                ok = mbar_wait(conv_done + s, (it / STAGES) & 1, abort_flag, status, ST_TIMEOUT_CONV);
-                if (!ok) break;
-                tc_fence_after_sync();
-                const uint32_t st = smem_base + s * NTILES * TILE_BYTES;
-#define TILE(i) (st + (i) * TILE_BYTES)
-#define DA(i) tile_desc<T::A_MN>(TILE(i), j)
-#define DB(i) tile_desc<T::B_MN>(TILE(i), j)
-#pragma unroll
-                for (int j = 0; j < BK / 8; j++) {
-                    if (OP == OP_FWD) {
-                        // D1 = mu_a . mu_w ; D2 = (mu_a^2 + var_a) . var_w + var_a . mu_w^2
-                        mma_tf32_ss(d1, DA(0), DB(6), IDESC, f1);
-                        f1 = 1;
-                        mma_tf32_ss(d1, DA(0), DB(8), IDESC, 1);
-                        mma_tf32_ss(d1, DA(2), DB(6), IDESC, 1);
-                        mma_tf32_ss(d2, DA(4), DB(7), IDESC, f2);
-                        f2 = 1;
-                        mma_tf32_ss(d2, DA(1), DB(10), IDESC, 1);
-                        mma_tf32_ss(d2, DA(4), DB(9), IDESC, 1);
-                        mma_tf32_ss(d2, DA(5), DB(7), IDESC, 1);
-                        mma_tf32_ss(d2, DA(1), DB(11), IDESC, 1);
-                        mma_tf32_ss(d2, DA(3), DB(10), IDESC, 1);
-                    } else {
-                        // D1 = a0 . w ; D2 = a1 . w^2
-                        mma_tf32_ss(d1, DA(0), DB(4), IDESC, f1);
-                        f1 = 1;
-                        mma_tf32_ss(d1, DA(0), DB(5), IDESC, 1);
-                        mma_tf32_ss(d1, DA(2), DB(4), IDESC, 1);
-                        mma_tf32_ss(d2, DA(1), DB(6), IDESC, f2);
-                        f2 = 1;
-                        mma_tf32_ss(d2, DA(1), DB(7), IDESC, 1);
-                        mma_tf32_ss(d2, DA(3), DB(6), IDESC, 1);
-                    }
-                }
-#undef TILE
-#undef DA
-#undef DB
-                mma_commit(empty + s);  // the stage may be refilled once these MMAs have read it
-                if (it % chunk_len == chunk_len - 1 || it == nk - 1) mma_commit(acc_full + ((it / chunk_len) & 1));
-            }
-        }
-    } else {
-        // ------------------------------------------------------------------ converters + accumulation + epilogue
-        const int ct = threadIdx.x - 64;
-        const int q = warp & 3;         // tensor-memory lane quadrant this warp may read
-        const int h = (warp - 2) >> 2;  // which half of the 128 columns
-        const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16) + h * 64;
-        float sum1[64], sum2[64];
-#pragma unroll
-        for (int i = 0; i < 64; i++) sum1[i] = sum2[i] = 0.f;
-
-        // adds chunk c (columns h*64 .. +63 of D1 and D2 of its set) to the register sums and frees the set
-        auto drain = [&](int c) -> bool {
-            const int set = c & 1;
-            if (!mbar_wait(acc_full + set, (c >> 1) & 1, abort_flag, status, ST_TIMEOUT_ACC)) return false;
-            tc_fence_after_sync();
-#pragma unroll
-            for (int blk = 0; blk < 2; blk++) {
-                float v[32];
-                tmem_ld_32x32(lane_base + set * 256 + blk * 32, v);
-#pragma unroll
-                for (int i = 0; i < 32; i++) sum1[blk * 32 + i] += v[i];
-                tmem_ld_32x32(lane_base + set * 256 + 128 + blk * 32, v);
-#pragma unroll
-                for (int i = 0; i < 32; i++) sum2[blk * 32 + i] += v[i];
-            }
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(acc_empty + set);
-            return true;
-        };
-
-        bool ok = true;
-        int pending = -1;  // chunk whose MMAs have been issued but which has not been added yet
-        for (int it = 0; it < nk && ok; it++) {
-            const int s = it % STAGES;
-            ok = mbar_wait(raw_full + s, (it / STAGES) & 1, abort_flag, status, ST_TIMEOUT_RAW);
-            if (!ok) break;
-            const uint32_t st = smem_base + s * NTILES * TILE_BYTES;
-#pragma unroll
-            for (int c = ct; c < CHUNKS; c += 32 * NCONV_WARPS) {
-                const uint32_t o = c * 16;
-                const float4 a0 = lds128(st + 0 * TILE_BYTES + o), a1 = lds128(st + 1 * TILE_BYTES + o);
-                sts128(st + 2 * TILE_BYTES + o, lo_part(a0));
-                sts128(st + 3 * TILE_BYTES + o, lo_part(a1));
-                if (OP == OP_FWD) {
-                    const float4 sq = make_float4(fmaf(a0.x, a0.x, a1.x), fmaf(a0.y, a0.y, a1.y),
-                                                  fmaf(a0.z, a0.z, a1.z), fmaf(a0.w, a0.w, a1.w));
-                    sts128(st + 4 * TILE_BYTES + o, sq);
-                    sts128(st + 5 * TILE_BYTES + o, lo_part(sq));
-                    const float4 b0 = lds128(st + 6 * TILE_BYTES + o), b1 = lds128(st + 7 * TILE_BYTES + o);
-                    const float4 qq = make_float4(b0.x * b0.x, b0.y * b0.y, b0.z * b0.z, b0.w * b0.w);
-                    sts128(st + 8 * TILE_BYTES + o, lo_part(b0));
-                    sts128(st + 9 * TILE_BYTES + o, lo_part(b1));
-                    sts128(st + 10 * TILE_BYTES + o, qq);
-                    sts128(st + 11 * TILE_BYTES + o, lo_part(qq));
-                } else {
-                    const float4 w = lds128(st + 4 * TILE_BYTES + o);
-                    const float4 qq = make_float4(w.x * w.x, w.y * w.y, w.z * w.z, w.w * w.w);
-                    sts128(st + 5 * TILE_BYTES + o, lo_part(w));
-                    sts128(st + 6 * TILE_BYTES + o, qq);
-                    sts128(st + 7 * TILE_BYTES + o, lo_part(qq));
-                }
-            }
-            fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core's async proxy
-            __syncwarp();
-            if (lane == 0) mbar_arrive(conv_done + s);
-            // The previous chunk is added one stage late, after the first stage of the next chunk has been handed
-            // to the MMA warp, so that the tensor core keeps running while the sums are updated.
-            if (pending >= 0) {
-                ok = drain(pending);
-                pending = -1;
-            }
-            if (it % chunk_len == chunk_len - 1 || it == nk - 1) pending = it / chunk_len;
-        }
-        if (ok && pending >= 0) ok = drain(pending);
-
-        if (ok) {
-            const int row = row0 + q * 32 + lane;
-            store_tile<OP>(epi, row, col0 + h * 64, bn - h * 64, sum1, sum2);
-        }
-    }
-    __syncwarp();
-    tc_fence_before_sync();
-    __syncthreads();
-    if (warp == 1) {
-        if (*abort_flag) {
-            // give copies and MMAs that are still in flight time to land before the memory is released
-            const long long t0 = clock64();
-            while (clock64() - t0 < 4000000LL) {
-            }
-        }
-        tmem_dealloc(tmem, NCOLS);
-    }
-}
-
 // =====================================================================================================
-// Variant "ts": the A-side operand tiles live in tensor memory instead of shared memory.
+// Kernel "ts": one CTA per tile, the A-side operand tiles live in tensor memory instead of shared memory.
 //
-// The all-shared-memory kernel above is bound by shared-memory bandwidth: per k-slab the tensor core reads
-// 18 x 8 KiB of operands while the converters read 32 KiB and write 64 KiB. Here the converters write the six
-// (forward) or four (backward) A-side tiles straight into tensor memory with tcgen05.st (lane = row, one tf32
+// With every operand tile in shared memory the kernel is bound by shared-memory bandwidth (measured: per k-slab the
+// tensor core reads 18 x 8 KiB of operands while the converters read 32 KiB and write 64 KiB). Here the converters write
+// the six (forward) or four (backward) A-side tiles straight into tensor memory with tcgen05.st (lane = row, one tf32
 // per column) and the MMAs take A from there, which halves the tensor core's shared-memory reads and removes
 // the A-side converter writes. Raw tiles and derived B tiles use separate rings so that TMA can run four
 // slabs ahead. Tensor memory: columns [0,256) = D1, D2 (one accumulator set; the MMA warp pauses while a
@@ -756,7 +529,7 @@ tagi_tc_linear_ts_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_
 }
 
 // =====================================================================================================
-// Variant "pair": as "ts", on CTA pairs (cta_group::2).
+// Kernel "pair": as "ts", on CTA pairs (cta_group::2).
 //
 // The ts kernel still asks more of the shared-memory pipe per k-slab (tensor-core reads of B, converter traffic, TMA
 // writes: about 1300 cycles' worth) than the MMAs take (about 1000 cycles), so it runs at the speed of shared memory.
@@ -1208,9 +981,7 @@ int *status_word() {
     return ptr[dev];
 }
 
-int g_deep = 0;     // deeper derived rings where tensor memory allows (diagnostic switch; measured: no gain)
-int g_variant = 3;  // 3: CTA pairs (default; passes with < 256 output rows use 1); 1: one CTA, A-side tiles in tensor
-                    // memory ("ts"); 0: every operand tile in shared memory ("ss")
+int g_variant = 3;  // 3: CTA pairs (default; passes with < 256 output rows use 1); 1: one CTA per tile everywhere
 int g_pair_bn = 0;  // forces the pair kernel's tile width (diagnostic); 0 = chosen per launch
 int g_sms = 148;    // SMs the tile planning counts on (tagi_tc_set_sm_budget)
 int g_chunked = 1;  // 1: contraction accumulated in chunks of 256 (default); 0: one accumulation chain (diagnostic)
@@ -1220,7 +991,6 @@ int launch(const CUtensorMap &a0, const CUtensorMap &a1, const CUtensorMap &b0, 
            const TcEpilogue &epi, int kdim, cudaStream_t st) {
     int *status = status_word();
     if (!status) return fail(TAGI_ERR_CUDA, "cannot allocate the tensor-core status word");
-    constexpr size_t smem = tc_smem_bytes<OP>();
     // Columns per tile: the width (a multiple of 16 up to 128) that minimises waves-of-148-CTAs x width, i.e. the
     // tensor-core time of the slowest SM; e.g. 4096 columns x 8 row tiles run as 296 tiles of 112 (two full waves)
     // rather than 256 tiles of 128 (two waves, the second 73 % full).
@@ -1235,42 +1005,17 @@ int launch(const CUtensorMap &a0, const CUtensorMap &a1, const CUtensorMap &b0, 
     const unsigned slices = epi.slabs_per_slice > 0 ? (unsigned)(((kdim + BK - 1) / BK + epi.slabs_per_slice - 1) / epi.slabs_per_slice) : 1u;
     dim3 grid((epi.cols + bn - 1) / bn, (unsigned)row_tiles, slices);
     cudaError_t e;
-    if (g_variant == 1 || g_variant == 3) {
-        // ring depths: the backward passes have room for four derived slots; the forward pass for three when the
-        // tile is at most 112 columns wide (accumulators then take 2 x 112 tensor-memory columns), else two
-#define TAGI_TS_LAUNCH(CHV, RSV, DSV)                                                                          \
+    // ring depths: four raw slots, two derived slots (what the forward pass's six A tiles per slot leave of tensor memory)
+#define TAGI_TS_LAUNCH(CHV)                                                                                      \
     do {                                                                                                         \
-        auto k = tagi_tc_linear_ts_kernel<OP, CHV, RSV, DSV>;                                                    \
-        constexpr size_t sm = ts_smem_bytes<OP, RSV, DSV>();                                                     \
+        auto k = tagi_tc_linear_ts_kernel<OP, CHV, 4, 2>;                                                        \
+        constexpr size_t sm = ts_smem_bytes<OP, 4, 2>();                                                         \
         e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);                       \
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");                                       \
-        k<<<grid, NTHREADS2, sm, st>>>(a0, a1, b0, b1, epi, kdim, bn, status);                            \
+        k<<<grid, NTHREADS2, sm, st>>>(a0, a1, b0, b1, epi, kdim, bn, status);                                   \
     } while (0)
-        if (OP == OP_FWD) {
-            if (bn <= 112 && g_deep) {
-                if (g_chunked) TAGI_TS_LAUNCH(CHUNK_STAGES, 3, 3); else TAGI_TS_LAUNCH(0, 3, 3);
-            } else {
-                if (g_chunked) TAGI_TS_LAUNCH(CHUNK_STAGES, 4, 2); else TAGI_TS_LAUNCH(0, 4, 2);
-            }
-        } else {
-            if (g_deep) {
-                if (g_chunked) TAGI_TS_LAUNCH(CHUNK_STAGES, 4, 4); else TAGI_TS_LAUNCH(0, 4, 4);
-            } else {
-                if (g_chunked) TAGI_TS_LAUNCH(CHUNK_STAGES, 4, 2); else TAGI_TS_LAUNCH(0, 4, 2);
-            }
-        }
+    if (g_chunked) TAGI_TS_LAUNCH(CHUNK_STAGES); else TAGI_TS_LAUNCH(0);
 #undef TAGI_TS_LAUNCH
-    } else if (g_chunked) {
-        auto k = tagi_tc_linear_kernel<OP, CHUNK_STAGES>;
-        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");
-        k<<<grid, NTHREADS, smem, st>>>(a0, a1, b0, b1, epi, kdim, bn, status);
-    } else {
-        auto k = tagi_tc_linear_kernel<OP, 0>;
-        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");
-        k<<<grid, NTHREADS, smem, st>>>(a0, a1, b0, b1, epi, kdim, bn, status);
-    }
     e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "tensor-core Linear kernel launch");
     return TAGI_OK;
@@ -1357,16 +1102,15 @@ bool linear_tc_supported(int B, int K, int N, std::initializer_list<const void *
 bool linear_tc_profitable(int B, int K, int N) { return B >= 128 && K >= 128 && N >= 128; }
 
 int linear_tc_set_variant(int v) {
-    if (v < 0 || (v > 3 && v < 64) || v > 128 || (v >= 64 && v % 16))
-        return fail(TAGI_ERR_INVALID_ARGUMENT, "variant must be 0 (ss), 1 (ts), 2 (ts, deeper rings) or 3 (CTA pairs)");
-    if (v >= 64) {  // 64, 80, ..., 128: CTA pairs with this tile width (diagnostic)
+    if (!(v == 1 || v == 3 || (v >= 64 && v <= 128 && v % 16 == 0)))
+        return fail(TAGI_ERR_INVALID_ARGUMENT, "variant must be 3 (CTA pairs), 1 (one CTA per tile) or a pair tile width "
+                                               "64, 80, 96, 112, 128");
+    if (v >= 64) {  // CTA pairs with this tile width (diagnostic)
         g_pair_bn = v;
         v = 3;
     } else {
         g_pair_bn = 0;
     }
-    g_deep = v == 2;
-    if (v == 2) v = 1;
     g_variant = v;
     return TAGI_OK;
 }

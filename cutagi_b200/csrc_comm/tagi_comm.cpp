@@ -51,6 +51,7 @@ struct Comm {
     ncclComm_t nccl = nullptr;
     cudaStream_t stream = nullptr;
     cudaEvent_t ev = nullptr;  // compute -> comm ordering
+    float *token = nullptr;    // one float for tagi_comm_barrier
     int rank = 0, world = 1, device = 0;
     bool finalized = false;
     std::vector<Tensor> tensors;
@@ -58,6 +59,20 @@ struct Comm {
     std::vector<char> ready;   // per tensor, this step
 };
 Comm *g = nullptr;
+int g_max_ctas = 0;  // 0: NCCL's default; else the upper bound on the CTAs one NCCL kernel may use (tagi_comm_set_max_ctas)
+
+// What travels through the rendezvous file of tagi_comm_init_file: enough to tell this job's id from a file that an
+// earlier job left at the same path.
+struct RendezvousBlob {
+    char magic[8];
+    int world;
+    int pid;
+    long long unix_ms;  // when rank 0 wrote it
+    unsigned char id[TAGI_COMM_ID_BYTES];
+};
+long long now_unix_ms() {
+    return std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::system_clock::now().time_since_epoch()).count();
+}
 
 int need_comm() { return g ? TAGI_OK : fail(TAGI_ERR_COMM, "communicator not initialised"); }
 
@@ -151,7 +166,15 @@ int tagi_comm_init(const void *id, int rank, int world_size, int device) {
     c->rank = rank, c->world = world_size, c->device = device;
     ncclUniqueId u;
     std::memcpy(&u, id, sizeof(u));
-    ncclResult_t r = ncclCommInitRank(&c->nccl, world_size, u, rank);
+    ncclResult_t r;
+    if (g_max_ctas > 0) {
+        // bound the SMs NCCL's kernels take from the compute kernels they overlap
+        ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
+        cfg.maxCTAs = g_max_ctas;
+        r = ncclCommInitRankConfig(&c->nccl, world_size, u, rank, &cfg);
+    } else {
+        r = ncclCommInitRank(&c->nccl, world_size, u, rank);
+    }
     if (r != ncclSuccess) {
         delete c;
         return fail(TAGI_ERR_COMM, std::string("ncclCommInitRank: ") + ncclGetErrorString(r));
@@ -167,16 +190,60 @@ int tagi_comm_init(const void *id, int rank, int world_size, int device) {
     return TAGI_OK;
 }
 
+int tagi_rendezvous_publish_id(const char *path, const void *id, int world_size) {
+    if (!path || !id) return fail(TAGI_ERR_INVALID_ARGUMENT, "rendezvous: null path or id");
+    RendezvousBlob blob;
+    std::memset(&blob, 0, sizeof(blob));
+    std::memcpy(blob.magic, "TAGIRDV1", 8);
+    blob.world = world_size, blob.pid = (int)getpid(), blob.unix_ms = now_unix_ms();
+    std::memcpy(blob.id, id, TAGI_COMM_ID_BYTES);
+    ::unlink(path);  // whatever an earlier job left there
+    return tagi_rendezvous_publish(path, &blob, sizeof(blob));
+}
+
+int tagi_rendezvous_fetch_id(const char *path, void *id, int world_size, int timeout_ms) {
+    if (!path || !id) return fail(TAGI_ERR_INVALID_ARGUMENT, "rendezvous: null path or id");
+    // A file that an earlier job left at this path is told apart by its header: wrong magic or world size, or written
+    // more than timeout_ms before this rank started waiting. Such a file is skipped and the wait goes on until rank 0
+    // replaces it or the deadline passes.
+    RendezvousBlob blob;
+    const long long started = now_unix_ms();
+    while (true) {
+        const long long left = (long long)timeout_ms - (now_unix_ms() - started);
+        if (left <= 0)
+            return fail(TAGI_ERR_COMM, std::string("rendezvous: no id of this job at ") + path + " within " +
+                                           std::to_string(timeout_ms) + " ms (did rank 0 start?)");
+        int rc = tagi_rendezvous_fetch(path, &blob, sizeof(blob), (int)left);
+        if (rc != TAGI_OK) return rc;
+        if (!std::memcmp(blob.magic, "TAGIRDV1", 8) && blob.world == world_size &&
+            blob.unix_ms >= started - (long long)timeout_ms)
+            break;
+        std::this_thread::sleep_for(std::chrono::milliseconds(20));
+    }
+    std::memcpy(id, blob.id, TAGI_COMM_ID_BYTES);
+    return TAGI_OK;
+}
+
 int tagi_comm_init_file(const char *path, int rank, int world_size, int device, int timeout_ms) {
     unsigned char id[TAGI_COMM_ID_BYTES];
     int rc;
     if (rank == 0) {
         if ((rc = tagi_comm_create_id(id)) != TAGI_OK) return rc;
-        if ((rc = tagi_rendezvous_publish(path, id, sizeof(id))) != TAGI_OK) return rc;
+        if ((rc = tagi_rendezvous_publish_id(path, id, world_size)) != TAGI_OK) return rc;
     } else {
-        if ((rc = tagi_rendezvous_fetch(path, id, sizeof(id), timeout_ms)) != TAGI_OK) return rc;
+        if ((rc = tagi_rendezvous_fetch_id(path, id, world_size, timeout_ms)) != TAGI_OK) return rc;
     }
-    return tagi_comm_init(id, rank, world_size, device);
+    rc = tagi_comm_init(id, rank, world_size, device);
+    // ncclCommInitRank returns once every rank has joined: nobody needs the file any more
+    if (rc == TAGI_OK && rank == 0) ::unlink(path);
+    return rc;
+}
+
+int tagi_comm_set_max_ctas(int max_ctas) {
+    if (max_ctas < 0 || max_ctas > 64) return fail(TAGI_ERR_INVALID_ARGUMENT, "max_ctas must be 0 (NCCL default) .. 64");
+    if (g) return fail(TAGI_ERR_COMM, "set_max_ctas must be called before the communicator is created");
+    g_max_ctas = max_ctas;
+    return TAGI_OK;
 }
 
 int tagi_comm_rank(void) { return g ? g->rank : 0; }
@@ -293,9 +360,20 @@ int tagi_comm_check(void) {
     return TAGI_OK;
 }
 
+int tagi_comm_sync_stream(void) {
+    int rc = need_comm();
+    if (rc != TAGI_OK) return rc;
+    CU(cudaStreamSynchronize(g->stream));
+    return TAGI_OK;
+}
+
 int tagi_comm_barrier(void) {
     int rc = need_comm();
     if (rc != TAGI_OK) return rc;
+    // an allreduce of one float that every rank must enter, then a host wait for it: no rank returns before all arrived
+    if (!g->token) CU(cudaMalloc(&g->token, sizeof(float)));
+    CU(cudaMemsetAsync(g->token, 0, sizeof(float), g->stream));
+    NC(ncclAllReduce(g->token, g->token, 1, ncclFloat32, ncclSum, g->nccl, g->stream));
     CU(cudaStreamSynchronize(g->stream));
     return TAGI_OK;
 }
@@ -306,6 +384,7 @@ int tagi_comm_destroy(void) {
     for (auto &b : g->buckets)
         if (b.done) cudaEventDestroy(b.done);
     if (g->ev) cudaEventDestroy(g->ev);
+    if (g->token) cudaFree(g->token);
     if (g->stream) cudaStreamDestroy(g->stream);
     if (g->nccl) ncclCommDestroy(g->nccl);
     delete g;

@@ -56,10 +56,9 @@ int tagi_tc_status(int *status, int reset);
  * 1e-5 / 1e-4 tolerance. on == 0: one accumulation chain over the whole contraction (less accurate; for measurement). */
 int tagi_tc_set_chunked(int on);
 /* Diagnostic switch of the TF32X3 kernels. 3 (default): CTA pairs (tcgen05 cta_group::2, 256-row tiles, A-side operand
- * tiles in tensor memory, each CTA stages half of the B rows; passes with fewer than 256 output rows use variant 1);
- * 1: one CTA per 128-row tile, A-side tiles in tensor memory; 2: as 1 with deeper rings of derived tiles; 0: every
- * operand tile in shared memory (the simplest kernel, bound by shared-memory bandwidth); 64, 80, 96, 112 or 128: as 3
- * with that tile width. Same results in all of them. */
+ * tiles in tensor memory, each CTA stages half of the B rows; passes with fewer than 256 output rows use the one-CTA
+ * kernel); 1: one CTA per 128-row tile for every pass; 64, 80, 96, 112 or 128: as 3 with that tile width. Same results
+ * in all of them. Process-wide, not thread-safe: set it before the first call, not between concurrent calls. */
 int tagi_tc_set_variant(int v);
 /* How many SMs the TF32X3 kernels plan their tile widths for: 0 (default) = all 148. A caller that runs another kernel
  * next to them (the data-parallel exchange's NCCL kernels on their own stream hold some SMs for the length of a pass)
@@ -67,6 +66,24 @@ int tagi_tc_set_variant(int v);
  * 148 tiles would need three waves of 70 pairs where 128 wider tiles need two. Results do not depend on it. No
  * counterpart in the reference. */
 int tagi_tc_set_sm_budget(int sms);
+
+/* Library-owned scratch memory. The Conv2d entry points (regrouped weights, partial sums of a split contraction, the
+ * operand matrices of the layers that still gather through memory) and tagi_bn2d_* (per-slice statistics) keep their
+ * temporaries in one block per device that grows on demand with cudaMalloc. A block that was handed out is never freed
+ * behind the caller's back: when a larger one is needed the old block is kept until tagi_release_scratch, so kernels in
+ * flight and CUDA graphs captured earlier stay valid. Growth is refused (TAGI_ERR_UNSUPPORTED) while the call's stream
+ * is being captured. To keep every allocation out of the training loop, size the block up front:
+ *   tagi_conv2d_workspace_bytes(g)  bytes the three Conv2d passes of geometry g can ask for (host, no CUDA call);
+ *   tagi_reserve_scratch(bytes)     make the current device's block at least that large (allocates; call at set-up);
+ *   tagi_release_scratch()          synchronise the current device and free its block and every retired one.
+ * Rules: calls that use scratch on one device must be ordered on the GPU (one stream, or events between streams), and
+ * only one host thread at a time may issue such calls for a device: the block's contents are not protected. The
+ * reference gives its launchers caller-owned temp_states.tmp_1 / tmp_2 for the same purpose
+ * (src/conv2d_layer_cuda.cu:90-227); no counterpart for the three calls themselves. */
+struct tagi_conv2d_geom;
+size_t tagi_conv2d_workspace_bytes(const struct tagi_conv2d_geom *g);
+int tagi_reserve_scratch(size_t bytes);
+int tagi_release_scratch(void);
 
 const char *tagi_last_error_string(void);
 /* Library version as major*10000 + minor*100 + patch. */
@@ -152,7 +169,8 @@ int tagi_conv2d_bwd_param(const tagi_conv2d_geom *g, const float *var_w, const f
  * hot path; they are here so that whole steps can run on the device through this library alone. */
 
 /* ReLU moments: mu_a = max(mu_z, 0); where that is 0: jcb = 0, var_a = 0, else jcb = 1, var_a = var_z.
- * CPU definition relu_mean_var (src/activation.cpp:7-29); replaces relu_mean_var_cuda (src/activation_cuda.cu:8-24). */
+ * CPU definition relu_mean_var (src/activation.cpp:7-29); replaces relu_mean_var_cuda (src/activation_cuda.cu:8-24).
+ * This call and tagi_mixture_relu_fwd may run in place: mu_a may be mu_z and var_a may be var_z (jcb must be distinct). */
 int tagi_relu_fwd(const float *mu_z, const float *var_z, size_t n, float *mu_a, float *var_a, float *jcb, void *stream);
 
 /* tagi_linear_fwd / tagi_conv2d_fwd followed by tagi_relu_fwd on their outputs, as one call: mu_a_out, var_a_out and

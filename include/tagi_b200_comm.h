@@ -33,6 +33,13 @@ const char *tagi_comm_last_error_string(void);
 int tagi_rendezvous_publish(const char *path, const void *blob, size_t bytes);
 int tagi_rendezvous_fetch(const char *path, void *blob, size_t bytes, int timeout_ms);
 
+/* The same for the communicator id, with a header that tells this job's file from one an earlier job left at the path:
+ * publish removes whatever lies at `path` first and records the world size and the time of writing; fetch skips a file
+ * with another world size or one written more than timeout_ms before the fetch started, and keeps polling until the
+ * deadline (TAGI_ERR_COMM then). `id` is TAGI_COMM_ID_BYTES long. */
+int tagi_rendezvous_publish_id(const char *path, const void *id, int world_size);
+int tagi_rendezvous_fetch_id(const char *path, void *id, int world_size, int timeout_ms);
+
 /* Bucket plan: tensors i = 0..n-1 of counts[i] floats, in registration order, are packed greedily into buckets of at
  * most bucket_bytes (a tensor larger than the budget gets a bucket of its own); bucket_of[i] receives the bucket
  * index. Returns the number of buckets, or a negative status. */
@@ -44,8 +51,13 @@ int tagi_comm_plan_buckets(const size_t *counts, int n, size_t bucket_bytes, int
 int tagi_comm_create_id(void *id);
 /* All ranks: join. `device` is made current. Replaces NCCLCommunicator's constructor (src/ddp.cpp:27-46). */
 int tagi_comm_init(const void *id, int rank, int world_size, int device);
-/* Convenience: create/publish or fetch the id through `path`, then join. */
+/* Convenience: create the id and tagi_rendezvous_publish_id it (rank 0) or tagi_rendezvous_fetch_id it (others), then
+ * join. Rank 0 removes the file again once every rank has joined. */
 int tagi_comm_init_file(const char *path, int rank, int world_size, int device, int timeout_ms);
+/* Before the communicator is created: upper bound on the CTAs (SMs) one NCCL kernel may use (ncclConfig_t::maxCTAs);
+ * 0 = NCCL's default. The exchange runs beside the backward pass's kernels, and every SM NCCL holds is one the
+ * tensor-core kernels' tile plan cannot count on (tagi_tc_set_sm_budget). No counterpart in the reference. */
+int tagi_comm_set_max_ctas(int max_ctas);
 int tagi_comm_rank(void);
 int tagi_comm_world_size(void);
 
@@ -76,7 +88,10 @@ int tagi_comm_broadcast(float *ptr, size_t count, int root, void *compute_stream
 /* Polls ncclCommGetAsyncError and the CUDA error state (check_cuda_nccl_async, include/cuda_error_checking.cuh:47-74):
  * TAGI_OK or TAGI_ERR_COMM with a message; never exits the process. */
 int tagi_comm_check(void);
-/* Stream-synchronise the communication stream (host blocks): Communicator::barrier without the MPI part. */
+/* Host waits until everything launched on the communication stream has finished (this rank only). */
+int tagi_comm_sync_stream(void);
+/* Barrier over the ranks: a one-float allreduce that every rank must enter, then tagi_comm_sync_stream. Replaces
+ * Communicator::barrier (src/ddp.cpp:59-62: stream synchronise + MPI_Barrier). */
 int tagi_comm_barrier(void);
 int tagi_comm_destroy(void);
 

@@ -16,7 +16,7 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, os.path.join(ROOT, "oracle", "_ref"))
-sys.path.insert(0, "/root/reference")
+sys.path.insert(0, os.environ.get("CUTAGI_SRC", "/root/reference"))   # the cuTAGI source tree (its pytagi package)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 from oracle_train import cfg0_problem  # noqa: E402

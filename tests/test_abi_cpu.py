@@ -37,7 +37,7 @@ def test_library_exports_every_declared_symbol(cdll):
 
 def test_python_binding_covers_every_symbol():
     from cutagi_b200 import capi
-    bound = set(capi._SIGNATURES) | {"tagi_last_error_string"}
+    bound = set(capi._SIGNATURES) | {"tagi_last_error_string", "tagi_conv2d_workspace_bytes"}
     assert set(declared_symbols()) <= bound
 
 
@@ -48,6 +48,12 @@ def test_host_only_entry_points(cdll):
     with pytest.raises(TagiError) as e:
         conv_out_size(3, 2, 8, 8, 0, 0)
     assert e.value.code == 1
+    # host-only sizing of the Conv2d scratch: positive for a valid geometry, 0 for an inconsistent one
+    from cutagi_b200.capi import ConvGeom as CG
+    good = CG(64, 64, 56, 56, 64, 56, 56, 3, 1, 1, 1, 0)
+    assert lib.tagi_conv2d_workspace_bytes(C.byref(good)) > 0
+    bad = CG(1, 1, 8, 8, 1, 5, 5, 3, 1, 0, 0, 0)
+    assert lib.tagi_conv2d_workspace_bytes(C.byref(bad)) == 0
     lib.tagi_set_impl(1)
     assert lib.tagi_get_impl() == 1
     lib.tagi_set_impl(0)

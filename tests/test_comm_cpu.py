@@ -55,6 +55,28 @@ def test_rendezvous_roundtrip_and_missing_publisher(tmp_path):
     assert e.value.code == 4 and "rank 0" in str(e.value) and time.time() - t0 < 5
 
 
+def test_id_rendezvous_skips_a_file_left_by_an_earlier_job(tmp_path):
+    """The id file carries the world size and the time of writing: a leftover with another world size, or one older than
+    the timeout, is not taken for this job's id."""
+    import struct
+    from cutagi_b200 import comm
+    from cutagi_b200.capi import TagiError
+    path = str(tmp_path / "id")
+    ident = bytes(range(128))
+    comm.rendezvous_publish_id(path, ident, 4)
+    assert comm.rendezvous_fetch_id(path, 4, 1000) == ident
+    with pytest.raises(TagiError) as e:            # same path, a job of another size
+        comm.rendezvous_fetch_id(path, 2, 300)
+    assert e.value.code == 4 and "no id of this job" in str(e.value)
+    # a file written an hour ago: header = magic, world, pid, unix time in ms, then the id
+    old = struct.pack("<8siiq", b"TAGIRDV1", 4, 1, int((time.time() - 3600) * 1000)) + bytes(128)
+    comm.rendezvous_publish(path, old)
+    with pytest.raises(TagiError):
+        comm.rendezvous_fetch_id(path, 4, 300)
+    comm.rendezvous_publish_id(path, ident, 4)     # rank 0 of this job replaces it
+    assert comm.rendezvous_fetch_id(path, 4, 1000) == ident
+
+
 def test_calls_without_communicator_fail_cleanly():
     from cutagi_b200 import comm
     from cutagi_b200.capi import TagiError

@@ -194,10 +194,9 @@ def test_tensor_core_cta_pair_variant(G, oracle, force_impl, B, K, N):
         lib.tagi_tc_set_variant(3)
 
 
-@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("variant", [1])
 def test_tensor_core_one_cta_variants(G, oracle, force_impl, variant):
-    """The one-CTA kernels (1: A tiles in tensor memory, 0: every tile in shared memory) at shapes where the default
-    would use CTA pairs."""
+    """The one-CTA kernel at shapes where the default would use CTA pairs."""
     from cutagi_b200 import capi
     from cutagi_b200.capi import lib
     force_impl(capi.IMPL_TF32X3)
