@@ -12,6 +12,11 @@ With N > 1 (launched by torchrun, one rank per GPU) every rank runs the step on 
 samples against a full parameter replica (weak scaling) and the parameter deltas are averaged across ranks with
 an NCCL allreduce inside the timed region, which is the one exchange step of the data-parallel path.
 
+The same invocation then runs the second half of the metric, one training step of the ResNet-18 configuration (64
+samples of 3 x 224 x 224 per GPU, data-parallel over the N ranks), and reports it under the "resnet18" key of the one JSON
+line (`--no-resnet` skips it). Every timed region is stretched to about two seconds by repeating the K steps, so that the
+clocks settle under load; times are reported per step.
+
 `--impl reference` times the reference's CPU implementation (the compiled reference classes in oracle/_ref when
 present, else the CPU restatement in oracle/) on the host cores, on a bounded batch sample of the same workload.
 """
@@ -144,25 +149,33 @@ def run_reference(args, rank):
     sample = f"{rows} of {B} batch rows per step, full 4096x4096 weights"
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": tflops, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps * (B / rows),
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample": sample, "ms_per_step_is": "scaled from the sample to 1024 rows"},
+        "config": {"workload": WORKLOAD, "sample": sample,
+                   "ms_per_step_is": "one step on the sample; scaled to all 1024 rows: %.0f ms" %
+                                     (1e3 * dt / args.steps * (B / rows))},
         "cpu_baseline": {"value": tflops, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": tflops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0}))
 
 
+def _repeat_for(ms_per_pass, target_s=2.0, lo=1, hi=2000):
+    """How often a pass of ms_per_pass milliseconds is repeated so that the timed region lasts about target_s."""
+    return int(max(lo, min(hi, round(target_s * 1e3 / max(ms_per_pass, 1e-3)))))
+
+
 def run_b200(args, rank, world, local_rank):
+    """The headline line. Returns the dict that rank 0 prints (None on other ranks); the process group stays up for
+    the ResNet-18 leg."""
     import torch
     import torch.distributed as dist
     from cutagi_b200.capi import lib, IMPL_FFMA, IMPL_TF32X3, tc_status as capi_tc_status
 
     torch.cuda.set_device(local_rank)
     lib.tagi_set_impl({"auto": 0, "ffma": 1, "tf32x3": 2}[args.kernel_impl])
-    lib.tagi_tc_set_sm_budget(args.sm_budget if args.sm_budget >= 0 else (0 if world == 1 else 132))
+    sm_budget = args.sm_budget if args.sm_budget >= 0 else (0 if world == 1 else 132)
+    lib.tagi_tc_set_sm_budget(sm_budget)
     devname = torch.cuda.get_device_name(local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     x = make_inputs(100 + rank)
     host = {k: torch.from_numpy(v).pin_memory() for k, v in x.items()}
     d = {k: v.cuda(non_blocking=True) for k, v in host.items()}
@@ -202,21 +215,28 @@ def run_b200(args, rank, world, local_rank):
         for n0, n1 in zip(cuts[:-1], cuts[1:]):
             views += [o["dmu_w"][n0:n1], o["dvar_w"][n0:n1], o["dmu_b"][n0:n1], o["dvar_b"][n0:n1]]
         xchg = DeltaExchange(views, rank, world, local_rank, token[0], bucket_bytes=(N // pieces) * K * 8 + (1 << 20),
-                             average=True)
+                             average=True, max_ctas=args.nccl_max_ctas)
+        n_buckets = xchg.num_buckets
 
-    def step(p=p):
+    def step(p=p, exchange=True):
         k_fwd(p)
         if xchg:
             for j, (n0, n1) in enumerate(zip(cuts[:-1], cuts[1:])):
                 lib.tagi_linear_bwd_param_rows(p["var_w"], p["var_b"], p["mu_a"], p["dmu_z"], p["dvar_z"], B, K, N, n0, n1,
                                                1, p["dmu_w"], p["dvar_w"], p["dmu_b"], p["dvar_b"], sp)
-                for i in range(4):
-                    xchg.ready(4 * j + i, sp)
+                if exchange:
+                    for i in range(4):
+                        xchg.ready(4 * j + i, sp)
         else:
             k_param(p)
         k_state(p)
-        if xchg:
+        if xchg and exchange:
             xchg.wait(sp)
+
+    def exchange_only():
+        for i in range(4 * pieces):
+            xchg.ready(i, sp)
+        xchg.wait(sp)
 
     def sync_all():
         torch.cuda.synchronize()
@@ -240,87 +260,139 @@ def run_b200(args, rank, world, local_rank):
             ms = float(t.item())
         return ms
 
+    def agree(v):   # every rank must run the same number of iterations
+        if world == 1:
+            return v
+        t = torch.tensor([v], device="cuda", dtype=torch.int64)
+        dist.broadcast(t, src=0)
+        return int(t.item())
+
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     for _ in range(args.warmup):
         step()
+    # K steps are repeated R times inside one timed region of about two seconds (burst clocks last a few
+    # milliseconds; a power-capped part settles lower); ms_per_step is the region divided by K * R
+    probe = timed(step, args.steps) / args.steps
+    rep = 1 if args.profile else agree(_repeat_for(probe * args.steps, args.region_s))
     t_begin = time.time()
-    ms_total = timed(step, args.steps)
+    ms_total = timed(step, args.steps * rep)
     t_end = time.time()
-    ms_step = ms_total / args.steps
+    ms_step = ms_total / (args.steps * rep)
     value = FLOP_STEP * world / (ms_step * 1e-3) / 1e12
 
     # per-kernel durations (same stream, CUDA events); each kernel's operands exceed the 126 MB L2
     kt = {}
     for name, fn in (("tagi_linear_fwd", k_fwd), ("tagi_linear_bwd_state", k_state), ("tagi_linear_bwd_param", k_param)):
         fn()
-        kt[name] = timed(fn, args.steps) / args.steps
+        n = args.steps if args.profile else agree(_repeat_for(timed(fn, 5) / 5, args.region_s / 4))
+        kt[name] = timed(fn, n) / n
 
-    # end to end: pinned host inputs -> device, three calls, results -> pinned host, all inside the timed region
-    h2d = sum(v.numel() * 4 for v in host.values())
-    d2h = sum(v.numel() * 4 for v in host_out.values())
+    # N > 1: what the exchange costs. The same step with the exchange left out, and the exchange alone (the buckets'
+    # allreduce with no kernel of this library beside it).
+    exchange_info = None
+    if xchg:
+        off = lambda: step(exchange=False)
+        n = agree(_repeat_for(timed(off, 5) / 5, args.region_s / 2))
+        ms_off = timed(off, n) / n
+        n = agree(_repeat_for(timed(exchange_only, 3) / 3, args.region_s / 4))
+        ms_alone = timed(exchange_only, n) / n
+        # Correctness of the exchange: sampled rows of this rank's local deltas (a step without exchange), then the
+        # same rows after a step with it; every rank's exchanged rows must equal the mean of all ranks' local rows and
+        # be the same bits on every rank.
+        rows = torch.tensor(sorted(np.random.default_rng(7).choice(N, 8, replace=False).tolist()), device="cuda")
+        step(exchange=False)
+        local = torch.cat([o["dmu_w"][rows].reshape(-1), o["dvar_w"][rows].reshape(-1), o["dmu_b"], o["dvar_b"]]).clone()
+        step()
+        torch.cuda.synchronize()
+        got = torch.cat([o["dmu_w"][rows].reshape(-1), o["dvar_w"][rows].reshape(-1), o["dmu_b"], o["dvar_b"]]).clone()
+        all_local = [torch.empty_like(local) for _ in range(world)]
+        all_got = [torch.empty_like(got) for _ in range(world)]
+        dist.all_gather(all_local, local)
+        dist.all_gather(all_got, got)
+        mean = torch.stack(all_local).double().mean(0)
+        err = float(((got.double() - mean).abs().max() / mean.abs().max()).item())
+        same = all(torch.equal(all_got[0], g) for g in all_got[1:])
+        exchange_info = {"exchange_ms_alone": ms_alone, "step_ms_exchange_off": ms_off, "step_ms": ms_step,
+                         "bytes_per_step": int(2 * (N * K + N) * 4),
+                         "exchange_check": {"max_rel_err": err, "ranks_bit_identical": bool(same),
+                                            "sample": "8 rows of dmu_w / dvar_w and all of dmu_b / dvar_b against the "
+                                                      "FP64 mean of the ranks' local deltas"}}
 
-    # Every step's inputs travel host -> device and every step's outputs device -> host inside the timed region. The copies
-    # run on their own streams: inputs are double-buffered on the device, so the upload of step i+1 overlaps the kernels
-    # and the download of step i (PCIe is full duplex); events order buffer reuse.
+    # End to end: host buffers in, host buffers out, copies inside the timed region. Every step's inputs travel host ->
+    # device and its outputs device -> host on their own streams: inputs are double-buffered on the device, so the
+    # upload of step i+1 overlaps the kernels and the download of step i (PCIe is full duplex); events order buffer
+    # reuse. Two variants: "layer" keeps the parameters and the parameter deltas on the device, as cuTAGI's LinearCuda
+    # does (d_mu_w ..., d_delta_mu_w ... are members of the layer; only activations and incoming deltas are a step's
+    # inputs, only the forward outputs, the state deltas and the bias deltas its results); "all" moves every tensor of
+    # the three calls both ways.
+    in_layer = ["mu_a", "var_a", "jcb", "dmu_z", "dvar_z"]
+    out_layer = ["mu_z", "var_z", "dmu_a", "dvar_a", "dmu_b", "dvar_b"]
     d_alt = {k: torch.empty_like(v) for k, v in d.items()}
-    psets = [p, {**p, **{k: v.data_ptr() for k, v in d_alt.items()}}]
-    dsets = [d, d_alt]
     s_h2d, s_d2h = torch.cuda.Stream(), torch.cuda.Stream()
-    ev_in_ready = [torch.cuda.Event(), torch.cuda.Event()]
-    ev_in_free = [torch.cuda.Event(), torch.cuda.Event()]
-    ev_out_ready, ev_out_free = torch.cuda.Event(), torch.cuda.Event()
-    e2e_i = [0]
 
-    def e2e_step():
-        b = e2e_i[0] & 1
-        e2e_i[0] += 1
-        s_h2d.wait_event(ev_in_free[b])          # the step that last used this input buffer has finished
-        with torch.cuda.stream(s_h2d):
-            for k_, v in host.items():
-                dsets[b][k_].copy_(v, non_blocking=True)
-            ev_in_ready[b].record(s_h2d)
-        stream.wait_event(ev_in_ready[b])
-        stream.wait_event(ev_out_free)           # the previous step's outputs have been downloaded
-        step(psets[b])
-        ev_in_free[b].record(stream)
-        ev_out_ready.record(stream)
-        s_d2h.wait_event(ev_out_ready)
-        with torch.cuda.stream(s_d2h):
-            for k_, v in host_out.items():
-                v.copy_(o[k_], non_blocking=True)
-            ev_out_free.record(s_d2h)
+    def make_e2e(in_keys, out_keys):
+        psets = [p, {**p, **{k: d_alt[k].data_ptr() for k in in_keys}}]
+        dsets = [d, {**d, **{k: d_alt[k] for k in in_keys}}]
+        ev_in_ready = [torch.cuda.Event(), torch.cuda.Event()]
+        ev_in_free = [torch.cuda.Event(), torch.cuda.Event()]
+        ev_out_ready, ev_out_free = torch.cuda.Event(), torch.cuda.Event()
+        it = [0]
 
-    def e2e_run(n):
-        for _ in range(n):
-            e2e_step()
-        stream.wait_event(ev_out_free)           # the timed region ends when the last download has landed
+        def one():
+            b = it[0] & 1
+            it[0] += 1
+            s_h2d.wait_event(ev_in_free[b])          # the step that last used this input buffer has finished
+            with torch.cuda.stream(s_h2d):
+                for k_ in in_keys:
+                    dsets[b][k_].copy_(host[k_], non_blocking=True)
+                ev_in_ready[b].record(s_h2d)
+            stream.wait_event(ev_in_ready[b])
+            stream.wait_event(ev_out_free)           # the previous step's outputs have been downloaded
+            step(psets[b])
+            ev_in_free[b].record(stream)
+            ev_out_ready.record(stream)
+            s_d2h.wait_event(ev_out_ready)
+            with torch.cuda.stream(s_d2h):
+                for k_ in out_keys:
+                    host_out[k_].copy_(o[k_], non_blocking=True)
+                ev_out_free.record(s_d2h)
 
-    if args.profile:
-        ms_e2e = float("nan")
-    else:
-        n_e2e = max(4, args.steps // 4)
-        e2e_run(2)
-        ms_e2e = timed(lambda: e2e_run(n_e2e), 1) / n_e2e
-    e2e_value = FLOP_STEP * world / (ms_e2e * 1e-3) / 1e12
+        def run(n):
+            for _ in range(n):
+                one()
+            stream.wait_event(ev_out_free)           # the timed region ends when the last download has landed
+        return run, sum(host[k_].numel() * 4 for k_ in in_keys), sum(host_out[k_].numel() * 4 for k_ in out_keys)
+
+    e2e = {}
+    for name, ik, ok_ in (("layer", in_layer, out_layer), ("all", list(host), list(host_out))):
+        run, h2d, d2h = make_e2e(ik, ok_)
+        if args.profile:
+            e2e[name] = (float("nan"), h2d, d2h)
+            continue
+        run(2)
+        n = agree(_repeat_for(timed(lambda: run(4), 1) / 4, args.region_s / 2, lo=4, hi=400))
+        e2e[name] = (timed(lambda: run(n), 1) / n, h2d, d2h)
     clocks = None
     if rank == 0:
         sampler.stop()
         clocks = sampler.summary(t_begin, t_end)
+    tc_status = capi_tc_status()
+    if xchg:
+        xchg.check()
+        xchg.close()
     if rank != 0:
-        if xchg:
-            xchg.close()
-        dist.destroy_process_group()
-        return
+        return None
 
     impl = lib.tagi_get_impl()
     if impl == 0:  # AUTO resolves to the tensor-core kernels for this shape (aligned, every dimension >= 128)
         impl = IMPL_TF32X3
-    tc_status = capi_tc_status()
     flops = {"tagi_linear_fwd": FLOP_FWD, "tagi_linear_bwd_state": FLOP_STATE, "tagi_linear_bwd_param": FLOP_PARAM}
+    tfl = {k_: flops[k_] / (v * 1e-3) / 1e12 for k_, v in kt.items()}
     dom = max(kt, key=kt.get)
-    achieved = flops[dom] / (kt[dom] * 1e-3) / 1e12
+    worst = min(tfl, key=tfl.get)
+    achieved = tfl[dom]
     peaks = {}
     try:
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -329,21 +401,28 @@ def run_b200(args, rank, world, local_rank):
     if impl == IMPL_TF32X3:
         bf16 = peaks.get("bf16_tflops", 1590.0)
         peak, bound = bf16 / 2.0 / 3.0, "tensor"
-        peak_note = ("measured dense bf16 %.0f TFLOP/s / 2 (tf32 rate) / 3 (three tf32 products per fp32 product), %s"
+        peak_note = ("measured dense bf16 %.0f TFLOP/s (burst) / 2 (tf32 rate) / 3 (three tf32 products per fp32 product), %s"
                      % (bf16, "of measured" if peaks else "of fallback"))
+        sustained = peaks.get("bf16_tflops_sustained", 1400.0) / 6.0
     else:
         peak, bound = FP32_NOMINAL_TFLOPS, "fp32"
         peak_note = ("FP32 FFMA path: 148 SMs x 128 lanes x 2 x 1.965 GHz, of nominal "
                      "(MEASURED_PEAKS.json holds no FP32 figure)")
-    # DRAM traffic of one launch of each kernel, from the ncu capture summarised in
-    # profiles/tagi_tc_linear_pair_kernel_b1024_4096.md (dram__bytes_read.sum + dram__bytes_write.sum); the FFMA kernels
-    # have not been captured
-    ncu_traffic = {"tagi_linear_fwd": 322.1e6, "tagi_linear_bwd_state": 203.3e6, "tagi_linear_bwd_param": 218.5e6}
+        sustained = peak
+    # DRAM traffic of one launch of each kernel (dram__bytes_read.sum + dram__bytes_write.sum): constants taken from an
+    # ncu capture of these kernels at this shape, not re-measured by this run; the FFMA kernels have not been captured
+    captured_traffic = {"tagi_linear_fwd": 322.1e6, "tagi_linear_bwd_state": 203.3e6, "tagi_linear_bwd_param": 218.5e6}
+    step_tflops = FLOP_STEP / (ms_step * 1e-3) / 1e12 if world == 1 else FLOP_STEP / (exchange_info["step_ms_exchange_off"] * 1e-3) / 1e12
     roofline = {"bound": bound, "kernel": dom, "achieved": achieved, "peak": peak, "unit": UNIT,
-                "frac": achieved / peak, "traffic": ncu_traffic[dom] if impl == IMPL_TF32X3 else None,
-                "traffic_unit": "bytes per launch (ncu, dram read + write)", "peak_note": peak_note,
-                "per_kernel_ms": kt,
-                "per_kernel_tflops": {k_: flops[k_] / (v * 1e-3) / 1e12 for k_, v in kt.items()}}
+                "frac": achieved / peak, "traffic": captured_traffic[dom] if impl == IMPL_TF32X3 else None,
+                "traffic_is": "a constant captured with ncu for this kernel and shape (bytes per launch, dram read + "
+                              "write); not re-measured by this run",
+                "peak_note": peak_note, "per_kernel_ms": kt, "per_kernel_tflops": tfl,
+                "per_kernel_frac": {k_: v / peak for k_, v in tfl.items()},
+                "worst_kernel": worst, "worst_kernel_frac": tfl[worst] / peak,
+                "step_tflops_per_gpu": step_tflops, "step_frac": step_tflops / peak,
+                "step_frac_of_sustained_peak": step_tflops / sustained,
+                "sustained_peak": sustained}
 
     cpu_baseline = None
     if world == 1 and not args.no_cpu:
@@ -353,26 +432,37 @@ def run_b200(args, rank, world, local_rank):
         cpu_baseline = {"value": 14.0 * rows * K * N / t / 1e12, "unit": UNIT, "cores": threads, "kind": kind,
                         "sample": f"{rows} of {B} batch rows, full 4096x4096 weights, {t:.1f} s"}
 
-    if xchg:
-        xchg.check()
-    print(json.dumps({
+    if clocks and clocks.get("sm_mhz"):
+        clocks["ms_per_step_x_sm_mhz"] = ms_step * clocks["sm_mhz"]
+    ms_e2e, h2d, d2h = e2e["layer"]
+    ms_all, h2d_all, d2h_all = e2e["all"]
+    return {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
         "config": {"workload": WORKLOAD, "impl": {1: "ffma (FP32 CUDA cores)", 2: "tf32x3 (tcgen05, 3 TF32 products per "
                                                   "FP32 product, FP32 accumulation)"}.get(impl, str(impl)),
                    "device": devname, "l2": "inputs (604 MB per step) exceed the 126 MB L2; no flush",
+                   "inner_repeat": rep, "timed_region_s": ms_total * 1e-3,
+                   "timing": "the K steps are repeated inner_repeat times inside one CUDA-event region; ms_per_step = "
+                             "region / (K * inner_repeat)",
+                   "sm_budget": sm_budget,
                    "exchange": ("allreduce(avg) of parameter deltas: parameter pass and exchange in %d ranges of output "
                                 "features, %d NCCL buckets on a side stream, each range's exchange overlapped with the "
-                                "next range's parameter pass and the state pass" % (pieces, xchg.num_buckets))
+                                "next range's parameter pass and the state pass" % (pieces, n_buckets))
                    if world > 1 else "none (1 GPU)"},
         "roofline": roofline, "cpu_baseline": cpu_baseline,
-        "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h},
-        "gpu_launches": (3 if world == 1 else 2 + pieces) * args.steps, "tc_status": tc_status, "clocks": clocks}))
-    if world > 1:
-        xchg.close()
-        dist.destroy_process_group()
+        "e2e": {"value": FLOP_STEP * world / (ms_e2e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "resident": "parameters and parameter deltas stay on the device, as in cuTAGI's LinearCuda; mu_a, var_a, "
+                            "jcb, dmu_z, dvar_z are uploaded and mu_z, var_z, dmu_a, dvar_a, dmu_b, dvar_b downloaded every "
+                            "step, per GPU",
+                "all_tensors": {"value": FLOP_STEP * world / (ms_all * 1e-3) / 1e12, "ms_per_step": ms_all,
+                                "h2d_bytes_per_step": h2d_all, "d2h_bytes_per_step": d2h_all,
+                                "note": "every input (weights included) uploaded and every output (weight deltas "
+                                        "included) downloaded every step"}},
+        "exchange": exchange_info,
+        "gpu_launches": (3 if world == 1 else 2 + pieces) * args.steps * rep, "tc_status": tc_status, "clocks": clocks}
 
 
 # Conv2d layer shapes of the CIFAR-shaped CNN (batch 128) and of the ResNet-18 configuration (batch 64, 224x224)
@@ -472,12 +562,12 @@ def resnet_flops(spec, shape):
 
 
 def run_network(args, rank, world, local_rank):
-    """Side workloads (not the headline line): one TAGI training step of a whole network of the benchmark configurations
-    through the device-side mirror of the pytagi API: the reference's ResNet-18 (ReLU variant, 11 hierarchical-softmax
-    outputs, 64 x 3 x 224 x 224 N(0,1) images per GPU), the CIFAR-shaped CNN (batch 128) or the deep regression MLP
-    (1 -> 4096 -> 4096 -> 4096 -> 1, batch 2048). Step = forward, output update, backward with the parameter deltas
-    averaged over the ranks (bucketed NCCL exchange overlapped with the rest of the backward pass), capped update.
-    Prints one JSON line: samples/s."""
+    """One TAGI training step of a whole network of the benchmark configurations through the device-side mirror of the
+    pytagi API: the reference's ResNet-18 (ReLU variant, 11 hierarchical-softmax outputs, 64 x 3 x 224 x 224 N(0,1) images
+    per GPU), the CIFAR-shaped CNN (batch 128) or the deep regression MLP (1 -> 4096 -> 4096 -> 4096 -> 1, batch 2048).
+    Step = forward, output update, backward with the parameter deltas averaged over the ranks (bucketed NCCL exchange
+    overlapped with the rest of the backward pass), capped update. Returns the result line (samples/s) as a dict on
+    rank 0, None elsewhere; the caller owns the process group."""
     import torch
     import torch.distributed as dist
     from cutagi_b200 import nn
@@ -485,8 +575,7 @@ def run_network(args, rank, world, local_rank):
 
     torch.cuda.set_device(local_rank)
     lib.tagi_set_impl({"auto": 0, "ffma": 1, "tf32x3": 2}[args.kernel_impl])
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    lib.tagi_tc_set_sm_budget(max(args.sm_budget, 0))   # the exchange overlaps a small part of this step: plan for all SMs
     image = args.image
     rng = np.random.default_rng(100 + rank)
     n_sets = 2
@@ -531,7 +620,8 @@ def run_network(args, rank, world, local_rank):
         from cutagi_b200.comm import DeltaExchange
         token = [f"/tmp/tagi_b200_rdv_{os.getpid()}_{time.time_ns()}"]
         dist.broadcast_object_list(token, src=0)
-        xchg = DeltaExchange(deltas, rank, world, local_rank, token[0], bucket_bytes=args.bucket_mb << 20, average=True)
+        xchg = DeltaExchange(deltas, rank, world, local_rank, token[0], bucket_bytes=args.bucket_mb << 20, average=True,
+                             max_ctas=args.nccl_max_ctas)
         pos = {t.data_ptr(): i for i, t in enumerate(deltas)}
 
         def hook(layer):
@@ -557,6 +647,8 @@ def run_network(args, rank, world, local_rank):
             upd.update_using_indices(net, d_obs[i], var_y, d_idx[i])
     it = [0]
 
+    exchange_on = [True]
+
     def step(e2e=False):
         i = it[0] % n_sets
         it[0] += 1
@@ -567,7 +659,7 @@ def run_network(args, rank, world, local_rank):
         mu, var = net(d_x[i])
         output_update(i)
         net.backward()
-        if xchg:
+        if xchg and exchange_on[0]:
             xchg.flush(sp)
             xchg.wait(sp)
         net.step()
@@ -636,6 +728,51 @@ def run_network(args, rank, world, local_rank):
     ms = timed(step, args.steps) / args.steps
     t1 = time.time()
     ms_e2e = ms if args.profile else timed(lambda: step(True), args.steps) / args.steps
+    # N > 1: the same step with the exchange left out, the exchange alone, and its correctness on a sample
+    exchange_info = None
+    if xchg and not args.profile:
+        hooks = {k: l.on_ready for k, l in net.named_layers().items()}
+
+        def set_exchange(on):
+            exchange_on[0] = on
+            for k, l in net.named_layers().items():
+                l.on_ready = hooks[k] if on else None
+        set_exchange(False)
+        n_off = max(3, args.steps // 4)
+        ms_off = timed(step, n_off) / n_off
+
+        def exchange_only():
+            xchg.flush(sp)
+            xchg.wait(sp)
+        exchange_only()
+        ms_alone = timed(exchange_only, 5) / 5
+        # local deltas of one step (parameters are not updated: forward, output update, backward only), then the same
+        # with the exchange
+        def half_step():
+            net(d_x[0])
+            output_update(0)
+            net.backward()
+        half_step()
+        pick = [t for t in deltas if t.numel() >= 1][:: max(1, len(deltas) // 12)]
+        local = torch.cat([t.reshape(-1)[:4096] for t in pick]).clone()
+        set_exchange(True)
+        half_step()
+        xchg.flush(sp)
+        xchg.wait(sp)
+        torch.cuda.synchronize()
+        got = torch.cat([t.reshape(-1)[:4096] for t in pick]).clone()
+        all_local = [torch.empty_like(local) for _ in range(world)]
+        all_got = [torch.empty_like(got) for _ in range(world)]
+        dist.all_gather(all_local, local)
+        dist.all_gather(all_got, got)
+        mean = torch.stack(all_local).double().mean(0)
+        err = float(((got.double() - mean).abs().max() / mean.abs().max()).item())
+        exchange_info = {"exchange_ms_alone": ms_alone, "step_ms_exchange_off": ms_off, "step_ms": ms,
+                         "bytes_per_step": int(sum(t.numel() for t in deltas) * 4), "buckets": xchg.num_buckets,
+                         "exchange_check": {"max_rel_err": err,
+                                            "ranks_bit_identical": bool(all(torch.equal(all_got[0], g) for g in all_got[1:])),
+                                            "sample": f"first 4096 entries of {len(pick)} of the {len(deltas)} delta tensors "
+                                                      "against the FP64 mean of the ranks' local deltas"}}
     # phases on one rank's stream (no exchange wait inside): forward / output update + backward / update
     phases = {}
     if not args.profile:
@@ -658,11 +795,10 @@ def run_network(args, rank, world, local_rank):
     status = capi_tc_status()
     if xchg:
         xchg.check()
+    if xchg:
+        xchg.close()
     if rank != 0:
-        if world > 1:
-            xchg.close()
-            dist.destroy_process_group()
-        return
+        return None
     flop = resnet_flops(spec, in_shape) * batch
     n_param = sum(t.numel() for t in deltas) // 2
     peak = 0.0
@@ -690,7 +826,7 @@ def run_network(args, rank, world, local_rank):
         dt = time.perf_counter() - tc0
         cpu = {"value": nb / dt, "unit": "samples/s", "cores": os.cpu_count(), "kind": "port",
                "sample": f"one training step at batch {nb} ({dt:.1f} s), oracle port with OpenMP; linear in the batch"}
-    print(json.dumps({
+    return {
         "metric": {"resnet18": "TAGI ResNet-18 training samples/s", "cnn": "TAGI CNN training samples/s",
                    "mlp": "TAGI regression MLP training samples/s"}[args.workload],
         "value": batch * world / (ms * 1e-3), "unit": "samples/s",
@@ -700,7 +836,7 @@ def run_network(args, rank, world, local_rank):
                    "launch": "one CUDA graph per step" if (args.graph and world == 1) else "one launch per kernel",
                    "parameters": n_param, "exchange": "none (1 GPU)" if world == 1 else
                    f"bucketed NCCL allreduce (average) of {2 * n_param * 4 / 1e6:.0f} MB of parameter deltas, "
-                   f"{xchg.num_buckets} buckets of {args.bucket_mb} MiB, overlapped with the backward pass",
+                   f"buckets of {args.bucket_mb} MiB, overlapped with the backward pass",
                    "l2": "activations of a step exceed the 126 MB L2 many times over; no flush"},
         "roofline": {"bound": "tensor", "achieved": flop / (ms * 1e-3) / 1e12, "peak": peak, "unit": "TFLOP/s",
                      "frac": flop / (ms * 1e-3) / 1e12 / peak, "traffic": None,
@@ -710,10 +846,7 @@ def run_network(args, rank, world, local_rank):
         "e2e": {"value": batch * world / (ms_e2e * 1e-3), "unit": "samples/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": int(xs[0].numel() * 4 + obs[0].numel() * 4 + idx[0].numel() * 4),
                 "d2h_bytes_per_step": int(host_out.numel() * 4)},
-        "gpu_launches": None, "tc_status": status, "clocks": clocks}))
-    if world > 1:
-        xchg.close()
-        dist.destroy_process_group()
+        "exchange": exchange_info, "gpu_launches": None, "tc_status": status, "clocks": clocks}
 
 
 def run_resnet_module(args):
@@ -832,25 +965,32 @@ def run_linear_module(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-resnet", action="store_true", help="linear workload: skip the ResNet-18 leg of the line")
+    ap.add_argument("--resnet-steps", type=int, default=50, help="timed steps of the ResNet-18 leg")
+    ap.add_argument("--region-s", type=float, default=2.0,
+                    help="linear workload: length each timed region is stretched to by repeating the K steps")
     ap.add_argument("--profile", action="store_true",
-                    help="for captures under ncu: one warm-up step, no end-to-end and no CPU leg (numbers printed "
-                         "in this mode are not benchmark values)")
+                    help="for captures under ncu: one warm-up step, no repeats, no end-to-end, ResNet-18 or CPU leg (numbers "
+                         "printed in this mode are not benchmark values)")
     ap.add_argument("--kernel-impl", default="auto", choices=["auto", "ffma", "tf32x3"],
                     help="arithmetic of the kernels (tagi_set_impl)")
     ap.add_argument("--conv-layers", action="store_true",
                     help="print a per-layer timing table of the Conv2d entry points instead of the benchmark line")
     ap.add_argument("--sm-budget", type=int, default=-1,
                     help="SMs the tensor-core kernels plan their tiles for (tagi_tc_set_sm_budget); default: all on one GPU, "
-                         "132 when the exchange's NCCL kernels run next to them (N > 1)")
+                         "132 for the Linear step when the exchange's NCCL kernels run next to it (N > 1)")
+    ap.add_argument("--nccl-max-ctas", type=int, default=0,
+                    help="N > 1: upper bound on the CTAs of one NCCL kernel of the exchange (0 = NCCL's default)")
     ap.add_argument("--param-pieces", type=int, default=2,
                     help="linear, N > 1: ranges of output features the parameter pass and the exchange are cut into")
     ap.add_argument("--workload", default="linear", choices=["linear", "resnet18", "cnn", "mlp"],
-                    help="linear: the headline micro-benchmark; resnet18 / cnn / mlp: one training step of the ResNet-18, "
-                         "CIFAR-shaped CNN or deep regression MLP configuration through the device-side mirror")
+                    help="linear: the benchmark line (Linear micro-benchmark + ResNet-18 leg); resnet18 / cnn / mlp: only one "
+                         "training step of the ResNet-18, CIFAR-shaped CNN or deep regression MLP configuration through the "
+                         "device-side mirror")
     ap.add_argument("--graph", action="store_true",
                     help="network workloads on one GPU: replay the training step as a CUDA graph")
     ap.add_argument("--engine", default="native", choices=["native", "dropin", "stock"],
@@ -862,37 +1002,70 @@ def main():
     ap.add_argument("--batch", type=int, default=0, help="network workloads: samples per GPU (default: the configuration's)")
     ap.add_argument("--bucket-mb", type=int, default=32, help="resnet18: exchange bucket size in MiB")
     args = ap.parse_args()
-    if args.workload != "linear" and args.impl == "b200":
-        if args.steps == 200:
-            args.steps = 10 if args.engine == "native" else 3
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+
+    def with_group(fn):
+        """One NCCL process group for the whole invocation (N > 1)."""
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        if world > 1:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        try:
+            return fn()
+        finally:
+            if world > 1:
+                dist.destroy_process_group()
+
+    if args.impl == "reference":
+        return run_reference(args, rank)
+    if args.workload != "linear":
         if args.engine != "native":
             if args.workload != "resnet18":
                 ap.error("--engine dropin / stock is available for the linear and resnet18 workloads")
             args.batch = args.batch or 64
+            args.steps = min(args.steps, 3)
             return run_resnet_module(args)
+        args.steps = min(args.steps, 50) if args.steps != 20 else 10
         args.warmup = 1 if args.profile else max(args.warmup, 3)
         args.no_cpu = args.no_cpu or args.profile
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        return run_network(args, int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")),
-                          int(os.environ.get("LOCAL_RANK", "0")))
-    if args.workload == "linear" and args.engine != "native" and args.impl == "b200":
+        line = with_group(lambda: run_network(args, rank, world, local_rank))
+        if line is not None:
+            print(json.dumps(line))
+        return
+    if args.engine != "native":
         args.steps = min(args.steps, 20)
         return run_linear_module(args)
     if args.conv_layers:
         args.steps = min(args.steps, 20)
         return run_conv_layers(args)
     if args.profile:
-        args.warmup, args.no_cpu = 1, True
+        args.warmup, args.no_cpu, args.no_resnet = 1, True, True
     else:
-        args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    if args.impl == "reference":
-        run_reference(args, rank)
-    else:
-        run_b200(args, rank, world, local_rank)
+        args.warmup = max(args.warmup, 3)
+
+    def both():
+        line = run_b200(args, rank, world, local_rank)
+        if not args.no_resnet:
+            # the second half of the metric: ResNet-18 training samples/s on the same ranks
+            ra = argparse.Namespace(**vars(args))
+            ra.workload, ra.steps, ra.warmup, ra.no_cpu, ra.graph, ra.batch, ra.image = \
+                "resnet18", args.resnet_steps, 3, True, False, 0, 224
+            rn = run_network(ra, rank, world, local_rank)
+            if line is not None and rn is not None:
+                line["resnet18"] = {
+                    "metric": rn["metric"], "samples_per_s": rn["value"], "ms_per_step": rn["ms_per_step"],
+                    "steps": rn["steps"], "samples_per_gpu": 64, "workload": rn["config"]["workload"],
+                    "e2e": rn["e2e"], "exchange": rn["exchange"] if world > 1 else "none (1 GPU)",
+                    "roofline_frac": rn["roofline"]["frac"], "roofline": rn["roofline"], "clocks": rn["clocks"],
+                    "tc_status": rn["tc_status"]}
+        return line
+    line = with_group(both)
+    if line is not None:
+        print(json.dumps(line))
 
 
 if __name__ == "__main__":

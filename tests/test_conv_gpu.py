@@ -228,3 +228,76 @@ def test_conv_forward_with_fused_mixture_relu(G, kw):
     assert capi.tc_status() == 0
     for name, a, b, tol in zip(("mu_a", "var_a", "jcb"), got, ref, (G.RTOL_MU, G.RTOL_VAR, G.RTOL_MU)):
         G.check(name, a, b, tol)
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# The layer shapes of the CIFAR-shaped CNN (batch 128) and of ResNet-18 (batch 64, 224 x 224) at full size
+# ------------------------------------------------------------------------------------------------------------------
+def _bench_layers():
+    import os
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    if root not in sys.path:
+        sys.path.insert(0, root)
+    import bench
+    return bench.CONV_LAYERS
+
+
+@pytest.mark.parametrize("name,kw", _bench_layers(), ids=lambda v: v.replace(" ", "_") if isinstance(v, str) else "")
+def test_configuration_layer_shapes_sampled(G, oracle, name, kw):
+    """Every Conv2d layer shape of the CNN and ResNet-18 configurations at its full batch and image size: the planner
+    picks other tile widths, slice counts and gather variants here than at the reduced sizes above. The GPU runs the
+    whole layer; the CPU oracle runs a sample. Forward and state-pass outputs of an image depend on that image only
+    (two images are checked); parameter deltas of an output channel depend on that channel's deltas only (three
+    channels are checked, over the whole batch)."""
+    from cutagi_b200 import capi
+    g = ConvGeom(**kw)
+    rng = np.random.default_rng(g.fi * 977 + g.fo * 13 + g.hi)
+    x = G.conv_inputs(rng, g)
+    imgs = np.sort(rng.choice(g.B, 2, replace=False))
+    chans = np.sort(rng.choice(g.fo, 3, replace=False))
+    gi = ConvGeom(**{**kw, "B": 2})
+    sub = lambda a: np.ascontiguousarray(a[imgs])
+    capi.tc_status()
+
+    mz, vz = G.conv_fwd(g, x["mu_w"], x["var_w"], x["mu_b"], x["var_b"], x["mu_a"], x["var_a"])
+    rmz, rvz = oracle.conv2d_fwd(gi, x["mu_w"], x["var_w"], x["mu_b"], x["var_b"], sub(x["mu_a"]), sub(x["var_a"]))
+    G.check("mu_z", mz[imgs], rmz, G.RTOL_MU)
+    G.check("var_z", vz[imgs], rvz, G.RTOL_VAR)
+    assert vz.min() > 0
+    del mz, vz
+
+    da, dv = G.conv_bwd_state(g, x["mu_w"], x["jcb"], x["dmu_z"], x["dvar_z"])
+    rda, rdv = oracle.conv2d_bwd_state(gi, x["mu_w"], sub(x["jcb"]), sub(x["dmu_z"]), sub(x["dvar_z"]))
+    G.check("dmu_a", da[imgs], rda, G.RTOL_MU)
+    G.check("dvar_a", dv[imgs], rdv, G.RTOL_VAR)
+    assert dv.max() <= 0
+    del da, dv
+
+    dmw, dvw, dmb, dvb = G.conv_bwd_param(g, x["var_w"], x["var_b"], x["mu_a"], x["dmu_z"], x["dvar_z"])
+    gc = ConvGeom(**{**kw, "fo": len(chans)})
+    woho = g.ho * g.wo
+    pick = lambda a: np.ascontiguousarray(a.reshape(g.B, g.fo, woho)[:, chans, :]).reshape(g.B, -1)
+    args = (gc, np.ascontiguousarray(x["var_w"][chans]),
+            None if x["var_b"] is None else np.ascontiguousarray(x["var_b"][chans]), x["mu_a"], pick(x["dmu_z"]),
+            pick(x["dvar_z"]))
+    r = oracle.conv2d_bwd_param(*args)
+    r64 = oracle.conv2d_bwd_param(*args, f64=True)
+    # The contraction of this pass runs over B * ho * wo terms (802 816 for the ResNet-18 stem). The reference sums them
+    # one after the other in FP32, and that sum's own rounding error, measured here against the FP64 restatement,
+    # reaches 3e-5 (means) / 5e-4 (variances, all terms of one sign) at these sizes: more than the tolerance. So the
+    # GPU result must be within the tolerance of the exactly rounded result, and within the tolerance plus the
+    # reference's own measured deviation of the reference.
+    names = ("dmu_w", "dvar_w", "dmu_b", "dvar_b")
+    got = (dmw[chans], dvw[chans], dmb[chans] if g.has_bias else None, dvb[chans] if g.has_bias else None)
+    for i, tol in enumerate((G.RTOL_MU, G.RTOL_VAR, G.RTOL_MU, G.RTOL_VAR)):
+        if got[i] is None:
+            continue
+        a, b32, b64 = (np.asarray(v, np.float64).reshape(got[i].shape) for v in (got[i], r[i], r64[i]))
+        G.check(f"{names[i]} vs FP64", a, b64, tol)
+        noise = np.abs(b32 - b64).max()
+        err = np.abs(a - b32).max()
+        assert err <= tol * np.abs(b32).max() + noise, \
+            f"{names[i]}: max err {err:.3e} vs the FP32 reference, whose own deviation from FP64 is {noise:.3e}"
+    assert dvw.max() <= 0
+    assert capi.tc_status() == 0, "a bounded device-side wait ran out"

@@ -242,3 +242,25 @@ def test_param_update_single_and_multi(G, golden, i):
         for a, b in (("mu_w0", "mu_w1"), ("var_w0", "var_w1"), ("mu_b0", "mu_b1"), ("var_b0", "var_b1")):
             G.check(b, t[a].cpu().numpy(), g[b], 1e-6)
         assert int(neg.item()) == int(g["neg"][0])
+
+
+@pytest.mark.parametrize("n", [1000003, 1 << 20])
+def test_activations_in_place(G, oracle, n):
+    """tagi_relu_fwd and tagi_mixture_relu_fwd with mu_a = mu_z and var_a = var_z (how tagi_*_fwd_act runs them after a
+    forward pass that could not fold the activation in): same results as the out-of-place call, bit for bit, on the
+    scalar (odd n) and the 16-byte (n a multiple of 4) kernels."""
+    import torch
+    from cutagi_b200.capi import lib
+    rng = np.random.default_rng(n)
+    mz = rng.standard_normal(n).astype(np.float32)
+    vz = rng.uniform(1e-3, 1.0, n).astype(np.float32)
+    for fn, ref in ((lib.tagi_relu_fwd, oracle.relu(mz, vz)), (lib.tagi_mixture_relu_fwd, None)):
+        m, v = torch.from_numpy(mz).cuda(), torch.from_numpy(vz).cuda()
+        om, ov, oj, j = torch.empty_like(m), torch.empty_like(m), torch.empty_like(m), torch.empty_like(m)
+        fn(m.data_ptr(), v.data_ptr(), n, om.data_ptr(), ov.data_ptr(), oj.data_ptr(), None)
+        fn(m.data_ptr(), v.data_ptr(), n, m.data_ptr(), v.data_ptr(), j.data_ptr(), None)
+        torch.cuda.synchronize()
+        assert torch.equal(m, om) and torch.equal(v, ov) and torch.equal(j, oj)
+        if ref is not None:
+            for a, b in zip((m, v, j), ref):
+                assert np.array_equal(a.cpu().numpy(), b)

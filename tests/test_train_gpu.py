@@ -102,6 +102,74 @@ def test_one_step_every_tensor_at_the_per_layer_bar(oracle):
         G.check(f"var_w{i}", l.var_w.cpu().numpy(), p["var_w"], G.RTOL_VAR)
 
 
+def test_deep_regression_mlp_full_width_one_step_sampled(oracle):
+    """Configuration 2 at its full size (1 -> 4096 -> 4096 -> 4096 -> 1, batch 2048), one training step. The CPU oracle
+    needs minutes for one such step, so every layer is checked on a sample, given the GPU's own inputs of that layer:
+    forward and state pass on six batch rows (they depend on that row only), parameter deltas and the capped update on
+    six output features (they depend on that feature's delta column only)."""
+    import torch
+    import gpu_util as G
+    from cutagi_b200 import capi, nn
+    sizes, B = (1, 4096, 4096, 4096, 1), 2048
+    params, _, _ = cfg0_problem(7, sizes=sizes, batch=B, steps=1)
+    rng = np.random.default_rng(8)
+    x = rng.uniform(-5, 5, (B, 1)).astype(np.float32)
+    y = (x ** 3 + rng.standard_normal((B, 1)) * 3).astype(np.float32)
+    rows = np.sort(rng.choice(B, 6, replace=False))
+    h = lambda t: t.detach().cpu().numpy()
+    lin = []
+    for p in params:
+        n, k = p["mu_w"].shape
+        layer = nn.Linear(k, n)
+        layer.load(p)
+        lin.append(layer)
+    capi.tc_status()
+    # forward, layer by layer, keeping every layer's input
+    mu, var, jcb = torch.from_numpy(x).cuda(), torch.zeros(B, 1, device="cuda"), None
+    inputs = []
+    for i, (layer, p) in enumerate(zip(lin, params)):
+        inputs.append((mu, var, jcb))
+        last = i == len(lin) - 1
+        out = layer.forward(mu, var, jcb, act=0 if last else capi.ACT_RELU)
+        rmu, rvar = oracle.linear_fwd(p["mu_w"], p["var_w"], p["mu_b"], p["var_b"],
+                                      np.ascontiguousarray(h(mu)[rows]), np.ascontiguousarray(h(var)[rows]))
+        if not last:
+            rmu, rvar, rj = G.relu_of(rmu, rvar)
+            assert np.array_equal(h(out[2])[rows], rj), f"layer {i}: ReLU Jacobian"
+        G.check(f"layer {i} mu", h(out[0])[rows], rmu, G.RTOL_MU)
+        G.check(f"layer {i} var", h(out[1])[rows], rvar, G.RTOL_VAR)
+        mu, var, jcb = out
+    # output innovation (observation variance 9), then backward layer by layer
+    rd = oracle.output_delta(h(mu), h(var), np.ones((B, 1), np.float32), y, np.full((B, 1), 9.0, np.float32))
+    dmu, dvar = torch.from_numpy(rd[0]).cuda(), torch.from_numpy(rd[1]).cuda()
+    for i in reversed(range(len(lin))):
+        layer, p = lin[i], params[i]
+        mu_a, _, j = inputs[i]
+        N = sizes[i + 1]
+        feats = np.sort(rng.choice(N, min(6, N), replace=False))
+        nxt = layer.backward(dmu, dvar, state_update=i > 0)
+        col = lambda t: np.ascontiguousarray(h(t)[:, feats])
+        r = oracle.linear_bwd_param(np.ascontiguousarray(p["var_w"][feats]), np.ascontiguousarray(p["var_b"][feats]),
+                                    h(mu_a), col(dmu), col(dvar))
+        got = [h(layer.delta_mu_w)[feats], h(layer.delta_var_w)[feats], h(layer.delta_mu_b)[feats],
+               h(layer.delta_var_b)[feats]]
+        for name, a, b, tol in zip(("dmu_w", "dvar_w", "dmu_b", "dvar_b"), got, r, (1e-5, 1e-4, 1e-5, 1e-4)):
+            G.check(f"layer {i} {name}", a, b, tol)
+        if i > 0:
+            rs = oracle.linear_bwd_state(p["mu_w"], np.ascontiguousarray(h(j)[rows]), np.ascontiguousarray(h(dmu)[rows]),
+                                         np.ascontiguousarray(h(dvar)[rows]))
+            G.check(f"layer {i} dmu_a", h(nxt[0])[rows], rs[0], G.RTOL_MU)
+            G.check(f"layer {i} dvar_a", h(nxt[1])[rows], rs[1], G.RTOL_VAR)
+            dmu, dvar = nxt
+        # capped update of the sampled features, from the GPU's own deltas
+        mw, vw = np.ascontiguousarray(p["mu_w"][feats]), np.ascontiguousarray(p["var_w"][feats])
+        oracle.param_update(B, mw, vw, np.ascontiguousarray(got[0]), np.ascontiguousarray(got[1]))
+        layer.step(B)
+        G.check(f"layer {i} mu_w after step", h(layer.mu_w)[feats], mw, G.RTOL_MU)
+        G.check(f"layer {i} var_w after step", h(layer.var_w)[feats], vw, G.RTOL_VAR)
+    assert capi.tc_status() == 0
+
+
 def test_deep_regression_mlp_steps(oracle):
     """Configuration 2 at reduced width (1 -> 512 -> 512 -> 512 -> 1, batch 256: the full 4096-wide network costs the CPU
     oracle minutes per step): x ~ U[-5, 5], y = x^3 + eps, eps ~ N(0, 9), observation variance 9; the hidden layers run
