@@ -24,6 +24,7 @@ _SIG = {
     "tagi_comm_register": [_p, _z],
     "tagi_comm_finalize_buckets": [_z],
     "tagi_comm_num_buckets": [],
+    "tagi_comm_num_tensors": [],
     "tagi_comm_bucket_of": [_i],
     "tagi_comm_tensor_ready": [_i, _p, _i],
     "tagi_comm_flush": [_p, _i],
@@ -36,7 +37,7 @@ _SIG = {
     "tagi_comm_set_max_ctas": [_i],
     "tagi_comm_destroy": [],
 }
-_RAW = {"tagi_comm_rank", "tagi_comm_world_size", "tagi_comm_num_buckets", "tagi_comm_bucket_of",
+_RAW = {"tagi_comm_rank", "tagi_comm_world_size", "tagi_comm_num_buckets", "tagi_comm_num_tensors", "tagi_comm_bucket_of",
         "tagi_comm_plan_buckets", "tagi_comm_register"}
 
 

@@ -285,6 +285,7 @@ int tagi_comm_finalize_buckets(size_t bucket_bytes) {
 }
 
 int tagi_comm_num_buckets(void) { return g ? (int)g->buckets.size() : 0; }
+int tagi_comm_num_tensors(void) { return g ? (int)g->tensors.size() : 0; }
 int tagi_comm_bucket_of(int i) { return (g && i >= 0 && i < (int)g->tensors.size()) ? g->tensors[i].bucket : -1; }
 
 int tagi_comm_tensor_ready(int i, void *compute_stream, int average) {

@@ -67,6 +67,7 @@ int tagi_comm_world_size(void);
 int tagi_comm_register(float *ptr, size_t count);
 int tagi_comm_finalize_buckets(size_t bucket_bytes);
 int tagi_comm_num_buckets(void);
+int tagi_comm_num_tensors(void); /* tensors registered so far */
 int tagi_comm_bucket_of(int tensor_index);
 
 /* Tell the communicator that tensor `tensor_index` has been written on `compute_stream`. When that completes a

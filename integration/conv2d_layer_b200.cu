@@ -8,6 +8,7 @@
 #include "conv2d_layer.h"
 #include "custom_logger.h"
 #include "param_init.h"
+#include "ddp_b200_hooks.h"
 #include "tagi_b200.h"
 
 namespace {
@@ -128,15 +129,24 @@ void Conv2dCuda::backward(BaseDeltaStates &input_delta_states, BaseDeltaStates &
     auto *dout = dynamic_cast<DeltaStateCuda *>(&output_delta_states);
     const tagi_conv2d_geom g = geometry_of(*this, static_cast<int>(input_delta_states.block_size));
     // parameters first, then states: the state pass overwrites the buffer the deltas may share in LayerBlock
-    if (param_update)
+    if (param_update) {
         require_ok(tagi_conv2d_bwd_param(&g, d_var_w, d_var_b, saved->d_mu_a, din->d_delta_mu, din->d_delta_var,
                                          d_delta_mu_w, d_delta_var_w, d_delta_mu_b, d_delta_var_b, nullptr));
+        // data-parallel runs: this layer's deltas may be exchanged from now on (no effect without a DDPSequential)
+        ddp_b200_deltas_ready(d_delta_mu_w);
+        ddp_b200_deltas_ready(d_delta_var_w);
+        if (bias) {
+            ddp_b200_deltas_ready(d_delta_mu_b);
+            ddp_b200_deltas_ready(d_delta_var_b);
+        }
+    }
     if (state_udapte)
         require_ok(tagi_conv2d_bwd_state(&g, d_mu_w, saved->d_jcb, din->d_delta_mu, din->d_delta_var, dout->d_delta_mu,
                                          dout->d_delta_var, nullptr));
 }
 
 std::unique_ptr<BaseLayer> Conv2dCuda::to_host() {
+    tagi_b200_raise_on_kernel_abort();  // this call synchronises anyway: report an aborted tensor-core launch here
     auto host = std::make_unique<Conv2d>(in_channels, out_channels, kernel_size, bias, stride, padding, padding_type,
                                          in_width, in_height, gain_w, gain_b, init_method);
     host->mu_w = mu_w;

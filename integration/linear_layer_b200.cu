@@ -8,6 +8,7 @@
 #include "custom_logger.h"
 #include "linear_layer.h"
 #include "param_init.h"
+#include "ddp_b200_hooks.h"
 #include "tagi_b200.h"
 
 namespace {
@@ -70,13 +71,22 @@ void LinearCuda::backward(BaseDeltaStates &input_delta_states, BaseDeltaStates &
     if (state_udapte)
         require_ok(tagi_linear_bwd_state(d_mu_w, saved->d_jcb, din->d_delta_mu, din->d_delta_var, batch, k, n,
                                          dout->d_delta_mu, dout->d_delta_var, nullptr));
-    if (param_update)
+    if (param_update) {
         require_ok(tagi_linear_bwd_param(d_var_w, d_var_b, saved->d_mu_a, din->d_delta_mu, din->d_delta_var, batch, k,
                                          n, bias ? 1 : 0, d_delta_mu_w, d_delta_var_w, d_delta_mu_b, d_delta_var_b,
                                          nullptr));
+        // data-parallel runs: this layer's deltas may be exchanged from now on (no effect without a DDPSequential)
+        ddp_b200_deltas_ready(d_delta_mu_w);
+        ddp_b200_deltas_ready(d_delta_var_w);
+        if (bias) {
+            ddp_b200_deltas_ready(d_delta_mu_b);
+            ddp_b200_deltas_ready(d_delta_var_b);
+        }
+    }
 }
 
 std::unique_ptr<BaseLayer> LinearCuda::to_host() {
+    tagi_b200_raise_on_kernel_abort();  // this call synchronises anyway: report an aborted tensor-core launch here
     auto host = std::make_unique<Linear>(input_size, output_size, bias, gain_w, gain_b, init_method);
     host->mu_w = mu_w;
     host->var_w = var_w;
