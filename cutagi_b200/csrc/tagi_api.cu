@@ -284,7 +284,9 @@ static int check_geom(const tagi_conv2d_geom *g) {
 
 size_t tagi_conv2d_workspace_bytes(const tagi_conv2d_geom *g) {
     if (check_geom(g) != TAGI_OK) return 0;
-    const size_t a = conv_tc_workspace_bytes(*g), b = conv_ffma_workspace_bytes(*g);
+    size_t a = conv_tc_workspace_bytes(*g), b = conv_ffma_workspace_bytes(*g);
+    const size_t c = conv_param_patch_workspace_bytes(*g);
+    a = a > c ? a : c;
     // BatchNorm statistics of the layer's output share the block: 16 bytes per channel and 4096-element slice
     const size_t bn = (size_t)g->fo * (((size_t)g->B * g->ho * g->wo + 4095) / 4096) * 16;
     const size_t m = a > b ? a : b;
@@ -385,6 +387,18 @@ int tagi_conv2d_bwd_param(const tagi_conv2d_geom *g, const float *var_w, const f
         TAGI_PTR(dvar_b);
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // Implicit GEMM on the tensor cores where the tensors can be read by TMA as they lie (image widths multiples of 4):
+    // no im2col matrix, no regrouped deltas. TAGI_B200_CONV_PARAM=explicit keeps the gather passes (for comparison).
+    static const bool explicit_param = [] {
+        const char *e = std::getenv("TAGI_B200_CONV_PARAM");
+        return e && !std::strcmp(e, "explicit");
+    }();
+    if (current_impl() != TAGI_IMPL_FFMA && !explicit_param && (long)g->B * g->ho * g->wo >= 1024 &&
+        conv_param_patch_supported(*g, {var_w, mu_a, dmu_z, dvar_z, dmu_w, dvar_w})) {
+        rc = conv2d_bwd_param_patch(*g, var_w, mu_a, dmu_z, dvar_z, dmu_w, dvar_w, st);
+        if (rc == TAGI_OK && g->has_bias) rc = conv_bias_delta(*g, var_b, dmu_z, dvar_z, dmu_b, dvar_b, st);
+        return rc;
+    }
     if (pick_conv_tc(__func__, *g, CONV_PASS_PARAM, {var_w, mu_a, dmu_z, dvar_z, dmu_w, dvar_w}, &rc)) {
         rc = conv2d_bwd_param_tc(*g, var_w, mu_a, dmu_z, dvar_z, dmu_w, dvar_w, st);
         if (rc == TAGI_OK && g->has_bias) rc = conv_bias_delta(*g, var_b, dmu_z, dvar_z, dmu_b, dvar_b, st);

@@ -111,6 +111,11 @@ int conv2d_bwd_state_tc(const tagi_conv2d_geom &g, const float *mu_w, const floa
                         const float *dvar_z, float *dmu_a, float *dvar_a, cudaStream_t st);
 int conv2d_bwd_param_tc(const tagi_conv2d_geom &g, const float *var_w, const float *mu_a, const float *dmu_z,
                         const float *dvar_z, float *dmu_w, float *dvar_w, cudaStream_t st);
+// Implicit-GEMM parameter pass on the tensor cores (tagi_conv_patch.cu): operands read by TMA as they lie in memory
+bool conv_param_patch_supported(const tagi_conv2d_geom &g, std::initializer_list<const void *> ptrs);
+size_t conv_param_patch_workspace_bytes(const tagi_conv2d_geom &g);
+int conv2d_bwd_param_patch(const tagi_conv2d_geom &g, const float *var_w, const float *mu_a, const float *dmu_z,
+                           const float *dvar_z, float *dmu_w, float *dvar_w, cudaStream_t st);
 int conv2d_bwd_param_noalloc(const tagi_conv2d_geom &g, const float *var_w, const float *var_b, const float *mu_a,
                              const float *dmu_z, const float *dvar_z, float *dmu_w, float *dvar_w, float *dmu_b,
                              float *dvar_b, cudaStream_t st);

@@ -123,6 +123,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const void *tmap,
         ::"r"(smem_dst), "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar))
         : "memory");
 }
+// 4-D tiled load (x innermost); same alignment rule for x. Coordinates outside the tensor read the fill value (zero).
+__device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const void *tmap, int x, int y, int z, int w, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+        ::"r"(smem_dst), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(w), "r"(smem_u32(bar))
+        : "memory");
+}
 __device__ __forceinline__ void prefetch_tmap(const void *tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
@@ -335,6 +342,11 @@ __device__ __forceinline__ void mma_commit_pair(uint64_t *bar) {
 #define TAGI_MMA_BWD_D2(CG, BS) \
     TAGI_MMA_HEAD TAGI_MMA(CG, 1, 1, 4, 1, BS, p2) TAGI_MMA(CG, 1, 1, 4, 2, BS, pt) TAGI_MMA(CG, 1, 3, 4, 1, BS, pt) "}"
 
+// Conv2d parameter pass with the roles swapped (tagi_conv_patch.cu): A tiles 0 x, 1 q = x^2, 2 x lo, 3 q lo ; raw B 0 dmu,
+// 1 dvar ; derived B 0 dmu lo, 1 dvar lo.  D1 = x.dmu (the three MMAs of TAGI_MMA_D1) ; D2 = q.dvar
+#define TAGI_MMA_CPARAM_D2(CG, BS) \
+    TAGI_MMA_HEAD TAGI_MMA(CG, 1, 1, 3, 1, BS, p2) TAGI_MMA(CG, 1, 1, 4, 1, BS, pt) TAGI_MMA(CG, 1, 3, 3, 1, BS, pt) "}"
+
 // CHAIN 1 or 2; BS = 512: B tiles of 8 KiB (one CTA); BS = 256: B half tiles of 4 KiB (CTA pairs, cta_group::2)
 template <bool FWD, int CHAIN>
 __device__ __forceinline__ void mma_kstep_ts(uint32_t d1, uint32_t d2, uint32_t at, uint32_t rbl, uint32_t dsl, uint32_t hi,
@@ -349,6 +361,12 @@ __device__ __forceinline__ void mma_kstep_pair(uint32_t d1, uint32_t d2, uint32_
     if (CHAIN == 1) asm volatile(TAGI_MMA_D1(2, 256) TAGI_MMA_OPERANDS);
     else if (FWD) asm volatile(TAGI_MMA_FWD_D2(2, 256) TAGI_MMA_OPERANDS);
     else asm volatile(TAGI_MMA_BWD_D2(2, 256) TAGI_MMA_OPERANDS);
+}
+template <int CHAIN>
+__device__ __forceinline__ void mma_kstep_cparam_pair(uint32_t d1, uint32_t d2, uint32_t at, uint32_t rbl, uint32_t dsl,
+                                                      uint32_t hi, uint32_t idesc, uint32_t f1, uint32_t f2) {
+    if (CHAIN == 1) asm volatile(TAGI_MMA_D1(2, 256) TAGI_MMA_OPERANDS);
+    else asm volatile(TAGI_MMA_CPARAM_D2(2, 256) TAGI_MMA_OPERANDS);
 }
 // low / high 32-bit words of a shared-memory matrix descriptor (see make_smem_desc)
 __device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
