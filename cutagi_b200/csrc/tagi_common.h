@@ -116,6 +116,13 @@ bool conv_param_patch_supported(const tagi_conv2d_geom &g, std::initializer_list
 size_t conv_param_patch_workspace_bytes(const tagi_conv2d_geom &g);
 int conv2d_bwd_param_patch(const tagi_conv2d_geom &g, const float *var_w, const float *mu_a, const float *dmu_z,
                            const float *dvar_z, float *dmu_w, float *dvar_w, cudaStream_t st);
+// Implicit-GEMM forward and stride-1 state pass with TMA-loaded patches (tagi_conv_patch.cu)
+bool conv_pix_patch_supported(const tagi_conv2d_geom &g, int pass, std::initializer_list<const void *> ptrs);
+size_t conv_pix_patch_workspace_bytes(const tagi_conv2d_geom &g);
+int conv2d_fwd_patch(const tagi_conv2d_geom &g, const float *mu_w, const float *var_w, const float *mu_b, const float *var_b,
+                     const float *mu_a, const float *var_a, float *mu_z, float *var_z, cudaStream_t st, float *relu_jcb);
+int conv2d_bwd_state_patch(const tagi_conv2d_geom &g, const float *mu_w, const float *jcb, const float *dmu_z,
+                           const float *dvar_z, float *dmu_a, float *dvar_a, cudaStream_t st);
 int conv2d_bwd_param_noalloc(const tagi_conv2d_geom &g, const float *var_w, const float *var_b, const float *mu_a,
                              const float *dmu_z, const float *dvar_z, float *dmu_w, float *dvar_w, float *dmu_b,
                              float *dvar_b, cudaStream_t st);

@@ -40,6 +40,8 @@ struct PatchParam {
     float *out1, *out2;   // [slice][fo][Kc]
     const float *scale;   // var_w when the contraction is not sliced, else null (raw partial sums)
     long slice_elems;
+    int ablate;           // timing diagnostics only (TAGI_B200_PATCH_ABLATE; results are wrong when set): bit 0 no
+                          // tensor-memory stores, bit 1 no B-side conversion, bit 2 no MMAs, bit 3 no patch reads
 };
 
 constexpr int P_NA = 4, P_NRAW_B = 2, P_NDER = 2;
@@ -49,14 +51,14 @@ size_t patch_param_smem(uint32_t a_slot) {
     return (size_t)RS * (a_slot + P_NRAW_B * HALF_BYTES) + (size_t)DS * P_NDER * HALF_BYTES + 1024 + 256;
 }
 
-template <int CH, int RS, int DS>
+template <int CH, int RS, int DS, int ACC>
 __global__ void __launch_bounds__(NTHREADS2 - 32, 1)
 tagi_tc_conv_param_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmD0,
                           const __grid_constant__ CUtensorMap tmD1, const PatchParam pp, const int bn, int *status) {
     constexpr int NA = P_NA, NDER = P_NDER;
     constexpr uint32_t DER_SLOT = NDER * HALF_BYTES;
     constexpr uint32_t NCOLS = 512;
-    constexpr uint32_t acc_stride = 128, A_COL0 = 256;
+    constexpr uint32_t acc_stride = ACC, A_COL0 = 2 * ACC;   // ACC >= bn: columns between the two accumulators
     static_assert(A_COL0 + DS * NA * BK <= 512, "tensor memory: accumulators + A slots");
     const uint32_t RAW_SLOT = pp.a_slot + P_NRAW_B * HALF_BYTES;
     const uint32_t IDESC = make_idesc_tf32(256, bn, 0, 0);
@@ -79,6 +81,7 @@ tagi_tc_conv_param_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
     const int c0 = tile * pp.CT;
     const int col0 = (blockIdx.x >> 1) * bn;                      // the pair's output channels
     const int brow0 = col0 + (int)cta * half;                     // this CTA's half of them (B rows)
+    const uint32_t b_bytes = (uint32_t)half * 64;                 // a delta tile holds exactly this CTA's half of the columns
     const int kb = (int)blockIdx.z * pp.slabs_per_slice;          // first slab of this slice
     const int nk = min(pp.total_slabs - kb, pp.slabs_per_slice);
     const int chunk_len = CH > 0 ? CH : nk;
@@ -112,7 +115,7 @@ tagi_tc_conv_param_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
                     break;
                 const int t = kb + it;                                  // slab -> (image, output row, 16-pixel chunk)
                 const int xc = t % pp.nxc, rr = t / pp.nxc, oy = rr % pp.ho, b = rr / pp.ho;
-                mbar_arrive_expect_tx(raw_full + r, pp.a_bytes + P_NRAW_B * HALF_BYTES);
+                mbar_arrive_expect_tx(raw_full + r, pp.a_bytes + P_NRAW_B * b_bytes);
                 const uint32_t st = raw_base + r * RAW_SLOT;
                 tma_load_4d(st, &tmX, xc * 16 * pp.stride + pp.x0, oy * pp.stride + pp.y0, c0, b, raw_full + r);
                 tma_load_4d(st + pp.a_slot, &tmD0, xc * 16, oy, brow0, b, raw_full + r);
@@ -142,7 +145,8 @@ tagi_tc_conv_param_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
                 constexpr uint32_t LBO = 16, KSTEP = 32 >> 4;
                 constexpr uint32_t HI = desc_hi(512, SWZ_64B);
                 const uint32_t rbl = desc_lo(rb, LBO), dsl = desc_lo(ds, LBO);
-                if (chain1) {
+                if (pp.ablate & 4) {
+                } else if (chain1) {
                     mma_kstep_cparam_pair<1>(d1, d2, at, rbl, dsl, HI, IDESC, f, f);
                     mma_kstep_cparam_pair<1>(d1, d2, at + 8, rbl + KSTEP, dsl + KSTEP, HI, IDESC, 1, 1);
                 } else {
@@ -178,15 +182,17 @@ tagi_tc_conv_param_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
         auto drain = [&](int c) -> bool {
             if (!mbar_wait(acc_full, c & 1, abort_flag, status, ST_TIMEOUT_ACC)) return false;
             tc_fence_after_sync();
+            if (h * 64 < ACC) {   // with narrow accumulators the second half of the converter warps holds no columns
 #pragma unroll
-            for (int blk = 0; blk < 2; blk++) {
-                float v[32];
-                tmem_ld_32x32(lane_addr + h * 64 + blk * 32, v);
+                for (int blk = 0; blk < 2; blk++) {
+                    float v[32];
+                    tmem_ld_32x32(lane_addr + h * 64 + blk * 32, v);
 #pragma unroll
-                for (int i = 0; i < 32; i++) sum1[blk * 32 + i] += v[i];
-                tmem_ld_32x32(lane_addr + acc_stride + h * 64 + blk * 32, v);
+                    for (int i = 0; i < 32; i++) sum1[blk * 32 + i] += v[i];
+                    tmem_ld_32x32(lane_addr + acc_stride + h * 64 + blk * 32, v);
 #pragma unroll
-                for (int i = 0; i < 32; i++) sum2[blk * 32 + i] += v[i];
+                    for (int i = 0; i < 32; i++) sum2[blk * 32 + i] += v[i];
+                }
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -217,24 +223,36 @@ tagi_tc_conv_param_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
 #pragma unroll
             for (int kh = 0; kh < 2; kh++) {  // the two 8-wide k steps: pixels kh*8 .. kh*8+7 of the slab
                 float x[8];
+                if (pp.ablate & 8) {
 #pragma unroll
-                for (int i = 0; i < 8; i++)
-                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(x[i]) : "r"(rs + row_off + (kh * 8 + i) * step_b));
+                    for (int i = 0; i < 8; i++) x[i] = (float)(it + i);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; i++)
+                        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(x[i]) : "r"(rs + row_off + (kh * 8 + i) * step_b));
+                }
                 const uint32_t at = lane_addr + A_COL0 + d * (NA * BK) + kh * 8;
                 float t0[8], t1[8], qq[8];
 #pragma unroll
                 for (int i = 0; i < 8; i++) qq[i] = x[i] * x[i], t0[i] = hi_part(x[i]), t1[i] = hi_part(qq[i]);
-                tmem_st_32x8(at + 0 * BK, t0);
-                tmem_st_32x8(at + 1 * BK, t1);
+                if (!(pp.ablate & 1)) {
+                    tmem_st_32x8(at + 0 * BK, t0);
+                    tmem_st_32x8(at + 1 * BK, t1);
+                }
 #pragma unroll
                 for (int i = 0; i < 8; i++) t0[i] = x[i] - t0[i], t1[i] = qq[i] - t1[i];
-                tmem_st_32x8(at + 2 * BK, t0);
-                tmem_st_32x8(at + 3 * BK, t1);
+                if (!(pp.ablate & 1)) {
+                    tmem_st_32x8(at + 2 * BK, t0);
+                    tmem_st_32x8(at + 3 * BK, t1);
+                } else if (t0[0] + t1[3] == 12345.678f) {
+                    tmem_st_32x8(at + 2 * BK, t0);   // keeps the arithmetic alive
+                }
             }
             // B halves (dmu_z, dvar_z tiles of this CTA's 64 channels): lo parts at the same swizzled offsets
 #pragma unroll
             for (int c = 0; c < 2; c++) {
                 const uint32_t o = gt * 16 + c * (HALF_BYTES / 2);
+                if ((pp.ablate & 2) || o >= b_bytes) break;
                 const float4 b0 = lds128(rb + o), b1 = lds128(rb + HALF_BYTES + o);
                 sts128(ds + 0 * HALF_BYTES + o, lo_part(b0));
                 sts128(ds + 1 * HALF_BYTES + o, lo_part(b1));
@@ -256,7 +274,7 @@ tagi_tc_conv_param_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
         // epilogue: row (c, tap) of the tile is weight column kc = c0 * k2 + arow; this thread holds 64 output channels
         // of it. out[co][kc]: for one co the 32 lanes of a warp write 32 consecutive kc (coalesced).
         const int kc = c0 * pp.k2 + arow;
-        if (ok && row_in_tile && kc < pp.Kc) {
+        if (ok && row_in_tile && kc < pp.Kc && h * 64 < bn) {
             float *o1 = pp.out1 + (long)blockIdx.z * pp.slice_elems + kc;
             float *o2 = pp.out2 + (long)blockIdx.z * pp.slice_elems + kc;
             const int cbase = col0 + h * 64, valid = min(bn - h * 64, pp.fo - cbase);
@@ -309,14 +327,386 @@ __global__ void __launch_bounds__(256) patch_reduce_slices_kernel(const float *_
     out2[i] = a2 * sc * sc;
 }
 
+// =====================================================================================================
+// Forward pass and stride-1 state pass as implicit GEMMs with TMA-loaded patches.
+//
+//   forward   rows = output pixels, columns = output channels, contraction over (tap, input channel):
+//             A(pixel (b, oy, ox); tap (ky, kx), ci) = mu_a / var_a [b][ci][oy - off + ky][ox - off + kx]
+//             B = the weights regrouped as [co][tap][ci] (K-major)
+//   state     rows = input pixels, columns = input channels, contraction over (tap, output channel):
+//             A(pixel (b, y, x); tap, co) = dmu_z / dvar_z [b][co][y + off - ky][x + off - kx]
+//             B = mu_w regrouped as [(tap, co)][ci] (MN-major)
+// A CTA's 128 rows are NI images x TR image rows x GW columns of the pixel grid (TR * GW <= 128; several whole images
+// per tile when an image has at most 64 pixels). One k-slab is 16 channels of one tap; the contraction runs channel
+// block by channel block, and inside a block over its k*k taps. The A operand of all k*k slabs of a channel block is ONE
+// box of the source tensor per operand, [PW columns][TR + k - 1 rows][16 channels][NI images], loaded once into a ring of
+// its own (two blocks deep) and read k*k times with the tap's shift: a tap moves the converter thread's read position by
+// (ky, kx) inside the patch. A TMA box must start on a 16-byte boundary, so the box always starts at the same aligned
+// column and is a few columns wider than the image. Zeros arrive for coordinates outside the image: the padding rule
+// without masks. Loading per tap instead cost 4.5 times the shared-memory fill traffic and left the kernel bound by the
+// L2's bandwidth. The converter thread of pixel (py, px) reads its 16 channel values at (c, py + ky, px + kx) and writes
+// the TF32 hi / lo (and mu^2 + var) operands to tensor memory; everything downstream (B-side conversion, MMAs, chunked
+// accumulation, barriers) is the Linear pair kernel's.
+// =====================================================================================================
+struct PixParam {
+    // pixel grid of the rows (output grid for the forward pass, input grid for the state pass) and tiling
+    int GH, GW, TR, NI, tiles_y, tiles_total, B;
+    // source tensor patches
+    int k, k2, cblocks;        // taps per side, taps, 16-channel blocks of the contraction (source channels / 16)
+    int sign, off;             // +1: source pixel = p - off + tap (forward); -1: p + off - tap (state)
+    int PW, PR, lead;          // patch row pitch in floats, rows per channel (TR + k - 1); `lead`: column of grid x = 0
+                               // for the smallest tap shift
+    int x0, y0;                // coordinates of the patch's first column (multiple of 4, may be negative) and of its
+                               // first row relative to the tile's first grid row
+    uint32_t a_bytes, a_slot;  // bytes of one operand's patch box; ring slot reserved for it (multiple of 1024)
+    int RS, AS;                // depth of the B ring and of the patch ring
+    // epilogue
+    float *out1, *out2, *out3; // [B][cols][GH*GW]; out3: ReLU Jacobian (forward with RELU)
+    const float *aux1, *aux2;  // forward: bias vectors (may be null); state: aux1 = Jacobian [B][cols][GH*GW] (may be null)
+    int cols;                  // output channels (forward) / input channels (state)
+};
+
+constexpr int PIX_MAX_RS = 8, PIX_MAX_AS = 3;
+
+template <int OP>
+size_t pix_smem(uint32_t a_slot, int AS, int RS, int DS) {
+    return (size_t)AS * 2 * a_slot + (size_t)RS * PairTraits<OP>::NRAW_B * HALF_BYTES +
+           (size_t)DS * PairTraits<OP>::NDER * HALF_BYTES + 1024 + 256;
+}
+
+// ACC: tensor-memory columns between the two accumulators (>= bn); DS derived slots
+template <int OP, int CH, int DS, int ACC, bool RELU>
+__global__ void __launch_bounds__(NTHREADS2 - 32, 1)
+tagi_tc_conv_pix_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
+                        const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
+                        const PixParam pp, const int bn, int *status) {
+    using T = OpTraits<OP>;
+    using S = PairTraits<OP>;
+    constexpr int NRAW_B = S::NRAW_B, NDER = S::NDER, NA = S::NA;
+    constexpr uint32_t DER_SLOT = NDER * HALF_BYTES;
+    constexpr uint32_t NCOLS = 512;
+    constexpr uint32_t acc_stride = ACC, A_COL0 = 2 * ACC;
+    static_assert(A_COL0 + DS * NA * BK <= 512, "tensor memory: accumulators + A slots");
+    const int RS = pp.RS, AS = pp.AS;
+    constexpr uint32_t RAW_SLOT = NRAW_B * HALF_BYTES;               // B ring slot: the raw B half tiles of one slab
+    const uint32_t A_SLOT = 2 * pp.a_slot;                           // patch ring slot: both operands of a channel block
+    const uint32_t IDESC = make_idesc_tf32(256, bn, 0, T::B_MN);
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *aligned = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t patch_base = smem_base, raw_base = patch_base + AS * A_SLOT, der_base = raw_base + RS * RAW_SLOT;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(aligned + (size_t)AS * A_SLOT + (size_t)RS * RAW_SLOT + (size_t)DS * DER_SLOT);
+    constexpr int LMAX = PIX_MAX_RS > DS ? PIX_MAX_RS : DS;
+    const int L = RS > DS ? RS : DS;
+    uint64_t *raw_full = bars, *stage_done = bars + PIX_MAX_RS, *conv_done = stage_done + LMAX;
+    uint64_t *acc_full = conv_done + DS, *acc_empty = acc_full + 1;
+    uint64_t *a_full = acc_empty + 1, *a_free = a_full + PIX_MAX_AS;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(a_free + PIX_MAX_AS);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t cta = cluster_ctarank();
+    const int half = bn / 2;
+    const int tile = blockIdx.y * 2 + (int)cta;                    // this CTA's pixel tile
+    const int bt = tile / pp.tiles_y, ytile = tile - bt * pp.tiles_y;
+    const int b0 = bt * pp.NI, py0 = ytile * pp.TR;                // first image and first grid row of the tile
+    const int col0 = (blockIdx.x >> 1) * bn;
+    const int brow0 = col0 + (int)cta * half;
+    const int nk = pp.k2 * pp.cblocks;
+    const int chunk_len = CH > 0 ? CH : nk;
+    // a B tile holds this CTA's half of the columns: K-major bn / 2 rows of 64 bytes, MN-major 2 KiB boxes of 32 rows
+    const int b_boxes = (half + 31) / 32;
+    const uint32_t b_bytes = T::B_MN ? (uint32_t)b_boxes * 2048 : (uint32_t)half * 64;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < RS; s++) mbar_init(raw_full + s, 1);
+        for (int s = 0; s < L; s++) mbar_init(stage_done + s, 2);
+        for (int s = 0; s < DS; s++) mbar_init(conv_done + s, NCONV_WARPS);
+        for (int s = 0; s < AS; s++) {
+            mbar_init(a_full + s, 1);
+            mbar_init(a_free + s, NCONV_WARPS);   // every converter warp of this CTA releases a patch once
+        }
+        mbar_init(acc_full, 2);
+        mbar_init(acc_empty, 2 * NCONV_WARPS);
+        *abort_flag = 0;
+        mbar_init_fence();
+        prefetch_tmap(&tmA0);
+        prefetch_tmap(&tmA1);
+        prefetch_tmap(&tmB0);
+        if (OP == OP_FWD) prefetch_tmap(&tmB1);
+    }
+    if (warp == 1) tmem_alloc_pair(tmem_slot, NCOLS);
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (each CTA for itself)
+        if (lane == 0) {
+            int tap = 0, cb = 0;   // slab it = cb * k2 + tap
+            for (int it = 0; it < nk; it++) {
+                if (tap == 0) {
+                    // the patch of channel block cb: both operands, once for all its taps
+                    const int a = cb % AS;
+                    if (cb >= AS && !mbar_wait(a_free + a, ((cb / AS) - 1) & 1, abort_flag, status, ST_TIMEOUT_EMPTY)) break;
+                    mbar_arrive_expect_tx(a_full + a, 2 * pp.a_bytes);
+                    const uint32_t pa = patch_base + a * A_SLOT;
+                    tma_load_4d(pa, &tmA0, pp.x0, py0 + pp.y0, cb * 16, b0, a_full + a);
+                    tma_load_4d(pa + pp.a_slot, &tmA1, pp.x0, py0 + pp.y0, cb * 16, b0, a_full + a);
+                }
+                const int r = it % RS;
+                if (it >= RS && !mbar_wait(stage_done + (it - RS) % L, ((it - RS) / L) & 1, abort_flag, status,
+                                           ST_TIMEOUT_EMPTY))
+                    break;
+                mbar_arrive_expect_tx(raw_full + r, NRAW_B * b_bytes);
+                const uint32_t st = raw_base + r * RAW_SLOT;
+                const int k0 = it * BK;
+                if (T::B_MN) {
+                    for (int gb = 0; gb < b_boxes; gb++)
+                        tma_load_2d(st + gb * 2048, &tmB0, brow0 + 32 * gb, k0, raw_full + r);
+                } else {
+                    tma_load_2d(st, &tmB0, k0, brow0, raw_full + r);
+                    if (OP == OP_FWD) tma_load_2d(st + HALF_BYTES, &tmB1, k0, brow0, raw_full + r);
+                }
+                if (++tap == pp.k2) tap = 0, cb++;
+            }
+        }
+    } else if (warp == 1 || warp == ISSUER2_WARP) {
+        // ------------------------------------------------------------------ MMA issuers (CTA 0): warp 1 -> D1, warp 10 -> D2
+        if (lane == 0 && cta == 0) {
+            const bool chain1 = warp == 1;
+            const uint32_t d1 = tmem, d2 = tmem + acc_stride;
+            uint32_t f = 0;
+            bool ok = true;
+            for (int it = 0; it < nk && ok; it++) {
+                const int r = it % RS, d = it % DS;
+                if (it > 0 && it % chunk_len == 0) {
+                    const int c = it / chunk_len;
+                    ok = mbar_wait_cluster(acc_empty, (c - 1) & 1, abort_flag, status, ST_TIMEOUT_ACC);
+                    if (!ok) break;
+                    f = 0;
+                }
+                ok = mbar_wait_cluster(conv_done + d, (it / DS) & 1, abort_flag, status, ST_TIMEOUT_CONV);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t rb = raw_base + r * RAW_SLOT, ds = der_base + d * DER_SLOT;
+                const uint32_t at = tmem + A_COL0 + d * (NA * BK);
+                constexpr uint32_t LBO = T::B_MN ? 2048 : 16, KSTEP = (T::B_MN ? 1024 : 32) >> 4;
+                constexpr uint32_t HI = desc_hi(512, T::B_MN ? SWZ_128B_BASE32B : SWZ_64B);
+                const uint32_t rbl = desc_lo(rb, LBO), dsl = desc_lo(ds, LBO);
+                if (chain1) {
+                    mma_kstep_pair<OP == OP_FWD, 1>(d1, d2, at, rbl, dsl, HI, IDESC, f, f);
+                    mma_kstep_pair<OP == OP_FWD, 1>(d1, d2, at + 8, rbl + KSTEP, dsl + KSTEP, HI, IDESC, 1, 1);
+                } else {
+                    mma_kstep_pair<OP == OP_FWD, 2>(d1, d2, at, rbl, dsl, HI, IDESC, f, f);
+                    mma_kstep_pair<OP == OP_FWD, 2>(d1, d2, at + 8, rbl + KSTEP, dsl + KSTEP, HI, IDESC, 1, 1);
+                }
+                f = 1;
+                mma_commit_pair(stage_done + it % L);
+                if (it % chunk_len == chunk_len - 1 || it == nk - 1) mma_commit_pair(acc_full);
+            }
+        }
+    } else if (warp >= 2 && warp < 2 + NCONV_WARPS) {
+        // ------------------------------------------------------------------ converters + accumulation + epilogue
+        const int ct = threadIdx.x - 64;
+        const int q = warp & 3;
+        const int h = (warp - 2) >> 2;
+        const int arow = q * 32 + lane;
+        const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16);
+        // this thread's pixel: image il of the tile, grid row pyl, grid column px
+        const int per_img = pp.TR * pp.GW;
+        const bool row_in_tile = arow < pp.NI * per_img;
+        const int mm = row_in_tile ? arow : 0;
+        const int il = mm / per_img, rem = mm - il * per_img, pyl = rem / pp.GW, px = rem - pyl * pp.GW;
+        // byte offset of (channel 0, patch row pyl, column px + lead) of image il inside a patch; a channel is cstride on
+        const uint32_t cstride = (uint32_t)(pp.PR * pp.PW * 4);
+        const uint32_t row_off = (uint32_t)(((il * 16 * pp.PR + pyl) * pp.PW + px + pp.lead) * 4);
+        int released = 0;   // channel blocks whose patch this warp has released
+        float sum1[64], sum2[64];
+#pragma unroll
+        for (int i = 0; i < 64; i++) sum1[i] = sum2[i] = 0.f;
+
+        auto drain = [&](int c) -> bool {
+            if (!mbar_wait(acc_full, c & 1, abort_flag, status, ST_TIMEOUT_ACC)) return false;
+            tc_fence_after_sync();
+            if (h * 64 < ACC) {   // with narrow accumulators the second half of the converter warps holds no columns
+#pragma unroll
+                for (int blk = 0; blk < 2; blk++) {
+                    float v[32];
+                    tmem_ld_32x32(lane_addr + h * 64 + blk * 32, v);
+#pragma unroll
+                    for (int i = 0; i < 32; i++) sum1[blk * 32 + i] += v[i];
+                    tmem_ld_32x32(lane_addr + acc_stride + h * 64 + blk * 32, v);
+#pragma unroll
+                    for (int i = 0; i < 32; i++) sum2[blk * 32 + i] += v[i];
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(acc_empty, 0);
+            return true;
+        };
+
+        bool ok = true;
+        int pending = -1, scanned = 0;
+        auto note_chunk_ends = [&](int upto) {
+            for (int sl = scanned; sl <= upto && sl < nk && ok; sl++)
+                if (sl % chunk_len == chunk_len - 1 || sl == nk - 1) {
+                    if (pending >= 0) ok = drain(pending);
+                    pending = sl / chunk_len;
+                }
+            scanned = upto + 1;
+        };
+        const int gt = ct & 127;
+        for (int it = h; it < nk && ok; it += 2) {
+            const int r = it % RS, d = it % DS;
+            ok = mbar_wait(raw_full + r, (it / RS) & 1, abort_flag, status, ST_TIMEOUT_RAW) &&
+                 (it < DS || mbar_wait(stage_done + (it - DS) % L, ((it - DS) / L) & 1, abort_flag, status,
+                                       ST_TIMEOUT_EMPTY));
+            if (!ok) break;
+            const uint32_t rb = raw_base + r * RAW_SLOT, ds = der_base + d * DER_SLOT;
+            // slab = (channel block cb, tap): the tap moves this thread's read position inside the block's patch
+            const int cb = it / pp.k2, tap = it - cb * pp.k2, ky = tap / pp.k, kx = tap - ky * pp.k;
+            ok = mbar_wait(a_full + cb % AS, (cb / AS) & 1, abort_flag, status, ST_TIMEOUT_RAW);
+            if (!ok) break;
+            const int sy = pp.sign > 0 ? ky : pp.k - 1 - ky, sx = pp.sign > 0 ? kx : pp.k - 1 - kx;
+            const uint32_t src = patch_base + (cb % AS) * A_SLOT + row_off + (uint32_t)((sy * pp.PW + sx) * 4);
+
+#pragma unroll
+            for (int kh = 0; kh < 2; kh++) {  // channels kh*8 .. kh*8+7 of the slab
+                float a0[8], a1[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const uint32_t o = src + (kh * 8 + i) * cstride;
+                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(a0[i]) : "r"(o));
+                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(a1[i]) : "r"(o + pp.a_slot));
+                }
+                const uint32_t at = lane_addr + A_COL0 + d * (NA * BK) + kh * 8;
+                float t0[8], t1[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) t0[i] = hi_part(a0[i]), t1[i] = hi_part(a1[i]);
+                tmem_st_32x8(at + 0 * BK, t0);
+                tmem_st_32x8(at + 1 * BK, t1);
+#pragma unroll
+                for (int i = 0; i < 8; i++) t0[i] = a0[i] - t0[i], t1[i] = a1[i] - t1[i];
+                tmem_st_32x8(at + 2 * BK, t0);
+                tmem_st_32x8(at + 3 * BK, t1);
+                if (OP == OP_FWD) {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const float sq = fmaf(a0[i], a0[i], a1[i]);
+                        t0[i] = hi_part(sq);
+                        t1[i] = sq - t0[i];
+                    }
+                    tmem_st_32x8(at + 4 * BK, t0);
+                    tmem_st_32x8(at + 5 * BK, t1);
+                }
+            }
+            {
+                // This warp's next slab is it + 2: the patches of all blocks below that slab's block are no longer
+                // read by it (its slabs come in increasing order), whether or not it had a slab in them.
+                const int nb = min((it + 2) / pp.k2, pp.cblocks);
+                __syncwarp();
+                for (; released < nb; released++)
+                    if (lane == 0) mbar_arrive(a_free + released % AS);
+            }
+            // B halves: two 16-byte chunks per thread of the group
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                const uint32_t o = gt * 16 + c * (HALF_BYTES / 2);
+                if (o >= b_bytes) break;
+                if (OP == OP_FWD) {
+                    const float4 b0 = lds128(rb + o), b1 = lds128(rb + HALF_BYTES + o);
+                    const float4 qq = make_float4(b0.x * b0.x, b0.y * b0.y, b0.z * b0.z, b0.w * b0.w);
+                    sts128(ds + 0 * HALF_BYTES + o, lo_part(b0));
+                    sts128(ds + 1 * HALF_BYTES + o, lo_part(b1));
+                    sts128(ds + 2 * HALF_BYTES + o, qq);
+                    sts128(ds + 3 * HALF_BYTES + o, lo_part(qq));
+                } else {
+                    const float4 w = lds128(rb + o);
+                    const float4 qq = make_float4(w.x * w.x, w.y * w.y, w.z * w.z, w.w * w.w);
+                    sts128(ds + 0 * HALF_BYTES + o, lo_part(w));
+                    sts128(ds + 1 * HALF_BYTES + o, qq);
+                    sts128(ds + 2 * HALF_BYTES + o, lo_part(qq));
+                }
+            }
+            fence_proxy_async_smem();
+            tmem_wait_st();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(conv_done + d, 0);
+            if (pending >= 0) {
+                ok = drain(pending);
+                pending = -1;
+            }
+            note_chunk_ends(it + 1);
+        }
+        if (ok) note_chunk_ends(nk - 1);
+        if (ok && pending >= 0) ok = drain(pending);
+        // (patches still unreleased here belong to the last blocks: nobody waits for them)
+
+        // epilogue: [image][channel][pixel]; the 32 lanes of a warp hold consecutive pixels, so each channel's store is
+        // (mostly) one contiguous run
+        const int b = b0 + il, py = py0 + pyl;
+        if (ok && row_in_tile && b < pp.B && py < pp.GH && h * 64 < bn) {
+            const long npix = (long)pp.GH * pp.GW;
+            const long base = (long)b * pp.cols * npix + (long)py * pp.GW + px;
+            const int cbase = col0 + h * 64, valid = min(bn - h * 64, pp.cols - cbase);
+#pragma unroll
+            for (int i0 = 0; i0 < 64; i0 += 8) {
+                float sc[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    sc[u] = 1.f;
+                    if (OP != OP_FWD && pp.aux1 && i0 + u < valid) sc[u] = __ldg(pp.aux1 + base + (long)(cbase + i0 + u) * npix);
+                }
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    if (i0 + u >= valid) continue;
+                    const int col = cbase + i0 + u;
+                    const long idx = base + (long)col * npix;
+                    float o1 = sum1[i0 + u], o2 = sum2[i0 + u];
+                    if (OP == OP_FWD) {
+                        if (pp.aux1) {
+                            o1 += __ldg(pp.aux1 + col);
+                            o2 += __ldg(pp.aux2 + col);
+                        }
+                    } else {
+                        o1 *= sc[u];
+                        o2 = o2 * sc[u] * sc[u];
+                    }
+                    if (RELU) __stcs(pp.out3 + idx, relu_moments(o1, o2));
+                    __stcs(pp.out1 + idx, o1);
+                    __stcs(pp.out2 + idx, o2);
+                }
+            }
+        }
+    }
+    __syncwarp();
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) {
+        if (*abort_flag) {
+            const long long t0 = clock64();
+            while (clock64() - t0 < 4000000LL) {
+            }
+        }
+        tmem_dealloc_pair(tmem, NCOLS);
+    }
+}
+
 // 4-D tensor map over a [B][C][H][W] FP32 tensor
 int make_tmap_nchw(CUtensorMap *tm, const float *ptr, int W, int H, int C, int B, unsigned bx, unsigned by, unsigned bc,
-                   CUtensorMapSwizzle swz) {
+                   CUtensorMapSwizzle swz, unsigned bb = 1) {
     EncodeTiledFn fn = tc_encode_fn();
     if (!fn) return fail(TAGI_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[4] = {(cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)C, (cuuint64_t)B};
     cuuint64_t strides[3] = {(cuuint64_t)W * 4, (cuuint64_t)W * H * 4, (cuuint64_t)W * H * C * 4};
-    cuuint32_t box[4] = {bx, by, bc, 1};
+    cuuint32_t box[4] = {bx, by, bc, bb};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(ptr), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -375,6 +765,152 @@ bool plan_param(const tagi_conv2d_geom &g, ParamPlan *out) {
     return true;
 }
 
+// 2-D tensor map over a row-major FP32 matrix [outer][inner] (the regrouped weights): K-major half tiles are boxes of
+// 16 x 64 in the 64-byte swizzle, MN-major ones boxes of 32 x 16 in the 128-byte swizzle with 32-byte atoms
+int make_tmap_weights(CUtensorMap *tm, const float *ptr, uint64_t inner, uint64_t outer, bool mn_major, unsigned rows = 64) {
+    EncodeTiledFn fn = tc_encode_fn();
+    if (!fn) return fail(TAGI_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {inner * sizeof(float)};
+    cuuint32_t box[2] = {mn_major ? 32u : (cuuint32_t)BK, mn_major ? (cuuint32_t)BK : (cuuint32_t)rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_64B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(TAGI_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+    return TAGI_OK;
+}
+
+// The contraction index of the patch kernels is (channel block cb, tap, channel cl inside the block), ci = cb*16 + cl.
+// forward: w2[co][(cb * k2 + tap) * 16 + cl] = w[co][ci * k2 + tap] for the means and the variances
+__global__ void __launch_bounds__(256) regroup_weights_fwd_kernel(const float *__restrict__ w0, const float *__restrict__ w1,
+                                                                  int fo, int fi, int k2, float *__restrict__ o0,
+                                                                  float *__restrict__ o1) {
+    const long total = (long)fo * fi * k2;
+    const int cblocks = fi / 16;
+    for (long t = (long)blockIdx.x * 256 + threadIdx.x; t < total; t += (long)gridDim.x * 256) {
+        const int cl = (int)(t & 15);
+        long r = t >> 4;
+        const int tap = (int)(r % k2);
+        r /= k2;
+        const int cb = (int)(r % cblocks), co = (int)(r / cblocks);
+        const long src = ((long)co * fi + cb * 16 + cl) * k2 + tap;
+        o0[t] = __ldg(w0 + src);
+        o1[t] = __ldg(w1 + src);
+    }
+}
+// state pass (contraction over output channels co = cb*16 + cl): w2[(cb * k2 + tap) * 16 + cl][ci] = w[co][ci * k2 + tap]
+__global__ void __launch_bounds__(256) regroup_weights_state_kernel(const float *__restrict__ w, int fo, int fi, int k2,
+                                                                    float *__restrict__ o) {
+    const long total = (long)fo * fi * k2;
+    for (long t = (long)blockIdx.x * 256 + threadIdx.x; t < total; t += (long)gridDim.x * 256) {
+        const int ci = (int)(t % fi);
+        long r = t / fi;
+        const int cl = (int)(r & 15);
+        r >>= 4;
+        const int tap = (int)(r % k2), cb = (int)(r / k2);
+        o[t] = __ldg(w + ((long)(cb * 16 + cl) * fi + ci) * k2 + tap);
+    }
+}
+
+struct PixPlan {
+    PixParam pp;
+    int bn, col_tiles, row_pairs, src_C, src_H, src_W;
+};
+
+inline int floor4(int v) { return v >= 0 ? v & ~3 : -(((-v) + 3) & ~3); }
+
+// pass: CONV_PASS_FWD or CONV_PASS_STATE
+bool plan_pix(const tagi_conv2d_geom &g, int pass, PixPlan *out) {
+    if (g.stride != 1) return false;
+    const int off = g.pad_type == 1 ? g.pad : 0;
+    const bool fwd = pass == CONV_PASS_FWD;
+    PixParam &p = out->pp;
+    p.GH = fwd ? g.ho : g.hi, p.GW = fwd ? g.wo : g.wi, p.B = g.B;
+    out->src_C = fwd ? g.fi : g.fo, out->src_H = fwd ? g.hi : g.ho, out->src_W = fwd ? g.wi : g.wo;
+    p.cols = fwd ? g.fo : g.fi;
+    if (out->src_C % 16 || out->src_W % 4 || p.GW > 128 || p.cols < 16 || p.cols % 4) return false;
+    p.k = g.k, p.k2 = g.k * g.k, p.cblocks = out->src_C / 16;
+    p.sign = fwd ? +1 : -1, p.off = off;
+    if (p.GH * p.GW <= 64) {
+        p.NI = 128 / (p.GH * p.GW), p.TR = p.GH;
+    } else {
+        p.NI = 1, p.TR = 128 / p.GW < p.GH ? 128 / p.GW : p.GH;
+    }
+    if (p.NI > g.B) p.NI = g.B;
+    p.tiles_y = (p.GH + p.TR - 1) / p.TR;
+    p.tiles_total = ((g.B + p.NI - 1) / p.NI) * p.tiles_y;
+    // x shift of a tap: forward kx - off, state off - kx; the box starts at the smallest shift rounded down to 16 bytes
+    const int dxmin = fwd ? -off : off - (g.k - 1);
+    p.x0 = floor4(dxmin);
+    p.lead = dxmin - p.x0;
+    p.PW = (p.GW - 1 + g.k - 1 + p.lead + 1 + 3) & ~3;
+    p.PR = p.TR + g.k - 1;
+    p.y0 = dxmin;   // the smallest tap shift is the same in y
+    if (p.PW > 256 || p.PR > 256) return false;
+    p.a_bytes = (uint32_t)p.PW * p.PR * 16 * p.NI * 4;
+    p.a_slot = (p.a_bytes + 1023u) & ~1023u;
+    if (p.a_slot > 24 * 1024) return false;
+    int bn = p.cols <= 128 ? ((p.cols + 15) / 16) * 16 : 128;
+    if (p.cols > 128) {
+        long best = -1;
+        for (int w = 128; w >= 64; w -= 16) {
+            const long waste = (long)((p.cols + w - 1) / w) * w - p.cols;
+            if (best < 0 || waste < best) best = waste, bn = w;
+        }
+    }
+    out->bn = bn;
+    out->col_tiles = (p.cols + bn - 1) / bn;
+    out->row_pairs = (p.tiles_total + 1) / 2;
+    return true;
+}
+
+template <int OP, int DS, int ACC>
+int launch_pix(const CUtensorMap &a0, const CUtensorMap &a1, const CUtensorMap &b0, const CUtensorMap &b1, PixPlan &plan,
+               bool relu, cudaStream_t st) {
+    int *status = tc_status_word();
+    if (!status) return fail(TAGI_ERR_CUDA, "cannot allocate the tensor-core status word");
+    PixParam &p = plan.pp;
+    // rings: two patch slots (three when they are small), then as many B slots as fit beside the derived ring
+    const size_t budget = 227 * 1024 - 1280;
+    const size_t der = (size_t)DS * PairTraits<OP>::NDER * HALF_BYTES;
+    const size_t raw = (size_t)PairTraits<OP>::NRAW_B * HALF_BYTES;
+    p.AS = 2 * (size_t)p.a_slot * 3 + der + 4 * raw <= budget ? 3 : 2;
+    long rs = ((long)budget - (long)der - (long)p.AS * 2 * p.a_slot) / (long)raw;
+    if (rs > PIX_MAX_RS) rs = PIX_MAX_RS;
+    if (rs < 3) return fail(TAGI_ERR_UNSUPPORTED, "patch too large for the shared-memory rings");
+    p.RS = (int)rs;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (unsigned)plan.col_tiles, (unsigned)plan.row_pairs, 1);
+    cfg.blockDim = dim3(NTHREADS2 - 32);
+    cfg.stream = st;
+    cfg.dynamicSmemBytes = pix_smem<OP>(p.a_slot, p.AS, p.RS, DS);
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    cudaError_t e;
+#define TAGI_PIX_LAUNCH(CHV, RELUV)                                                                              \
+    do {                                                                                                         \
+        auto kfn = tagi_tc_conv_pix_kernel<OP, CHV, DS, ACC, RELUV>;                                             \
+        e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);                  \
+        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");                                       \
+        e = cudaLaunchKernelEx(&cfg, kfn, a0, a1, b0, b1, p, plan.bn, status);                                   \
+    } while (0)
+    if (OP == OP_FWD && relu) {
+        if (tc_chunked()) TAGI_PIX_LAUNCH(CHUNK_STAGES, true); else TAGI_PIX_LAUNCH(0, true);
+    } else {
+        if (tc_chunked()) TAGI_PIX_LAUNCH(CHUNK_STAGES, false); else TAGI_PIX_LAUNCH(0, false);
+    }
+#undef TAGI_PIX_LAUNCH
+    if (e != cudaSuccess) return cuda_fail(e, "implicit Conv2d kernel launch");
+    return TAGI_OK;
+}
+
 }  // namespace
 
 bool conv_param_patch_supported(const tagi_conv2d_geom &g, std::initializer_list<const void *> ptrs) {
@@ -400,10 +936,13 @@ int conv2d_bwd_param_patch(const tagi_conv2d_geom &g, const float *var_w, const 
     CUtensorMap tx, td0, td1;
     int rc;
     if ((rc = make_tmap_nchw(&tx, mu_a, g.wi, g.hi, g.fi, g.B, p.PW, g.k, p.CT, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
-    if ((rc = make_tmap_nchw(&td0, dmu_z, g.wo, g.ho, g.fo, g.B, 16, 1, 64, CU_TENSOR_MAP_SWIZZLE_64B))) return rc;
-    if ((rc = make_tmap_nchw(&td1, dvar_z, g.wo, g.ho, g.fo, g.B, 16, 1, 64, CU_TENSOR_MAP_SWIZZLE_64B))) return rc;
+    // a CTA stages exactly its half of the pair's output channels: box of bn / 2 channel rows
+    if ((rc = make_tmap_nchw(&td0, dmu_z, g.wo, g.ho, g.fo, g.B, 16, 1, plan.bn / 2, CU_TENSOR_MAP_SWIZZLE_64B))) return rc;
+    if ((rc = make_tmap_nchw(&td1, dvar_z, g.wo, g.ho, g.fo, g.B, 16, 1, plan.bn / 2, CU_TENSOR_MAP_SWIZZLE_64B))) return rc;
     const long slice = (long)g.fo * p.Kc;
     p.slice_elems = slice;
+    static const int ablate = [] { const char *v = getenv("TAGI_B200_PATCH_ABLATE"); return v ? atoi(v) : 0; }();
+    p.ablate = ablate;
     if (plan.slices > 1) {
         float *ws = nullptr;
         if ((rc = conv_scratch((size_t)2 * plan.slices * slice * sizeof(float), &ws, st)) != TAGI_OK) return rc;
@@ -422,18 +961,27 @@ int conv2d_bwd_param_patch(const tagi_conv2d_geom &g, const float *var_w, const 
     attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    constexpr int RS = 6, DS = 4;
-    cfg.dynamicSmemBytes = patch_param_smem<RS, DS>(p.a_slot);
-    if (cfg.dynamicSmemBytes > 227 * 1024) return fail(TAGI_ERR_UNSUPPORTED, "patch too large for the shared-memory ring");
-    cudaError_t e;
-#define TAGI_PATCH_LAUNCH(CHV)                                                                                   \
+    cudaError_t e = cudaSuccess;
+    // ring depths: RS raw slots (patch + two delta tiles), DS slots of A operands in tensor memory, which holds the two
+    // accumulators (ACC columns each) and DS * 64 columns of A operands: six slots when the output tile is at most 64 wide
+#define TAGI_PATCH_LAUNCH(CHV, RSV, DSV, ACCV)                                                                   \
     do {                                                                                                         \
-        auto kfn = tagi_tc_conv_param_kernel<CHV, RS, DS>;                                                       \
+        auto kfn = tagi_tc_conv_param_kernel<CHV, RSV, DSV, ACCV>;                                               \
+        cfg.dynamicSmemBytes = patch_param_smem<RSV, DSV>(p.a_slot);                                             \
+        if (cfg.dynamicSmemBytes > 227 * 1024) return fail(TAGI_ERR_UNSUPPORTED, "patch too large for the shared-memory ring"); \
         e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);                  \
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");                                       \
         e = cudaLaunchKernelEx(&cfg, kfn, tx, td0, td1, p, plan.bn, status);                                     \
     } while (0)
-    if (tc_chunked()) TAGI_PATCH_LAUNCH(CHUNK_STAGES); else TAGI_PATCH_LAUNCH(0);
+    static const int cfg_id = [] { const char *v = getenv("TAGI_B200_PATCH_CFG"); return v ? atoi(v) : 0; }();
+    const bool deep = p.a_slot <= 8 * 1024;
+    if (plan.bn <= 64 && cfg_id != 1) {
+        if (deep && cfg_id != 2) { if (tc_chunked()) TAGI_PATCH_LAUNCH(CHUNK_STAGES, 10, 6, 64); else TAGI_PATCH_LAUNCH(0, 10, 6, 64); }
+        else { if (tc_chunked()) TAGI_PATCH_LAUNCH(CHUNK_STAGES, 6, 6, 64); else TAGI_PATCH_LAUNCH(0, 6, 6, 64); }
+    } else {
+        if (deep && cfg_id != 1 && cfg_id != 2) { if (tc_chunked()) TAGI_PATCH_LAUNCH(CHUNK_STAGES, 10, 4, 128); else TAGI_PATCH_LAUNCH(0, 10, 4, 128); }
+        else { if (tc_chunked()) TAGI_PATCH_LAUNCH(CHUNK_STAGES, 6, 4, 128); else TAGI_PATCH_LAUNCH(0, 6, 4, 128); }
+    }
 #undef TAGI_PATCH_LAUNCH
     if (e != cudaSuccess) return cuda_fail(e, "implicit Conv2d parameter pass launch");
     if (plan.slices > 1) {
@@ -443,6 +991,64 @@ int conv2d_bwd_param_patch(const tagi_conv2d_geom &g, const float *var_w, const 
         if (e != cudaSuccess) return cuda_fail(e, "patch_reduce_slices_kernel launch");
     }
     return TAGI_OK;
+}
+
+bool conv_pix_patch_supported(const tagi_conv2d_geom &g, int pass, std::initializer_list<const void *> ptrs) {
+    for (const void *q : ptrs)
+        if (q && !aligned16(q)) return false;
+    PixPlan plan;
+    return plan_pix(g, pass, &plan);
+}
+
+size_t conv_pix_patch_workspace_bytes(const tagi_conv2d_geom &g) {
+    return (size_t)2 * g.fo * g.fi * g.k * g.k * sizeof(float);   // the regrouped weights (means and variances)
+}
+
+int conv2d_fwd_patch(const tagi_conv2d_geom &g, const float *mu_w, const float *var_w, const float *mu_b, const float *var_b,
+                     const float *mu_a, const float *var_a, float *mu_z, float *var_z, cudaStream_t st, float *relu_jcb) {
+    PixPlan plan;
+    if (!plan_pix(g, CONV_PASS_FWD, &plan)) return fail(TAGI_ERR_UNSUPPORTED, "Conv2d geometry not supported by the implicit forward pass");
+    PixParam &p = plan.pp;
+    const long nw = (long)g.fo * g.fi * p.k2;
+    float *ws = nullptr;
+    int rc = conv_scratch((size_t)2 * nw * sizeof(float), &ws, st);
+    if (rc != TAGI_OK) return rc;
+    const long blocks = (nw + 255) / 256;
+    regroup_weights_fwd_kernel<<<(unsigned)(blocks < 148 * 8 ? blocks : 148 * 8), 256, 0, st>>>(mu_w, var_w, g.fo, g.fi, p.k2, ws,
+                                                                                             ws + nw);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "regroup_weights_fwd_kernel launch");
+    CUtensorMap a0, a1, b0, b1;
+    if ((rc = make_tmap_nchw(&a0, mu_a, g.wi, g.hi, g.fi, g.B, p.PW, p.PR, 16, CU_TENSOR_MAP_SWIZZLE_NONE, p.NI))) return rc;
+    if ((rc = make_tmap_nchw(&a1, var_a, g.wi, g.hi, g.fi, g.B, p.PW, p.PR, 16, CU_TENSOR_MAP_SWIZZLE_NONE, p.NI))) return rc;
+    if ((rc = make_tmap_weights(&b0, ws, (uint64_t)g.fi * p.k2, g.fo, false, plan.bn / 2))) return rc;
+    if ((rc = make_tmap_weights(&b1, ws + nw, (uint64_t)g.fi * p.k2, g.fo, false, plan.bn / 2))) return rc;
+    p.out1 = mu_z, p.out2 = var_z, p.out3 = relu_jcb, p.aux1 = mu_b, p.aux2 = var_b;
+    if (plan.bn <= 64) return launch_pix<OP_FWD, 4, 64>(a0, a1, b0, b1, plan, relu_jcb != nullptr, st);
+    if (plan.bn <= 112) return launch_pix<OP_FWD, 3, 112>(a0, a1, b0, b1, plan, relu_jcb != nullptr, st);
+    return launch_pix<OP_FWD, 2, 128>(a0, a1, b0, b1, plan, relu_jcb != nullptr, st);
+}
+
+int conv2d_bwd_state_patch(const tagi_conv2d_geom &g, const float *mu_w, const float *jcb, const float *dmu_z,
+                           const float *dvar_z, float *dmu_a, float *dvar_a, cudaStream_t st) {
+    PixPlan plan;
+    if (!plan_pix(g, CONV_PASS_STATE, &plan)) return fail(TAGI_ERR_UNSUPPORTED, "Conv2d geometry not supported by the implicit state pass");
+    PixParam &p = plan.pp;
+    const long nw = (long)g.fo * g.fi * p.k2;
+    float *ws = nullptr;
+    int rc = conv_scratch((size_t)nw * sizeof(float), &ws, st);
+    if (rc != TAGI_OK) return rc;
+    const long blocks = (nw + 255) / 256;
+    regroup_weights_state_kernel<<<(unsigned)(blocks < 148 * 8 ? blocks : 148 * 8), 256, 0, st>>>(mu_w, g.fo, g.fi, p.k2, ws);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "regroup_weights_state_kernel launch");
+    CUtensorMap a0, a1, b0;
+    if ((rc = make_tmap_nchw(&a0, dmu_z, g.wo, g.ho, g.fo, g.B, p.PW, p.PR, 16, CU_TENSOR_MAP_SWIZZLE_NONE, p.NI))) return rc;
+    if ((rc = make_tmap_nchw(&a1, dvar_z, g.wo, g.ho, g.fo, g.B, p.PW, p.PR, 16, CU_TENSOR_MAP_SWIZZLE_NONE, p.NI))) return rc;
+    if ((rc = make_tmap_weights(&b0, ws, g.fi, (uint64_t)g.fo * p.k2, true))) return rc;
+    p.out1 = dmu_a, p.out2 = dvar_a, p.out3 = nullptr, p.aux1 = jcb, p.aux2 = nullptr;
+    if (plan.bn <= 64) return launch_pix<OP_BWD_STATE, 6, 64>(a0, a1, b0, b0, plan, false, st);
+    return launch_pix<OP_BWD_STATE, 4, 128>(a0, a1, b0, b0, plan, false, st);
 }
 
 }  // namespace tagi

@@ -234,11 +234,24 @@ inline int ok_or(cudaError_t e, const char *what) { return e == cudaSuccess ? TA
 // again, so this pays while the output is at most two tiles (256 columns) wide: measured on the ResNet-18 shapes,
 // 64 / 128 channels gain 30 % against the gather pass through scratch memory, 256 channels are level, 512 channels lose
 // 10-20 %. TAGI_B200_CONV_GATHER=explicit / implicit forces one of the two, for comparison.
-inline bool implicit_ok(const G &g, long rows, int cols) {
+inline int gather_mode() {
     static const int mode = [] {
         const char *e = getenv("TAGI_B200_CONV_GATHER");
-        return !e ? 0 : std::string(e) == "explicit" ? 1 : std::string(e) == "implicit" ? 2 : 0;
+        return !e ? 0 : std::string(e) == "explicit" ? 1 : std::string(e) == "implicit" ? 2 : std::string(e) == "patch" ? 3 : 0;
     }();
+    return mode;
+}
+// The patch kernels (tagi_conv_patch.cu) read the operand of a k-slab as one TMA box and take precedence where they
+// apply (stride 1, 16 | channels, 4 | image width); TAGI_B200_CONV_GATHER=patch also lifts the width rule below,
+// =implicit selects the cp.async gather of the Linear pair kernel instead.
+inline bool patch_ok(const tagi_conv2d_geom &cg, int pass, long rows, int cols, std::initializer_list<const void *> ptrs) {
+    const int mode = gather_mode();
+    if (mode == 1 || mode == 2 || rows < 256) return false;
+    if (mode != 3 && cols > 256) return false;
+    return conv_pix_patch_supported(cg, pass, ptrs);
+}
+inline bool implicit_ok(const G &g, long rows, int cols) {
+    const int mode = gather_mode();
     // (the kernel keeps one validity bit per tap in a 64-bit word, bit 63 reserved: kernels up to 7 x 7)
     if (mode == 1 || g.k > 7 || rows >= (1L << 31) || !linear_tc_pair_for((int)rows)) return false;
     return mode == 2 || cols <= 256;
@@ -327,6 +340,8 @@ int conv2d_fwd_tc(const tagi_conv2d_geom &cg, const float *mu_w, const float *va
                   cudaStream_t st, float *relu_jcb) {
     const G g = geom_of(cg);
     const long rows = (long)g.B * g.woho;
+    if (patch_ok(cg, CONV_PASS_FWD, rows, g.fo, {mu_a, var_a}))
+        return conv2d_fwd_patch(cg, mu_w, var_w, mu_b, var_b, mu_a, var_a, mu_z, var_z, st, relu_jcb);
     if (implicit_ok(g, rows, g.fo)) {
         // implicit GEMM: the kernel gathers the receptive fields itself while it stages its A tiles
         ConvGather ig{1, mu_a, var_a, g.fi, g.hi, g.wi, g.wo, g.woho, g.k, g.stride, g.off, +1, rows};
@@ -372,6 +387,8 @@ int conv2d_bwd_state_tc(const tagi_conv2d_geom &cg, const float *mu_w, const flo
     }
     const long rows = (long)g.B * g.wihi;
     const int kd = g.fo * g.k2;
+    if (patch_ok(cg, CONV_PASS_STATE, rows, g.fi, {dmu_z, dvar_z}))
+        return conv2d_bwd_state_patch(cg, mu_w, jcb, dmu_z, dvar_z, dmu_a, dvar_a, st);
     if (implicit_ok(g, rows, g.fi)) {
         float *w2i = nullptr;
         if ((rc = conv_scratch((size_t)g.fo * g.Kc * sizeof(float), &w2i, st)) != TAGI_OK) return rc;

@@ -337,27 +337,10 @@ tagi_tc_linear_ts_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_
 // issuing CTA, the other CTA's warps arrive there through the cluster's shared-memory window.
 // =====================================================================================================
 
-template <int OP> struct PairTraits;
-// raw slot: A0 A1 (8 KiB each) then B halves (4 KiB each); derived slot: B halves only
-template <> struct PairTraits<OP_FWD> { static constexpr int NRAW_B = 2, NDER = 4, NA = 6; };
-template <> struct PairTraits<OP_BWD_STATE> { static constexpr int NRAW_B = 1, NDER = 3, NA = 4; };
-template <> struct PairTraits<OP_BWD_PARAM> { static constexpr int NRAW_B = 1, NDER = 3, NA = 4; };
-
 template <int OP, int RS, int DS>
 constexpr size_t pair_smem_bytes() {
     return at_least_stage((size_t)RS * (2 * TILE_BYTES + PairTraits<OP>::NRAW_B * HALF_BYTES) +
                           (size_t)DS * PairTraits<OP>::NDER * HALF_BYTES) + 1024 + 256;
-}
-
-// B half tile: K-major one box of 64 rows; MN-major two boxes of 32 rows
-template <int MN>
-__device__ __forceinline__ void load_half_tile(uint32_t dst, const CUtensorMap *tm, int row0, int k0, uint64_t *bar) {
-    if (MN) {
-#pragma unroll
-        for (int g = 0; g < 2; g++) tma_load_2d(dst + g * 2048, tm, row0 + 32 * g, k0, bar);
-    } else {
-        tma_load_2d(dst, tm, k0, row0, bar);
-    }
 }
 
 // FL bit 0 (GATHER): the A tiles of the forward / state pass are gathered inside the kernel (Conv2d, launched with 384

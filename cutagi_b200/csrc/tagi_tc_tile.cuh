@@ -229,5 +229,23 @@ constexpr int HALF_BYTES = TILE_BYTES / 2;  // B half tile: 64 rows x 16 k
 // added to the register sums. CHUNK_STAGES == 0 (template) means a single chunk: everything stays in set 0.
 constexpr int CHUNK_STAGES = 16;
 
+template <int OP> struct PairTraits;
+// raw slot: A0 A1 (8 KiB each) then B halves (4 KiB each); derived slot: B halves only
+template <> struct PairTraits<OP_FWD> { static constexpr int NRAW_B = 2, NDER = 4, NA = 6; };
+template <> struct PairTraits<OP_BWD_STATE> { static constexpr int NRAW_B = 1, NDER = 3, NA = 4; };
+template <> struct PairTraits<OP_BWD_PARAM> { static constexpr int NRAW_B = 1, NDER = 3, NA = 4; };
+
+
+// B half tile: K-major one box of 64 rows; MN-major two boxes of 32 rows
+template <int MN>
+__device__ __forceinline__ void load_half_tile(uint32_t dst, const CUtensorMap *tm, int row0, int k0, uint64_t *bar) {
+    if (MN) {
+#pragma unroll
+        for (int g = 0; g < 2; g++) tma_load_2d(dst + g * 2048, tm, row0 + 32 * g, k0, bar);
+    } else {
+        tma_load_2d(dst, tm, k0, row0, bar);
+    }
+}
+
 }  // namespace
 }  // namespace tagi
