@@ -237,22 +237,22 @@ __global__ void __launch_bounds__(256) reduce_slices_scale_kernel(const float *_
     out2[i] = a2 * s * s;
 }
 
-// Bias deltas: per output channel the sum over (b, pixel) of the deltas, one CTA per channel,
-// fixed-order tree so the result does not depend on scheduling.
-__global__ void __launch_bounds__(256) conv_bias_delta_kernel(const float *__restrict__ var_b,
-                                                              const float *__restrict__ dmu_z,
-                                                              const float *__restrict__ dvar_z, int B, int fo,
-                                                              int woho, float *__restrict__ dmu_b,
-                                                              float *__restrict__ dvar_b) {
+// Bias deltas: dmu_b[co] = var_b * sum over (b, pixel) of dmu_z[b][co][pixel], dvar_b likewise with var_b^2
+// (src/conv2d_layer.cpp:538-556). HBM-bound: one pass over the deltas. Stage 1: block (co, s) sums the images
+// b = s, s + S, ... of channel co (fixed order inside the block); stage 2: one thread per channel adds the S partial
+// sums in order and scales. The result does not depend on scheduling.
+__global__ void __launch_bounds__(256) conv_bias_partial_kernel(const float *__restrict__ dmu_z,
+                                                                const float *__restrict__ dvar_z, int B, int fo,
+                                                                int woho, int S, float2 *__restrict__ part) {
     __shared__ float s1[256], s2[256];
-    const int co = blockIdx.x;
+    const int co = blockIdx.x, sl = blockIdx.y;
     float a1 = 0.f, a2 = 0.f;
-    const long total = (long)B * woho;
-    for (long t = threadIdx.x; t < total; t += 256) {
-        const long b = t / woho, p = t - b * woho;
-        const long i = (b * fo + co) * woho + p;
-        a1 += __ldg(dmu_z + i);
-        a2 += __ldg(dvar_z + i);
+    for (int b = sl; b < B; b += S) {
+        const long base = ((long)b * fo + co) * woho;
+        for (int p = threadIdx.x; p < woho; p += 256) {
+            a1 += __ldg(dmu_z + base + p);
+            a2 += __ldg(dvar_z + base + p);
+        }
     }
     s1[threadIdx.x] = a1;
     s2[threadIdx.x] = a2;
@@ -264,11 +264,22 @@ __global__ void __launch_bounds__(256) conv_bias_delta_kernel(const float *__res
         }
         __syncthreads();
     }
-    if (threadIdx.x == 0) {
-        const float vb = __ldg(var_b + co);
-        dmu_b[co] = s1[0] * vb;
-        dvar_b[co] = s2[0] * vb * vb;
+    if (threadIdx.x == 0) part[(long)co * S + sl] = make_float2(s1[0], s2[0]);
+}
+__global__ void __launch_bounds__(128) conv_bias_final_kernel(const float *__restrict__ var_b,
+                                                              const float2 *__restrict__ part, int fo, int S,
+                                                              float *__restrict__ dmu_b, float *__restrict__ dvar_b) {
+    const int co = blockIdx.x * 128 + threadIdx.x;
+    if (co >= fo) return;
+    float a1 = 0.f, a2 = 0.f;
+    for (int s = 0; s < S; s++) {
+        const float2 v = part[(long)co * S + s];
+        a1 += v.x;
+        a2 += v.y;
     }
+    const float vb = __ldg(var_b + co);
+    dmu_b[co] = a1 * vb;
+    dvar_b[co] = a2 * vb * vb;
 }
 
 inline int done(cudaError_t e, const char *what) { return e == cudaSuccess ? TAGI_OK : cuda_fail(e, what); }
@@ -320,10 +331,31 @@ std::mutex g_scratch_mu;
 
 }  // namespace
 
+// The partial sums live in a small array of their own in the library image (8 bytes x channels x 64 slices at most), so
+// the pass needs no scratch from the shared block and may follow any other pass on the same stream.
+constexpr int kBiasSlices = 64, kBiasMaxChannels = 4096;
+static __device__ float2 g_bias_part[kBiasSlices * kBiasMaxChannels];
+
 int conv_bias_delta(const tagi_conv2d_geom &cg, const float *var_b, const float *dmu_z, const float *dvar_z,
                     float *dmu_b, float *dvar_b, cudaStream_t st) {
-    conv_bias_delta_kernel<<<cg.fo, 256, 0, st>>>(var_b, dmu_z, dvar_z, cg.B, cg.fo, cg.ho * cg.wo, dmu_b, dvar_b);
-    return done(cudaGetLastError(), "conv_bias_delta_kernel launch");
+    if (cg.fo > kBiasMaxChannels) return fail(TAGI_ERR_UNSUPPORTED, "bias deltas: more than 4096 output channels");
+    static float2 *part[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (dev < 0 || dev >= 64) return fail(TAGI_ERR_UNSUPPORTED, "device index out of range");
+    {
+        std::lock_guard<std::mutex> lk(g_scratch_mu);
+        if (!part[dev]) {
+            e = cudaGetSymbolAddress(reinterpret_cast<void **>(&part[dev]), g_bias_part);
+            if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(bias partial sums)");
+        }
+    }
+    const int S = cg.B < kBiasSlices ? cg.B : kBiasSlices;
+    conv_bias_partial_kernel<<<dim3(cg.fo, S), 256, 0, st>>>(dmu_z, dvar_z, cg.B, cg.fo, cg.ho * cg.wo, S, part[dev]);
+    if (cudaGetLastError() != cudaSuccess) return done(cudaGetLastError(), "conv_bias_partial_kernel launch");
+    conv_bias_final_kernel<<<(cg.fo + 127) / 128, 128, 0, st>>>(var_b, part[dev], cg.fo, S, dmu_b, dvar_b);
+    return done(cudaGetLastError(), "conv_bias_final_kernel launch");
 }
 
 int conv_scratch(size_t bytes, float **out, cudaStream_t st) {
@@ -444,10 +476,7 @@ int conv2d_bwd_param_ffma(const tagi_conv2d_geom &cg, const float *var_w, const 
         rc = done(cudaGetLastError(), "reduce_slices_scale_kernel launch");
     }
     if (rc != TAGI_OK) return rc;
-    if (cg.has_bias) {
-        conv_bias_delta_kernel<<<g.fo, 256, 0, st>>>(var_b, dmu_z, dvar_z, g.B, g.fo, g.woho, dmu_b, dvar_b);
-        rc = done(cudaGetLastError(), "conv_bias_delta_kernel launch");
-    }
+    if (cg.has_bias) rc = conv_bias_delta(cg, var_b, dmu_z, dvar_z, dmu_b, dvar_b, st);
     return rc;
 }
 
@@ -539,10 +568,7 @@ int conv2d_bwd_param_noalloc(const tagi_conv2d_geom &cg, const float *var_w, con
         rc = done(cudaGetLastError(), "reduce_slices_scale_kernel launch");
     }
     if (rc != TAGI_OK) return rc;
-    if (cg.has_bias) {
-        conv_bias_delta_kernel<<<g.fo, 256, 0, st>>>(var_b, dmu_z, dvar_z, g.B, g.fo, g.woho, dmu_b, dvar_b);
-        rc = done(cudaGetLastError(), "conv_bias_delta_kernel launch");
-    }
+    if (cg.has_bias) rc = conv_bias_delta(cg, var_b, dmu_z, dvar_z, dmu_b, dvar_b, st);
     return rc;
 }
 

@@ -31,7 +31,7 @@ namespace {
 struct PatchParam {
     int fi, k, k2, Kc, fo;
     int CT;               // channels per CTA row tile
-    int ho, nxc;          // output rows per image, 16-pixel chunks per output row
+    int ho, nxc;          // output rows per image, slabs (chunks of 16 or 32 pixels) per output row
     int stride, PW, lead; // patch row pitch in floats; a row's first useful column
     int x0, y0;           // patch origin relative to (ox0 * stride, oy * stride): -(off + lead), -off
     int total_slabs, slabs_per_slice;
@@ -40,28 +40,40 @@ struct PatchParam {
     float *out1, *out2;   // [slice][fo][Kc]
     const float *scale;   // var_w when the contraction is not sliced, else null (raw partial sums)
     long slice_elems;
-    int ablate;           // timing diagnostics only (TAGI_B200_PATCH_ABLATE; results are wrong when set): bit 0 no
-                          // tensor-memory stores, bit 1 no B-side conversion, bit 2 no MMAs, bit 3 no patch reads
 };
 
 constexpr int P_NA = 4, P_NRAW_B = 2, P_NDER = 2;
 
-template <int RS, int DS>
+template <int RS, int DS, int KS>
 size_t patch_param_smem(uint32_t a_slot) {
-    return (size_t)RS * (a_slot + P_NRAW_B * HALF_BYTES) + (size_t)DS * P_NDER * HALF_BYTES + 1024 + 256;
+    return (size_t)RS * (a_slot + P_NRAW_B * HALF_BYTES * (KS / 2)) + (size_t)DS * P_NDER * HALF_BYTES * (KS / 2) + 1024 + 256;
 }
 
-template <int CH, int RS, int DS, int ACC>
-__global__ void __launch_bounds__(NTHREADS2 - 32, 1)
+// NCW converter warps (8 or 16): groups of four take the slabs in turn.
+// PAIR: two CTAs of a cluster share every MMA (cta_group::2, 256 rows, each CTA stages half of the B rows), as in the
+// Linear pair kernel. !PAIR: every CTA works alone on its 128 rows (cta_group::1) and stages all bn <= 64 B rows: no
+// barrier or commit crosses an SM boundary.
+// KS: 8-wide k steps per slab: 2 (16 pixels, delta tiles in the 64-byte swizzle) or 4 (32 pixels, 128-byte swizzle). Every
+// slab costs about a thousand cycles of hand-offs and TMA row requests whatever it holds, so wide rows use 32 pixels.
+template <int CH, int RS, int DS, int ACC, int NCW, bool PAIR, int KS>
+__global__ void __launch_bounds__(32 * (3 + NCW), 1)
 tagi_tc_conv_param_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmD0,
                           const __grid_constant__ CUtensorMap tmD1, const PatchParam pp, const int bn, int *status) {
     constexpr int NA = P_NA, NDER = P_NDER;
-    constexpr uint32_t DER_SLOT = NDER * HALF_BYTES;
+    constexpr int SK = KS * 8;                               // contraction steps (pixels) per slab
+    constexpr uint32_t B_TILE = HALF_BYTES * (KS / 2);       // shared memory of one delta tile: up to 64 rows of SK floats
+    constexpr uint32_t DER_SLOT = NDER * B_TILE;
     constexpr uint32_t NCOLS = 512;
     constexpr uint32_t acc_stride = ACC, A_COL0 = 2 * ACC;   // ACC >= bn: columns between the two accumulators
-    static_assert(A_COL0 + DS * NA * BK <= 512, "tensor memory: accumulators + A slots");
-    const uint32_t RAW_SLOT = pp.a_slot + P_NRAW_B * HALF_BYTES;
-    const uint32_t IDESC = make_idesc_tf32(256, bn, 0, 0);
+    static_assert(KS == 2 || KS == 4, "16 or 32 pixels per slab");
+    static_assert(A_COL0 + DS * NA * SK <= 512, "tensor memory: accumulators + A slots");
+    // columns of each accumulator a converter thread sums and stores: with accumulators of at most 64 columns the eight
+    // converter warps split them 32 / 32, which leaves the registers to read a whole slab of patch values at once
+    constexpr int NG = NCW / 4;                        // converter groups
+    constexpr int SUMW = (ACC <= 64 ? 64 : 128) / NG;  // 64, 32 or 16
+    static_assert(NCW == 8 || (NCW == 16 && ACC <= 64), "sixteen converter warps only with narrow accumulators");
+    const uint32_t RAW_SLOT = pp.a_slot + P_NRAW_B * B_TILE;
+    const uint32_t IDESC = make_idesc_tf32(PAIR ? 256 : 128, bn, 0, 0);
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -75,13 +87,13 @@ tagi_tc_conv_param_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t cta = cluster_ctarank();  // 0 issues the MMAs
-    const int half = bn / 2;
-    const int tile = blockIdx.y * 2 + (int)cta;                   // this CTA's row tile: channels c0 .. c0 + CT - 1
+    const uint32_t cta = PAIR ? cluster_ctarank() : 0;  // 0 issues the MMAs
+    const int half = PAIR ? bn / 2 : bn;                          // B rows this CTA stages
+    const int tile = PAIR ? blockIdx.y * 2 + (int)cta : blockIdx.y;  // this CTA's row tile: channels c0 .. c0 + CT - 1
     const int c0 = tile * pp.CT;
-    const int col0 = (blockIdx.x >> 1) * bn;                      // the pair's output channels
+    const int col0 = (PAIR ? blockIdx.x >> 1 : blockIdx.x) * bn;  // the output channels of the tile
     const int brow0 = col0 + (int)cta * half;                     // this CTA's half of them (B rows)
-    const uint32_t b_bytes = (uint32_t)half * 64;                 // a delta tile holds exactly this CTA's half of the columns
+    const uint32_t b_bytes = (uint32_t)half * SK * 4;             // a delta tile holds exactly the channel rows this CTA stages
     const int kb = (int)blockIdx.z * pp.slabs_per_slice;          // first slab of this slice
     const int nk = min(pp.total_slabs - kb, pp.slabs_per_slice);
     const int chunk_len = CH > 0 ? CH : nk;
@@ -89,19 +101,21 @@ tagi_tc_conv_param_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
     if (threadIdx.x == 0) {
         for (int s = 0; s < RS; s++) mbar_init(raw_full + s, 1);
         for (int s = 0; s < L; s++) mbar_init(stage_done + s, 2);            // one commit from each MMA issuer
-        for (int s = 0; s < DS; s++) mbar_init(conv_done + s, NCONV_WARPS);  // used in CTA 0: one warp group of each CTA
+        for (int s = 0; s < DS; s++) mbar_init(conv_done + s, PAIR ? 8 : 4);  // one warp group (of each CTA of a pair)
         mbar_init(acc_full, 2);
-        mbar_init(acc_empty, 2 * NCONV_WARPS);                              // used in CTA 0 only
+        mbar_init(acc_empty, PAIR ? 2 * NCW : NCW);                 // pairs: used in CTA 0 only
         *abort_flag = 0;
         mbar_init_fence();
         prefetch_tmap(&tmX);
         prefetch_tmap(&tmD0);
         prefetch_tmap(&tmD1);
     }
-    if (warp == 1) tmem_alloc_pair(tmem_slot, NCOLS);
+    if (warp == 1) {
+        if (PAIR) tmem_alloc_pair(tmem_slot, NCOLS); else tmem_alloc(tmem_slot, NCOLS);
+    }
     tc_fence_before_sync();
     __syncthreads();
-    cluster_sync_all();  // the peer's barriers exist before anyone arrives on them
+    if (PAIR) cluster_sync_all();  // the peer's barriers exist before anyone arrives on them
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
 
@@ -117,12 +131,12 @@ tagi_tc_conv_param_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
                 const int xc = t % pp.nxc, rr = t / pp.nxc, oy = rr % pp.ho, b = rr / pp.ho;
                 mbar_arrive_expect_tx(raw_full + r, pp.a_bytes + P_NRAW_B * b_bytes);
                 const uint32_t st = raw_base + r * RAW_SLOT;
-                tma_load_4d(st, &tmX, xc * 16 * pp.stride + pp.x0, oy * pp.stride + pp.y0, c0, b, raw_full + r);
-                tma_load_4d(st + pp.a_slot, &tmD0, xc * 16, oy, brow0, b, raw_full + r);
-                tma_load_4d(st + pp.a_slot + HALF_BYTES, &tmD1, xc * 16, oy, brow0, b, raw_full + r);
+                tma_load_4d(st, &tmX, xc * SK * pp.stride + pp.x0, oy * pp.stride + pp.y0, c0, b, raw_full + r);
+                tma_load_4d(st + pp.a_slot, &tmD0, xc * SK, oy, brow0, b, raw_full + r);
+                tma_load_4d(st + pp.a_slot + B_TILE, &tmD1, xc * SK, oy, brow0, b, raw_full + r);
             }
         }
-    } else if (warp == 1 || warp == ISSUER2_WARP) {
+    } else if (warp == 1 || warp == 2 + NCW) {
         // ------------------------------------------------------------------ MMA issuers (CTA 0): warp 1 -> D1, warp 10 -> D2
         if (lane == 0 && cta == 0) {
             const bool chain1 = warp == 1;
@@ -133,32 +147,44 @@ tagi_tc_conv_param_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
                 const int r = it % RS, d = it % DS;
                 if (it > 0 && it % chunk_len == 0) {
                     const int c = it / chunk_len;
-                    ok = mbar_wait_cluster(acc_empty, (c - 1) & 1, abort_flag, status, ST_TIMEOUT_ACC);
+                    ok = PAIR ? mbar_wait_cluster(acc_empty, (c - 1) & 1, abort_flag, status, ST_TIMEOUT_ACC)
+                              : mbar_wait(acc_empty, (c - 1) & 1, abort_flag, status, ST_TIMEOUT_ACC);
                     if (!ok) break;
                     f = 0;
                 }
-                ok = mbar_wait_cluster(conv_done + d, (it / DS) & 1, abort_flag, status, ST_TIMEOUT_CONV);
+                ok = PAIR ? mbar_wait_cluster(conv_done + d, (it / DS) & 1, abort_flag, status, ST_TIMEOUT_CONV)
+                          : mbar_wait(conv_done + d, (it / DS) & 1, abort_flag, status, ST_TIMEOUT_CONV);
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t rb = raw_base + r * RAW_SLOT + pp.a_slot, ds = der_base + d * DER_SLOT;
-                const uint32_t at = tmem + A_COL0 + d * (NA * BK);
+                const uint32_t at = tmem + A_COL0 + d * (NA * SK);
+                // K-major delta tiles: rows of SK floats, 8-row groups 8 * SK * 4 bytes apart, an 8-wide k step 32 bytes on
                 constexpr uint32_t LBO = 16, KSTEP = 32 >> 4;
-                constexpr uint32_t HI = desc_hi(512, SWZ_64B);
+                constexpr uint32_t HI = desc_hi(KS == 2 ? 512 : 1024, KS == 2 ? SWZ_64B : SWZ_128B);
                 const uint32_t rbl = desc_lo(rb, LBO), dsl = desc_lo(ds, LBO);
-                if (pp.ablate & 4) {
-                } else if (chain1) {
-                    mma_kstep_cparam_pair<1>(d1, d2, at, rbl, dsl, HI, IDESC, f, f);
-                    mma_kstep_cparam_pair<1>(d1, d2, at + 8, rbl + KSTEP, dsl + KSTEP, HI, IDESC, 1, 1);
-                } else {
-                    mma_kstep_cparam_pair<2>(d1, d2, at, rbl, dsl, HI, IDESC, f, f);
-                    mma_kstep_cparam_pair<2>(d1, d2, at + 8, rbl + KSTEP, dsl + KSTEP, HI, IDESC, 1, 1);
+#pragma unroll
+                for (int j = 0; j < KS; j++) {
+                    const uint32_t fj = j == 0 ? f : 1u;
+                    if (KS == 4) {
+                        if (chain1) mma_kstep_cparam_w<PAIR, 1>(d1, d2, at + 8 * j, rbl + KSTEP * j, dsl + KSTEP * j, HI, IDESC, fj, fj);
+                        else mma_kstep_cparam_w<PAIR, 2>(d1, d2, at + 8 * j, rbl + KSTEP * j, dsl + KSTEP * j, HI, IDESC, fj, fj);
+                    } else if (PAIR) {
+                        if (chain1) mma_kstep_cparam_pair<1>(d1, d2, at + 8 * j, rbl + KSTEP * j, dsl + KSTEP * j, HI, IDESC, fj, fj);
+                        else mma_kstep_cparam_pair<2>(d1, d2, at + 8 * j, rbl + KSTEP * j, dsl + KSTEP * j, HI, IDESC, fj, fj);
+                    } else {
+                        if (chain1) mma_kstep_cparam_solo<1>(d1, d2, at + 8 * j, rbl + KSTEP * j, dsl + KSTEP * j, HI, IDESC, fj, fj);
+                        else mma_kstep_cparam_solo<2>(d1, d2, at + 8 * j, rbl + KSTEP * j, dsl + KSTEP * j, HI, IDESC, fj, fj);
+                    }
                 }
                 f = 1;
-                mma_commit_pair(stage_done + it % L);  // both CTAs may refill the raw slot and overwrite the derived one
-                if (it % chunk_len == chunk_len - 1 || it == nk - 1) mma_commit_pair(acc_full);
+                // the raw slot may be refilled and the derived one overwritten (in both CTAs of a pair)
+                if (PAIR) mma_commit_pair(stage_done + it % L); else mma_commit(stage_done + it % L);
+                if (it % chunk_len == chunk_len - 1 || it == nk - 1) {
+                    if (PAIR) mma_commit_pair(acc_full); else mma_commit(acc_full);
+                }
             }
         }
-    } else if (warp >= 2 && warp < 2 + NCONV_WARPS) {
+    } else if (warp >= 2 && warp < 2 + NCW) {
         // ------------------------------------------------------------------ converters + accumulation + epilogue
         const int ct = threadIdx.x - 64;
         const int q = warp & 3;
@@ -175,28 +201,38 @@ tagi_tc_conv_param_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
             row_off = (uint32_t)(((cl * pp.k + ky) * pp.PW + kx + pp.lead) * 4);
         }
         const uint32_t step_b = (uint32_t)pp.stride * 4;
-        float sum1[64], sum2[64];
+        float sum1[SUMW], sum2[SUMW];
 #pragma unroll
-        for (int i = 0; i < 64; i++) sum1[i] = sum2[i] = 0.f;
+        for (int i = 0; i < SUMW; i++) sum1[i] = sum2[i] = 0.f;
 
         auto drain = [&](int c) -> bool {
             if (!mbar_wait(acc_full, c & 1, abort_flag, status, ST_TIMEOUT_ACC)) return false;
             tc_fence_after_sync();
-            if (h * 64 < ACC) {   // with narrow accumulators the second half of the converter warps holds no columns
+            if (SUMW >= 32) {
 #pragma unroll
-                for (int blk = 0; blk < 2; blk++) {
+                for (int blk = 0; blk < SUMW / 32; blk++) {
                     float v[32];
-                    tmem_ld_32x32(lane_addr + h * 64 + blk * 32, v);
+                    tmem_ld_32x32(lane_addr + h * SUMW + blk * 32, v);
 #pragma unroll
                     for (int i = 0; i < 32; i++) sum1[blk * 32 + i] += v[i];
-                    tmem_ld_32x32(lane_addr + acc_stride + h * 64 + blk * 32, v);
+                    tmem_ld_32x32(lane_addr + acc_stride + h * SUMW + blk * 32, v);
 #pragma unroll
                     for (int i = 0; i < 32; i++) sum2[blk * 32 + i] += v[i];
                 }
+            } else {
+                float v[16];
+                tmem_ld_32x16(lane_addr + h * SUMW, v);
+#pragma unroll
+                for (int i = 0; i < 16; i++) sum1[i] += v[i];
+                tmem_ld_32x16(lane_addr + acc_stride + h * SUMW, v);
+#pragma unroll
+                for (int i = 0; i < 16; i++) sum2[i] += v[i];
             }
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(acc_empty, 0);
+            if (lane == 0) {
+                if (PAIR) mbar_arrive_cluster(acc_empty, 0); else mbar_arrive(acc_empty);
+            }
             return true;
         };
 
@@ -212,7 +248,7 @@ tagi_tc_conv_param_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
             scanned = upto + 1;
         };
         const int gt = ct & 127;  // thread index inside the group
-        for (int it = h; it < nk && ok; it += 2) {
+        for (int it = h; it < nk && ok; it += NG) {
             const int r = it % RS, d = it % DS;
             ok = mbar_wait(raw_full + r, (it / RS) & 1, abort_flag, status, ST_TIMEOUT_RAW) &&
                  (it < DS || mbar_wait(stage_done + (it - DS) % L, ((it - DS) / L) & 1, abort_flag, status,
@@ -220,53 +256,51 @@ tagi_tc_conv_param_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
             if (!ok) break;
             const uint32_t rs = raw_base + r * RAW_SLOT, rb = rs + pp.a_slot, ds = der_base + d * DER_SLOT;
 
+            constexpr int KW = (SUMW == 32 && NCW == 8) ? 16 : 8;   // pixels read before they are converted
 #pragma unroll
-            for (int kh = 0; kh < 2; kh++) {  // the two 8-wide k steps: pixels kh*8 .. kh*8+7 of the slab
-                float x[8];
-                if (pp.ablate & 8) {
+            for (int kh = 0; kh < SK / KW; kh++) {
+                float x[KW];
 #pragma unroll
-                    for (int i = 0; i < 8; i++) x[i] = (float)(it + i);
-                } else {
+                for (int i = 0; i < KW; i++)
+                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(x[i]) : "r"(rs + row_off + (kh * KW + i) * step_b));
 #pragma unroll
-                    for (int i = 0; i < 8; i++)
-                        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(x[i]) : "r"(rs + row_off + (kh * 8 + i) * step_b));
-                }
-                const uint32_t at = lane_addr + A_COL0 + d * (NA * BK) + kh * 8;
-                float t0[8], t1[8], qq[8];
+                for (int p8 = 0; p8 < KW / 8; p8++) {
+                    const uint32_t at = lane_addr + A_COL0 + d * (NA * SK) + kh * KW + p8 * 8;
+                    float t0[8], t1[8], qq[8];
 #pragma unroll
-                for (int i = 0; i < 8; i++) qq[i] = x[i] * x[i], t0[i] = hi_part(x[i]), t1[i] = hi_part(qq[i]);
-                if (!(pp.ablate & 1)) {
-                    tmem_st_32x8(at + 0 * BK, t0);
-                    tmem_st_32x8(at + 1 * BK, t1);
-                }
+                    for (int i = 0; i < 8; i++) {
+                        const float v = x[p8 * 8 + i];
+                        qq[i] = v * v, t0[i] = hi_part(v), t1[i] = hi_part(qq[i]);
+                    }
+                    tmem_st_32x8(at + 0 * SK, t0);
+                    tmem_st_32x8(at + 1 * SK, t1);
 #pragma unroll
-                for (int i = 0; i < 8; i++) t0[i] = x[i] - t0[i], t1[i] = qq[i] - t1[i];
-                if (!(pp.ablate & 1)) {
-                    tmem_st_32x8(at + 2 * BK, t0);
-                    tmem_st_32x8(at + 3 * BK, t1);
-                } else if (t0[0] + t1[3] == 12345.678f) {
-                    tmem_st_32x8(at + 2 * BK, t0);   // keeps the arithmetic alive
+                    for (int i = 0; i < 8; i++) t0[i] = x[p8 * 8 + i] - t0[i], t1[i] = qq[i] - t1[i];
+                    tmem_st_32x8(at + 2 * SK, t0);
+                    tmem_st_32x8(at + 3 * SK, t1);
                 }
             }
-            // B halves (dmu_z, dvar_z tiles of this CTA's 64 channels): lo parts at the same swizzled offsets
+            // the delta tiles (dmu_z, dvar_z, the channel rows this CTA stages): lo parts at the same swizzled offsets
 #pragma unroll
-            for (int c = 0; c < 2; c++) {
-                const uint32_t o = gt * 16 + c * (HALF_BYTES / 2);
-                if ((pp.ablate & 2) || o >= b_bytes) break;
-                const float4 b0 = lds128(rb + o), b1 = lds128(rb + HALF_BYTES + o);
-                sts128(ds + 0 * HALF_BYTES + o, lo_part(b0));
-                sts128(ds + 1 * HALF_BYTES + o, lo_part(b1));
+            for (int c = 0; c < (int)(B_TILE / 2048); c++) {
+                const uint32_t o = gt * 16 + c * 2048;
+                if (o >= b_bytes) break;
+                const float4 b0 = lds128(rb + o), b1 = lds128(rb + B_TILE + o);
+                sts128(ds + 0 * B_TILE + o, lo_part(b0));
+                sts128(ds + 1 * B_TILE + o, lo_part(b1));
             }
             fence_proxy_async_smem();
             tmem_wait_st();
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(conv_done + d, 0);
+            if (lane == 0) {
+                if (PAIR) mbar_arrive_cluster(conv_done + d, 0); else mbar_arrive(conv_done + d);
+            }
             if (pending >= 0) {
                 ok = drain(pending);
                 pending = -1;
             }
-            note_chunk_ends(it + 1);
+            note_chunk_ends(it + NG - 1);
         }
         if (ok) note_chunk_ends(nk - 1);
         if (ok && pending >= 0) ok = drain(pending);
@@ -274,12 +308,12 @@ tagi_tc_conv_param_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
         // epilogue: row (c, tap) of the tile is weight column kc = c0 * k2 + arow; this thread holds 64 output channels
         // of it. out[co][kc]: for one co the 32 lanes of a warp write 32 consecutive kc (coalesced).
         const int kc = c0 * pp.k2 + arow;
-        if (ok && row_in_tile && kc < pp.Kc && h * 64 < bn) {
+        if (ok && row_in_tile && kc < pp.Kc && h * SUMW < bn) {
             float *o1 = pp.out1 + (long)blockIdx.z * pp.slice_elems + kc;
             float *o2 = pp.out2 + (long)blockIdx.z * pp.slice_elems + kc;
-            const int cbase = col0 + h * 64, valid = min(bn - h * 64, pp.fo - cbase);
+            const int cbase = col0 + h * SUMW, valid = min(bn - h * SUMW, pp.fo - cbase);
 #pragma unroll
-            for (int i0 = 0; i0 < 64; i0 += 8) {
+            for (int i0 = 0; i0 < SUMW; i0 += 8) {
                 float sc[8];
 #pragma unroll
                 for (int u = 0; u < 8; u++) {
@@ -299,14 +333,14 @@ tagi_tc_conv_param_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
     __syncwarp();
     tc_fence_before_sync();
     __syncthreads();
-    cluster_sync_all();  // neither CTA leaves (or frees tensor memory) while the other may still signal or read it
+    if (PAIR) cluster_sync_all();  // neither CTA leaves (or frees tensor memory) while the other may still signal or read it
     if (warp == 1) {
         if (*abort_flag) {
             const long long t0 = clock64();
             while (clock64() - t0 < 4000000LL) {
             }
         }
-        tmem_dealloc_pair(tmem, NCOLS);
+        if (PAIR) tmem_dealloc_pair(tmem, NCOLS); else tmem_dealloc(tmem, NCOLS);
     }
 }
 
@@ -367,16 +401,18 @@ struct PixParam {
 };
 
 constexpr int PIX_MAX_RS = 8, PIX_MAX_AS = 3;
+constexpr int PIX_MAX_SLABS = 768, PIX_TAB_BYTES = PIX_MAX_SLABS * 8;   // slab table: k*k taps x 16-channel blocks
 
 template <int OP>
 size_t pix_smem(uint32_t a_slot, int AS, int RS, int DS) {
     return (size_t)AS * 2 * a_slot + (size_t)RS * PairTraits<OP>::NRAW_B * HALF_BYTES +
-           (size_t)DS * PairTraits<OP>::NDER * HALF_BYTES + 1024 + 256;
+           (size_t)DS * PairTraits<OP>::NDER * HALF_BYTES + 1024 + 256 + PIX_TAB_BYTES;
 }
 
 // ACC: tensor-memory columns between the two accumulators (>= bn); DS derived slots
-template <int OP, int CH, int DS, int ACC, bool RELU>
-__global__ void __launch_bounds__(NTHREADS2 - 32, 1)
+// NCW converter warps (8 or 16): groups of four take the slabs in turn
+template <int OP, int CH, int DS, int ACC, bool RELU, int NCW>
+__global__ void __launch_bounds__(32 * (3 + NCW), 1)
 tagi_tc_conv_pix_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
                         const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
                         const PixParam pp, const int bn, int *status) {
@@ -387,6 +423,11 @@ tagi_tc_conv_pix_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_c
     constexpr uint32_t NCOLS = 512;
     constexpr uint32_t acc_stride = ACC, A_COL0 = 2 * ACC;
     static_assert(A_COL0 + DS * NA * BK <= 512, "tensor memory: accumulators + A slots");
+    // columns of each accumulator a converter thread sums and stores: with accumulators of at most 64 columns the eight
+    // converter warps split them 32 / 32, which leaves the registers to read a whole slab of A values at once
+    constexpr int NG = NCW / 4;                        // converter groups
+    constexpr int SUMW = (ACC <= 64 ? 64 : 128) / NG;  // 64, 32 or 16
+    static_assert(NCW == 8 || (NCW == 16 && ACC <= 64), "sixteen converter warps only with narrow accumulators");
     const int RS = pp.RS, AS = pp.AS;
     constexpr uint32_t RAW_SLOT = NRAW_B * HALF_BYTES;               // B ring slot: the raw B half tiles of one slab
     const uint32_t A_SLOT = 2 * pp.a_slot;                           // patch ring slot: both operands of a channel block
@@ -404,6 +445,8 @@ tagi_tc_conv_pix_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_c
     uint64_t *a_full = acc_empty + 1, *a_free = a_full + PIX_MAX_AS;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(a_free + PIX_MAX_AS);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    // per slab: byte offset of the slab's read position inside the patch ring (ring slot + tap shift), and its channel block
+    uint2 *slab_tab = reinterpret_cast<uint2 *>(bars + 32);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t cta = cluster_ctarank();
@@ -415,6 +458,11 @@ tagi_tc_conv_pix_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_c
     const int brow0 = col0 + (int)cta * half;
     const int nk = pp.k2 * pp.cblocks;
     const int chunk_len = CH > 0 ? CH : nk;
+    for (int i = threadIdx.x; i < nk; i += blockDim.x) {
+        const int cb = i / pp.k2, tap = i - cb * pp.k2, ky = tap / pp.k, kx = tap - ky * pp.k;
+        const int sy = pp.sign > 0 ? ky : pp.k - 1 - ky, sx = pp.sign > 0 ? kx : pp.k - 1 - kx;
+        slab_tab[i] = make_uint2((uint32_t)(cb % pp.AS) * 2 * pp.a_slot + (uint32_t)((sy * pp.PW + sx) * 4), (uint32_t)cb);
+    }
     // a B tile holds this CTA's half of the columns: K-major bn / 2 rows of 64 bytes, MN-major 2 KiB boxes of 32 rows
     const int b_boxes = (half + 31) / 32;
     const uint32_t b_bytes = T::B_MN ? (uint32_t)b_boxes * 2048 : (uint32_t)half * 64;
@@ -425,10 +473,10 @@ tagi_tc_conv_pix_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_c
         for (int s = 0; s < DS; s++) mbar_init(conv_done + s, NCONV_WARPS);
         for (int s = 0; s < AS; s++) {
             mbar_init(a_full + s, 1);
-            mbar_init(a_free + s, NCONV_WARPS);   // every converter warp of this CTA releases a patch once
+            mbar_init(a_free + s, NCW);   // every converter warp of this CTA releases a patch once
         }
         mbar_init(acc_full, 2);
-        mbar_init(acc_empty, 2 * NCONV_WARPS);
+        mbar_init(acc_empty, 2 * NCW);
         *abort_flag = 0;
         mbar_init_fence();
         prefetch_tmap(&tmA0);
@@ -474,7 +522,7 @@ tagi_tc_conv_pix_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_c
                 if (++tap == pp.k2) tap = 0, cb++;
             }
         }
-    } else if (warp == 1 || warp == ISSUER2_WARP) {
+    } else if (warp == 1 || warp == 2 + NCW) {
         // ------------------------------------------------------------------ MMA issuers (CTA 0): warp 1 -> D1, warp 10 -> D2
         if (lane == 0 && cta == 0) {
             const bool chain1 = warp == 1;
@@ -509,7 +557,7 @@ tagi_tc_conv_pix_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_c
                 if (it % chunk_len == chunk_len - 1 || it == nk - 1) mma_commit_pair(acc_full);
             }
         }
-    } else if (warp >= 2 && warp < 2 + NCONV_WARPS) {
+    } else if (warp >= 2 && warp < 2 + NCW) {
         // ------------------------------------------------------------------ converters + accumulation + epilogue
         const int ct = threadIdx.x - 64;
         const int q = warp & 3;
@@ -525,24 +573,32 @@ tagi_tc_conv_pix_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_c
         const uint32_t cstride = (uint32_t)(pp.PR * pp.PW * 4);
         const uint32_t row_off = (uint32_t)(((il * 16 * pp.PR + pyl) * pp.PW + px + pp.lead) * 4);
         int released = 0;   // channel blocks whose patch this warp has released
-        float sum1[64], sum2[64];
+        float sum1[SUMW], sum2[SUMW];
 #pragma unroll
-        for (int i = 0; i < 64; i++) sum1[i] = sum2[i] = 0.f;
+        for (int i = 0; i < SUMW; i++) sum1[i] = sum2[i] = 0.f;
 
         auto drain = [&](int c) -> bool {
             if (!mbar_wait(acc_full, c & 1, abort_flag, status, ST_TIMEOUT_ACC)) return false;
             tc_fence_after_sync();
-            if (h * 64 < ACC) {   // with narrow accumulators the second half of the converter warps holds no columns
+            if (SUMW >= 32) {
 #pragma unroll
-                for (int blk = 0; blk < 2; blk++) {
+                for (int blk = 0; blk < SUMW / 32; blk++) {
                     float v[32];
-                    tmem_ld_32x32(lane_addr + h * 64 + blk * 32, v);
+                    tmem_ld_32x32(lane_addr + h * SUMW + blk * 32, v);
 #pragma unroll
                     for (int i = 0; i < 32; i++) sum1[blk * 32 + i] += v[i];
-                    tmem_ld_32x32(lane_addr + acc_stride + h * 64 + blk * 32, v);
+                    tmem_ld_32x32(lane_addr + acc_stride + h * SUMW + blk * 32, v);
 #pragma unroll
                     for (int i = 0; i < 32; i++) sum2[blk * 32 + i] += v[i];
                 }
+            } else {
+                float v[16];
+                tmem_ld_32x16(lane_addr + h * SUMW, v);
+#pragma unroll
+                for (int i = 0; i < 16; i++) sum1[i] += v[i];
+                tmem_ld_32x16(lane_addr + acc_stride + h * SUMW, v);
+#pragma unroll
+                for (int i = 0; i < 16; i++) sum2[i] += v[i];
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -561,7 +617,7 @@ tagi_tc_conv_pix_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_c
             scanned = upto + 1;
         };
         const int gt = ct & 127;
-        for (int it = h; it < nk && ok; it += 2) {
+        for (int it = h; it < nk && ok; it += NG) {
             const int r = it % RS, d = it % DS;
             ok = mbar_wait(raw_full + r, (it / RS) & 1, abort_flag, status, ST_TIMEOUT_RAW) &&
                  (it < DS || mbar_wait(stage_done + (it - DS) % L, ((it - DS) / L) & 1, abort_flag, status,
@@ -569,46 +625,50 @@ tagi_tc_conv_pix_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_c
             if (!ok) break;
             const uint32_t rb = raw_base + r * RAW_SLOT, ds = der_base + d * DER_SLOT;
             // slab = (channel block cb, tap): the tap moves this thread's read position inside the block's patch
-            const int cb = it / pp.k2, tap = it - cb * pp.k2, ky = tap / pp.k, kx = tap - ky * pp.k;
+            const uint2 te = slab_tab[it];
+            const int cb = (int)te.y;
             ok = mbar_wait(a_full + cb % AS, (cb / AS) & 1, abort_flag, status, ST_TIMEOUT_RAW);
             if (!ok) break;
-            const int sy = pp.sign > 0 ? ky : pp.k - 1 - ky, sx = pp.sign > 0 ? kx : pp.k - 1 - kx;
-            const uint32_t src = patch_base + (cb % AS) * A_SLOT + row_off + (uint32_t)((sy * pp.PW + sx) * 4);
+            const uint32_t src = patch_base + row_off + te.x;
 
+            constexpr int KW = (SUMW == 32 && NCW == 8) ? 16 : 8;   // channels read before they are converted
 #pragma unroll
-            for (int kh = 0; kh < 2; kh++) {  // channels kh*8 .. kh*8+7 of the slab
-                float a0[8], a1[8];
+            for (int kh = 0; kh < 16 / KW; kh++) {
+                float a0[KW], a1[KW];
 #pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    const uint32_t o = src + (kh * 8 + i) * cstride;
+                for (int i = 0; i < KW; i++) {
+                    const uint32_t o = src + (kh * KW + i) * cstride;
                     asm volatile("ld.shared.f32 %0, [%1];" : "=f"(a0[i]) : "r"(o));
                     asm volatile("ld.shared.f32 %0, [%1];" : "=f"(a1[i]) : "r"(o + pp.a_slot));
                 }
-                const uint32_t at = lane_addr + A_COL0 + d * (NA * BK) + kh * 8;
-                float t0[8], t1[8];
 #pragma unroll
-                for (int i = 0; i < 8; i++) t0[i] = hi_part(a0[i]), t1[i] = hi_part(a1[i]);
-                tmem_st_32x8(at + 0 * BK, t0);
-                tmem_st_32x8(at + 1 * BK, t1);
+                for (int p8 = 0; p8 < KW / 8; p8++) {
+                    const uint32_t at = lane_addr + A_COL0 + d * (NA * BK) + kh * KW + p8 * 8;
+                    float t0[8], t1[8];
 #pragma unroll
-                for (int i = 0; i < 8; i++) t0[i] = a0[i] - t0[i], t1[i] = a1[i] - t1[i];
-                tmem_st_32x8(at + 2 * BK, t0);
-                tmem_st_32x8(at + 3 * BK, t1);
-                if (OP == OP_FWD) {
+                    for (int i = 0; i < 8; i++) t0[i] = hi_part(a0[p8 * 8 + i]), t1[i] = hi_part(a1[p8 * 8 + i]);
+                    tmem_st_32x8(at + 0 * BK, t0);
+                    tmem_st_32x8(at + 1 * BK, t1);
 #pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        const float sq = fmaf(a0[i], a0[i], a1[i]);
-                        t0[i] = hi_part(sq);
-                        t1[i] = sq - t0[i];
+                    for (int i = 0; i < 8; i++) t0[i] = a0[p8 * 8 + i] - t0[i], t1[i] = a1[p8 * 8 + i] - t1[i];
+                    tmem_st_32x8(at + 2 * BK, t0);
+                    tmem_st_32x8(at + 3 * BK, t1);
+                    if (OP == OP_FWD) {
+#pragma unroll
+                        for (int i = 0; i < 8; i++) {
+                            const float sq = fmaf(a0[p8 * 8 + i], a0[p8 * 8 + i], a1[p8 * 8 + i]);
+                            t0[i] = hi_part(sq);
+                            t1[i] = sq - t0[i];
+                        }
+                        tmem_st_32x8(at + 4 * BK, t0);
+                        tmem_st_32x8(at + 5 * BK, t1);
                     }
-                    tmem_st_32x8(at + 4 * BK, t0);
-                    tmem_st_32x8(at + 5 * BK, t1);
                 }
             }
             {
-                // This warp's next slab is it + 2: the patches of all blocks below that slab's block are no longer
+                // This warp's next slab is it + NG: the patches of all blocks below that slab's block are no longer
                 // read by it (its slabs come in increasing order), whether or not it had a slab in them.
-                const int nb = min((it + 2) / pp.k2, pp.cblocks);
+                const int nb = min((it + NG) / pp.k2, pp.cblocks);
                 __syncwarp();
                 for (; released < nb; released++)
                     if (lane == 0) mbar_arrive(a_free + released % AS);
@@ -642,7 +702,7 @@ tagi_tc_conv_pix_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_c
                 ok = drain(pending);
                 pending = -1;
             }
-            note_chunk_ends(it + 1);
+            note_chunk_ends(it + NG - 1);
         }
         if (ok) note_chunk_ends(nk - 1);
         if (ok && pending >= 0) ok = drain(pending);
@@ -651,12 +711,12 @@ tagi_tc_conv_pix_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_c
         // epilogue: [image][channel][pixel]; the 32 lanes of a warp hold consecutive pixels, so each channel's store is
         // (mostly) one contiguous run
         const int b = b0 + il, py = py0 + pyl;
-        if (ok && row_in_tile && b < pp.B && py < pp.GH && h * 64 < bn) {
+        if (ok && row_in_tile && b < pp.B && py < pp.GH && h * SUMW < bn) {
             const long npix = (long)pp.GH * pp.GW;
             const long base = (long)b * pp.cols * npix + (long)py * pp.GW + px;
-            const int cbase = col0 + h * 64, valid = min(bn - h * 64, pp.cols - cbase);
+            const int cbase = col0 + h * SUMW, valid = min(bn - h * SUMW, pp.cols - cbase);
 #pragma unroll
-            for (int i0 = 0; i0 < 64; i0 += 8) {
+            for (int i0 = 0; i0 < SUMW; i0 += 8) {
                 float sc[8];
 #pragma unroll
                 for (int u = 0; u < 8; u++) {
@@ -717,7 +777,8 @@ int make_tmap_nchw(CUtensorMap *tm, const float *ptr, int W, int H, int C, int B
 
 struct ParamPlan {
     PatchParam pp;
-    int bn, col_tiles, row_pairs, slices;
+    int bn, col_tiles, row_pairs, row_tiles, slices, sk;   // sk: pixels per slab (16 or 32)
+    bool pair;   // CTA pairs (tiles wider than 64 columns) or single CTAs
 };
 
 inline int round_up4(int v) { return (v + 3) & ~3; }
@@ -729,19 +790,7 @@ bool plan_param(const tagi_conv2d_geom &g, ParamPlan *out) {
     PatchParam &p = out->pp;
     p.fi = g.fi, p.k = g.k, p.k2 = k2, p.Kc = k2 * g.fi, p.fo = g.fo;
     p.CT = 128 / k2 < g.fi ? 128 / k2 : g.fi;
-    p.ho = g.ho, p.nxc = (g.wo + 15) / 16;
-    p.stride = g.stride;
-    p.lead = round_up4(off) - off;
-    p.x0 = -round_up4(off), p.y0 = -off;
-    p.PW = round_up4(15 * g.stride + g.k + p.lead);
-    if (p.PW > 256 || p.CT > 256 || g.k > 256) return false;
-    p.a_bytes = (uint32_t)p.PW * g.k * p.CT * 4;
-    p.a_slot = (p.a_bytes + 1023u) & ~1023u;
-    if (p.a_slot > 24 * 1024) return false;
-    const long total = (long)g.B * g.ho * p.nxc;
-    if (total >= (1L << 31)) return false;
-    p.total_slabs = (int)total;
-    // output channels per pair: one tile when it fits, else the width that wastes least
+    // output channels per tile: one tile when it fits, else the width that wastes least
     int bn = g.fo <= 128 ? ((g.fo + 15) / 16) * 16 : 128;
     if (g.fo > 128) {
         long best = -1;
@@ -750,13 +799,35 @@ bool plan_param(const tagi_conv2d_geom &g, ParamPlan *out) {
             if (best < 0 || waste < best) best = waste, bn = w;
         }
     }
+    static const int solo_mode = [] { const char *v = getenv("TAGI_B200_CONV_SOLO"); return v ? atoi(v) : 1; }();
+    out->pair = bn > 64 || solo_mode == 0;
+    // 32 pixels per slab for single-CTA tiles (measured: 20 % faster on the 64-channel ResNet layers, nothing or a loss
+    // on CTA pairs, whose tensor memory holds only two slots of that size), unless the row's last chunk would be mostly
+    // padding
+    const int pad16 = (g.wo + 15) / 16 * 16, pad32 = (g.wo + 31) / 32 * 32;
+    static const int force_sk = [] { const char *v = getenv("TAGI_B200_CONV_SLABK"); return v ? atoi(v) : 0; }();
+    const int sk = force_sk == 16 || force_sk == 32 ? force_sk : (!out->pair && pad32 * 85 <= pad16 * 100 ? 32 : 16);
+    out->sk = sk;
+    p.ho = g.ho, p.nxc = (g.wo + sk - 1) / sk;
+    p.stride = g.stride;
+    p.lead = round_up4(off) - off;
+    p.x0 = -round_up4(off), p.y0 = -off;
+    p.PW = round_up4((sk - 1) * g.stride + g.k + p.lead);
+    if (p.PW > 256 || p.CT > 256 || g.k > 256) return false;
+    p.a_bytes = (uint32_t)p.PW * g.k * p.CT * 4;
+    p.a_slot = (p.a_bytes + 1023u) & ~1023u;
+    if (p.a_slot > 24 * 1024) return false;
+    const long total = (long)g.B * g.ho * p.nxc;
+    if (total >= (1L << 31)) return false;
+    p.total_slabs = (int)total;
     out->bn = bn;
     out->col_tiles = (g.fo + bn - 1) / bn;
     const int row_tiles = (g.fi + p.CT - 1) / p.CT;
+    out->row_tiles = row_tiles;
     out->row_pairs = (row_tiles + 1) / 2;
-    // slices: about one wave of CTA pairs (two when the contraction is long), at least 32 slabs each
-    const long pairs = (long)out->row_pairs * out->col_tiles;
-    const int slots = tc_sm_budget() / 2;
+    // slices: about one wave of CTAs (or CTA pairs), at least 32 slabs each
+    const long pairs = out->pair ? (long)out->row_pairs * out->col_tiles : (long)row_tiles * out->col_tiles;
+    const int slots = out->pair ? tc_sm_budget() / 2 : tc_sm_budget();
     long s = pairs >= slots ? 1 : slots / pairs;
     if (s > total / 32) s = total / 32;
     if (s < 1) s = 1;
@@ -832,6 +903,7 @@ bool plan_pix(const tagi_conv2d_geom &g, int pass, PixPlan *out) {
     p.cols = fwd ? g.fo : g.fi;
     if (out->src_C % 16 || out->src_W % 4 || p.GW > 128 || p.cols < 16 || p.cols % 4) return false;
     p.k = g.k, p.k2 = g.k * g.k, p.cblocks = out->src_C / 16;
+    if ((long)p.k2 * p.cblocks > PIX_MAX_SLABS) return false;
     p.sign = fwd ? +1 : -1, p.off = off;
     if (p.GH * p.GW <= 64) {
         p.NI = 128 / (p.GH * p.GW), p.TR = p.GH;
@@ -866,14 +938,14 @@ bool plan_pix(const tagi_conv2d_geom &g, int pass, PixPlan *out) {
     return true;
 }
 
-template <int OP, int DS, int ACC>
+template <int OP, int DS, int ACC, int NCW>
 int launch_pix(const CUtensorMap &a0, const CUtensorMap &a1, const CUtensorMap &b0, const CUtensorMap &b1, PixPlan &plan,
                bool relu, cudaStream_t st) {
     int *status = tc_status_word();
     if (!status) return fail(TAGI_ERR_CUDA, "cannot allocate the tensor-core status word");
     PixParam &p = plan.pp;
     // rings: two patch slots (three when they are small), then as many B slots as fit beside the derived ring
-    const size_t budget = 227 * 1024 - 1280;
+    const size_t budget = 227 * 1024 - 1280 - PIX_TAB_BYTES;
     const size_t der = (size_t)DS * PairTraits<OP>::NDER * HALF_BYTES;
     const size_t raw = (size_t)PairTraits<OP>::NRAW_B * HALF_BYTES;
     p.AS = 2 * (size_t)p.a_slot * 3 + der + 4 * raw <= budget ? 3 : 2;
@@ -883,7 +955,7 @@ int launch_pix(const CUtensorMap &a0, const CUtensorMap &a1, const CUtensorMap &
     p.RS = (int)rs;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * (unsigned)plan.col_tiles, (unsigned)plan.row_pairs, 1);
-    cfg.blockDim = dim3(NTHREADS2 - 32);
+    cfg.blockDim = dim3(32 * (3 + NCW));
     cfg.stream = st;
     cfg.dynamicSmemBytes = pix_smem<OP>(p.a_slot, p.AS, p.RS, DS);
     cudaLaunchAttribute attr;
@@ -896,7 +968,7 @@ int launch_pix(const CUtensorMap &a0, const CUtensorMap &a1, const CUtensorMap &
     cudaError_t e;
 #define TAGI_PIX_LAUNCH(CHV, RELUV)                                                                              \
     do {                                                                                                         \
-        auto kfn = tagi_tc_conv_pix_kernel<OP, CHV, DS, ACC, RELUV>;                                             \
+        auto kfn = tagi_tc_conv_pix_kernel<OP, CHV, DS, ACC, RELUV, NCW>;                                             \
         e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);                  \
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");                                       \
         e = cudaLaunchKernelEx(&cfg, kfn, a0, a1, b0, b1, p, plan.bn, status);                                   \
@@ -936,13 +1008,13 @@ int conv2d_bwd_param_patch(const tagi_conv2d_geom &g, const float *var_w, const 
     CUtensorMap tx, td0, td1;
     int rc;
     if ((rc = make_tmap_nchw(&tx, mu_a, g.wi, g.hi, g.fi, g.B, p.PW, g.k, p.CT, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
-    // a CTA stages exactly its half of the pair's output channels: box of bn / 2 channel rows
-    if ((rc = make_tmap_nchw(&td0, dmu_z, g.wo, g.ho, g.fo, g.B, 16, 1, plan.bn / 2, CU_TENSOR_MAP_SWIZZLE_64B))) return rc;
-    if ((rc = make_tmap_nchw(&td1, dvar_z, g.wo, g.ho, g.fo, g.B, 16, 1, plan.bn / 2, CU_TENSOR_MAP_SWIZZLE_64B))) return rc;
+    // a CTA stages exactly the output channels it needs: half of the pair's, or all of a single CTA's
+    const unsigned brows = plan.pair ? plan.bn / 2 : plan.bn;
+    const CUtensorMapSwizzle bswz = plan.sk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+    if ((rc = make_tmap_nchw(&td0, dmu_z, g.wo, g.ho, g.fo, g.B, plan.sk, 1, brows, bswz))) return rc;
+    if ((rc = make_tmap_nchw(&td1, dvar_z, g.wo, g.ho, g.fo, g.B, plan.sk, 1, brows, bswz))) return rc;
     const long slice = (long)g.fo * p.Kc;
     p.slice_elems = slice;
-    static const int ablate = [] { const char *v = getenv("TAGI_B200_PATCH_ABLATE"); return v ? atoi(v) : 0; }();
-    p.ablate = ablate;
     if (plan.slices > 1) {
         float *ws = nullptr;
         if ((rc = conv_scratch((size_t)2 * plan.slices * slice * sizeof(float), &ws, st)) != TAGI_OK) return rc;
@@ -951,12 +1023,13 @@ int conv2d_bwd_param_patch(const tagi_conv2d_geom &g, const float *var_w, const 
         p.out1 = dmu_w, p.out2 = dvar_w, p.scale = var_w;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2 * (unsigned)plan.col_tiles, (unsigned)plan.row_pairs, (unsigned)plan.slices);
+    cfg.gridDim = plan.pair ? dim3(2 * (unsigned)plan.col_tiles, (unsigned)plan.row_pairs, (unsigned)plan.slices)
+                            : dim3((unsigned)plan.col_tiles, (unsigned)plan.row_tiles, (unsigned)plan.slices);
     cfg.blockDim = dim3(NTHREADS2 - 32);
     cfg.stream = st;
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.x = plan.pair ? 2 : 1;
     attr.val.clusterDim.y = 1;
     attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
@@ -964,23 +1037,27 @@ int conv2d_bwd_param_patch(const tagi_conv2d_geom &g, const float *var_w, const 
     cudaError_t e = cudaSuccess;
     // ring depths: RS raw slots (patch + two delta tiles), DS slots of A operands in tensor memory, which holds the two
     // accumulators (ACC columns each) and DS * 64 columns of A operands: six slots when the output tile is at most 64 wide
-#define TAGI_PATCH_LAUNCH(CHV, RSV, DSV, ACCV)                                                                   \
+    // (measured: deeper rings change nothing; the pass is bound by the converter warps' instruction stream)
+#define TAGI_PATCH_LAUNCH(CHV, RSV, DSV, ACCV, NCWV, PAIRV, KSV)                                                 \
     do {                                                                                                         \
-        auto kfn = tagi_tc_conv_param_kernel<CHV, RSV, DSV, ACCV>;                                               \
-        cfg.dynamicSmemBytes = patch_param_smem<RSV, DSV>(p.a_slot);                                             \
+        auto kfn = tagi_tc_conv_param_kernel<CHV, RSV, DSV, ACCV, NCWV, PAIRV, KSV>;                             \
+        cfg.blockDim = dim3(32 * (3 + NCWV));                                                                    \
+        cfg.dynamicSmemBytes = patch_param_smem<RSV, DSV, KSV>(p.a_slot);                                        \
         if (cfg.dynamicSmemBytes > 227 * 1024) return fail(TAGI_ERR_UNSUPPORTED, "patch too large for the shared-memory ring"); \
         e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);                  \
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");                                       \
         e = cudaLaunchKernelEx(&cfg, kfn, tx, td0, td1, p, plan.bn, status);                                     \
     } while (0)
-    static const int cfg_id = [] { const char *v = getenv("TAGI_B200_PATCH_CFG"); return v ? atoi(v) : 0; }();
-    const bool deep = p.a_slot <= 8 * 1024;
-    if (plan.bn <= 64 && cfg_id != 1) {
-        if (deep && cfg_id != 2) { if (tc_chunked()) TAGI_PATCH_LAUNCH(CHUNK_STAGES, 10, 6, 64); else TAGI_PATCH_LAUNCH(0, 10, 6, 64); }
-        else { if (tc_chunked()) TAGI_PATCH_LAUNCH(CHUNK_STAGES, 6, 6, 64); else TAGI_PATCH_LAUNCH(0, 6, 6, 64); }
+    // chunk of the accumulation: 256 contraction steps = 16 slabs of 16 pixels or 8 slabs of 32
+    const bool ch = tc_chunked() != 0;
+    if (plan.sk == 32) {
+        if (plan.bn <= 64 && !plan.pair) { if (ch) TAGI_PATCH_LAUNCH(8, 5, 3, 64, 8, false, 4); else TAGI_PATCH_LAUNCH(0, 5, 3, 64, 8, false, 4); }
+        else if (plan.bn <= 64) { if (ch) TAGI_PATCH_LAUNCH(8, 5, 3, 64, 8, true, 4); else TAGI_PATCH_LAUNCH(0, 5, 3, 64, 8, true, 4); }
+        else { if (ch) TAGI_PATCH_LAUNCH(8, 5, 2, 128, 8, true, 4); else TAGI_PATCH_LAUNCH(0, 5, 2, 128, 8, true, 4); }
     } else {
-        if (deep && cfg_id != 1 && cfg_id != 2) { if (tc_chunked()) TAGI_PATCH_LAUNCH(CHUNK_STAGES, 10, 4, 128); else TAGI_PATCH_LAUNCH(0, 10, 4, 128); }
-        else { if (tc_chunked()) TAGI_PATCH_LAUNCH(CHUNK_STAGES, 6, 4, 128); else TAGI_PATCH_LAUNCH(0, 6, 4, 128); }
+        if (plan.bn <= 64 && !plan.pair) { if (ch) TAGI_PATCH_LAUNCH(16, 6, 6, 64, 8, false, 2); else TAGI_PATCH_LAUNCH(0, 6, 6, 64, 8, false, 2); }
+        else if (plan.bn <= 64) { if (ch) TAGI_PATCH_LAUNCH(16, 6, 6, 64, 8, true, 2); else TAGI_PATCH_LAUNCH(0, 6, 6, 64, 8, true, 2); }
+        else { if (ch) TAGI_PATCH_LAUNCH(16, 6, 4, 128, 8, true, 2); else TAGI_PATCH_LAUNCH(0, 6, 4, 128, 8, true, 2); }
     }
 #undef TAGI_PATCH_LAUNCH
     if (e != cudaSuccess) return cuda_fail(e, "implicit Conv2d parameter pass launch");
@@ -1024,9 +1101,10 @@ int conv2d_fwd_patch(const tagi_conv2d_geom &g, const float *mu_w, const float *
     if ((rc = make_tmap_weights(&b0, ws, (uint64_t)g.fi * p.k2, g.fo, false, plan.bn / 2))) return rc;
     if ((rc = make_tmap_weights(&b1, ws + nw, (uint64_t)g.fi * p.k2, g.fo, false, plan.bn / 2))) return rc;
     p.out1 = mu_z, p.out2 = var_z, p.out3 = relu_jcb, p.aux1 = mu_b, p.aux2 = var_b;
-    if (plan.bn <= 64) return launch_pix<OP_FWD, 4, 64>(a0, a1, b0, b1, plan, relu_jcb != nullptr, st);
-    if (plan.bn <= 112) return launch_pix<OP_FWD, 3, 112>(a0, a1, b0, b1, plan, relu_jcb != nullptr, st);
-    return launch_pix<OP_FWD, 2, 128>(a0, a1, b0, b1, plan, relu_jcb != nullptr, st);
+    // (sixteen converter warps were measured on the 64-column tiles: no gain in the forward pass, 8 % in the state pass)
+    if (plan.bn <= 64) return launch_pix<OP_FWD, 4, 64, 8>(a0, a1, b0, b1, plan, relu_jcb != nullptr, st);
+    if (plan.bn <= 112) return launch_pix<OP_FWD, 3, 112, 8>(a0, a1, b0, b1, plan, relu_jcb != nullptr, st);
+    return launch_pix<OP_FWD, 2, 128, 8>(a0, a1, b0, b1, plan, relu_jcb != nullptr, st);
 }
 
 int conv2d_bwd_state_patch(const tagi_conv2d_geom &g, const float *mu_w, const float *jcb, const float *dmu_z,
@@ -1047,8 +1125,8 @@ int conv2d_bwd_state_patch(const tagi_conv2d_geom &g, const float *mu_w, const f
     if ((rc = make_tmap_nchw(&a1, dvar_z, g.wo, g.ho, g.fo, g.B, p.PW, p.PR, 16, CU_TENSOR_MAP_SWIZZLE_NONE, p.NI))) return rc;
     if ((rc = make_tmap_weights(&b0, ws, g.fi, (uint64_t)g.fo * p.k2, true))) return rc;
     p.out1 = dmu_a, p.out2 = dvar_a, p.out3 = nullptr, p.aux1 = jcb, p.aux2 = nullptr;
-    if (plan.bn <= 64) return launch_pix<OP_BWD_STATE, 6, 64>(a0, a1, b0, b0, plan, false, st);
-    return launch_pix<OP_BWD_STATE, 4, 128>(a0, a1, b0, b0, plan, false, st);
+    if (plan.bn <= 64) return launch_pix<OP_BWD_STATE, 6, 64, 16>(a0, a1, b0, b0, plan, false, st);
+    return launch_pix<OP_BWD_STATE, 4, 128, 8>(a0, a1, b0, b0, plan, false, st);
 }
 
 }  // namespace tagi

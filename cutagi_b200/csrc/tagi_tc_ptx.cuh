@@ -164,6 +164,21 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, float (&v)[32]) {
     for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
 }
 
+// 32 lanes x 16 consecutive 32-bit columns
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
+}
+
 // 32 lanes x 8 consecutive 32-bit columns written from registers: thread i of the warp writes row (lane base + i).
 __device__ __forceinline__ void tmem_st_32x8(uint32_t taddr, const float (&v)[8]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
@@ -347,6 +362,22 @@ __device__ __forceinline__ void mma_commit_pair(uint64_t *bar) {
 #define TAGI_MMA_CPARAM_D2(CG, BS) \
     TAGI_MMA_HEAD TAGI_MMA(CG, 1, 1, 3, 1, BS, p2) TAGI_MMA(CG, 1, 1, 4, 1, BS, pt) TAGI_MMA(CG, 1, 3, 3, 1, BS, pt) "}"
 
+// The same chains with 32-wide k slabs: A tiles 32 tensor-memory columns apart, B tiles BS units of 16 bytes apart
+#define TAGI_MMAW(CG, D, AT, BB, BT, BS, P)                                         \
+    "add.u32 ta, %2, " TAGI_STR(AT) " * 32;\n\t"                                    \
+    "add.u32 tb, %" #BB ", " TAGI_STR(BT) " * " TAGI_STR(BS) ";\n\t"                \
+    "mov.b64 db, {tb, %5};\n\t"                                                     \
+    "tcgen05.mma.cta_group::" #CG ".kind::tf32 [%" #D "], [ta], db, %6, " #P ";\n\t"
+#define TAGI_MMAW_D1(CG, BS) \
+    TAGI_MMA_HEAD TAGI_MMAW(CG, 0, 0, 3, 0, BS, p1) TAGI_MMAW(CG, 0, 0, 4, 0, BS, pt) TAGI_MMAW(CG, 0, 2, 3, 0, BS, pt) "}"
+#define TAGI_MMAW_CPARAM_D2(CG, BS) \
+    TAGI_MMA_HEAD TAGI_MMAW(CG, 1, 1, 3, 1, BS, p2) TAGI_MMAW(CG, 1, 1, 4, 1, BS, pt) TAGI_MMAW(CG, 1, 3, 3, 1, BS, pt) "}"
+#define TAGI_MMAW_FWD_D2(CG, BS)                                                                                      \
+    TAGI_MMA_HEAD TAGI_MMAW(CG, 1, 4, 3, 1, BS, p2) TAGI_MMAW(CG, 1, 1, 4, 2, BS, pt) TAGI_MMAW(CG, 1, 4, 4, 1, BS, pt) \
+        TAGI_MMAW(CG, 1, 5, 3, 1, BS, pt) TAGI_MMAW(CG, 1, 1, 4, 3, BS, pt) TAGI_MMAW(CG, 1, 3, 4, 2, BS, pt) "}"
+#define TAGI_MMAW_BWD_D2(CG, BS) \
+    TAGI_MMA_HEAD TAGI_MMAW(CG, 1, 1, 4, 1, BS, p2) TAGI_MMAW(CG, 1, 1, 4, 2, BS, pt) TAGI_MMAW(CG, 1, 3, 4, 1, BS, pt) "}"
+
 // CHAIN 1 or 2; BS = 512: B tiles of 8 KiB (one CTA); BS = 256: B half tiles of 4 KiB (CTA pairs, cta_group::2)
 template <bool FWD, int CHAIN>
 __device__ __forceinline__ void mma_kstep_ts(uint32_t d1, uint32_t d2, uint32_t at, uint32_t rbl, uint32_t dsl, uint32_t hi,
@@ -367,6 +398,45 @@ __device__ __forceinline__ void mma_kstep_cparam_pair(uint32_t d1, uint32_t d2, 
                                                       uint32_t hi, uint32_t idesc, uint32_t f1, uint32_t f2) {
     if (CHAIN == 1) asm volatile(TAGI_MMA_D1(2, 256) TAGI_MMA_OPERANDS);
     else asm volatile(TAGI_MMA_CPARAM_D2(2, 256) TAGI_MMA_OPERANDS);
+}
+// The same k steps issued by one CTA for itself (cta_group::1, 128 rows), B tiles 4 KiB apart as in the pair kernels
+template <int CHAIN>
+__device__ __forceinline__ void mma_kstep_cparam_solo(uint32_t d1, uint32_t d2, uint32_t at, uint32_t rbl, uint32_t dsl,
+                                                      uint32_t hi, uint32_t idesc, uint32_t f1, uint32_t f2) {
+    if (CHAIN == 1) asm volatile(TAGI_MMA_D1(1, 256) TAGI_MMA_OPERANDS);
+    else asm volatile(TAGI_MMA_CPARAM_D2(1, 256) TAGI_MMA_OPERANDS);
+}
+template <bool FWD, int CHAIN>
+__device__ __forceinline__ void mma_kstep_solo(uint32_t d1, uint32_t d2, uint32_t at, uint32_t rbl, uint32_t dsl,
+                                               uint32_t hi, uint32_t idesc, uint32_t f1, uint32_t f2) {
+    if (CHAIN == 1) asm volatile(TAGI_MMA_D1(1, 256) TAGI_MMA_OPERANDS);
+    else if (FWD) asm volatile(TAGI_MMA_FWD_D2(1, 256) TAGI_MMA_OPERANDS);
+    else asm volatile(TAGI_MMA_BWD_D2(1, 256) TAGI_MMA_OPERANDS);
+}
+// 32-wide k slabs: one 8-wide k step; PAIR selects cta_group::2; B tiles 8 KiB apart
+template <bool PAIR, int CHAIN>
+__device__ __forceinline__ void mma_kstep_cparam_w(uint32_t d1, uint32_t d2, uint32_t at, uint32_t rbl, uint32_t dsl,
+                                                   uint32_t hi, uint32_t idesc, uint32_t f1, uint32_t f2) {
+    if (PAIR) {
+        if (CHAIN == 1) asm volatile(TAGI_MMAW_D1(2, 512) TAGI_MMA_OPERANDS);
+        else asm volatile(TAGI_MMAW_CPARAM_D2(2, 512) TAGI_MMA_OPERANDS);
+    } else {
+        if (CHAIN == 1) asm volatile(TAGI_MMAW_D1(1, 512) TAGI_MMA_OPERANDS);
+        else asm volatile(TAGI_MMAW_CPARAM_D2(1, 512) TAGI_MMA_OPERANDS);
+    }
+}
+template <bool PAIR, bool FWD, int CHAIN>
+__device__ __forceinline__ void mma_kstep_w(uint32_t d1, uint32_t d2, uint32_t at, uint32_t rbl, uint32_t dsl, uint32_t hi,
+                                            uint32_t idesc, uint32_t f1, uint32_t f2) {
+    if (PAIR) {
+        if (CHAIN == 1) asm volatile(TAGI_MMAW_D1(2, 512) TAGI_MMA_OPERANDS);
+        else if (FWD) asm volatile(TAGI_MMAW_FWD_D2(2, 512) TAGI_MMA_OPERANDS);
+        else asm volatile(TAGI_MMAW_BWD_D2(2, 512) TAGI_MMA_OPERANDS);
+    } else {
+        if (CHAIN == 1) asm volatile(TAGI_MMAW_D1(1, 512) TAGI_MMA_OPERANDS);
+        else if (FWD) asm volatile(TAGI_MMAW_FWD_D2(1, 512) TAGI_MMA_OPERANDS);
+        else asm volatile(TAGI_MMAW_BWD_D2(1, 512) TAGI_MMA_OPERANDS);
+    }
 }
 // low / high 32-bit words of a shared-memory matrix descriptor (see make_smem_desc)
 __device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
