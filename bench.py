@@ -509,6 +509,8 @@ def run_conv_layers(args):
     print("| layer (B, fi -> fo, image, k, stride) | P | forward | state backward | parameter backward |")
     print("|---|---|---|---|---|")
     for name, kw in CONV_LAYERS:
+        if args.layer and args.layer not in name:
+            continue
         g = ConvGeom(**kw)
         n_in, n_out, nw = g.B * g.n_in, g.B * g.n_out, g.fo * g.Kc
         t = lambda n: torch.rand(n, device="cuda") * 0.1 + 0.01
@@ -980,6 +982,7 @@ def main():
                     help="arithmetic of the kernels (tagi_set_impl)")
     ap.add_argument("--conv-layers", action="store_true",
                     help="print a per-layer timing table of the Conv2d entry points instead of the benchmark line")
+    ap.add_argument("--layer", default="", help="--conv-layers: only the rows whose name contains this text")
     ap.add_argument("--sm-budget", type=int, default=-1,
                     help="SMs the tensor-core kernels plan their tiles for (tagi_tc_set_sm_budget); default: all on one GPU, "
                          "132 for the Linear step when the exchange's NCCL kernels run next to it (N > 1)")

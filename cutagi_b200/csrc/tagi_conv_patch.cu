@@ -813,6 +813,11 @@ bool plan_param(const tagi_conv2d_geom &g, ParamPlan *out) {
     p.lead = round_up4(off) - off;
     p.x0 = -round_up4(off), p.y0 = -off;
     p.PW = round_up4((sk - 1) * g.stride + g.k + p.lead);
+    // The 32 lanes of a converter warp read 32 consecutive (channel, ky, kx) rows of the patch, i.e. about 11 patch rows of
+    // k consecutive floats each. With a pitch that is a multiple of 32 bytes those rows fall on 4 bank groups (measured:
+    // half of the LSU's shared-memory wavefronts were conflict replays with a pitch of 40 floats); an odd multiple of 16
+    // bytes spreads them over 8.
+    if ((p.PW / 4) % 2 == 0) p.PW += 4;
     if (p.PW > 256 || p.CT > 256 || g.k > 256) return false;
     p.a_bytes = (uint32_t)p.PW * g.k * p.CT * 4;
     p.a_slot = (p.a_bytes + 1023u) & ~1023u;
