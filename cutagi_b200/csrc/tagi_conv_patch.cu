@@ -23,6 +23,13 @@
 // and the barriers between the roles are those of the Linear CTA-pair kernel (tagi_linear_tc.cu).
 // The output is small (fo x fi*k*k) and the contraction long (B * ho * ceil(wo/16) slabs), so the slabs are cut into
 // slices across CTA pairs; slices go to scratch and are summed in slice order (results do not depend on scheduling).
+//
+// Flat mode, for images whose rows are not a multiple of 16 bytes (14 x 14) but whose planes are: TMA cannot address image
+// rows then, so an image plane is treated as one row of H*W pixels (stride-1 layers that keep the image size). A slab is
+// 16 consecutive pixels p0..p0+15 of the flattened plane, its patch the run [p0 - halo, p0 + 16 + halo) of each channel,
+// and tap (ky, kx) of pixel p is the patch entry p + (ky - off) * W + (kx - off). Entries whose column leaves the image row
+// belong to the neighbouring row instead of the padding; the converter thread sets them to zero (the column of pixel i is
+// (p0 + i) mod W). Rows above and below the image fall outside the plane and arrive as zeros as before.
 #include "tagi_tc_tile.cuh"
 
 namespace tagi {
@@ -40,6 +47,7 @@ struct PatchParam {
     float *out1, *out2;   // [slice][fo][Kc]
     const float *scale;   // var_w when the contraction is not sliced, else null (raw partial sums)
     long slice_elems;
+    int flat, W, off;     // flat mode (see above): image width, padding offset; nxc = 16-pixel chunks per plane, ho = 1
 };
 
 constexpr int P_NA = 4, P_NRAW_B = 2, P_NDER = 2;
@@ -127,7 +135,7 @@ tagi_tc_conv_param_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
                 if (it >= RS && !mbar_wait(stage_done + (it - RS) % L, ((it - RS) / L) & 1, abort_flag, status,
                                            ST_TIMEOUT_EMPTY))
                     break;
-                const int t = kb + it;                                  // slab -> (image, output row, 16-pixel chunk)
+                const int t = kb + it;                 // slab -> (image, output row, chunk of the row); flat mode: ho = 1
                 const int xc = t % pp.nxc, rr = t / pp.nxc, oy = rr % pp.ho, b = rr / pp.ho;
                 mbar_arrive_expect_tx(raw_full + r, pp.a_bytes + P_NRAW_B * b_bytes);
                 const uint32_t st = raw_base + r * RAW_SLOT;
@@ -195,10 +203,15 @@ tagi_tc_conv_param_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
         // Rows past the tile's CT * k * k read the patch's first values: finite numbers whose sums are never stored.
         const bool row_in_tile = arow < pp.CT * pp.k2;
         uint32_t row_off = 0;
+        int flat_dx = 0;   // flat mode: this row's column shift
         {
             const int m = row_in_tile ? arow : 0;
             const int cl = m / pp.k2, tap = m - cl * pp.k2, ky = tap / pp.k, kx = tap - ky * pp.k;
             row_off = (uint32_t)(((cl * pp.k + ky) * pp.PW + kx + pp.lead) * 4);
+            if (pp.flat) {   // one patch row per channel; `lead` is the halo
+                row_off = (uint32_t)((cl * pp.PW + pp.lead + (ky - pp.off) * pp.W + (kx - pp.off)) * 4);
+                flat_dx = kx - pp.off;
+            }
         }
         const uint32_t step_b = (uint32_t)pp.stride * 4;
         float sum1[SUMW], sum2[SUMW];
@@ -263,6 +276,15 @@ tagi_tc_conv_param_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
 #pragma unroll
                 for (int i = 0; i < KW; i++)
                     asm volatile("ld.shared.f32 %0, [%1];" : "=f"(x[i]) : "r"(rs + row_off + (kh * KW + i) * step_b));
+                if (pp.flat && flat_dx != 0) {
+                    // column of pixel i of the slab: (p0 + i) mod W; a tap that leaves the image row reads padding
+                    int px = ((kb + it) % pp.nxc * SK + kh * KW) % pp.W;
+#pragma unroll
+                    for (int i = 0; i < KW; i++) {
+                        if ((unsigned)(px + flat_dx) >= (unsigned)pp.W) x[i] = 0.f;
+                        px = px + 1 == pp.W ? 0 : px + 1;
+                    }
+                }
 #pragma unroll
                 for (int p8 = 0; p8 < KW / 8; p8++) {
                     const uint32_t at = lane_addr + A_COL0 + d * (NA * SK) + kh * KW + p8 * 8;
@@ -786,8 +808,12 @@ inline int round_up4(int v) { return (v + 3) & ~3; }
 bool plan_param(const tagi_conv2d_geom &g, ParamPlan *out) {
     const int off = g.pad_type == 1 ? g.pad : 0;
     const int k2 = g.k * g.k;
-    if (k2 > 128 || g.wi % 4 || g.wo % 4 || g.fo < 16) return false;
+    if (k2 > 128 || g.fo < 16) return false;
     PatchParam &p = out->pp;
+    // flat mode: rows are not 16-byte multiples but planes are, and the layer keeps the image size at stride 1
+    const bool flat = (g.wi % 4 || g.wo % 4) && g.stride == 1 && g.wi == g.wo && g.hi == g.ho && (g.hi * g.wi) % 4 == 0;
+    if ((g.wi % 4 || g.wo % 4) && !flat) return false;
+    p.flat = flat ? 1 : 0, p.W = g.wi, p.off = off;
     p.fi = g.fi, p.k = g.k, p.k2 = k2, p.Kc = k2 * g.fi, p.fo = g.fo;
     p.CT = 128 / k2 < g.fi ? 128 / k2 : g.fi;
     // output channels per tile: one tile when it fits, else the width that wastes least
@@ -807,22 +833,30 @@ bool plan_param(const tagi_conv2d_geom &g, ParamPlan *out) {
     const int pad16 = (g.wo + 15) / 16 * 16, pad32 = (g.wo + 31) / 32 * 32;
     static const int force_sk = [] { const char *v = getenv("TAGI_B200_CONV_SLABK"); return v ? atoi(v) : 0; }();
     const int sk = force_sk == 16 || force_sk == 32 ? force_sk : (!out->pair && pad32 * 85 <= pad16 * 100 ? 32 : 16);
-    out->sk = sk;
+    out->sk = flat ? 16 : sk;
     p.ho = g.ho, p.nxc = (g.wo + sk - 1) / sk;
     p.stride = g.stride;
     p.lead = round_up4(off) - off;
     p.x0 = -round_up4(off), p.y0 = -off;
     p.PW = round_up4((sk - 1) * g.stride + g.k + p.lead);
+    if (flat) {
+        // one row per channel: [p0 - halo, p0 + 16 + halo), halo = the largest tap shift off * W + off rounded up to 16 bytes
+        const int halo = round_up4(off * g.wi + off);
+        p.ho = 1, p.nxc = (g.hi * g.wi + 15) / 16;
+        p.lead = halo, p.x0 = -halo, p.y0 = 0;
+        p.PW = 16 + 2 * halo;
+        if (g.k - 1 - off > off) return false;   // (taps reach further down-right than up-left: not a same-size layer)
+    }
     // The 32 lanes of a converter warp read 32 consecutive (channel, ky, kx) rows of the patch, i.e. about 11 patch rows of
     // k consecutive floats each. With a pitch that is a multiple of 32 bytes those rows fall on 4 bank groups (measured:
     // half of the LSU's shared-memory wavefronts were conflict replays with a pitch of 40 floats); an odd multiple of 16
     // bytes spreads them over 8.
     if ((p.PW / 4) % 2 == 0) p.PW += 4;
     if (p.PW > 256 || p.CT > 256 || g.k > 256) return false;
-    p.a_bytes = (uint32_t)p.PW * g.k * p.CT * 4;
+    p.a_bytes = (uint32_t)p.PW * (flat ? 1 : g.k) * p.CT * 4;
     p.a_slot = (p.a_bytes + 1023u) & ~1023u;
     if (p.a_slot > 24 * 1024) return false;
-    const long total = (long)g.B * g.ho * p.nxc;
+    const long total = (long)g.B * p.ho * p.nxc;
     if (total >= (1L << 31)) return false;
     p.total_slabs = (int)total;
     out->bn = bn;
@@ -1012,12 +1046,14 @@ int conv2d_bwd_param_patch(const tagi_conv2d_geom &g, const float *var_w, const 
     if (!status) return fail(TAGI_ERR_CUDA, "cannot allocate the tensor-core status word");
     CUtensorMap tx, td0, td1;
     int rc;
-    if ((rc = make_tmap_nchw(&tx, mu_a, g.wi, g.hi, g.fi, g.B, p.PW, g.k, p.CT, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
+    // flat mode: the plane is one row of H * W pixels
+    const int mw = p.flat ? g.hi * g.wi : g.wi, mh = p.flat ? 1 : g.hi, ow = p.flat ? g.ho * g.wo : g.wo, oh = p.flat ? 1 : g.ho;
+    if ((rc = make_tmap_nchw(&tx, mu_a, mw, mh, g.fi, g.B, p.PW, p.flat ? 1 : g.k, p.CT, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
     // a CTA stages exactly the output channels it needs: half of the pair's, or all of a single CTA's
     const unsigned brows = plan.pair ? plan.bn / 2 : plan.bn;
     const CUtensorMapSwizzle bswz = plan.sk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
-    if ((rc = make_tmap_nchw(&td0, dmu_z, g.wo, g.ho, g.fo, g.B, plan.sk, 1, brows, bswz))) return rc;
-    if ((rc = make_tmap_nchw(&td1, dvar_z, g.wo, g.ho, g.fo, g.B, plan.sk, 1, brows, bswz))) return rc;
+    if ((rc = make_tmap_nchw(&td0, dmu_z, ow, oh, g.fo, g.B, plan.sk, 1, brows, bswz))) return rc;
+    if ((rc = make_tmap_nchw(&td1, dvar_z, ow, oh, g.fo, g.B, plan.sk, 1, brows, bswz))) return rc;
     const long slice = (long)g.fo * p.Kc;
     p.slice_elems = slice;
     if (plan.slices > 1) {

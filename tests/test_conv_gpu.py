@@ -125,6 +125,10 @@ TC_GEOMS = [
     dict(B=4, fi=192, hi=10, wi=10, fo=32, k=3, stride=1, pad=1, pad_type=1, has_bias=1),   # state pass explicit, forward implicit
     dict(B=4, fi=32, hi=10, wi=10, fo=192, k=3, stride=1, pad=1, pad_type=1, has_bias=1),   # forward explicit, state pass implicit
     dict(B=5, fi=16, hi=13, wi=11, fo=32, k=3, stride=1, pad=1, pad_type=1, has_bias=0),    # 715 rows: ragged last row tile
+    # image rows that are no 16-byte multiples while the planes are: the implicit parameter pass treats a plane as one row
+    dict(B=8, fi=32, hi=14, wi=14, fo=48, k=3, stride=1, pad=1, pad_type=1, has_bias=1),    # 14 x 14, as ResNet layer3
+    dict(B=12, fi=20, hi=10, wi=10, fo=24, k=5, stride=1, pad=2, pad_type=1, has_bias=0),   # 10 x 10, 5 x 5 taps
+    dict(B=24, fi=8, hi=6, wi=6, fo=160, k=3, stride=1, pad=1, pad_type=1, has_bias=0),     # 6 x 6 planes, two column tiles
 ]
 
 
