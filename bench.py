@@ -988,7 +988,7 @@ def main():
                          "132 for the Linear step when the exchange's NCCL kernels run next to it (N > 1)")
     ap.add_argument("--nccl-max-ctas", type=int, default=0,
                     help="N > 1: upper bound on the CTAs of one NCCL kernel of the exchange (0 = NCCL's default)")
-    ap.add_argument("--param-pieces", type=int, default=2,
+    ap.add_argument("--param-pieces", type=int, default=4,
                     help="linear, N > 1: ranges of output features the parameter pass and the exchange are cut into")
     ap.add_argument("--workload", default="linear", choices=["linear", "resnet18", "cnn", "mlp"],
                     help="linear: the benchmark line (Linear micro-benchmark + ResNet-18 leg); resnet18 / cnn / mlp: only one "
