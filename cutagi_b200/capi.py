@@ -58,6 +58,14 @@ _SIGNATURES = {
     "tagi_avgpool2d_fwd": [C.POINTER(ConvGeom), _p, _p, _p, _p, _p],
     "tagi_avgpool2d_bwd_state": [C.POINTER(ConvGeom), _p, _p, _p, _p, _p, _p],
     "tagi_add_shortcut": [_p, _p, _p, C.c_size_t, _p, _p, _p],
+    "tagi_io_create": [C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, _i, C.POINTER(_p)],
+    "tagi_io_destroy": [_p],
+    "tagi_io_host_buffers": [_p, _i, C.POINTER(_p), C.POINTER(_p), C.POINTER(_p)],
+    "tagi_io_device_buffers": [_p, _i, C.POINTER(_p), C.POINTER(_p), C.POINTER(_p)],
+    "tagi_io_upload": [_p, _i, _p],
+    "tagi_io_consumed": [_p, _i, _p],
+    "tagi_io_download": [_p, _i, _p, _p, C.c_size_t, _p],
+    "tagi_io_wait_output": [_p, _i, C.POINTER(_p), C.POINTER(_p)],
 }
 
 _lib = None
@@ -75,6 +83,8 @@ def load():
         _lib.tagi_last_error_string.restype = C.c_char_p
         _lib.tagi_conv2d_workspace_bytes.restype = C.c_size_t
         _lib.tagi_conv2d_workspace_bytes.argtypes = [C.POINTER(ConvGeom)]
+        _lib.tagi_scratch_bytes.restype = C.c_size_t
+        _lib.tagi_scratch_bytes.argtypes = []
         for name, args in _SIGNATURES.items():
             fn = getattr(_lib, name)
             fn.argtypes = args
@@ -87,7 +97,8 @@ class _Lib:
 
     def __getattr__(self, name):
         fn = getattr(load(), name)
-        if name in ("tagi_get_impl", "tagi_version", "tagi_last_error_string", "tagi_conv2d_workspace_bytes"):
+        if name in ("tagi_get_impl", "tagi_version", "tagi_last_error_string", "tagi_conv2d_workspace_bytes",
+                    "tagi_scratch_bytes"):
             return fn
 
         def checked(*args):

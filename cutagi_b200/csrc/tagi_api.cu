@@ -56,6 +56,7 @@ int tagi_tc_status(int *status, int reset) {
 }
 int tagi_reserve_scratch(size_t bytes) { return reserve_scratch(bytes); }
 int tagi_release_scratch(void) { return release_scratch(); }
+size_t tagi_scratch_bytes(void) { return scratch_bytes(); }
 int tagi_tc_set_chunked(int on) { return linear_tc_set_chunked(on); }
 int tagi_tc_set_sm_budget(int sms) { return linear_tc_set_sm_budget(sms); }
 int tagi_tc_set_variant(int v) { return linear_tc_set_variant(v); }
@@ -285,8 +286,9 @@ static int check_geom(const tagi_conv2d_geom *g) {
 size_t tagi_conv2d_workspace_bytes(const tagi_conv2d_geom *g) {
     if (check_geom(g) != TAGI_OK) return 0;
     size_t a = conv_tc_workspace_bytes(*g), b = conv_ffma_workspace_bytes(*g);
-    const size_t c = conv_param_patch_workspace_bytes(*g);
+    const size_t c = conv_param_patch_workspace_bytes(*g), d = conv_pix_patch_workspace_bytes(*g);
     a = a > c ? a : c;
+    a = a > d ? a : d;
     // BatchNorm statistics of the layer's output share the block: 16 bytes per channel and 4096-element slice
     const size_t bn = (size_t)g->fo * (((size_t)g->B * g->ho * g->wo + 4095) / 4096) * 16;
     const size_t m = a > b ? a : b;

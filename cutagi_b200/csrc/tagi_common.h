@@ -97,6 +97,7 @@ int reserve_scratch(size_t bytes);
 size_t conv_tc_workspace_bytes(const tagi_conv2d_geom &g);
 size_t conv_ffma_workspace_bytes(const tagi_conv2d_geom &g);
 int release_scratch();
+size_t scratch_bytes();
 int conv_bias_delta(const tagi_conv2d_geom &g, const float *var_b, const float *dmu_z, const float *dvar_z,
                     float *dmu_b, float *dvar_b, cudaStream_t st);
 // Conv2d on the tensor-core Linear kernels (tagi_conv_tc.cu)

@@ -401,6 +401,13 @@ int reserve_scratch(size_t bytes) {
     return TAGI_OK;
 }
 
+size_t scratch_bytes() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    std::lock_guard<std::mutex> lk(g_scratch_mu);
+    return g_scratch[dev].bytes;
+}
+
 int release_scratch() {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);

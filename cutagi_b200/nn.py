@@ -433,6 +433,7 @@ class Sequential:
         """name -> (mu_w, var_w, mu_b, var_b) as numpy arrays, with the reference's names (src/sequential.cpp:630-700)."""
         def h(t):
             return None if t is None else t.detach().cpu().numpy()
+        self.check_kernels()
         return {k: (h(l.mu_w), h(l.var_w), h(l.mu_b), h(l.var_b)) for k, l in self.named_layers().items()}
 
     def load_state_dict(self, sd):
@@ -465,6 +466,22 @@ class Sequential:
         self.output = (mu, var, jcb)
         self.delta = (torch.zeros_like(mu), torch.zeros_like(mu))   # input_delta_z_buffer
         return mu, var
+
+    def forward_staged(self, io, slot):
+        """Forward pass on the batch staged in slot `slot` of a hostio.HostPipeline: the upload runs on the pipeline's
+        stream and the kernels wait for it on the device. Returns (mu, var) and the slot's device observations and
+        indices for the output updater."""
+        io.upload(slot, _stream())
+        x, obs, idx = io.device_tensors(slot)
+        mu, var = self.forward(x)
+        return mu, var, obs, idx
+
+    def check_kernels(self):
+        """Raises when a bounded device-side wait of the tensor-core kernels ran out since the last check (the launch
+        that it belonged to left its outputs incomplete). Synchronises with the device; state_dict() calls it."""
+        status = capi.tc_status()
+        if status != 0:
+            raise capi.TagiError(capi.TAGI_OK, f"a bounded wait of the tensor-core kernels ran out (status {status})")
 
     def backward(self):
         dmu, dvar = self.delta

@@ -75,7 +75,8 @@ int tagi_tc_set_sm_budget(int sms);
  * is being captured. To keep every allocation out of the training loop, size the block up front:
  *   tagi_conv2d_workspace_bytes(g)  bytes the three Conv2d passes of geometry g can ask for (host, no CUDA call);
  *   tagi_reserve_scratch(bytes)     make the current device's block at least that large (allocates; call at set-up);
- *   tagi_release_scratch()          synchronise the current device and free its block and every retired one.
+ *   tagi_release_scratch()          synchronise the current device and free its block and every retired one;
+ *   tagi_scratch_bytes()            size of the current device's block (host, no CUDA call besides cudaGetDevice).
  * Rules: calls that use scratch on one device must be ordered on the GPU (one stream, or events between streams), and
  * only one host thread at a time may issue such calls for a device: the block's contents are not protected. The
  * reference gives its launchers caller-owned temp_states.tmp_1 / tmp_2 for the same purpose
@@ -84,6 +85,7 @@ struct tagi_conv2d_geom;
 size_t tagi_conv2d_workspace_bytes(const struct tagi_conv2d_geom *g);
 int tagi_reserve_scratch(size_t bytes);
 int tagi_release_scratch(void);
+size_t tagi_scratch_bytes(void);
 
 const char *tagi_last_error_string(void);
 /* Library version as major*10000 + minor*100 + patch. */
@@ -304,6 +306,31 @@ int tagi_avgpool2d_bwd_state(const tagi_conv2d_geom *g, const float *jcb, const 
  * add_shortcut_mean_var_cuda / add_shortcut_delta_cuda (src/resnet_block_cuda.cu:7-33). */
 int tagi_add_shortcut(const float *mu_s, const float *var_s, const float *jcb, size_t n, float *mu_a, float *var_a,
                       void *stream);
+
+/* ---- Host I/O path of a training step ------------------------------------------------------------------------------
+ * A pipeline owns `depth` slots. A slot holds, in pinned host memory and mirrored on the device, one batch's inputs
+ * (in_floats), observations (obs_floats) and selected indices (idx_ints), and a pinned buffer for 2 * out_floats output
+ * moments. The data loader writes a batch into the host buffers of a free slot; tagi_io_upload copies the slot to the
+ * device asynchronously on the pipeline's own stream and makes compute_stream wait for it (a stream wait: the host does
+ * not block), so the upload of batch i+1 overlaps the kernels of batch i. After the step's last kernel that reads the
+ * slot's device buffers, tagi_io_consumed tells the pipeline the slot may be refilled. tagi_io_download copies exactly
+ * n = B * n_out floats of mu and of var to the slot's pinned output buffer on a second stream after the work queued on
+ * compute_stream so far, and tagi_io_wait_output blocks the host until they have landed.
+ * Replaces, for the caller that adopts it, the blocking whole-buffer copies of cuTAGI's state carriers
+ * (HiddenStateCuda::to_device / to_host, src/data_struct_cuda.cu:83-123: capacity = batch x widest layer, pageable host
+ * vectors), ObservationCuda::to_device (src/data_struct_cuda.cu:300-330) and the list conversions of
+ * pytagi/nn/output_updater.py:45-47. All allocations happen in tagi_io_create; no other call allocates.
+ * One pipeline belongs to one device (the one current at creation) and one host thread. */
+typedef struct tagi_io tagi_io;
+int tagi_io_create(size_t in_floats, size_t obs_floats, size_t idx_ints, size_t out_floats, int depth, tagi_io **io);
+int tagi_io_destroy(tagi_io *io);
+/* Host (pinned) and device addresses of a slot's three input arrays; any of the out-pointers may be NULL. */
+int tagi_io_host_buffers(tagi_io *io, int slot, float **inputs, float **obs, int **idx);
+int tagi_io_device_buffers(tagi_io *io, int slot, const float **inputs, const float **obs, const int **idx);
+int tagi_io_upload(tagi_io *io, int slot, void *compute_stream);
+int tagi_io_consumed(tagi_io *io, int slot, void *compute_stream);
+int tagi_io_download(tagi_io *io, int slot, const float *mu, const float *var, size_t n, void *compute_stream);
+int tagi_io_wait_output(tagi_io *io, int slot, const float **mu, const float **var);
 
 #ifdef __cplusplus
 }

@@ -117,6 +117,9 @@ void Conv2dCuda::forward(BaseHiddenStates &input_states, BaseHiddenStates &outpu
     output_states.actual_size = output_size;
 
     const tagi_conv2d_geom g = geometry_of(*this, batch);
+    // the library's scratch block is sized here for all three passes of this layer, so that the backward pass never
+    // allocates (a no-op once the block is large enough)
+    if (training) require_ok(tagi_reserve_scratch(tagi_conv2d_workspace_bytes(&g)));
     require_ok(tagi_conv2d_fwd(&g, d_mu_w, d_var_w, d_mu_b, d_var_b, in->d_mu_a, in->d_var_a, out->d_mu_a, out->d_var_a,
                                nullptr));
     if (training) store_states_for_training_cuda(*in, *out);

@@ -37,7 +37,7 @@ def test_library_exports_every_declared_symbol(cdll):
 
 def test_python_binding_covers_every_symbol():
     from cutagi_b200 import capi
-    bound = set(capi._SIGNATURES) | {"tagi_last_error_string", "tagi_conv2d_workspace_bytes"}
+    bound = set(capi._SIGNATURES) | {"tagi_last_error_string", "tagi_conv2d_workspace_bytes", "tagi_scratch_bytes"}
     assert set(declared_symbols()) <= bound
 
 

@@ -305,3 +305,36 @@ def test_configuration_layer_shapes_sampled(G, oracle, name, kw):
             f"{names[i]}: max err {err:.3e} vs the FP32 reference, whose own deviation from FP64 is {noise:.3e}"
     assert dvw.max() <= 0
     assert capi.tc_status() == 0, "a bounded device-side wait ran out"
+
+
+def test_reserved_scratch_covers_all_three_passes(G):
+    """tagi_conv2d_workspace_bytes + tagi_reserve_scratch: once the library's scratch block has been sized for a layer,
+    none of its passes makes the block grow or allocates device memory (free memory as the driver reports it stays the
+    same), whichever kernels the planner picks. Layers of three kinds: patch kernels, gather through scratch (7 x 7 images), strided."""
+    import torch
+    from cutagi_b200.capi import lib
+    P = lambda t: t.data_ptr()
+    for kw in (dict(B=16, fi=64, hi=28, wi=28, fo=64, k=3, stride=1, pad=1, pad_type=1, has_bias=1),
+               dict(B=32, fi=128, hi=7, wi=7, fo=256, k=3, stride=1, pad=1, pad_type=1, has_bias=0),
+               dict(B=16, fi=32, hi=28, wi=28, fo=64, k=3, stride=2, pad=1, pad_type=2, has_bias=0)):
+        g = ConvGeom(**kw)
+        cg = G.cgeom(g)
+        need = lib.tagi_conv2d_workspace_bytes(C.byref(cg))
+        assert need > 0
+        lib.tagi_reserve_scratch(need)
+        t = lambda n: torch.rand(n, device="cuda") * 0.1 + 0.01
+        n_in, n_out, nw = g.B * g.n_in, g.B * g.n_out, g.fo * g.Kc
+        mw, vw, mb, vb, ma, va, j, dm, dv = t(nw), t(nw), t(g.fo), t(g.fo), t(n_in), t(n_in), t(n_in), t(n_out), t(n_out)
+        mz, vz, da, dva, dw, dvw, db, dvb = t(n_out), t(n_out), t(n_in), t(n_in), t(nw), t(nw), t(g.fo), t(g.fo)
+        cap0 = lib.tagi_scratch_bytes()
+        assert cap0 >= need
+        for attempt in range(2):   # the first round may load kernel code; the second must not change free memory at all
+            torch.cuda.synchronize()
+            free0, _ = torch.cuda.mem_get_info()
+            lib.tagi_conv2d_fwd(C.byref(cg), P(mw), P(vw), P(mb), P(vb), P(ma), P(va), P(mz), P(vz), None)
+            lib.tagi_conv2d_bwd_param(C.byref(cg), P(vw), P(vb), P(ma), P(dm), P(dv), P(dw), P(dvw), P(db), P(dvb), None)
+            lib.tagi_conv2d_bwd_state(C.byref(cg), P(mw), P(j), P(dm), P(dv), P(da), P(dva), None)
+            torch.cuda.synchronize()
+            free1, _ = torch.cuda.mem_get_info()
+            assert lib.tagi_scratch_bytes() == cap0, "the scratch block grew although it had been reserved"
+        assert free1 == free0, (kw, free0 - free1)
