@@ -117,3 +117,42 @@ def test_cnn_forward_backward_through_cutagi(cutagi):
             net.step()
         tol = (1e-5, 1e-4) if s == 0 else (1e-3, 1e-3)
         assert _rel(outs[1][0], outs[0][0]) < tol[0] * 10 and _rel(outs[1][1], outs[0][1]) < tol[1] * 10, s
+
+
+def test_small_resnet_through_cutagi_sequential(cutagi, oracle):
+    """The block structure of the reference's ResNet-18 at reduced size (conv stem, identity block, projection block with
+    stride 2, global pooling, Linear head) trained through cuTAGI's own Sequential / LayerBlock / ResNetBlock on "cuda",
+    where Linear, Conv2d, BatchNorm2d, AvgPool2d, ReLU and the capped update run on this library (integration/), against
+    the CPU oracle, whose runs of this network are pinned bit for bit on the reference's CPU classes."""
+    from oracle_net import OracleNet, net_golden_problems
+    from test_ddp_dropin import build_net, load_oracle_parameters
+    m = cutagi
+    spec, in_shape, batch, _ = net_golden_problems()["resnet"]
+    cpu = OracleNet(oracle, spec, in_shape, seed=1)
+    keep = []
+    net = build_net(m, spec, in_shape, keep)
+    net.to_device("cuda")
+    net.preinit_layer()
+    load_oracle_parameters(net, cpu)
+    upd = m.OutputUpdater(net.device)
+    rng = np.random.default_rng(11)
+    n_in = int(np.prod(in_shape))
+    for s in range(3):
+        x = rng.standard_normal((batch, n_in)).astype(np.float32)
+        obs = rng.standard_normal((batch, 11)).astype(np.float32)
+        var_obs = np.full((batch, 11), 0.5, np.float32)
+        net.forward(x.reshape(-1), None)
+        mu, var = net.get_outputs()
+        rmu, rvar = cpu.forward(x)
+        tol = (2e-5, 2e-4) if s == 0 else (1e-3, 1e-3)
+        assert _rel(mu, rmu) < tol[0] and _rel(var, rvar) < tol[1], (s, _rel(mu, rmu), _rel(var, rvar))
+        upd.update(net.output_z_buffer, obs.reshape(-1), var_obs.reshape(-1), net.input_delta_z_buffer)
+        cpu.update(obs, var_obs)
+        net.backward()
+        cpu.backward()
+        net.step()
+        cpu.step()
+    ref = cpu.state_dict()
+    for k, v in net.state_dict().items():
+        r = ref[k.replace("Cuda", "")]
+        assert _rel(v[0], r["mu_w"].reshape(-1)) < 1e-3 and _rel(v[1], r["var_w"].reshape(-1)) < 1e-3, k
