@@ -182,6 +182,11 @@ class Conv2d(Linear):
         mu_z = torch.empty(B, self.fo * self.ho * self.wo, device=mu_a.device)
         var_z = torch.empty_like(mu_z)
         g = self._g(B)
+        if train and getattr(self, "_reserved_for", None) != B:
+            # size the library's scratch pool for all three passes of this layer before the first of them runs, so that no
+            # pass has to grow the pool in the middle of a step (or of a stream capture)
+            lib.tagi_reserve_scratch(lib.tagi_conv2d_workspace_bytes(ctypes.byref(g)))
+            self._reserved_for = B
         if act:
             j = torch.empty_like(mu_z)
             lib.tagi_conv2d_fwd_act(ctypes.byref(g), _p(self.mu_w), _p(self.var_w), _p(self.mu_b), _p(self.var_b),
