@@ -873,7 +873,12 @@ def run_network(args, rank, world, local_rank):
                 "h2d_bytes_per_step": int(xs[0].numel() * 4 + obs[0].numel() * 4 + idx[0].numel() * 4),
                 "d2h_bytes_per_step": int(host_out.numel() * 4),
                 "path": "tagi_io_* host pipeline: pinned staging, upload on its own stream, read-back of B x n_out moments"},
-        "exchange": exchange_info, "gpu_launches": None, "tc_status": status, "clocks": clocks}
+        "exchange": exchange_info,
+        # kernel launches of one step counted in an ncu launch list of this workload (ReLU ResNet-18 at 224 x 224: 257
+        # launches of this library's kernels between two capped updates); other workloads were not counted
+        "gpu_launches": 257 * args.steps if args.workload == "resnet18" and image == 224 and args.act == "relu" else None,
+        "gpu_launches_is": "launches per step from an ncu launch list of this workload x timed steps",
+        "tc_status": status, "clocks": clocks}
 
 
 def run_resnet_module(args):
@@ -1089,7 +1094,7 @@ def main():
                     "steps": rn["steps"], "samples_per_gpu": 64, "workload": rn["config"]["workload"],
                     "e2e": rn["e2e"], "exchange": rn["exchange"] if world > 1 else "none (1 GPU)",
                     "roofline_frac": rn["roofline"]["frac"], "roofline": rn["roofline"], "clocks": rn["clocks"],
-                    "tc_status": rn["tc_status"]}
+                    "gpu_launches": rn["gpu_launches"], "tc_status": rn["tc_status"]}
         return line
     line = with_group(both)
     if line is not None:

@@ -4,6 +4,7 @@
 //   AvgPool2dCuda::forward / backward     (src/pooling_layer_cuda.cu:167-270)     -> tagi_avgpool2d_fwd / _bwd_state
 //   ReLUCuda::forward                     (src/activation_cuda.cu:510-544)        -> tagi_relu_fwd
 //   BaseLayerCuda::update_weights / update_biases (src/base_layer_cuda.cu:161-202) -> tagi_param_update
+//   HiddenStateCuda::set_input_x          (src/data_struct_cuda.cu:39-63)         -> one copy of the batch, fills on the device
 // Everything else of those classes (constructors, parameter storage, save / load, to_host, bindings) stays cuTAGI's own
 // code: its translation units are compiled unchanged and only the symbols of the methods above are weakened in the
 // resulting objects (objcopy --weaken-symbol, integration/Makefile), so that the definitions here win at link time.
@@ -16,6 +17,7 @@
 #include "base_layer_cuda.cuh"
 #include "batchnorm_layer_cuda.cuh"
 #include "custom_logger.h"
+#include "data_struct_cuda.cuh"
 #include "ddp_b200_hooks.h"
 #include "pooling_layer_cuda.cuh"
 #include "tagi_b200.h"
@@ -161,4 +163,37 @@ void BaseLayerCuda::update_biases() {
     if (!bias || num_biases == 0 || d_mu_b == nullptr) return;
     require_ok(tagi_param_update(batch_for_cap(cap_factor_update), num_biases, d_mu_b, d_var_b, d_delta_mu_b, d_delta_var_b,
                                  nullptr, nullptr));
+}
+
+// ------------------------------------------------------------------------------------------------ network input
+// cuTAGI copies the batch element by element into the state's host vectors (means, a variance of zero or the given one,
+// Jacobians of one) and then uploads all three from pageable memory. Here the means go to the device in one copy straight
+// from the caller's vector and the other two arrays are written on the device; for the 64 x 3 x 224 x 224 batch of the
+// ResNet-18 configuration that is one 38.5 MB copy instead of three plus 29 million host-side assignments. The host
+// mirrors keep whatever they held: cuTAGI reads them only after to_host(), which overwrites them.
+namespace {
+__global__ void fill_input_aux_kernel(size_t n, bool zero_var, float *var_a, float *jcb) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        if (zero_var) var_a[i] = 0.0f;
+        jcb[i] = 1.0f;
+    }
+}
+}  // namespace
+
+void HiddenStateCuda::set_input_x(const std::vector<float> &mu_x, const std::vector<float> &var_x, const size_t block_size) {
+    const size_t n = mu_x.size();
+    this->actual_size = n / block_size;
+    this->block_size = block_size;
+    if (n > this->size) LOG(LogLevel::ERROR, "Input batch is larger than the hidden-state buffer");
+    cudaSetDevice(this->device_idx);
+    const bool has_var = var_x.size() == n;
+    cudaError_t e = cudaMemcpy(this->d_mu_a, mu_x.data(), n * sizeof(float), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess && has_var) e = cudaMemcpy(this->d_var_a, var_x.data(), n * sizeof(float), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) LOG(LogLevel::ERROR, std::string("Failed to copy the input batch to the device: ") + cudaGetErrorString(e));
+    if (n > 0) {
+        const unsigned blocks = (unsigned)((n + 1023) / 1024 < 148 * 8 ? (n + 1023) / 1024 : 148 * 8);
+        fill_input_aux_kernel<<<blocks, 256>>>(n, !has_var, this->d_var_a, this->d_jcb);
+        if (cudaGetLastError() != cudaSuccess) LOG(LogLevel::ERROR, "Failed to launch the input fill kernel");
+    }
 }
