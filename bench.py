@@ -321,23 +321,31 @@ def run_b200(args, rank, world, local_rank):
                                                       "FP64 mean of the ranks' local deltas"}}
 
     # End to end: host buffers in, host buffers out, copies inside the timed region. Every step's inputs travel host ->
-    # device and its outputs device -> host on their own streams: inputs are double-buffered on the device, so the
-    # upload of step i+1 overlaps the kernels and the download of step i (PCIe is full duplex); events order buffer
-    # reuse. Two variants: "layer" keeps the parameters and the parameter deltas on the device, as cuTAGI's LinearCuda
-    # does (d_mu_w ..., d_delta_mu_w ... are members of the layer; only activations and incoming deltas are a step's
-    # inputs, only the forward outputs, the state deltas and the bias deltas its results); "all" moves every tensor of
-    # the three calls both ways.
+    # device and its outputs device -> host on their own streams. Inputs and the large outputs (forward moments, state
+    # deltas) are double-buffered on the device, so the upload of step i+1, the kernels of step i and the download of
+    # step i-1 overlap (PCIe is full duplex); events order buffer reuse. The parameter and bias deltas keep one buffer
+    # (they are what the exchange has registered for N > 1); they are downloaded first, so the next step waits for a few
+    # KB at most in the "layer" variant. Two variants: "layer" keeps the parameters and the parameter deltas on the
+    # device, as cuTAGI's LinearCuda does (d_mu_w ..., d_delta_mu_w ... are members of the layer; only activations and
+    # incoming deltas are a step's inputs, only the forward outputs, the state deltas and the bias deltas its results);
+    # "all" moves every tensor of the three calls both ways.
     in_layer = ["mu_a", "var_a", "jcb", "dmu_z", "dvar_z"]
     out_layer = ["mu_z", "var_z", "dmu_a", "dvar_a", "dmu_b", "dvar_b"]
     d_alt = {k: torch.empty_like(v) for k, v in d.items()}
+    o_alt = {k: torch.empty_like(o[k]) for k in ("mu_z", "var_z", "dmu_a", "dvar_a")}
     s_h2d, s_d2h = torch.cuda.Stream(), torch.cuda.Stream()
 
     def make_e2e(in_keys, out_keys):
-        psets = [p, {**p, **{k: d_alt[k].data_ptr() for k in in_keys}}]
-        dsets = [d, {**d, **{k: d_alt[k] for k in in_keys}}]
+        twice = [k_ for k_ in out_keys if k_ in o_alt]
+        once = [k_ for k_ in out_keys if k_ not in o_alt]
+        psets = [p, {**p, **{k_: d_alt[k_].data_ptr() for k_ in in_keys}, **{k_: o_alt[k_].data_ptr() for k_ in twice}}]
+        dsets = [d, {**d, **{k_: d_alt[k_] for k_ in in_keys}}]
+        osets = [o, {**o, **{k_: o_alt[k_] for k_ in twice}}]
         ev_in_ready = [torch.cuda.Event(), torch.cuda.Event()]
         ev_in_free = [torch.cuda.Event(), torch.cuda.Event()]
-        ev_out_ready, ev_out_free = torch.cuda.Event(), torch.cuda.Event()
+        ev_out_ready = [torch.cuda.Event(), torch.cuda.Event()]
+        ev_out_free = [torch.cuda.Event(), torch.cuda.Event()]
+        ev_once_free = torch.cuda.Event()
         it = [0]
 
         def one():
@@ -349,20 +357,25 @@ def run_b200(args, rank, world, local_rank):
                     dsets[b][k_].copy_(host[k_], non_blocking=True)
                 ev_in_ready[b].record(s_h2d)
             stream.wait_event(ev_in_ready[b])
-            stream.wait_event(ev_out_free)           # the previous step's outputs have been downloaded
+            stream.wait_event(ev_out_free[b])        # this output buffer's previous contents have been downloaded
+            stream.wait_event(ev_once_free)          # and so have the single-buffered outputs of the previous step
             step(psets[b])
             ev_in_free[b].record(stream)
-            ev_out_ready.record(stream)
-            s_d2h.wait_event(ev_out_ready)
+            ev_out_ready[b].record(stream)
+            s_d2h.wait_event(ev_out_ready[b])
             with torch.cuda.stream(s_d2h):
-                for k_ in out_keys:
+                for k_ in once:
                     host_out[k_].copy_(o[k_], non_blocking=True)
-                ev_out_free.record(s_d2h)
+                ev_once_free.record(s_d2h)
+                for k_ in twice:
+                    host_out[k_].copy_(osets[b][k_], non_blocking=True)
+                ev_out_free[b].record(s_d2h)
 
         def run(n):
             for _ in range(n):
                 one()
-            stream.wait_event(ev_out_free)           # the timed region ends when the last download has landed
+            stream.wait_event(ev_out_free[0])        # the timed region ends when the last downloads have landed
+            stream.wait_event(ev_out_free[1])
         return run, sum(host[k_].numel() * 4 for k_ in in_keys), sum(host_out[k_].numel() * 4 for k_ in out_keys)
 
     e2e = {}
