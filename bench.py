@@ -219,7 +219,13 @@ def run_b200(args, rank, world, local_rank):
         n_buckets = xchg.num_buckets
 
     def step(p=p, exchange=True):
+        # The forward pass overlaps no exchange (the step before ended with the stream waiting for it), so it plans its
+        # tiles for every SM; the parameter and state passes run beside NCCL's kernels and plan for the budget.
+        if xchg and sm_budget:
+            lib.tagi_tc_set_sm_budget(0)
         k_fwd(p)
+        if xchg and sm_budget:
+            lib.tagi_tc_set_sm_budget(sm_budget)
         if xchg:
             for j, (n0, n1) in enumerate(zip(cuts[:-1], cuts[1:])):
                 lib.tagi_linear_bwd_param_rows(p["var_w"], p["var_b"], p["mu_a"], p["dmu_z"], p["dvar_z"], B, K, N, n0, n1,
@@ -459,7 +465,8 @@ def run_b200(args, rank, world, local_rank):
                    "inner_repeat": rep, "timed_region_s": ms_total * 1e-3,
                    "timing": "the K steps are repeated inner_repeat times inside one CUDA-event region; ms_per_step = "
                              "region / (K * inner_repeat)",
-                   "sm_budget": sm_budget,
+                   "sm_budget": sm_budget if world == 1 else "%d for the parameter and state passes (they run beside the "
+                                "exchange), all SMs for the forward pass" % sm_budget,
                    "exchange": ("allreduce(avg) of parameter deltas: parameter pass and exchange in %d ranges of output "
                                 "features, %d NCCL buckets on a side stream, each range's exchange overlapped with the "
                                 "next range's parameter pass and the state pass" % (pieces, n_buckets))
