@@ -9,6 +9,8 @@
 // while the data is read once.
 #include "tagi_common.h"
 
+#include <type_traits>
+
 namespace tagi {
 namespace {
 
@@ -302,9 +304,10 @@ __global__ void __launch_bounds__(BLOCK) avgpool2d_bwd_kernel(const float *__res
             lo[v] = max(0, (x + g.off - g.k + g.stride) / g.stride), hi[v] = min(g.wo - 1, (x + g.off) / g.stride);
             sm[v] = sv[v] = 0.f;
         }
-        constexpr int MAXC = 8;  // cells of a row that the VEC pixels share (3 for 3 x 3 windows at stride 2)
-        if (VEC > 1 && hi[VEC - 1] - lo[0] < MAXC) {
-            // every cell is loaded once for the VEC pixels; each pixel adds its own cells in the same ascending order
+        // every cell is loaded once for the VEC pixels; each pixel adds its own cells in the same ascending order.
+        // MAXC: cells of a row that the VEC pixels share (3 for 3 x 3 windows at stride 2: the narrow variant)
+        auto shared_cells = [&](auto maxc_tag) {
+            constexpr int MAXC = decltype(maxc_tag)::value;
             for (int oy = oy_lo; oy <= oy_hi; oy++) {
                 float cm[MAXC], cv[MAXC];
 #pragma unroll
@@ -319,6 +322,12 @@ __global__ void __launch_bounds__(BLOCK) avgpool2d_bwd_kernel(const float *__res
                     for (int c = 0; c < MAXC; c++)
                         if (lo[0] + c >= lo[v] && lo[0] + c <= hi[v]) sm[v] += cm[c], sv[v] += cv[c];
             }
+        };
+        const int span = hi[VEC - 1] - lo[0];
+        if (VEC > 1 && span < 4) {
+            shared_cells(std::integral_constant<int, 4>());
+        } else if (VEC > 1 && span < 8) {
+            shared_cells(std::integral_constant<int, 8>());
         } else {
 #pragma unroll
             for (int v = 0; v < VEC; v++)
