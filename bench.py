@@ -966,7 +966,8 @@ def run_resnet_module(args):
     dt = (time.perf_counter() - t0) / args.steps
     print(json.dumps({"metric": "TAGI ResNet-18 training samples/s", "engine":
                       {"stock": "unmodified cuTAGI CUDA build (its own Linear / Conv2d kernels)",
-                       "dropin": "cuTAGI with LinearCuda / Conv2dCuda on libtagi_b200"}[args.engine],
+                       "dropin": "cuTAGI with its Linear / Conv2d / BatchNorm2d / AvgPool2d / ReLU layers, capped update and "
+                                 "numpy input / output path on libtagi_b200"}[args.engine],
                       "value": batch / dt, "unit": "samples/s", "n_gpus": 1, "steps": args.steps, "ms_per_step": dt * 1e3,
                       "timing": "wall clock around the module's own forward / backward / step calls (host input arrays, "
                                 "outputs read back at the end)",
