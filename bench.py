@@ -636,7 +636,8 @@ def run_network(args, rank, world, local_rank):
         var_y = torch.full((batch * 4,), 1.0, device="cuda")
     stream = torch.cuda.current_stream()
     sp = stream.cuda_stream
-    deltas = net.delta_tensors()
+    # N > 1: the delta tensors live back to back in one buffer, so that a bucket travels as one collective
+    deltas = net.pack_deltas() if world > 1 else net.delta_tensors()
     xchg = None
     if world > 1:
         from cutagi_b200.comm import DeltaExchange
@@ -815,6 +816,7 @@ def run_network(args, rank, world, local_rank):
         err = float(((got.double() - mean).abs().max() / mean.abs().max()).item())
         exchange_info = {"exchange_ms_alone": ms_alone, "step_ms_exchange_off": ms_off, "step_ms": ms,
                          "bytes_per_step": int(sum(t.numel() for t in deltas) * 4), "buckets": xchg.num_buckets,
+                         "tensors": len(deltas), "collectives_per_step": xchg.num_collectives,
                          "exchange_check": {"max_rel_err": err,
                                             "ranks_bit_identical": bool(all(torch.equal(all_got[0], g) for g in all_got[1:])),
                                             "sample": f"first 4096 entries of {len(pick)} of the {len(deltas)} delta tensors "

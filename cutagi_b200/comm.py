@@ -25,6 +25,7 @@ _SIG = {
     "tagi_comm_finalize_buckets": [_z],
     "tagi_comm_num_buckets": [],
     "tagi_comm_num_tensors": [],
+    "tagi_comm_num_collectives": [],
     "tagi_comm_bucket_of": [_i],
     "tagi_comm_tensor_ready": [_i, _p, _i],
     "tagi_comm_flush": [_p, _i],
@@ -37,7 +38,8 @@ _SIG = {
     "tagi_comm_set_max_ctas": [_i],
     "tagi_comm_destroy": [],
 }
-_RAW = {"tagi_comm_rank", "tagi_comm_world_size", "tagi_comm_num_buckets", "tagi_comm_num_tensors", "tagi_comm_bucket_of",
+_RAW = {"tagi_comm_rank", "tagi_comm_world_size", "tagi_comm_num_buckets", "tagi_comm_num_tensors", "tagi_comm_num_collectives",
+        "tagi_comm_bucket_of",
         "tagi_comm_plan_buckets", "tagi_comm_register"}
 
 
@@ -126,6 +128,7 @@ class DeltaExchange:
         self.index = [_call("tagi_comm_register", t.data_ptr(), t.numel()) for t in tensors]
         _call("tagi_comm_finalize_buckets", bucket_bytes)
         self.num_buckets = load().tagi_comm_num_buckets()
+        self.num_collectives = load().tagi_comm_num_collectives()   # fewer than tensors when adjacent ones were merged
 
     def ready(self, i, stream_ptr):
         _call("tagi_comm_tensor_ready", self.index[i], stream_ptr, self.average)

@@ -12,6 +12,7 @@
 #include <cstring>
 #include <string>
 #include <thread>
+#include <algorithm>
 #include <vector>
 
 #include "../../include/tagi_b200.h"
@@ -41,8 +42,13 @@ struct Tensor {
     size_t count;
     int bucket;
 };
+struct Run {   // tensors of a bucket that lie back to back in memory: exchanged as one allreduce
+    float *ptr;
+    size_t count;
+};
 struct Bucket {
     std::vector<int> tensors;
+    std::vector<Run> runs;   // filled when every rank found the same runs (see tagi_comm_finalize_buckets)
     int ready = 0;       // tensors marked ready in this step
     bool launched = false;
     cudaEvent_t done = nullptr;
@@ -81,9 +87,14 @@ int launch_bucket(Bucket &b, cudaStream_t compute, int average) {
     CU(cudaEventRecord(g->ev, compute));
     CU(cudaStreamWaitEvent(g->stream, g->ev, 0));
     NC(ncclGroupStart());
-    for (int t : b.tensors) {
-        Tensor &x = g->tensors[t];
-        NC(ncclAllReduce(x.ptr, x.ptr, x.count, ncclFloat32, average ? ncclAvg : ncclSum, g->nccl, g->stream));
+    if (!b.runs.empty()) {
+        for (const Run &r : b.runs)
+            NC(ncclAllReduce(r.ptr, r.ptr, r.count, ncclFloat32, average ? ncclAvg : ncclSum, g->nccl, g->stream));
+    } else {
+        for (int t : b.tensors) {
+            Tensor &x = g->tensors[t];
+            NC(ncclAllReduce(x.ptr, x.ptr, x.count, ncclFloat32, average ? ncclAvg : ncclSum, g->nccl, g->stream));
+        }
     }
     NC(ncclGroupEnd());
     CU(cudaEventRecord(b.done, g->stream));
@@ -281,7 +292,54 @@ int tagi_comm_finalize_buckets(size_t bucket_bytes) {
     for (auto &b : g->buckets) CU(cudaEventCreateWithFlags(&b.done, cudaEventDisableTiming));
     g->ready.assign(n, 0);
     g->finalized = true;
+    // Tensors of a bucket that lie back to back in memory (a caller that carves its delta tensors out of one buffer)
+    // travel as one allreduce: a network's many small tensors otherwise cost a collective each, and NCCL's bandwidth
+    // falls with the message size (ResNet-18, 124 tensors in 3 buckets, 8 GPUs: 1.16 ms for 94 MB). Every rank must issue
+    // the same sequence of collectives, so the runs are used only if all ranks found the same ones: a hash over the run
+    // boundaries and the registration indices inside them is compared across the ranks (min == max).
+    std::vector<std::vector<Run>> runs(nb);
+    unsigned long long h = 1469598103934665603ull;
+    auto mix = [&h](unsigned long long v) { h = (h ^ v) * 1099511628211ull; };
+    bool any_merge = false;
+    for (int bi = 0; bi < nb; bi++) {
+        std::vector<int> order = g->buckets[bi].tensors;
+        std::sort(order.begin(), order.end(), [](int a, int b) { return g->tensors[a].ptr < g->tensors[b].ptr; });
+        mix(0xB0000000ull + (unsigned long long)bi);
+        for (int t : order) {
+            const Tensor &x = g->tensors[t];
+            if (!runs[bi].empty() && runs[bi].back().ptr + runs[bi].back().count == x.ptr) {
+                runs[bi].back().count += x.count;
+                any_merge = true;
+            } else {
+                runs[bi].push_back(Run{x.ptr, x.count});
+                mix(0xA0000000ull);   // a run starts here
+            }
+            mix((unsigned long long)t);
+            mix((unsigned long long)x.count);
+        }
+    }
+    unsigned long long *dev = nullptr;
+    CU(cudaMalloc(&dev, 2 * sizeof(unsigned long long)));
+    const unsigned long long mine[2] = {any_merge ? h : 0ull, any_merge ? h : ~0ull};   // a rank without merges vetoes
+    CU(cudaMemcpyAsync(dev, mine, sizeof(mine), cudaMemcpyHostToDevice, g->stream));
+    NC(ncclGroupStart());
+    NC(ncclAllReduce(dev, dev, 1, ncclUint64, ncclMin, g->nccl, g->stream));
+    NC(ncclAllReduce(dev + 1, dev + 1, 1, ncclUint64, ncclMax, g->nccl, g->stream));
+    NC(ncclGroupEnd());
+    unsigned long long agreed[2] = {0, 1};
+    CU(cudaMemcpyAsync(agreed, dev, sizeof(agreed), cudaMemcpyDeviceToHost, g->stream));
+    CU(cudaStreamSynchronize(g->stream));
+    CU(cudaFree(dev));
+    if (any_merge && agreed[0] == h && agreed[1] == h)
+        for (int bi = 0; bi < nb; bi++) g->buckets[bi].runs = std::move(runs[bi]);
     return TAGI_OK;
+}
+
+int tagi_comm_num_collectives(void) {
+    if (!g) return 0;
+    int n = 0;
+    for (const auto &b : g->buckets) n += (int)(b.runs.empty() ? b.tensors.size() : b.runs.size());
+    return n;
 }
 
 int tagi_comm_num_buckets(void) { return g ? (int)g->buckets.size() : 0; }

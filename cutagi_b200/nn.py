@@ -101,9 +101,14 @@ class Linear:
             lib.tagi_param_update(batch_size, self.mu_b.numel(), _p(self.mu_b), _p(self.var_b), _p(self.delta_mu_b),
                                   _p(self.delta_var_b), None, _stream())
 
+    def _delta_slots(self):
+        """(object, attribute) of every parameter-delta tensor, in the order the backward pass produces them."""
+        return [(self, a) for a in ("delta_mu_w", "delta_var_w", "delta_mu_b", "delta_var_b")
+                if getattr(self, a) is not None]
+
     def delta_tensors(self):
         """Parameter-delta tensors in the order the backward pass produces them (for the data-parallel exchange)."""
-        return [t for t in (self.delta_mu_w, self.delta_var_w, self.delta_mu_b, self.delta_var_b) if t is not None]
+        return [getattr(o, a) for o, a in self._delta_slots()]
 
 
 class _NoParams:
@@ -115,6 +120,9 @@ class _NoParams:
 
     def step(self, batch_size):
         pass
+
+    def _delta_slots(self):
+        return []
 
     def delta_tensors(self):
         return []
@@ -356,6 +364,9 @@ class LayerBlock:
             out.update(layer.named(f"{prefix}{idx}.", i))
         return out
 
+    def _delta_slots(self):
+        return [s for layer in reversed(self.layers) for s in layer._delta_slots()]
+
     def delta_tensors(self):
         return [t for layer in reversed(self.layers) for t in layer.delta_tensors()]
 
@@ -401,8 +412,11 @@ class ResNetBlock:
             out.update(self.shortcut.named(f"{prefix}shortcut.", idx))
         return out
 
-    def delta_tensors(self):
+    def _delta_slots(self):
         # backward order: main block first, then the shortcut
+        return self.main._delta_slots() + (self.shortcut._delta_slots() if self.shortcut is not None else [])
+
+    def delta_tensors(self):
         return self.main.delta_tensors() + (self.shortcut.delta_tensors() if self.shortcut is not None else [])
 
 
@@ -452,10 +466,40 @@ class Sequential:
                                mu_b=None if v[2] is None else np.asarray(v[2], np.float32),
                                var_b=None if v[3] is None else np.asarray(v[3], np.float32)))
         self._ptable = None   # the tensors were replaced: the update table is rebuilt on the next step
+        self._delta_views = None
+
+    def _delta_slots(self):
+        return [s for layer in reversed(self.layers) for s in layer._delta_slots()]
 
     def delta_tensors(self):
-        """All parameter-delta tensors in the order the backward pass produces them."""
+        """All parameter-delta tensors in the order the backward pass produces them (after pack_deltas(): the padded
+        views of the one buffer that holds them)."""
+        if getattr(self, "_delta_views", None) is not None:
+            return list(self._delta_views)
         return [t for layer in reversed(self.layers) for t in layer.delta_tensors()]
+
+    def pack_deltas(self):
+        """Moves every layer's parameter-delta tensors into one buffer, back to back in the order the backward pass
+        produces them, each padded to a multiple of four floats (every tensor stays 16-byte aligned; the padding is
+        zero and stays zero). The data-parallel exchange then moves the tensors of a bucket as one collective instead
+        of one per tensor (tagi_comm_finalize_buckets merges tensors that are adjacent in memory). Returns the padded
+        1-D views in that order; a layer's own delta attributes are views of the same memory. load_state_dict()
+        undoes the packing."""
+        slots = self._delta_slots()
+        sizes = [getattr(o, a).numel() for o, a in slots]
+        padded = [(n + 3) // 4 * 4 for n in sizes]
+        flat = torch.zeros(sum(padded), device="cuda")
+        views, off = [], 0
+        for (o, a), n, m in zip(slots, sizes, padded):
+            old = getattr(o, a)
+            new = flat[off:off + n].view(old.shape)
+            new.copy_(old)
+            setattr(o, a, new)
+            views.append(flat[off:off + m])
+            off += m
+        self._delta_flat, self._delta_views = flat, views
+        self._ptable = None   # the update table holds the old addresses
+        return list(views)
 
     def __call__(self, mu_x, var_x=None):
         return self.forward(mu_x, var_x)

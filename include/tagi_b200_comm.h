@@ -65,9 +65,14 @@ int tagi_comm_world_size(void);
  * (last layer first). Returns the tensor's index (>= 0) or a negative status. tagi_comm_finalize_buckets closes the
  * registration and builds the buckets. */
 int tagi_comm_register(float *ptr, size_t count);
+/* Collective: every rank calls it once, after the same registrations. Tensors of a bucket that lie back to back in device
+ * memory (a caller that carves its delta tensors out of one buffer, in registration order) are exchanged as ONE allreduce
+ * per run instead of one per tensor, provided every rank found the same runs (checked here with a small allreduce of a
+ * hash; any difference and all ranks keep one collective per tensor). */
 int tagi_comm_finalize_buckets(size_t bucket_bytes);
 int tagi_comm_num_buckets(void);
-int tagi_comm_num_tensors(void); /* tensors registered so far */
+int tagi_comm_num_tensors(void);     /* tensors registered so far */
+int tagi_comm_num_collectives(void); /* allreduce calls one step issues: runs where they were merged, tensors otherwise */
 int tagi_comm_bucket_of(int tensor_index);
 
 /* Tell the communicator that tensor `tensor_index` has been written on `compute_stream`. When that completes a

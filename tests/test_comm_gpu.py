@@ -72,8 +72,9 @@ def _train_worker(rank, world, path, q):
     net = nn.build(spec, in_shape)
     net.load_state_dict(OracleNet(None, spec, in_shape, seed=1).state_dict())   # identical replicas, the oracle's parameters
     upd = nn.OutputUpdater()
-    deltas = net.delta_tensors()
+    deltas = net.pack_deltas()   # one buffer: the tensors of a bucket are merged into one collective
     ex = DeltaExchange(deltas, rank, world, rank, path, bucket_bytes=4 << 10, average=True, timeout_ms=60000)
+    assert ex.num_collectives < len(deltas), (ex.num_collectives, len(deltas))
     sp = torch.cuda.current_stream().cuda_stream
     pos = {t.data_ptr(): i for i, t in enumerate(deltas)}
     for layer in net.named_layers().values():
