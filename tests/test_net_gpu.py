@@ -117,3 +117,38 @@ def test_shape_errors_are_raised():
         nn.build([("conv", 3, 4, 3, 2, 0, 0, True)], (3, 8, 8))   # (8 - 3) not divisible by the stride
     with pytest.raises(RuntimeError):
         nn.build([("res", [("conv", 3, 4, 3, 1, 1, 1, False)], None)], (3, 8, 8))   # identity shortcut, 3 != 4 channels
+
+
+def test_packed_deltas_train_the_same_bits(oracle):
+    """nn.Sequential.pack_deltas() moves every parameter-delta tensor into one buffer (what the data-parallel exchange
+    wants: tensors of a bucket adjacent in memory travel as one collective). Two training steps of the small ResNet with
+    and without packing must leave bit-identical parameters, the packed views must be adjacent and 16-byte aligned, and
+    the padding between tensors must stay zero."""
+    import torch
+    spec, in_shape, batch, _ = net_golden_problems()["resnet"]
+    cpu = OracleNet(oracle, spec, in_shape, seed=1)
+    nets = [_device_net(spec, in_shape, cpu) for _ in range(2)]
+    views = nets[1][0].pack_deltas()
+    for a, b in zip(views[:-1], views[1:]):
+        assert a.data_ptr() + 4 * a.numel() == b.data_ptr() and a.data_ptr() % 16 == 0
+    assert [t.data_ptr() for t in views] == [t.data_ptr() for l in [nets[1][0]] for t in l.delta_tensors()]
+    xs, var_y = GOLD["resnet_x"], np.full(batch * 4, 1.0, np.float32)
+    for s in range(2):
+        for net, upd in nets:
+            net(xs[s])
+            upd.update_using_indices(net, GOLD["resnet_obs"][s], var_y, GOLD["resnet_idx"][s])
+            net.backward()
+            net.step()
+    plain, packed = nets[0][0].state_dict(), nets[1][0].state_dict()
+    for k in plain:
+        for a, b in zip(plain[k], packed[k]):
+            assert (a is None and b is None) or np.array_equal(a, b), k
+    # every delta tensor of the packed network is a view of the one buffer, and what lies between them is still zero
+    flat = nets[1][0]._delta_flat
+    used = torch.zeros_like(flat, dtype=torch.bool)
+    for o, a in nets[1][0]._delta_slots():
+        t = getattr(o, a)
+        off = (t.data_ptr() - flat.data_ptr()) // 4
+        assert 0 <= off and off + t.numel() <= flat.numel()
+        used[off:off + t.numel()] = True
+    assert bool((flat[~used] == 0).all())
