@@ -1,4 +1,5 @@
 // C-ABI entry points (include/tagi_b200.h): argument checks, implementation choice, status codes.
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 
@@ -20,7 +21,7 @@ int cuda_fail(cudaError_t e, const char *where) {
 }
 
 namespace {
-int g_impl = -1;
+std::atomic<int> g_impl{-1};
 int impl_from_env() {
     const char *v = std::getenv("TAGI_B200_IMPL");
     if (!v) return TAGI_IMPL_AUTO;
@@ -30,8 +31,12 @@ int impl_from_env() {
 }
 }  // namespace
 int current_impl() {
-    if (g_impl < 0) g_impl = impl_from_env();
-    return g_impl;
+    int impl = g_impl;
+    if (impl < 0) {
+        impl = impl_from_env();
+        g_impl = impl;
+    }
+    return impl;
 }
 
 }  // namespace tagi

@@ -30,6 +30,8 @@
 #include <mutex>
 
 #include "tagi_common.h"
+
+#include <atomic>
 #include "tagi_tc_ptx.cuh"
 #include "tagi_tc_tile.cuh"
 
@@ -755,10 +757,10 @@ int *status_word() {
     return ptr[dev];
 }
 
-int g_variant = 3;  // 3: CTA pairs (default; passes with < 256 output rows use 1); 1: one CTA per tile everywhere
+std::atomic<int> g_variant{3};  // 3: CTA pairs (default; passes with < 256 output rows use 1); 1: one CTA per tile everywhere
 int g_pair_bn = 0;  // forces the pair kernel's tile width (diagnostic); 0 = chosen per launch
-int g_sms = 148;    // SMs the tile planning counts on (tagi_tc_set_sm_budget)
-int g_chunked = 1;  // 1: contraction accumulated in chunks of 256 (default); 0: one accumulation chain (diagnostic)
+std::atomic<int> g_sms{148};    // SMs the tile planning counts on (tagi_tc_set_sm_budget)
+std::atomic<int> g_chunked{1};  // 1: contraction accumulated in chunks of 256 (default); 0: one accumulation chain (diagnostic)
 
 template <int OP>
 int launch(const CUtensorMap &a0, const CUtensorMap &a1, const CUtensorMap &b0, const CUtensorMap &b1,
@@ -769,11 +771,12 @@ int launch(const CUtensorMap &a0, const CUtensorMap &a1, const CUtensorMap &b0, 
     // tensor-core time of the slowest SM; e.g. 4096 columns x 8 row tiles run as 296 tiles of 112 (two full waves)
     // rather than 256 tiles of 128 (two waves, the second 73 % full).
     const long row_tiles = (epi.rows + TM - 1) / TM;
+    const long sms = g_sms;   // read once: another host thread may change the budget while this call plans
     int bn = TN;
     long best = -1;
     for (int w = TN; w >= 64; w -= 16) {
         const long tiles = row_tiles * ((epi.cols + w - 1) / w);
-        const long cost = ((tiles + g_sms - 1) / g_sms) * (w + 16);  // + 16: per-tile work that does not shrink with the width
+        const long cost = ((tiles + sms - 1) / sms) * (w + 16);  // + 16: per-tile work that does not shrink with the width
         if (best < 0 || cost < best) best = cost, bn = w;
     }
     const unsigned slices = epi.slabs_per_slice > 0 ? (unsigned)(((kdim + BK - 1) / BK + epi.slabs_per_slice - 1) / epi.slabs_per_slice) : 1u;
@@ -802,11 +805,12 @@ int launch_pair(const CUtensorMap &a0, const CUtensorMap &a1, const CUtensorMap 
     int *status = status_word();
     if (!status) return fail(TAGI_ERR_CUDA, "cannot allocate the tensor-core status word");
     const long row_tiles = (epi.rows + 255) / 256;
+    const long sms = g_sms;   // read once: another host thread may change the budget while this call plans
     int bn = TN;
     long best = -1;
     for (int w = TN; w >= 64; w -= 16) {  // 74 pairs run at a time
         const long tiles = row_tiles * ((epi.cols + w - 1) / w);
-        const long cost = ((tiles + g_sms / 2 - 1) / (g_sms / 2)) * (w + 16);
+        const long cost = ((tiles + sms / 2 - 1) / (sms / 2)) * (w + 16);
         if (best < 0 || cost < best) best = cost, bn = w;
     }
     if (g_pair_bn) bn = g_pair_bn;

@@ -58,7 +58,9 @@ int tagi_tc_set_chunked(int on);
 /* Diagnostic switch of the TF32X3 kernels. 3 (default): CTA pairs (tcgen05 cta_group::2, 256-row tiles, A-side operand
  * tiles in tensor memory, each CTA stages half of the B rows; passes with fewer than 256 output rows use the one-CTA
  * kernel); 1: one CTA per 128-row tile for every pass; 64, 80, 96, 112 or 128: as 3 with that tile width. Same results
- * in all of them. Process-wide, not thread-safe: set it before the first call, not between concurrent calls. */
+ * in all of them. Process-wide like the other switches here (tagi_set_impl, tagi_tc_set_chunked, tagi_tc_set_sm_budget):
+ * each is one atomic word, read when a kernel launch is planned, so a change from another host thread takes effect for
+ * the launches planned after it (an entry point that launches several kernels may see it between two of them). */
 int tagi_tc_set_variant(int v);
 /* How many SMs the TF32X3 kernels plan their tile widths for: 0 (default) = all 148. A caller that runs another kernel
  * next to them (the data-parallel exchange's NCCL kernels on their own stream hold some SMs for the length of a pass)
