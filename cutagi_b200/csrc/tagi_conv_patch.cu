@@ -449,7 +449,7 @@ tagi_tc_conv_pix_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_c
     // converter warps split them 32 / 32, which leaves the registers to read a whole slab of A values at once
     constexpr int NG = NCW / 4;                        // converter groups
     constexpr int SUMW = (ACC <= 64 ? 64 : 128) / NG;  // 64, 32 or 16
-    static_assert(NCW == 8 || (NCW == 16 && ACC <= 64), "sixteen converter warps only with narrow accumulators");
+    static_assert(NCW == 8 || NCW == 16, "eight or sixteen converter warps");
     const int RS = pp.RS, AS = pp.AS;
     constexpr uint32_t RAW_SLOT = NRAW_B * HALF_BYTES;               // B ring slot: the raw B half tiles of one slab
     const uint32_t A_SLOT = 2 * pp.a_slot;                           // patch ring slot: both operands of a channel block
@@ -1167,7 +1167,9 @@ int conv2d_bwd_state_patch(const tagi_conv2d_geom &g, const float *mu_w, const f
     if ((rc = make_tmap_weights(&b0, ws, g.fi, (uint64_t)g.fo * p.k2, true))) return rc;
     p.out1 = dmu_a, p.out2 = dvar_a, p.out3 = nullptr, p.aux1 = jcb, p.aux2 = nullptr;
     if (plan.bn <= 64) return launch_pix<OP_BWD_STATE, 6, 64, 16>(a0, a1, b0, b0, plan, false, st);
-    return launch_pix<OP_BWD_STATE, 4, 128, 8>(a0, a1, b0, b0, plan, false, st);
+    // wider tiles: sixteen converter warps as well, each with a 32-column slice of the accumulators (measured on ResNet-18
+    // layer2, 128 columns: 0.309 ms with eight warps, 0.272 ms with sixteen)
+    return launch_pix<OP_BWD_STATE, 4, 128, 16>(a0, a1, b0, b0, plan, false, st);
 }
 
 }  // namespace tagi

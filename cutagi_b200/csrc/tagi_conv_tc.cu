@@ -248,9 +248,11 @@ inline bool patch_ok(const tagi_conv2d_geom &cg, int pass, long rows, int cols, 
     const int mode = gather_mode();
     if (mode == 1 || mode == 2 || rows < 256) return false;
     // measured on the ResNet-18 shapes: the patch kernels win on tiles of at most 64 columns (64-channel layers: forward
-    // 0.52 -> 0.48 ms, state pass 0.64 -> 0.42 ms); with 128 columns the cp.async gather of the Linear pair kernel is as
-    // fast or faster
-    if (mode != 3 && cols > 64) return false;
+    // 0.52 -> 0.48 ms, state pass 0.64 -> 0.42 ms) and in the state pass of 128-column layers with many rows (layer2:
+    // 0.293 -> 0.272 ms); the forward pass with 128 columns is faster with the cp.async gather of the Linear pair kernel
+    // (0.256 against 0.335 ms)
+    const int widest = pass == CONV_PASS_STATE && rows >= 32768 ? 128 : 64;
+    if (mode != 3 && cols > widest) return false;
     return conv_pix_patch_supported(cg, pass, ptrs);
 }
 inline bool implicit_ok(const G &g, long rows, int cols) {
